@@ -1,0 +1,215 @@
+/*
+ * riftco_b200 - C ABI of the B200 (sm_100a) backend for Riftco's quantized
+ * inference hot path: the packed-NF4 linear operator (forward and QLoRA
+ * input-backward) and paged-KV single-token decode attention.
+ *
+ * The reference engine (quangng2000/riftco-transformer) reaches its backends
+ * through a private C++ vtable; the entry points below are the function table a
+ * binary CUDA plugin for that vtable binds. Each one names the reference
+ * interface it replaces (paths are inside the reference project).
+ *
+ * Conventions
+ *  - Plain pointers and sizes only. Unless a function says "host", every data
+ *    pointer is a DEVICE pointer valid on the current CUDA device.
+ *  - `stream` is a cudaStream_t passed as void* (NULL = the default stream).
+ *    Device-pointer entry points only enqueue work: they return once the
+ *    launches are queued and are ordered by the stream.
+ *  - Every function returns a status with the numeric values of the
+ *    reference's rt_status (include/riftco_transformer/c_api.h:41-49); the
+ *    message of the last failure on the calling thread is b2_last_error().
+ *  - There is no CPU fallback: without a usable CUDA device every compute entry
+ *    point fails with B2_STATUS_BACKEND_UNAVAILABLE.
+ */
+#ifndef RIFTCO_B200_H
+#define RIFTCO_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B2_ABI_VERSION 1
+
+#if defined(__GNUC__)
+#define B2_API __attribute__((visibility("default")))
+#else
+#define B2_API
+#endif
+
+#define B2_STATUS_OK 0
+#define B2_STATUS_INVALID_ARGUMENT 1
+#define B2_STATUS_OUT_OF_RANGE 2
+#define B2_STATUS_OVERFLOW 3
+#define B2_STATUS_BACKEND_UNAVAILABLE 4
+#define B2_STATUS_OUT_OF_MEMORY 5
+#define B2_STATUS_RUNTIME_ERROR 6
+/* Not an rt_status value: marks the cases the reference reports by throwing
+ * std::domain_error (non-finite attention scores,
+ * src/core/backend/attention/reference/paged_decode.cpp:78-93). A C++ adapter
+ * rethrows it as std::domain_error; the reference's C ABI then folds it into
+ * RT_STATUS_INVALID_ARGUMENT (src/c_api/internal/error.hpp:25-27). */
+#define B2_STATUS_DOMAIN_ERROR 7
+
+/* Scale encodings: Nf4ScaleEncoding,
+ * src/core/backend/nn/quantized_linear/storage.hpp:13-16. */
+#define B2_SCALES_FLOAT32 0u
+#define B2_SCALES_DOUBLE_QUANTIZED_UINT8 1u
+
+/* Bits of the device status word written by b2_paged_decode_attention. */
+#define B2_ATTN_STATUS_NAN_OR_POS_INF 1u   /* a score was NaN or +infinity      */
+#define B2_ATTN_STATUS_ALL_NEG_INF 2u      /* every score of one head was -inf  */
+
+/*
+ * Borrowed view of one packed NF4 weight, flat row-major [out_features,
+ * in_features]. It carries what QuantizedWeightStorage exposes
+ * (src/core/backend/nn/quantized_linear/storage.hpp:81-108: packed codes,
+ * primary and secondary scale handles) plus Nf4ScaleStorageView's scalars
+ * (storage.hpp:31-46) and QuantizedLinearDimensions' widths and block size
+ * (src/core/backend/nn/quantized_linear/contracts.hpp:10-15).
+ *
+ * Layout consumed unchanged: element i lives in byte i/2, even i in the low
+ * nibble (src/core/quantization/nf4.cpp:70-85); block b = i / block_size over
+ * the FLAT index. A row shard [r0, r1) of a larger weight is described by
+ * pointing `codes` and `scales_primary` at the shard's first byte/block,
+ * leaving `scales_secondary` at the parent's first second-level scale and
+ * setting flat_block_base to the parent's index of the shard's first block
+ * (the shard must start on a block boundary and on a whole byte).
+ */
+typedef struct b2_nf4_weight {
+    const uint8_t* codes;           /* ceil(out*in/2) bytes                         */
+    const void* scales_primary;     /* float[blocks] or uint8_t[blocks]             */
+    const float* scales_secondary;  /* NULL, or float[ceil(blocks/scale_block_size)] */
+    uint32_t encoding;              /* B2_SCALES_*                                  */
+    uint32_t block_size;            /* 32..4096, power of two (nf4.cpp:39-52)       */
+    uint64_t scale_block_size;      /* 0 for FLOAT32, else 32..4096 power of two    */
+    float scale_offset;             /* shared mean of first-level scales, 0 for F32 */
+    uint32_t reserved;              /* must be 0                                    */
+    uint64_t out_features;
+    uint64_t in_features;
+    uint64_t flat_block_base;       /* 0 for a whole weight                         */
+} b2_nf4_weight;
+
+/* ---- library ----------------------------------------------------------- */
+
+B2_API int32_t b2_abi_version(void);
+
+/* Thread-local message of the last failed call on this thread; "" if none.
+ * Counterpart of rt_last_error (include/riftco_transformer/c_api.h:339-345). */
+B2_API const char* b2_last_error(void);
+
+/* 1 when a CUDA device of compute capability 10.x is current and usable.
+ * Replaces BackendAdapter::is_available (src/core/backend/adapter.hpp:74-79). */
+B2_API int32_t b2_is_available(void);
+
+/* Reason string for b2_is_available() == 0; "" otherwise. Replaces
+ * BackendAdapter::unavailability_reason (adapter.hpp:76-79). */
+B2_API const char* b2_unavailability_reason(void);
+
+/* ---- packed NF4 linear ------------------------------------------------- */
+
+/* out[i] = codebook[code(i)] * decoded_scale(i / block_size), bit-exact with
+ * QuantizedWeight::dequantize (src/core/quantization/quantized_weight.cpp,
+ * scale decode per storage.hpp:48-65). out: float[out*in]. */
+B2_API int32_t b2_nf4_dequantize(const b2_nf4_weight* weight, float* out, void* stream);
+
+/* y[r,o] = sum_i x[r,i] * W[o,i]. x: float[rows,in], y: float[rows,out].
+ * Replaces QuantizedLinearCapability::quantized_linear_forward
+ * (src/core/backend/nn/quantized_linear/capability.hpp:35-41; CUDA launcher
+ * cuda_quantized_linear_forward, quantized_linear/cuda/launch.hpp:16-17; loop
+ * reference/operations.cpp:49-81). Validation follows
+ * dispatch_quantized_linear_forward (quantized_linear/dispatch.cpp:317-341):
+ * zero/overflowing dimensions and aliasing x/y or weight/y are rejected.
+ * workspace may be NULL: the library then uses its own per-device arena, and
+ * calls that share the arena must be ordered on one stream. */
+B2_API int32_t b2_nf4_linear_forward(const b2_nf4_weight* weight, const float* x, float* y,
+                              uint64_t rows, void* workspace, size_t workspace_bytes,
+                              void* stream);
+
+/* dx[r,i] = sum_o dy[r,o] * W[o,i]. dy: float[rows,out], dx: float[rows,in].
+ * Replaces QuantizedLinearCapability::quantized_linear_input_backward
+ * (capability.hpp:43-49; launch.hpp:19-20; loop reference/operations.cpp:83-115;
+ * validation dispatch.cpp:343-370). */
+B2_API int32_t b2_nf4_linear_input_backward(const b2_nf4_weight* weight, const float* dy,
+                                     float* dx, uint64_t rows, void* workspace,
+                                     size_t workspace_bytes, void* stream);
+
+/* Bytes of scratch the two calls above need for `rows` rows of this weight
+ * (0 when the chosen kernel needs none). `backward` selects the operator. */
+B2_API size_t b2_nf4_linear_workspace_bytes(const b2_nf4_weight* weight, uint64_t rows,
+                                     int32_t backward);
+
+/* ---- paged-KV decode attention ----------------------------------------- */
+
+/*
+ * Single-token decode attention over block-addressed K/V pages for a batch of
+ * sequences with grouped-query heads.
+ *   q, ctx      float[n_seq, q_heads, head_width]
+ *   k/v_pages   float[physical_blocks, kv_heads, block_size, head_width]
+ *   block_tables uint32[n_seq, max_blocks]; row s uses its first
+ *               ceil(seq_lens[s] / block_size) entries
+ *   seq_lens    uint32[n_seq], each >= 1
+ * Query head h reads KV head h / (q_heads / kv_heads).
+ * With n_seq == 1 and q_heads == kv_heads this is exactly
+ * AttentionCapability::paged_decode_attention_forward
+ * (src/core/backend/attention/capability.hpp:28-30; request and page layout
+ * src/core/backend/attention/contracts.hpp:88-106; loop
+ * attention/reference/paged_decode.cpp:37-132; CUDA launcher
+ * attention/cuda/paged_decode.cu:144-215).
+ * `status` (device uint32, may be NULL) receives B2_ATTN_STATUS_* bits; the
+ * caller zeroes it and reads it after synchronising, which is how the
+ * reference's CUDA path reports std::domain_error (paged_decode.cu:208-214).
+ * Block ids are checked on the device: an id >= physical_blocks is never
+ * dereferenced and sets bit 4 of the status word.
+ */
+#define B2_ATTN_STATUS_BAD_BLOCK 4u
+B2_API int32_t b2_paged_decode_attention(const float* q, const float* k_pages,
+                                  const float* v_pages, const uint32_t* block_tables,
+                                  const uint32_t* seq_lens, float* ctx,
+                                  uint32_t n_seq, uint32_t q_heads, uint32_t kv_heads,
+                                  uint32_t head_width, uint32_t block_size,
+                                  uint64_t physical_blocks, uint32_t max_blocks,
+                                  uint32_t max_seq_len, void* workspace,
+                                  size_t workspace_bytes, uint32_t* status,
+                                  void* stream);
+
+/* Scratch bytes for the call above (split-K partial results). */
+B2_API size_t b2_paged_decode_workspace_bytes(uint32_t n_seq, uint32_t q_heads,
+                                       uint32_t head_width, uint32_t block_size,
+                                       uint32_t max_seq_len);
+
+/* ---- host-buffer seam --------------------------------------------------- */
+/*
+ * The reference adapter contract is synchronous over host-visible storage
+ * (TensorStorage::data() is a host span, src/core/backend/storage.hpp:15-29;
+ * "must finish writing output before returning", adapter.hpp:50-52). These
+ * forms take HOST pointers for activations, copy them to the device, run the
+ * same kernels, copy the result back and return after the stream is idle.
+ * The weight / KV pools stay device-resident, as the reference's CUDA storage
+ * keeps them (quantized_linear/cuda/storage.cu:72-135).
+ */
+B2_API int32_t b2_host_nf4_linear_forward(const b2_nf4_weight* weight, const float* x_host,
+                                   float* y_host, uint64_t rows, void* stream);
+B2_API int32_t b2_host_nf4_linear_input_backward(const b2_nf4_weight* weight,
+                                          const float* dy_host, float* dx_host,
+                                          uint64_t rows, void* stream);
+/* q_host/ctx_host/block_tables_host/seq_lens_host are host pointers; pages are
+ * device pointers. Block ids and lengths are validated on the host first, as
+ * dispatch_paged_decode_attention_forward does
+ * (src/core/backend/attention/dispatch.cpp:440-509): a short table or zero
+ * dimension is INVALID_ARGUMENT, an id >= physical_blocks OUT_OF_RANGE, and a
+ * non-finite score comes back as B2_STATUS_DOMAIN_ERROR. */
+B2_API int32_t b2_host_paged_decode_attention(const float* q_host, const float* k_pages,
+                                       const float* v_pages,
+                                       const uint32_t* block_tables_host,
+                                       const uint32_t* seq_lens_host, float* ctx_host,
+                                       uint32_t n_seq, uint32_t q_heads,
+                                       uint32_t kv_heads, uint32_t head_width,
+                                       uint32_t block_size, uint64_t physical_blocks,
+                                       uint32_t max_blocks, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* RIFTCO_B200_H */

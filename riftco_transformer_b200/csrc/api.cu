@@ -1,0 +1,518 @@
+// C-ABI layer of riftco_b200: argument validation mirroring the reference's
+// dispatch layer, per-device state, kernel selection, and the synchronous
+// host-buffer forms that a reference BackendAdapter calls.
+#include "b2_common.cuh"
+#include "b2_kernels.h"
+
+#include <cmath>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+#include <string>
+
+namespace b2 {
+namespace {
+
+thread_local std::string g_last_error;
+thread_local std::string g_unavailable_reason;
+
+constexpr int kMaxDevices = 64;
+DeviceContext g_contexts[kMaxDevices];
+std::once_flag g_context_once[kMaxDevices];
+int32_t g_context_status[kMaxDevices];
+std::string g_context_error[kMaxDevices];
+std::mutex g_arena_mutex;
+
+bool is_power_of_two(uint64_t v) { return v != 0 && (v & (v - 1)) == 0; }
+
+uint32_t log2_u64(uint64_t v) {
+    uint32_t s = 0;
+    while ((1ull << s) < v) ++s;
+    return s;
+}
+
+// nf4_block_size_supported, src/core/quantization/nf4.cpp:39-52.
+bool block_size_supported(uint64_t v) { return is_power_of_two(v) && v >= 32 && v <= 4096; }
+
+bool mul_overflows(uint64_t a, uint64_t b, uint64_t* out) {
+    if (a != 0 && b > UINT64_MAX / a) return true;
+    *out = a * b;
+    return false;
+}
+
+}  // namespace
+
+int32_t fail(int32_t status, const char* format, ...) {
+    char buffer[512];
+    va_list args;
+    va_start(args, format);
+    vsnprintf(buffer, sizeof(buffer), format, args);
+    va_end(args);
+    g_last_error = buffer;
+    return status;
+}
+
+void clear_error() { g_last_error.clear(); }
+
+int32_t fail_cuda(cudaError_t error, const char* what) {
+    const int32_t status =
+        error == cudaErrorMemoryAllocation ? B2_STATUS_OUT_OF_MEMORY : B2_STATUS_RUNTIME_ERROR;
+    return fail(status, "CUDA error in %s: %s", what, cudaGetErrorString(error));
+}
+
+DeviceContext* device_context(int32_t* status) {
+    int device = -1;
+    const cudaError_t err = cudaGetDevice(&device);
+    if (err != cudaSuccess || device < 0 || device >= kMaxDevices) {
+        cudaGetLastError();
+        *status = fail(B2_STATUS_BACKEND_UNAVAILABLE, "CUDA backend unavailable: %s",
+                       err != cudaSuccess ? cudaGetErrorString(err) : "device index out of range");
+        return nullptr;
+    }
+    std::call_once(g_context_once[device], [device] {
+        DeviceContext& ctx = g_contexts[device];
+        cudaDeviceProp prop;
+        cudaError_t e = cudaGetDeviceProperties(&prop, device);
+        if (e != cudaSuccess) {
+            g_context_status[device] = B2_STATUS_BACKEND_UNAVAILABLE;
+            g_context_error[device] = std::string("CUDA backend unavailable: ") + cudaGetErrorString(e);
+            return;
+        }
+        if (prop.major != 10) {
+            g_context_status[device] = B2_STATUS_BACKEND_UNAVAILABLE;
+            g_context_error[device] = "CUDA backend unavailable: this library is built for sm_100a "
+                                      "(compute capability 10.x) only, device reports " +
+                                      std::to_string(prop.major) + "." + std::to_string(prop.minor);
+            return;
+        }
+        ctx.device = device;
+        ctx.sm_count = prop.multiProcessorCount;
+        ctx.cc_major = prop.major;
+        const int32_t s = init_gemv_lut(&ctx);
+        if (s != B2_STATUS_OK) {
+            g_context_status[device] = s;
+            g_context_error[device] = g_last_error;
+            return;
+        }
+        g_context_status[device] = B2_STATUS_OK;
+    });
+    if (g_context_status[device] != B2_STATUS_OK) {
+        *status = fail(g_context_status[device], "%s", g_context_error[device].c_str());
+        return nullptr;
+    }
+    *status = B2_STATUS_OK;
+    return &g_contexts[device];
+}
+
+int32_t reserve_arena(DeviceContext* ctx, size_t bytes) {
+    std::lock_guard<std::mutex> lock(g_arena_mutex);
+    if (bytes <= ctx->arena_bytes) return B2_STATUS_OK;
+    B2_CUDA_TRY(cudaDeviceSynchronize());
+    if (ctx->arena != nullptr) B2_CUDA_TRY(cudaFree(ctx->arena));
+    ctx->arena = nullptr;
+    ctx->arena_bytes = 0;
+    const size_t rounded = (bytes + (size_t{1} << 20) - 1) & ~((size_t{1} << 20) - 1);
+    B2_CUDA_TRY(cudaMalloc(&ctx->arena, rounded));
+    ctx->arena_bytes = rounded;
+    return B2_STATUS_OK;
+}
+
+int32_t reserve_stage(DeviceContext* ctx, size_t device_bytes, size_t pinned_bytes) {
+    std::lock_guard<std::mutex> lock(g_arena_mutex);
+    if (device_bytes > ctx->stage_bytes) {
+        B2_CUDA_TRY(cudaDeviceSynchronize());
+        if (ctx->stage != nullptr) B2_CUDA_TRY(cudaFree(ctx->stage));
+        ctx->stage = nullptr;
+        ctx->stage_bytes = 0;
+        B2_CUDA_TRY(cudaMalloc(&ctx->stage, device_bytes));
+        ctx->stage_bytes = device_bytes;
+    }
+    if (pinned_bytes > ctx->pinned_bytes) {
+        B2_CUDA_TRY(cudaDeviceSynchronize());
+        if (ctx->pinned != nullptr) B2_CUDA_TRY(cudaFreeHost(ctx->pinned));
+        ctx->pinned = nullptr;
+        ctx->pinned_bytes = 0;
+        B2_CUDA_TRY(cudaMallocHost(&ctx->pinned, pinned_bytes));
+        ctx->pinned_bytes = pinned_bytes;
+    }
+    return B2_STATUS_OK;
+}
+
+int32_t make_weight_view(const b2_nf4_weight* weight, WeightView* view) {
+    if (weight == nullptr) return fail(B2_STATUS_INVALID_ARGUMENT, "NF4 weight must not be null");
+    if (weight->out_features == 0 || weight->in_features == 0) {
+        return fail(B2_STATUS_INVALID_ARGUMENT, "NF4 weight dimensions must be positive");
+    }
+    uint64_t numel = 0;
+    if (mul_overflows(weight->out_features, weight->in_features, &numel)) {
+        return fail(B2_STATUS_OVERFLOW, "NF4 weight element count overflows");
+    }
+    if (weight->block_size == 0) {
+        return fail(B2_STATUS_INVALID_ARGUMENT, "NF4 block size must be greater than zero");
+    }
+    if (!block_size_supported(weight->block_size)) {
+        return fail(B2_STATUS_INVALID_ARGUMENT,
+                    "NF4 block size must be a power of two between 32 and 4096");
+    }
+    if (weight->codes == nullptr || weight->scales_primary == nullptr) {
+        return fail(B2_STATUS_INVALID_ARGUMENT, "NF4 packed codes and scales must not be null");
+    }
+    if (weight->reserved != 0) {
+        return fail(B2_STATUS_INVALID_ARGUMENT, "NF4 weight reserved field must be zero");
+    }
+    view->codes = weight->codes;
+    view->encoding = weight->encoding;
+    view->block_size = weight->block_size;
+    view->block_shift = log2_u64(weight->block_size);
+    view->out_features = weight->out_features;
+    view->in_features = weight->in_features;
+    view->flat_block_base = weight->flat_block_base;
+    view->fp32_scales = nullptr;
+    view->scale_codes = nullptr;
+    view->second_level = nullptr;
+    view->scale_block_shift = 0;
+    view->offset = 0.0f;
+    if (weight->encoding == B2_SCALES_FLOAT32) {
+        // require_scale_storage, dispatch.cpp:112-123: the legacy form carries
+        // no second level, block size or offset.
+        if (weight->scales_secondary != nullptr || weight->scale_block_size != 0 ||
+            weight->scale_offset != 0.0f) {
+            return fail(B2_STATUS_INVALID_ARGUMENT,
+                        "legacy NF4 scale storage has an invalid representation");
+        }
+        if ((reinterpret_cast<uintptr_t>(weight->scales_primary) & 3u) != 0) {
+            return fail(B2_STATUS_INVALID_ARGUMENT, "FP32 NF4 scales must be 4-byte aligned");
+        }
+        view->fp32_scales = static_cast<const float*>(weight->scales_primary);
+    } else if (weight->encoding == B2_SCALES_DOUBLE_QUANTIZED_UINT8) {
+        // dispatch.cpp:124-137.
+        if (weight->scales_secondary == nullptr || !block_size_supported(weight->scale_block_size) ||
+            !std::isfinite(weight->scale_offset) || weight->scale_offset < 0.0f) {
+            return fail(B2_STATUS_INVALID_ARGUMENT,
+                        "double-quantized NF4 scale storage has an invalid representation");
+        }
+        view->scale_codes = static_cast<const uint8_t*>(weight->scales_primary);
+        view->second_level = weight->scales_secondary;
+        view->scale_block_shift = log2_u64(weight->scale_block_size);
+        view->offset = weight->scale_offset;
+    } else {
+        return fail(B2_STATUS_INVALID_ARGUMENT, "unknown NF4 scale encoding");
+    }
+    return B2_STATUS_OK;
+}
+
+namespace {
+
+// require_dimensions + size products, dispatch.cpp:244-258,322-331.
+int32_t check_linear_dims(const WeightView& w, uint64_t rows) {
+    if (rows == 0) return fail(B2_STATUS_INVALID_ARGUMENT, "quantized linear needs at least one row");
+    uint64_t tmp = 0;
+    if (mul_overflows(rows, w.in_features, &tmp) || mul_overflows(tmp, w.out_features, &tmp)) {
+        return fail(B2_STATUS_OVERFLOW, "quantized linear dimension product overflows");
+    }
+    return B2_STATUS_OK;
+}
+
+bool aliases_weight(const b2_nf4_weight* weight, const void* p) {
+    return p == weight->codes || p == weight->scales_primary ||
+           (weight->scales_secondary != nullptr && p == weight->scales_secondary);
+}
+
+int32_t linear_forward_impl(const b2_nf4_weight* weight, const float* x, float* y, uint64_t rows,
+                            void*, size_t, cudaStream_t stream) {
+    int32_t status = B2_STATUS_OK;
+    DeviceContext* ctx = device_context(&status);
+    if (ctx == nullptr) return status;
+    WeightView w;
+    B2_TRY(make_weight_view(weight, &w));
+    B2_TRY(check_linear_dims(w, rows));
+    if (x == nullptr || y == nullptr) {
+        return fail(B2_STATUS_INVALID_ARGUMENT, "quantized linear input and output must not be null");
+    }
+    if (x == y) return fail(B2_STATUS_INVALID_ARGUMENT, "quantized linear input and output must not alias");
+    if (aliases_weight(weight, y)) {
+        return fail(B2_STATUS_INVALID_ARGUMENT, "quantized linear weight and output storage must not alias");
+    }
+    if (nf4_gemv_supported(w, x, y, rows)) return launch_nf4_gemv(*ctx, w, x, y, rows, stream);
+    return launch_nf4_linear_forward_generic(*ctx, w, x, y, rows, stream);
+}
+
+int32_t linear_backward_impl(const b2_nf4_weight* weight, const float* dy, float* dx, uint64_t rows,
+                             void*, size_t, cudaStream_t stream) {
+    int32_t status = B2_STATUS_OK;
+    DeviceContext* ctx = device_context(&status);
+    if (ctx == nullptr) return status;
+    WeightView w;
+    B2_TRY(make_weight_view(weight, &w));
+    B2_TRY(check_linear_dims(w, rows));
+    if (dy == nullptr || dx == nullptr) {
+        return fail(B2_STATUS_INVALID_ARGUMENT,
+                    "quantized linear upstream and input gradient must not be null");
+    }
+    if (dy == dx) {
+        return fail(B2_STATUS_INVALID_ARGUMENT,
+                    "quantized linear upstream and input gradient must not alias");
+    }
+    if (aliases_weight(weight, dx)) {
+        return fail(B2_STATUS_INVALID_ARGUMENT, "quantized linear weight and output storage must not alias");
+    }
+    return launch_nf4_linear_input_backward_generic(*ctx, w, dy, dx, rows, stream);
+}
+
+// checked_paged_decode_query_size and the table checks of
+// dispatch_paged_decode_attention_forward, attention/dispatch.cpp:179-219,440-509
+// (the parts that need no host view of device data).
+int32_t check_paged_dims(uint32_t n_seq, uint32_t q_heads, uint32_t kv_heads, uint32_t head_width,
+                         uint32_t block_size, uint64_t physical_blocks, uint32_t max_blocks,
+                         uint32_t max_seq_len) {
+    if (n_seq == 0 || q_heads == 0 || kv_heads == 0 || head_width == 0 || block_size == 0 ||
+        physical_blocks == 0 || max_seq_len == 0 || max_blocks == 0) {
+        return fail(B2_STATUS_INVALID_ARGUMENT, "paged decode attention dimensions must be positive");
+    }
+    if (physical_blocks - 1 > 0xFFFFFFFFull) {
+        return fail(B2_STATUS_OVERFLOW, "paged decode attention physical block IDs exceed uint32_t");
+    }
+    if (q_heads % kv_heads != 0) {
+        return fail(B2_STATUS_INVALID_ARGUMENT,
+                    "paged decode attention query heads must be a multiple of KV heads");
+    }
+    const uint64_t required_blocks = (static_cast<uint64_t>(max_seq_len) - 1) / block_size + 1;
+    if (required_blocks > max_blocks) {
+        return fail(B2_STATUS_INVALID_ARGUMENT,
+                    "paged decode attention block table size does not match the sequence");
+    }
+    if (required_blocks > physical_blocks) {
+        return fail(B2_STATUS_INVALID_ARGUMENT,
+                    "paged decode attention has fewer physical than logical blocks");
+    }
+    uint64_t pool = 0;
+    if (mul_overflows(physical_blocks, kv_heads, &pool) || mul_overflows(pool, block_size, &pool) ||
+        mul_overflows(pool, head_width, &pool)) {
+        return fail(B2_STATUS_OVERFLOW, "paged decode attention pool size overflows");
+    }
+    return B2_STATUS_OK;
+}
+
+}  // namespace
+}  // namespace b2
+
+using namespace b2;
+
+extern "C" {
+
+int32_t b2_abi_version(void) { return B2_ABI_VERSION; }
+
+const char* b2_last_error(void) { return g_last_error.c_str(); }
+
+int32_t b2_is_available(void) {
+    int32_t status = B2_STATUS_OK;
+    const std::string saved = g_last_error;
+    const bool ok = device_context(&status) != nullptr;
+    if (!ok) g_unavailable_reason = g_last_error;
+    g_last_error = saved;
+    return ok ? 1 : 0;
+}
+
+const char* b2_unavailability_reason(void) {
+    if (b2_is_available()) return "";
+    return g_unavailable_reason.c_str();
+}
+
+int32_t b2_nf4_dequantize(const b2_nf4_weight* weight, float* out, void* stream) {
+    clear_error();
+    int32_t status = B2_STATUS_OK;
+    DeviceContext* ctx = device_context(&status);
+    if (ctx == nullptr) return status;
+    WeightView w;
+    B2_TRY(make_weight_view(weight, &w));
+    if (out == nullptr) return fail(B2_STATUS_INVALID_ARGUMENT, "dequantize output must not be null");
+    if (aliases_weight(weight, out)) {
+        return fail(B2_STATUS_INVALID_ARGUMENT, "dequantize output must not alias the packed weight");
+    }
+    return launch_nf4_dequantize(*ctx, w, out, static_cast<cudaStream_t>(stream));
+}
+
+int32_t b2_nf4_linear_forward(const b2_nf4_weight* weight, const float* x, float* y, uint64_t rows,
+                              void* workspace, size_t workspace_bytes, void* stream) {
+    clear_error();
+    return linear_forward_impl(weight, x, y, rows, workspace, workspace_bytes,
+                               static_cast<cudaStream_t>(stream));
+}
+
+int32_t b2_nf4_linear_input_backward(const b2_nf4_weight* weight, const float* dy, float* dx,
+                                     uint64_t rows, void* workspace, size_t workspace_bytes,
+                                     void* stream) {
+    clear_error();
+    return linear_backward_impl(weight, dy, dx, rows, workspace, workspace_bytes,
+                                static_cast<cudaStream_t>(stream));
+}
+
+size_t b2_nf4_linear_workspace_bytes(const b2_nf4_weight*, uint64_t, int32_t) { return 0; }
+
+size_t b2_paged_decode_workspace_bytes(uint32_t n_seq, uint32_t q_heads, uint32_t head_width,
+                                       uint32_t block_size, uint32_t max_seq_len) {
+    return paged_decode_workspace_bytes(n_seq, q_heads, head_width, block_size, max_seq_len);
+}
+
+int32_t b2_paged_decode_attention(const float* q, const float* k_pages, const float* v_pages,
+                                  const uint32_t* block_tables, const uint32_t* seq_lens, float* ctx_out,
+                                  uint32_t n_seq, uint32_t q_heads, uint32_t kv_heads,
+                                  uint32_t head_width, uint32_t block_size, uint64_t physical_blocks,
+                                  uint32_t max_blocks, uint32_t max_seq_len, void* workspace,
+                                  size_t workspace_bytes, uint32_t* status_word, void* stream) {
+    clear_error();
+    int32_t status = B2_STATUS_OK;
+    DeviceContext* ctx = device_context(&status);
+    if (ctx == nullptr) return status;
+    B2_TRY(check_paged_dims(n_seq, q_heads, kv_heads, head_width, block_size, physical_blocks,
+                            max_blocks, max_seq_len));
+    if (q == nullptr || k_pages == nullptr || v_pages == nullptr || block_tables == nullptr ||
+        seq_lens == nullptr || ctx_out == nullptr) {
+        return fail(B2_STATUS_INVALID_ARGUMENT, "paged decode attention pointers must not be null");
+    }
+    // require_distinct, attention/dispatch.cpp:504-506.
+    if (ctx_out == q || ctx_out == k_pages || ctx_out == v_pages) {
+        return fail(B2_STATUS_INVALID_ARGUMENT, "paged decode attention output must not alias an input");
+    }
+    PagedDecodeArgs args{q, k_pages, v_pages, block_tables, seq_lens, ctx_out,
+                         n_seq, q_heads, kv_heads, head_width, block_size, max_blocks, max_seq_len,
+                         physical_blocks, status_word};
+    const size_t need =
+        paged_decode_workspace_bytes(n_seq, q_heads, head_width, block_size, max_seq_len);
+    if (workspace == nullptr && need > 0) {
+        B2_TRY(reserve_arena(ctx, need));
+        workspace = ctx->arena;
+        workspace_bytes = ctx->arena_bytes;
+    }
+    return launch_paged_decode(*ctx, args, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
+}
+
+// ---- host-buffer seam ---------------------------------------------------------
+
+static int32_t host_linear(const b2_nf4_weight* weight, const float* src_host, float* dst_host,
+                           uint64_t rows, bool backward, cudaStream_t stream) {
+    int32_t status = B2_STATUS_OK;
+    DeviceContext* ctx = device_context(&status);
+    if (ctx == nullptr) return status;
+    WeightView w;
+    B2_TRY(make_weight_view(weight, &w));
+    B2_TRY(check_linear_dims(w, rows));
+    if (src_host == nullptr || dst_host == nullptr) {
+        return fail(B2_STATUS_INVALID_ARGUMENT, "quantized linear host buffers must not be null");
+    }
+    if (src_host == dst_host) {
+        return fail(B2_STATUS_INVALID_ARGUMENT, backward
+                        ? "quantized linear upstream and input gradient must not alias"
+                        : "quantized linear input and output must not alias");
+    }
+    const uint64_t src_width = backward ? w.out_features : w.in_features;
+    const uint64_t dst_width = backward ? w.in_features : w.out_features;
+    const size_t src_bytes = rows * src_width * sizeof(float);
+    const size_t dst_bytes = rows * dst_width * sizeof(float);
+    const size_t src_padded = (src_bytes + 255) & ~size_t{255};
+    B2_TRY(reserve_stage(ctx, src_padded + dst_bytes, 0));
+    float* d_src = static_cast<float*>(ctx->stage);
+    float* d_dst = reinterpret_cast<float*>(static_cast<uint8_t*>(ctx->stage) + src_padded);
+    B2_CUDA_TRY(cudaMemcpyAsync(d_src, src_host, src_bytes, cudaMemcpyHostToDevice, stream));
+    if (backward) {
+        B2_TRY(linear_backward_impl(weight, d_src, d_dst, rows, nullptr, 0, stream));
+    } else {
+        B2_TRY(linear_forward_impl(weight, d_src, d_dst, rows, nullptr, 0, stream));
+    }
+    B2_CUDA_TRY(cudaMemcpyAsync(dst_host, d_dst, dst_bytes, cudaMemcpyDeviceToHost, stream));
+    B2_CUDA_TRY(cudaStreamSynchronize(stream));
+    return B2_STATUS_OK;
+}
+
+int32_t b2_host_nf4_linear_forward(const b2_nf4_weight* weight, const float* x_host, float* y_host,
+                                   uint64_t rows, void* stream) {
+    clear_error();
+    return host_linear(weight, x_host, y_host, rows, false, static_cast<cudaStream_t>(stream));
+}
+
+int32_t b2_host_nf4_linear_input_backward(const b2_nf4_weight* weight, const float* dy_host,
+                                          float* dx_host, uint64_t rows, void* stream) {
+    clear_error();
+    return host_linear(weight, dy_host, dx_host, rows, true, static_cast<cudaStream_t>(stream));
+}
+
+int32_t b2_host_paged_decode_attention(const float* q_host, const float* k_pages, const float* v_pages,
+                                       const uint32_t* block_tables_host,
+                                       const uint32_t* seq_lens_host, float* ctx_host, uint32_t n_seq,
+                                       uint32_t q_heads, uint32_t kv_heads, uint32_t head_width,
+                                       uint32_t block_size, uint64_t physical_blocks,
+                                       uint32_t max_blocks, void* stream_ptr) {
+    clear_error();
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+    int32_t status = B2_STATUS_OK;
+    DeviceContext* ctx = device_context(&status);
+    if (ctx == nullptr) return status;
+    if (q_host == nullptr || k_pages == nullptr || v_pages == nullptr || block_tables_host == nullptr ||
+        seq_lens_host == nullptr || ctx_host == nullptr) {
+        return fail(B2_STATUS_INVALID_ARGUMENT, "paged decode attention pointers must not be null");
+    }
+    if (n_seq == 0 || block_size == 0) {
+        return fail(B2_STATUS_INVALID_ARGUMENT, "paged decode attention dimensions must be positive");
+    }
+    if (q_host == ctx_host) {
+        return fail(B2_STATUS_INVALID_ARGUMENT, "paged decode attention output must not alias an input");
+    }
+    uint32_t max_seq_len = 0;
+    for (uint32_t s = 0; s < n_seq; ++s) {
+        if (seq_lens_host[s] == 0) {
+            return fail(B2_STATUS_INVALID_ARGUMENT, "paged decode attention dimensions must be positive");
+        }
+        if (seq_lens_host[s] > max_seq_len) max_seq_len = seq_lens_host[s];
+    }
+    B2_TRY(check_paged_dims(n_seq, q_heads, kv_heads, head_width, block_size, physical_blocks,
+                            max_blocks, max_seq_len));
+    for (uint32_t s = 0; s < n_seq; ++s) {
+        const uint32_t blocks = (seq_lens_host[s] - 1) / block_size + 1;
+        for (uint32_t b = 0; b < blocks; ++b) {
+            if (block_tables_host[static_cast<uint64_t>(s) * max_blocks + b] >= physical_blocks) {
+                return fail(B2_STATUS_OUT_OF_RANGE,
+                            "paged decode attention block table contains an invalid block");
+            }
+        }
+    }
+    const size_t q_bytes = static_cast<size_t>(n_seq) * q_heads * head_width * sizeof(float);
+    const size_t table_bytes = static_cast<size_t>(n_seq) * max_blocks * sizeof(uint32_t);
+    const size_t len_bytes = static_cast<size_t>(n_seq) * sizeof(uint32_t);
+    auto pad = [](size_t v) { return (v + 255) & ~size_t{255}; };
+    const size_t off_ctx = pad(q_bytes), off_table = off_ctx + pad(q_bytes),
+                 off_len = off_table + pad(table_bytes), off_status = off_len + pad(len_bytes),
+                 off_ws = off_status + 256;
+    const size_t ws_bytes =
+        paged_decode_workspace_bytes(n_seq, q_heads, head_width, block_size, max_seq_len);
+    B2_TRY(reserve_stage(ctx, off_ws + ws_bytes, 0));
+    uint8_t* base = static_cast<uint8_t*>(ctx->stage);
+    float* d_q = reinterpret_cast<float*>(base);
+    float* d_ctx = reinterpret_cast<float*>(base + off_ctx);
+    uint32_t* d_table = reinterpret_cast<uint32_t*>(base + off_table);
+    uint32_t* d_len = reinterpret_cast<uint32_t*>(base + off_len);
+    uint32_t* d_status = reinterpret_cast<uint32_t*>(base + off_status);
+    B2_CUDA_TRY(cudaMemcpyAsync(d_q, q_host, q_bytes, cudaMemcpyHostToDevice, stream));
+    B2_CUDA_TRY(cudaMemcpyAsync(d_table, block_tables_host, table_bytes, cudaMemcpyHostToDevice, stream));
+    B2_CUDA_TRY(cudaMemcpyAsync(d_len, seq_lens_host, len_bytes, cudaMemcpyHostToDevice, stream));
+    B2_CUDA_TRY(cudaMemsetAsync(d_status, 0, sizeof(uint32_t), stream));
+    PagedDecodeArgs args{d_q, k_pages, v_pages, d_table, d_len, d_ctx,
+                         n_seq, q_heads, kv_heads, head_width, block_size, max_blocks, max_seq_len,
+                         physical_blocks, d_status};
+    B2_TRY(launch_paged_decode(*ctx, args, base + off_ws, ws_bytes, stream));
+    uint32_t host_status = 0;
+    B2_CUDA_TRY(cudaMemcpyAsync(ctx_host, d_ctx, q_bytes, cudaMemcpyDeviceToHost, stream));
+    B2_CUDA_TRY(cudaMemcpyAsync(&host_status, d_status, sizeof(uint32_t), cudaMemcpyDeviceToHost, stream));
+    B2_CUDA_TRY(cudaStreamSynchronize(stream));
+    if (host_status & B2_ATTN_STATUS_BAD_BLOCK) {
+        return fail(B2_STATUS_OUT_OF_RANGE, "paged decode attention block table contains an invalid block");
+    }
+    if (host_status & B2_ATTN_STATUS_NAN_OR_POS_INF) {
+        return fail(B2_STATUS_DOMAIN_ERROR, "softmax rejects NaN and positive infinity");
+    }
+    if (host_status & B2_ATTN_STATUS_ALL_NEG_INF) {
+        return fail(B2_STATUS_DOMAIN_ERROR, "softmax requires one finite value per slice");
+    }
+    return B2_STATUS_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,44 @@
+// Internal launcher interface between the C-ABI layer (api.cu) and the kernel
+// translation units. Every launcher only enqueues work on `stream`.
+#pragma once
+
+#include "b2_common.cuh"
+
+namespace b2 {
+
+// nf4_dequant.cu
+int32_t launch_nf4_dequantize(const DeviceContext& ctx, const WeightView& w, float* out,
+                              cudaStream_t stream);
+
+// nf4_linear_generic.cu - any shape, any block size, FP32 SIMT.
+int32_t launch_nf4_linear_forward_generic(const DeviceContext& ctx, const WeightView& w,
+                                          const float* x, float* y, uint64_t rows,
+                                          cudaStream_t stream);
+int32_t launch_nf4_linear_input_backward_generic(const DeviceContext& ctx, const WeightView& w,
+                                                 const float* dy, float* dx, uint64_t rows,
+                                                 cudaStream_t stream);
+
+// nf4_gemv.cu - decode path, rows <= 32.
+bool nf4_gemv_supported(const WeightView& w, const float* x, const float* y, uint64_t rows);
+int32_t launch_nf4_gemv(const DeviceContext& ctx, const WeightView& w, const float* x, float* y,
+                        uint64_t rows, cudaStream_t stream);
+int32_t init_gemv_lut(DeviceContext* ctx);
+
+// paged_decode.cu
+struct PagedDecodeArgs {
+    const float* q;
+    const float* k_pages;
+    const float* v_pages;
+    const uint32_t* block_tables;
+    const uint32_t* seq_lens;
+    float* ctx;
+    uint32_t n_seq, q_heads, kv_heads, head_width, block_size, max_blocks, max_seq_len;
+    uint64_t physical_blocks;
+    uint32_t* status;  // may be null
+};
+size_t paged_decode_workspace_bytes(uint32_t n_seq, uint32_t q_heads, uint32_t head_width,
+                                    uint32_t block_size, uint32_t max_seq_len);
+int32_t launch_paged_decode(const DeviceContext& ctx, const PagedDecodeArgs& args, void* workspace,
+                            size_t workspace_bytes, cudaStream_t stream);
+
+}  // namespace b2

@@ -1,0 +1,386 @@
+// Paged-KV single-token decode attention for a batch of sequences with
+// grouped-query heads (query head h reads KV head h / rep).
+//
+// Pages are consumed in the reference's layout, FP32
+// [physical_block, kv_head, block_offset, head_width]
+// (src/core/backend/attention/contracts.hpp:88-106), through per-sequence block
+// tables; the arithmetic restates
+// src/core/backend/attention/reference/paged_decode.cpp:37-132 as an online
+// softmax split over the sequence (split-K), so each K/V byte is read from HBM
+// exactly once for all `rep` query heads that share it. The kernel is bound by
+// that read: 8 * head_width bytes per (token, kv head).
+//
+// Two paths:
+//  * paged_decode_fast_kernel  - head_width 128, block_size 16, rep in {1,2,4,8}.
+//  * paged_decode_generic_*    - any shape (the reference's own test uses
+//    head_width 3 and block_size 2), scores spilled to workspace.
+// Non-finite scores are reported through a device status word, never by
+// trapping: bit 0 a NaN or +inf score, bit 1 all scores of a head -inf, bit 2 a
+// block id outside the pool (which is then not dereferenced).
+#include "b2_common.cuh"
+#include "b2_kernels.h"
+
+#include <cmath>
+
+namespace b2 {
+namespace {
+
+constexpr int kD = 128;            // head width of the fast path
+constexpr int kPage = 16;          // tokens per page of the fast path
+constexpr int kFastWarps = 4;
+constexpr int kTokensPerCta = 256; // split size: 16 pages, 4 per warp
+constexpr int kPartialStride = kD + 2;  // m, l, acc[128]
+
+__device__ __forceinline__ float4 ldg_stream_f4(const float* p) {
+    float4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.f32 {%0,%1,%2,%3}, [%4];\n"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+                 : "l"(p));
+    return v;
+}
+
+template <int REP>
+__global__ void __launch_bounds__(kFastWarps * 32)
+paged_decode_fast_kernel(const PagedDecodeArgs a, float* __restrict__ partials, uint32_t max_splits) {
+    const uint32_t split = blockIdx.x, kvh = blockIdx.y, seq = blockIdx.z;
+    const uint32_t len = __ldg(a.seq_lens + seq);
+    const uint32_t n_splits = (len + kTokensPerCta - 1) / kTokensPerCta;
+    if (split >= n_splits) return;
+
+    const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
+    const uint32_t grp = lane >> 3, sub = lane & 7u;
+    const float scale = 1.0f / sqrtf(static_cast<float>(kD));
+
+    __shared__ __align__(16) float s_p[kFastWarps][kPage][REP];
+    __shared__ float s_m[kFastWarps][REP], s_l[kFastWarps][REP];
+    __shared__ __align__(16) float s_acc[kFastWarps][REP][kD];
+
+    // Query slices used by the score phase: dims 4*sub + 32*j .. +3.
+    float4 q[REP][4];
+    const float* qbase = a.q + (static_cast<uint64_t>(seq) * a.q_heads + kvh * REP) * kD;
+#pragma unroll
+    for (int h = 0; h < REP; ++h)
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+            q[h][j] = __ldg(reinterpret_cast<const float4*>(qbase + h * kD + 4 * sub + 32 * j));
+
+    float m[REP], l[REP];
+    float4 acc[REP];
+#pragma unroll
+    for (int h = 0; h < REP; ++h) {
+        m[h] = -INFINITY;
+        l[h] = 0.0f;
+        acc[h] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    uint32_t flags = 0;
+
+    const uint32_t tok_begin = split * kTokensPerCta;
+    const uint32_t tok_end = min(tok_begin + kTokensPerCta, len);
+    const uint32_t page_begin = tok_begin / kPage;
+    const uint32_t page_end = (tok_end + kPage - 1) / kPage;
+    const uint32_t* table = a.block_tables + static_cast<uint64_t>(seq) * a.max_blocks;
+    const uint64_t page_stride = static_cast<uint64_t>(a.kv_heads) * kPage * kD;
+
+    for (uint32_t pg = page_begin + warp; pg < page_end; pg += kFastWarps) {
+        uint64_t phys = __ldg(table + pg);
+        if (phys >= a.physical_blocks) {
+            flags |= B2_ATTN_STATUS_BAD_BLOCK;
+            phys = 0;
+        }
+        const float* kp = a.k_pages + phys * page_stride + static_cast<uint64_t>(kvh) * kPage * kD;
+        const float* vp = a.v_pages + phys * page_stride + static_cast<uint64_t>(kvh) * kPage * kD;
+        const uint32_t valid = min(static_cast<uint32_t>(kPage), len - pg * kPage);
+
+        // ---- scores: 4 passes of 4 tokens, 8 lanes per token ----
+        float4 kreg[4][4];
+#pragma unroll
+        for (int ps = 0; ps < 4; ++ps)
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                kreg[ps][j] = ldg_stream_f4(kp + (4 * ps + grp) * kD + 4 * sub + 32 * j);
+
+        float sc[4][REP];
+#pragma unroll
+        for (int ps = 0; ps < 4; ++ps) {
+#pragma unroll
+            for (int h = 0; h < REP; ++h) {
+                float d = 0.0f;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    d = fmaf(q[h][j].x, kreg[ps][j].x, d);
+                    d = fmaf(q[h][j].y, kreg[ps][j].y, d);
+                    d = fmaf(q[h][j].z, kreg[ps][j].z, d);
+                    d = fmaf(q[h][j].w, kreg[ps][j].w, d);
+                }
+                d += __shfl_xor_sync(0xFFFFFFFFu, d, 1);
+                d += __shfl_xor_sync(0xFFFFFFFFu, d, 2);
+                d += __shfl_xor_sync(0xFFFFFFFFu, d, 4);
+                d *= scale;
+                const bool in_range = static_cast<uint32_t>(4 * ps + grp) < valid;
+                if (in_range && (isnan(d) || d == INFINITY)) flags |= B2_ATTN_STATUS_NAN_OR_POS_INF;
+                sc[ps][h] = in_range ? d : -INFINITY;
+            }
+        }
+
+        // ---- online softmax update (all lanes keep identical m, l) ----
+        float rescale[REP];
+#pragma unroll
+        for (int h = 0; h < REP; ++h) {
+            float pm = fmaxf(fmaxf(sc[0][h], sc[1][h]), fmaxf(sc[2][h], sc[3][h]));
+            pm = fmaxf(pm, __shfl_xor_sync(0xFFFFFFFFu, pm, 8));
+            pm = fmaxf(pm, __shfl_xor_sync(0xFFFFFFFFu, pm, 16));
+            const float m_new = fmaxf(m[h], pm);
+            const bool dead = (m_new == -INFINITY) || isnan(m_new);
+            rescale[h] = dead ? 1.0f : __expf(m[h] - m_new);
+            float ps_sum = 0.0f;
+#pragma unroll
+            for (int ps = 0; ps < 4; ++ps) {
+                const float e = dead ? 0.0f : __expf(sc[ps][h] - m_new);
+                sc[ps][h] = e;
+                ps_sum += e;
+            }
+            ps_sum += __shfl_xor_sync(0xFFFFFFFFu, ps_sum, 8);
+            ps_sum += __shfl_xor_sync(0xFFFFFFFFu, ps_sum, 16);
+            l[h] = l[h] * rescale[h] + ps_sum;
+            m[h] = dead ? m[h] : m_new;
+        }
+        // Lane `sub` of each token group publishes head `sub`'s probability.
+        __syncwarp();
+        if (sub < REP) {
+#pragma unroll
+            for (int ps = 0; ps < 4; ++ps) {
+                float v = sc[ps][0];
+#pragma unroll
+                for (int h = 1; h < REP; ++h) v = (sub == static_cast<uint32_t>(h)) ? sc[ps][h] : v;
+                s_p[warp][4 * ps + grp][sub] = v;
+            }
+        }
+        __syncwarp();
+
+        // ---- values: lane owns dims 4*lane .. 4*lane+3 for every head ----
+#pragma unroll
+        for (int h = 0; h < REP; ++h) {
+            acc[h].x *= rescale[h];
+            acc[h].y *= rescale[h];
+            acc[h].z *= rescale[h];
+            acc[h].w *= rescale[h];
+        }
+#pragma unroll 4
+        for (uint32_t tk = 0; tk < valid; ++tk) {
+            const float4 v = ldg_stream_f4(vp + tk * kD + 4 * lane);
+#pragma unroll
+            for (int h = 0; h < REP; ++h) {
+                const float pr = s_p[warp][tk][h];
+                acc[h].x = fmaf(pr, v.x, acc[h].x);
+                acc[h].y = fmaf(pr, v.y, acc[h].y);
+                acc[h].z = fmaf(pr, v.z, acc[h].z);
+                acc[h].w = fmaf(pr, v.w, acc[h].w);
+            }
+        }
+    }
+
+    // ---- combine the warps of the CTA ----
+#pragma unroll
+    for (int h = 0; h < REP; ++h) {
+        if (lane == 0) {
+            s_m[warp][h] = m[h];
+            s_l[warp][h] = l[h];
+        }
+        *reinterpret_cast<float4*>(&s_acc[warp][h][4 * lane]) = acc[h];
+    }
+    if (flags != 0 && a.status != nullptr) atomicOr(a.status, flags);
+    __syncthreads();
+
+    // Thread c (0..127) finishes dim c of every head.
+    const uint32_t c = threadIdx.x;
+#pragma unroll
+    for (int h = 0; h < REP; ++h) {
+        float mm = -INFINITY;
+#pragma unroll
+        for (int wv = 0; wv < kFastWarps; ++wv) mm = fmaxf(mm, s_m[wv][h]);
+        float ll = 0.0f, o = 0.0f;
+#pragma unroll
+        for (int wv = 0; wv < kFastWarps; ++wv) {
+            const float f = (s_m[wv][h] == -INFINITY) ? 0.0f : __expf(s_m[wv][h] - mm);
+            ll = fmaf(s_l[wv][h], f, ll);
+            o = fmaf(s_acc[wv][h][c], f, o);
+        }
+        const uint64_t head = static_cast<uint64_t>(seq) * a.q_heads + kvh * REP + h;
+        if (n_splits == 1) {
+            if (mm == -INFINITY) {
+                if (c == 0 && a.status != nullptr) atomicOr(a.status, B2_ATTN_STATUS_ALL_NEG_INF);
+                a.ctx[head * kD + c] = 0.0f;
+            } else {
+                a.ctx[head * kD + c] = o / ll;
+            }
+        } else {
+            float* dst = partials + (head * max_splits + split) * kPartialStride;
+            if (c == 0) {
+                dst[0] = mm;
+                dst[1] = ll;
+            }
+            dst[2 + c] = o;
+        }
+    }
+}
+
+// Combines the split partials of every (sequence, query head) that was split.
+__global__ void __launch_bounds__(kD)
+paged_decode_merge_kernel(const PagedDecodeArgs a, const float* __restrict__ partials,
+                          uint32_t max_splits) {
+    const uint32_t h = blockIdx.x, seq = blockIdx.y, c = threadIdx.x;
+    const uint32_t len = __ldg(a.seq_lens + seq);
+    const uint32_t n_splits = (len + kTokensPerCta - 1) / kTokensPerCta;
+    if (n_splits <= 1) return;
+    const uint64_t head = static_cast<uint64_t>(seq) * a.q_heads + h;
+    const float* src = partials + head * max_splits * kPartialStride;
+    float mm = -INFINITY;
+    for (uint32_t s = 0; s < n_splits; ++s) mm = fmaxf(mm, __ldg(src + s * kPartialStride));
+    float ll = 0.0f, o = 0.0f;
+    for (uint32_t s = 0; s < n_splits; ++s) {
+        const float ms = __ldg(src + s * kPartialStride);
+        const float f = (ms == -INFINITY) ? 0.0f : __expf(ms - mm);
+        ll = fmaf(__ldg(src + s * kPartialStride + 1), f, ll);
+        o = fmaf(__ldg(src + s * kPartialStride + 2 + c), f, o);
+    }
+    if (mm == -INFINITY) {
+        if (c == 0 && a.status != nullptr) atomicOr(a.status, B2_ATTN_STATUS_ALL_NEG_INF);
+        a.ctx[head * kD + c] = 0.0f;
+    } else {
+        a.ctx[head * kD + c] = o / ll;
+    }
+}
+
+// ---- generic path ----------------------------------------------------------------
+
+// One warp per (sequence, query head); scores live in workspace
+// [n_seq, q_heads, max_seq_len]. The normaliser is accumulated in double and
+// the context in position order, like the reference loop.
+__global__ void __launch_bounds__(128)
+paged_decode_generic_kernel(const PagedDecodeArgs a, float* __restrict__ scores) {
+    const uint32_t lane = threadIdx.x & 31u;
+    const uint64_t task = (static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+    const uint64_t tasks = static_cast<uint64_t>(a.n_seq) * a.q_heads;
+    if (task >= tasks) return;
+    const uint32_t seq = static_cast<uint32_t>(task / a.q_heads);
+    const uint32_t h = static_cast<uint32_t>(task % a.q_heads);
+    const uint32_t kvh = h / (a.q_heads / a.kv_heads);
+    const uint32_t len = __ldg(a.seq_lens + seq);
+    const uint32_t d = a.head_width, bs = a.block_size;
+    const float scale = 1.0f / sqrtf(static_cast<float>(d));
+    const float* qv = a.q + task * d;
+    const uint32_t* table = a.block_tables + static_cast<uint64_t>(seq) * a.max_blocks;
+    float* sc = scores + task * a.max_seq_len;
+    uint32_t flags = 0;
+
+    auto page_offset = [&](uint32_t pos, uint32_t& flag_out) -> uint64_t {
+        uint64_t phys = __ldg(table + pos / bs);
+        if (phys >= a.physical_blocks) {
+            flag_out |= B2_ATTN_STATUS_BAD_BLOCK;
+            phys = 0;
+        }
+        return ((phys * a.kv_heads + kvh) * bs + pos % bs) * d;
+    };
+
+    float mx = -INFINITY;
+    for (uint32_t pos = lane; pos < len; pos += 32) {
+        const float* kv = a.k_pages + page_offset(pos, flags);
+        float s = 0.0f;
+        for (uint32_t c = 0; c < d; ++c) s = __fadd_rn(s, __fmul_rn(__ldg(qv + c), __ldg(kv + c)));
+        s *= scale;
+        if (isnan(s) || s == INFINITY) flags |= B2_ATTN_STATUS_NAN_OR_POS_INF;
+        sc[pos] = s;
+        mx = fmaxf(mx, s);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
+        flags |= __shfl_xor_sync(0xFFFFFFFFu, flags, o);
+    }
+    if (mx == -INFINITY && !(flags & B2_ATTN_STATUS_NAN_OR_POS_INF)) flags |= B2_ATTN_STATUS_ALL_NEG_INF;
+    if (flags & (B2_ATTN_STATUS_NAN_OR_POS_INF | B2_ATTN_STATUS_ALL_NEG_INF)) {
+        for (uint32_t c = lane; c < d; c += 32) a.ctx[task * d + c] = 0.0f;
+        if (lane == 0 && a.status != nullptr) atomicOr(a.status, flags);
+        return;
+    }
+    double denom = 0.0;
+    for (uint32_t pos = lane; pos < len; pos += 32) {
+        const double e = exp(static_cast<double>(sc[pos] - mx));
+        sc[pos] = static_cast<float>(e);
+        denom += e;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) denom += __shfl_xor_sync(0xFFFFFFFFu, denom, o);
+    __syncwarp();
+    for (uint32_t c = lane; c < d; c += 32) {
+        float total = 0.0f;
+        for (uint32_t pos = 0; pos < len; ++pos) {
+            const float pr = static_cast<float>(static_cast<double>(sc[pos]) / denom);
+            total = __fadd_rn(total, __fmul_rn(pr, __ldg(a.v_pages + page_offset(pos, flags) + c)));
+        }
+        a.ctx[task * d + c] = total;
+    }
+    if (flags != 0 && lane == 0 && a.status != nullptr) atomicOr(a.status, flags);
+}
+
+bool fast_path(const PagedDecodeArgs& a) {
+    const uint32_t rep = a.q_heads / a.kv_heads;
+    return a.head_width == kD && a.block_size == kPage &&
+           (rep == 1 || rep == 2 || rep == 4 || rep == 8) &&
+           (reinterpret_cast<uintptr_t>(a.q) & 15u) == 0 &&
+           (reinterpret_cast<uintptr_t>(a.k_pages) & 15u) == 0 &&
+           (reinterpret_cast<uintptr_t>(a.v_pages) & 15u) == 0 && a.kv_heads <= 65535 &&
+           a.n_seq <= 65535;
+}
+
+uint32_t splits_for(uint32_t max_seq_len) { return (max_seq_len + kTokensPerCta - 1) / kTokensPerCta; }
+
+}  // namespace
+
+size_t paged_decode_workspace_bytes(uint32_t n_seq, uint32_t q_heads, uint32_t head_width,
+                                    uint32_t block_size, uint32_t max_seq_len) {
+    const size_t heads = static_cast<size_t>(n_seq) * q_heads;
+    if (head_width == kD && block_size == kPage) {
+        const uint32_t splits = splits_for(max_seq_len);
+        return splits > 1 ? heads * splits * kPartialStride * sizeof(float) : 0;
+    }
+    return heads * max_seq_len * sizeof(float);
+}
+
+int32_t launch_paged_decode(const DeviceContext&, const PagedDecodeArgs& a, void* workspace,
+                            size_t workspace_bytes, cudaStream_t stream) {
+    const size_t need = paged_decode_workspace_bytes(a.n_seq, a.q_heads, a.head_width, a.block_size,
+                                                     a.max_seq_len);
+    if (need > workspace_bytes) {
+        return fail(B2_STATUS_INVALID_ARGUMENT,
+                    "paged decode attention workspace too small: need %zu bytes, got %zu", need,
+                    workspace_bytes);
+    }
+    if (fast_path(a)) {
+        const uint32_t splits = splits_for(a.max_seq_len);
+        if (splits > 65535) return fail(B2_STATUS_OVERFLOW, "paged decode sequence too long");
+        const dim3 grid(splits, a.kv_heads, a.n_seq);
+        float* partials = static_cast<float*>(workspace);
+        switch (a.q_heads / a.kv_heads) {
+        case 1: paged_decode_fast_kernel<1><<<grid, kFastWarps * 32, 0, stream>>>(a, partials, splits); break;
+        case 2: paged_decode_fast_kernel<2><<<grid, kFastWarps * 32, 0, stream>>>(a, partials, splits); break;
+        case 4: paged_decode_fast_kernel<4><<<grid, kFastWarps * 32, 0, stream>>>(a, partials, splits); break;
+        default: paged_decode_fast_kernel<8><<<grid, kFastWarps * 32, 0, stream>>>(a, partials, splits); break;
+        }
+        B2_CUDA_TRY(cudaGetLastError());
+        if (splits > 1) {
+            paged_decode_merge_kernel<<<dim3(a.q_heads, a.n_seq), kD, 0, stream>>>(a, partials, splits);
+            B2_CUDA_TRY(cudaGetLastError());
+        }
+        return B2_STATUS_OK;
+    }
+    const uint64_t tasks = static_cast<uint64_t>(a.n_seq) * a.q_heads;
+    const uint64_t blocks = (tasks + 3) / 4;
+    if (blocks > 0x7FFFFFFFull) return fail(B2_STATUS_OVERFLOW, "paged decode batch too large");
+    paged_decode_generic_kernel<<<static_cast<unsigned>(blocks), 128, 0, stream>>>(
+        a, static_cast<float*>(workspace));
+    B2_CUDA_TRY(cudaGetLastError());
+    return B2_STATUS_OK;
+}
+
+}  // namespace b2
