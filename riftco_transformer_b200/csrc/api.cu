@@ -233,7 +233,16 @@ int32_t linear_forward_impl(const b2_nf4_weight* weight, const float* x, float* 
     if (aliases_weight(weight, y)) {
         return fail(B2_STATUS_INVALID_ARGUMENT, "quantized linear weight and output storage must not alias");
     }
-    if (nf4_gemv_supported(w, x, y, rows)) return launch_nf4_gemv(*ctx, w, x, y, rows, stream);
+    if (nf4_gemv_supported(w, x, y, rows)) {
+        // B2_GEMV_IMPL=tile forces the non-persistent kernel (for A/B measurements).
+        static const char* impl = getenv("B2_GEMV_IMPL");
+        uint32_t spw = 0, ksplit = 0;
+        if ((impl == nullptr || strcmp(impl, "tile") != 0) &&
+            nf4_gemv_stream_plan(*ctx, w, rows, &spw, &ksplit)) {
+            return launch_nf4_gemv_stream(*ctx, w, x, y, rows, spw, ksplit, stream);
+        }
+        return launch_nf4_gemv(*ctx, w, x, y, rows, stream);
+    }
     return launch_nf4_linear_forward_generic(*ctx, w, x, y, rows, stream);
 }
 

@@ -24,6 +24,12 @@ int32_t launch_nf4_gemv(const DeviceContext& ctx, const WeightView& w, const flo
                         uint64_t rows, cudaStream_t stream);
 int32_t init_gemv_lut(DeviceContext* ctx);
 
+// nf4_gemv_stream.cu - persistent, software-pipelined decode kernel, rows <= 16.
+bool nf4_gemv_stream_plan(const DeviceContext& ctx, const WeightView& w, uint64_t rows,
+                          uint32_t* spw_out, uint32_t* ksplit_out);
+int32_t launch_nf4_gemv_stream(const DeviceContext& ctx, const WeightView& w, const float* x, float* y,
+                               uint64_t rows, uint32_t spw, uint32_t ksplit, cudaStream_t stream);
+
 // paged_decode.cu
 struct PagedDecodeArgs {
     const float* q;

@@ -34,12 +34,15 @@ namespace {
 
 constexpr int kWarps = 8;
 constexpr int kThreads = kWarps * 32;
-constexpr int kStepK = 64;            // weights per step (one scale block or a part of one)
-// Steps of activations staged in shared memory at once (per batch-tile count).
-template <int MT> constexpr int chunk_steps_for() { return MT >= 4 ? 16 : 32; }
-constexpr int kXRowHalves = 72;       // 64 fp16 + 8 of padding: conflict-free 128-bit reads
-constexpr int kLutBytes = 256 * 256;  // byte table, 256-byte stride, 128 bytes used per row
-constexpr int kUnit = 4;              // steps whose loads are in flight together per warp
+constexpr int kStepK = 64;    // weights per step; a step never straddles a scale block
+constexpr int kWR = 2;        // warp rows: each warp owns 32 weight rows (two MMA row groups)
+constexpr int kWK = 4;        // warps that split the contraction inside a CTA
+constexpr int kRowsTile = 64; // weight rows per CTA
+constexpr int kLutBytes = 256 * 256;
+
+// Steps staged per chunk: the fp16 activations of a chunk live in the unused
+// upper half of the 256 table rows (one 128-byte row per (step, batch row)).
+template <int MT> constexpr int chunk_steps_for() { return 256 / (8 * MT); }
 
 struct GemvParams {
     WeightView w;
@@ -48,8 +51,7 @@ struct GemvParams {
     uint32_t rows;           // batch rows M
     uint32_t steps_total;    // in_features / 64
     uint32_t steps_per_cta;  // contraction slice of one cluster rank
-    uint32_t row_tiles;      // ceil(out / (16 * WR))
-    const uint32_t* lut;
+    const uint32_t* lut;     // compact [256][32] words
 };
 
 __device__ __forceinline__ void mma_f16_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
@@ -69,34 +71,35 @@ __device__ __forceinline__ uint2 ldg_stream_u2(const uint8_t* p) {
     return v;
 }
 
-// Shared memory carve-up (dynamic): [lut 64 KB][x chunk][scales][reduction].
-template <int MT, int WR>
+__device__ __forceinline__ void cp_async_16(void* smem_dst, const void* gmem_src) {
+    const uint32_t dst = static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst));
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(gmem_src));
+}
+
+// Shared memory (dynamic): 64 KB of 256-byte rows - bytes [0,128) of row v are
+// the byte table entry v for the 32 lanes, bytes [128,256) of row h hold the
+// 64 fp16 activations of (step, batch row) h - then scales / reduction scratch.
+template <int MT>
 struct Smem {
     static constexpr int kChunkSteps = chunk_steps_for<MT>();
-    static constexpr int kRowsTile = 16 * WR;
-    static constexpr int kWK = kWarps / WR;
-    static constexpr int kXBytes = kChunkSteps * 8 * MT * kXRowHalves * 2;
-    static constexpr int kScaleBytes = kRowsTile * kChunkSteps * 4;
+    static constexpr int kScaleBytes = kRowsTile * (kChunkSteps + 1) * 4;  // +1: rows land in different banks
     static constexpr int kRedBytes = kWK * kRowsTile * 8 * MT * 4;
+    static constexpr int kScratchBytes = kScaleBytes > kRedBytes ? kScaleBytes : kRedBytes;
     static constexpr int kOutBytes = kRowsTile * 8 * MT * 4;
-    static constexpr int kXOff = kLutBytes;
-    static constexpr int kScaleOff = kXOff + kXBytes;
-    static constexpr int kRedOff = kScaleOff + kScaleBytes;
-    static constexpr int kOutOff = kRedOff + kRedBytes;
+    static constexpr int kScratchOff = kLutBytes;
+    static constexpr int kOutOff = kScratchOff + kScratchBytes;
     static constexpr int kTotal = kOutOff + kOutBytes;
 };
 
-template <int MT, int WR>
-__global__ void __launch_bounds__(kThreads, 1) nf4_gemv_kernel(const GemvParams p) {
-    using S = Smem<MT, WR>;
-    constexpr int WK = S::kWK;
-    constexpr int NB = 8 * MT;  // padded batch rows
-    constexpr int kChunkSteps = S::kChunkSteps;
+template <int MT>
+__global__ void __launch_bounds__(kThreads, 2) nf4_gemv_kernel(const GemvParams p) {
+    using S = Smem<MT>;
+    constexpr int NB = 8 * MT;                      // padded batch rows
+    constexpr int CH = S::kChunkSteps;              // steps per chunk
+    constexpr int SPW = CH / kWK;                   // steps per warp per chunk
     extern __shared__ __align__(1024) uint8_t smem[];
-    const uint8_t* s_lut = smem;
-    __half* s_x = reinterpret_cast<__half*>(smem + S::kXOff);
-    float* s_scale = reinterpret_cast<float*>(smem + S::kScaleOff);
-    float* s_red = reinterpret_cast<float*>(smem + S::kRedOff);
+    float* s_scale = reinterpret_cast<float*>(smem + S::kScratchOff);  // [64][CH]
+    float* s_red = reinterpret_cast<float*>(smem + S::kScratchOff);    // aliases s_scale after compute
     float* s_out = reinterpret_cast<float*>(smem + S::kOutOff);
 
     cg::cluster_group cluster = cg::this_cluster();
@@ -106,229 +109,223 @@ __global__ void __launch_bounds__(kThreads, 1) nf4_gemv_kernel(const GemvParams 
     const uint32_t tid = threadIdx.x;
     const uint32_t lane = tid & 31u, warp = tid >> 5;
     const uint32_t g = lane >> 2, t = lane & 3u;
-    const uint32_t wr = warp % WR, wk = warp / WR;
+    const uint32_t wr = warp % kWR, wk = warp / kWR;
     const uint32_t lane4 = lane * 4u;
 
     const WeightView& w = p.w;
     const uint64_t in = w.in_features, out = w.out_features;
     const uint64_t row_bytes = in >> 1;
-
-    // Contraction slice of this cluster rank.
     const uint32_t step_begin = min(krank * p.steps_per_cta, p.steps_total);
     const uint32_t step_end = min(step_begin + p.steps_per_cta, p.steps_total);
+    const uint64_t row0 = static_cast<uint64_t>(blockIdx.x / ksplit) * kRowsTile;
 
-    // ---- prologue: byte table into shared memory (used 128 B of each row) ----
-    for (uint32_t i = tid; i < 256 * 8; i += kThreads) {
-        const uint32_t row = i >> 3, part = i & 7u;
-        const uint4 v = __ldg(reinterpret_cast<const uint4*>(p.lut) + row * 16 + part);
-        *reinterpret_cast<uint4*>(smem + row * 256 + part * 16) = v;
+    // The four weight rows of this thread (two MMA row groups), clamped for loads.
+    const uint8_t* code_ptr[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const uint64_t r = min(row0 + wr * 32 + g + 8 * j, out - 1);
+        code_ptr[j] = w.codes + r * row_bytes + t * 8;
     }
 
-    // Row tiles are handed out round-robin over the clusters of the grid.
-    const uint32_t cluster_id = blockIdx.x / ksplit;
-    const uint32_t n_clusters = gridDim.x / ksplit;
-
-    for (uint32_t tile = cluster_id; tile < p.row_tiles; tile += n_clusters) {
-        const uint64_t row0 = static_cast<uint64_t>(tile) * S::kRowsTile;
-        // Rows of this warp's two 8-row halves, clamped for loads.
-        const uint64_t rA = min(row0 + wr * 16 + g, out - 1);
-        const uint64_t rB = min(row0 + wr * 16 + g + 8, out - 1);
-        const uint8_t* codeA = w.codes + rA * row_bytes + t * 8;
-        const uint8_t* codeB = w.codes + rB * row_bytes + t * 8;
-
-        float acc[MT][4];
+    float acc[2][MT][4];
+#pragma unroll
+    for (int rg = 0; rg < 2; ++rg)
 #pragma unroll
         for (int m = 0; m < MT; ++m)
 #pragma unroll
-            for (int e = 0; e < 4; ++e) acc[m][e] = 0.0f;
+            for (int e = 0; e < 4; ++e) acc[rg][m][e] = 0.0f;
 
-        for (uint32_t chunk0 = step_begin; chunk0 < step_end; chunk0 += kChunkSteps) {
-            const uint32_t chunk_steps = min(static_cast<uint32_t>(kChunkSteps), step_end - chunk0);
-            // Steps of this warp inside the chunk: wk, wk + WK, ...
-            const uint32_t my_steps = chunk_steps > wk ? (chunk_steps - wk + WK - 1) / WK : 0;
+    // Byte table: 8 x 16 B per thread, asynchronously.
+    for (uint32_t i = tid; i < 256 * 8; i += kThreads) {
+        cp_async_16(smem + (i >> 3) * 256 + (i & 7u) * 16, p.lut + i * 4);
+    }
+    asm volatile("cp.async.commit_group;\n" ::);
 
-            // Issue the first unit's code loads before the staging work.
-            uint2 curA[kUnit], curB[kUnit];
+    for (uint32_t chunk0 = step_begin; chunk0 < step_end; chunk0 += CH) {
+        const uint32_t chunk_steps = min(static_cast<uint32_t>(CH), step_end - chunk0);
+
+        // 1. All packed-code loads of the chunk: SPW steps x 4 rows x 8 B per thread.
+        uint2 code[SPW][4];
 #pragma unroll
-            for (int u = 0; u < kUnit; ++u) {
-                const uint32_t s = wk + u * WK;
-                if (static_cast<uint32_t>(u) < my_steps) {
-                    const uint64_t off = static_cast<uint64_t>(chunk0 + s) * 32;
-                    curA[u] = ldg_stream_u2(codeA + off);
-                    curB[u] = ldg_stream_u2(codeB + off);
-                } else {
-                    curA[u] = make_uint2(0x77777777u, 0x77777777u);
-                    curB[u] = curA[u];
-                }
-            }
+        for (int u = 0; u < SPW; ++u) {
+            const uint32_t s = wk + u * kWK;
+            const uint64_t off = static_cast<uint64_t>(chunk0 + min(s, chunk_steps - 1)) * 32;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) code[u][j] = ldg_stream_u2(code_ptr[j] + off);
+        }
 
-            __syncthreads();  // previous chunk / tile finished with s_x and s_scale
-            // Activations of the chunk -> fp16 [step][batch row][64 (+8 pad)].
-            {
-                const uint32_t quads = chunk_steps * 16;  // float4 per batch row
-                for (uint32_t i = tid; i < quads * NB; i += kThreads) {
-                    const uint32_t n = i / quads, q4 = i % quads;
-                    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-                    if (n < p.rows) {
-                        v = __ldg(reinterpret_cast<const float4*>(
-                            p.x + static_cast<uint64_t>(n) * in +
-                            static_cast<uint64_t>(chunk0) * kStepK + q4 * 4));
+        __syncthreads();  // previous chunk done with activations / scales
+
+        // 2. Activations of the chunk -> fp16 in the upper halves of the table rows.
+        {
+            constexpr int kQuads = CH * 16 * NB;            // float4 of a full chunk
+            constexpr int kPerThread = kQuads / kThreads;   // 16 for every MT
+            constexpr int kBatch = 8;                       // loads in flight per pass
+#pragma unroll
+            for (int k0 = 0; k0 < kPerThread; k0 += kBatch) {
+                float4 v[kBatch];
+#pragma unroll
+                for (int k = 0; k < kBatch; ++k) {
+                    const uint32_t i = tid + (k0 + k) * kThreads;
+                    const uint32_t n = i / (CH * 16), q4 = i % (CH * 16);
+                    v[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (n < p.rows && (q4 >> 4) < chunk_steps) {
+                        v[k] = __ldg(reinterpret_cast<const float4*>(
+                            p.x + static_cast<uint64_t>(n) * in + static_cast<uint64_t>(chunk0) * kStepK + q4 * 4));
                     }
-                    const uint32_t s = q4 >> 4, c = (q4 & 15u) * 4;
-                    __half2 lo = __floats2half2_rn(v.x, v.y), hi = __floats2half2_rn(v.z, v.w);
+                }
+#pragma unroll
+                for (int k = 0; k < kBatch; ++k) {
+                    const uint32_t i = tid + (k0 + k) * kThreads;
+                    const uint32_t n = i / (CH * 16), q4 = i % (CH * 16);
+                    const uint32_t s = q4 >> 4, c4 = q4 & 15u;       // c4: group of 4 halves (8 B)
+                    const uint32_t chunk16 = (c4 >> 1) ^ (n & 1u);   // swizzled 16-byte chunk
+                    __half2 lo = __floats2half2_rn(v[k].x, v[k].y), hi = __floats2half2_rn(v[k].z, v[k].w);
                     uint2 packed;
                     packed.x = *reinterpret_cast<uint32_t*>(&lo);
                     packed.y = *reinterpret_cast<uint32_t*>(&hi);
-                    *reinterpret_cast<uint2*>(s_x + (s * NB + n) * kXRowHalves + c) = packed;
-                }
-            }
-            // Decoded block scales of the tile's rows for the chunk.
-            for (uint32_t i = tid; i < S::kRowsTile * chunk_steps; i += kThreads) {
-                const uint32_t r = i / chunk_steps, s = i % chunk_steps;
-                const uint64_t row = min(row0 + r, out - 1);
-                const uint64_t flat = row * in + static_cast<uint64_t>(chunk0 + s) * kStepK;
-                s_scale[r * kChunkSteps + s] = decode_block_scale(w, flat >> w.block_shift);
-            }
-            __syncthreads();
-
-            for (uint32_t u0 = 0; u0 < my_steps; u0 += kUnit) {
-                // Prefetch the next unit while this one is consumed.
-                uint2 nxtA[kUnit], nxtB[kUnit];
-#pragma unroll
-                for (int u = 0; u < kUnit; ++u) {
-                    const uint32_t idx = u0 + kUnit + u;
-                    if (idx < my_steps) {
-                        const uint64_t off = static_cast<uint64_t>(chunk0 + wk + idx * WK) * 32;
-                        nxtA[u] = ldg_stream_u2(codeA + off);
-                        nxtB[u] = ldg_stream_u2(codeB + off);
-                    } else {
-                        nxtA[u] = make_uint2(0x77777777u, 0x77777777u);
-                        nxtB[u] = nxtA[u];
-                    }
-                }
-#pragma unroll
-                for (int u = 0; u < kUnit; ++u) {
-                    const uint32_t idx = u0 + u;
-                    if (idx < my_steps) {
-                        const uint32_t s = wk + idx * WK;
-                        const uint32_t wa[2] = {curA[u].x, curA[u].y};
-                        const uint32_t wb[2] = {curB[u].x, curB[u].y};
-                        float part[MT][4];
-#pragma unroll
-                        for (int m = 0; m < MT; ++m)
-#pragma unroll
-                            for (int e = 0; e < 4; ++e) part[m][e] = 0.0f;
-                        uint4 xf[MT][2];
-#pragma unroll
-                        for (int m = 0; m < MT; ++m) {
-                            const __half* xp = s_x + (s * NB + m * 8 + g) * kXRowHalves + t * 16;
-                            xf[m][0] = *reinterpret_cast<const uint4*>(xp);
-                            xf[m][1] = *reinterpret_cast<const uint4*>(xp + 8);
-                        }
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            const uint32_t word_a = wa[i >> 1], word_b = wb[i >> 1];
-                            const uint32_t sel0 = (i & 1) ? 0x5524u : 0x5504u;
-                            const uint32_t sel1 = (i & 1) ? 0x5534u : 0x5514u;
-                            const uint32_t a0 = *reinterpret_cast<const uint32_t*>(
-                                s_lut + __byte_perm(word_a, lane4, sel0));
-                            const uint32_t a2 = *reinterpret_cast<const uint32_t*>(
-                                s_lut + __byte_perm(word_a, lane4, sel1));
-                            const uint32_t a1 = *reinterpret_cast<const uint32_t*>(
-                                s_lut + __byte_perm(word_b, lane4, sel0));
-                            const uint32_t a3 = *reinterpret_cast<const uint32_t*>(
-                                s_lut + __byte_perm(word_b, lane4, sel1));
-#pragma unroll
-                            for (int m = 0; m < MT; ++m) {
-                                const uint4& xv = xf[m][i >> 1];
-                                const uint32_t b0 = (i & 1) ? xv.z : xv.x;
-                                const uint32_t b1 = (i & 1) ? xv.w : xv.y;
-                                mma_f16_16816(part[m], a0, a1, a2, a3, b0, b1);
-                            }
-                        }
-                        const float sA = s_scale[(wr * 16 + g) * kChunkSteps + s];
-                        const float sB = s_scale[(wr * 16 + g + 8) * kChunkSteps + s];
-#pragma unroll
-                        for (int m = 0; m < MT; ++m) {
-                            acc[m][0] = fmaf(sA, part[m][0], acc[m][0]);
-                            acc[m][1] = fmaf(sA, part[m][1], acc[m][1]);
-                            acc[m][2] = fmaf(sB, part[m][2], acc[m][2]);
-                            acc[m][3] = fmaf(sB, part[m][3], acc[m][3]);
-                        }
-                    }
-                }
-#pragma unroll
-                for (int u = 0; u < kUnit; ++u) {
-                    curA[u] = nxtA[u];
-                    curB[u] = nxtB[u];
+                    *reinterpret_cast<uint2*>(smem + (s * NB + n) * 256 + 128 + chunk16 * 16 + (c4 & 1u) * 8) = packed;
                 }
             }
         }
+        // 3. Decoded block scales of the tile's 64 rows for the chunk.
+        {
+            constexpr int kPerThread = kRowsTile * CH / kThreads;
+            float sc[kPerThread];
+#pragma unroll
+            for (int k = 0; k < kPerThread; ++k) {
+                const uint32_t i = tid + k * kThreads;
+                const uint32_t r = i / CH, s = i % CH;
+                const uint64_t row = min(row0 + r, out - 1);
+                const uint64_t flat = row * in + static_cast<uint64_t>(chunk0 + min(s, chunk_steps - 1)) * kStepK;
+                sc[k] = decode_block_scale(w, flat >> w.block_shift);
+            }
+#pragma unroll
+            for (int k = 0; k < kPerThread; ++k) {
+                const uint32_t i = tid + k * kThreads;
+                s_scale[(i / CH) * (CH + 1) + i % CH] = sc[k];
+            }
+        }
+        asm volatile("cp.async.wait_group 0;\n" ::);
+        __syncthreads();
 
-        // ---- combine the WK warps of the CTA (fixed order) ----
+        // 4. Tensor-core accumulation of this warp's steps.
+#pragma unroll
+        for (int u = 0; u < SPW; ++u) {
+            const uint32_t s = wk + u * kWK;
+            if (s < chunk_steps) {
+                uint4 xf[MT][2];
+#pragma unroll
+                for (int m = 0; m < MT; ++m) {
+                    const uint32_t n = m * 8 + g;
+                    const uint8_t* xrow = smem + (s * NB + n) * 256 + 128;
+                    xf[m][0] = *reinterpret_cast<const uint4*>(xrow + (((2 * t) ^ (n & 1u)) * 16));
+                    xf[m][1] = *reinterpret_cast<const uint4*>(xrow + (((2 * t + 1) ^ (n & 1u)) * 16));
+                }
+#pragma unroll
+                for (int rg = 0; rg < 2; ++rg) {
+                    float part[MT][4];
+#pragma unroll
+                    for (int m = 0; m < MT; ++m)
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) part[m][e] = 0.0f;
+                    const uint32_t wa[2] = {code[u][2 * rg].x, code[u][2 * rg].y};
+                    const uint32_t wb[2] = {code[u][2 * rg + 1].x, code[u][2 * rg + 1].y};
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const uint32_t word_a = wa[i >> 1], word_b = wb[i >> 1];
+                        const uint32_t sel0 = (i & 1) ? 0x5524u : 0x5504u;
+                        const uint32_t sel1 = (i & 1) ? 0x5534u : 0x5514u;
+                        const uint32_t a0 = *reinterpret_cast<const uint32_t*>(smem + __byte_perm(word_a, lane4, sel0));
+                        const uint32_t a2 = *reinterpret_cast<const uint32_t*>(smem + __byte_perm(word_a, lane4, sel1));
+                        const uint32_t a1 = *reinterpret_cast<const uint32_t*>(smem + __byte_perm(word_b, lane4, sel0));
+                        const uint32_t a3 = *reinterpret_cast<const uint32_t*>(smem + __byte_perm(word_b, lane4, sel1));
+#pragma unroll
+                        for (int m = 0; m < MT; ++m) {
+                            const uint4& xv = xf[m][i >> 1];
+                            const uint32_t b0 = (i & 1) ? xv.z : xv.x;
+                            const uint32_t b1 = (i & 1) ? xv.w : xv.y;
+                            mma_f16_16816(part[m], a0, a1, a2, a3, b0, b1);
+                        }
+                    }
+                    const float sA = s_scale[(wr * 32 + rg * 16 + g) * (CH + 1) + s];
+                    const float sB = s_scale[(wr * 32 + rg * 16 + g + 8) * (CH + 1) + s];
+#pragma unroll
+                    for (int m = 0; m < MT; ++m) {
+                        acc[rg][m][0] = fmaf(sA, part[m][0], acc[rg][m][0]);
+                        acc[rg][m][1] = fmaf(sA, part[m][1], acc[rg][m][1]);
+                        acc[rg][m][2] = fmaf(sB, part[m][2], acc[rg][m][2]);
+                        acc[rg][m][3] = fmaf(sB, part[m][3], acc[rg][m][3]);
+                    }
+                }
+            }
+        }
+    }
+    asm volatile("cp.async.wait_group 0;\n" ::);
+    __syncthreads();  // scales no longer needed: the scratch becomes the reduction buffer
+
+    // ---- combine the kWK warps of the CTA (fixed order) ----
+#pragma unroll
+    for (int rg = 0; rg < 2; ++rg)
 #pragma unroll
         for (int m = 0; m < MT; ++m) {
-            float* dst = s_red + (wk * S::kRowsTile + wr * 16) * NB + m * 8;
-            dst[g * NB + 2 * t] = acc[m][0];
-            dst[g * NB + 2 * t + 1] = acc[m][1];
-            dst[(g + 8) * NB + 2 * t] = acc[m][2];
-            dst[(g + 8) * NB + 2 * t + 1] = acc[m][3];
+            float* dst = s_red + (wk * kRowsTile + wr * 32 + rg * 16) * NB + m * 8;
+            dst[g * NB + 2 * t] = acc[rg][m][0];
+            dst[g * NB + 2 * t + 1] = acc[rg][m][1];
+            dst[(g + 8) * NB + 2 * t] = acc[rg][m][2];
+            dst[(g + 8) * NB + 2 * t + 1] = acc[rg][m][3];
         }
-        __syncthreads();
-        for (uint32_t i = tid; i < S::kRowsTile * NB; i += kThreads) {
-            float v = 0.0f;
+    __syncthreads();
+    for (uint32_t i = tid; i < kRowsTile * NB; i += kThreads) {
+        float v = 0.0f;
 #pragma unroll
-            for (int k = 0; k < WK; ++k) v += s_red[k * S::kRowsTile * NB + i];
-            s_out[i] = v;
-        }
-
-        // ---- combine the ranks of the cluster through distributed shared memory ----
-        if (ksplit > 1) {
-            cluster.sync();
-        } else {
-            __syncthreads();
-        }
-        // Element i = n * rows_tile + r so that consecutive threads write
-        // consecutive output columns of one batch row.
-        for (uint32_t i = tid + krank * kThreads; i < S::kRowsTile * NB; i += kThreads * ksplit) {
-            const uint32_t n = i / S::kRowsTile, r = i % S::kRowsTile;
-            float v = 0.0f;
-            for (uint32_t k = 0; k < ksplit; ++k) {
-                const float* remote = ksplit > 1 ? cluster.map_shared_rank(s_out, k) : s_out;
-                v += remote[r * NB + n];
-            }
-            if (n < p.rows && row0 + r < out) p.y[static_cast<uint64_t>(n) * out + row0 + r] = v;
-        }
-        if (ksplit > 1) cluster.sync();  // peers may still be reading this CTA's s_out
+        for (int k = 0; k < kWK; ++k) v += s_red[k * kRowsTile * NB + i];
+        s_out[i] = v;
     }
+
+    // ---- combine the ranks of the cluster through distributed shared memory ----
+    if (ksplit > 1) {
+        cluster.sync();
+    } else {
+        __syncthreads();
+    }
+    // Element i = n * 64 + r: consecutive threads write consecutive outputs of a batch row.
+    for (uint32_t i = tid + krank * kThreads; i < kRowsTile * NB; i += kThreads * ksplit) {
+        const uint32_t n = i / kRowsTile, r = i % kRowsTile;
+        float v = 0.0f;
+        for (uint32_t k = 0; k < ksplit; ++k) {
+            const float* remote = ksplit > 1 ? cluster.map_shared_rank(s_out, k) : s_out;
+            v += remote[r * NB + n];
+        }
+        if (n < p.rows && row0 + r < out) p.y[static_cast<uint64_t>(n) * out + row0 + r] = v;
+    }
+    if (ksplit > 1) cluster.sync();  // peers may still be reading this CTA's s_out
 }
 
 __global__ void gemv_lut_init_kernel(uint32_t* lut) {
-    // 256 rows x 64 words; words 0..31 of row v hold the fp16 pair of byte v.
+    // Compact [256][32] words: entry v, replicated for the 32 lanes, holds the
+    // fp16 pair (low nibble's value in the low half) of packed byte v.
     const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= 256 * 64) return;
-    const uint32_t v = i >> 6, word = i & 63u;
-    uint32_t value = 0;
-    if (word < 32) {
-        const __half lo = __float2half_rn(kNf4Codebook[v & 15u]);
-        const __half hi = __float2half_rn(kNf4Codebook[v >> 4]);
-        value = static_cast<uint32_t>(__half_as_ushort(lo)) |
-                (static_cast<uint32_t>(__half_as_ushort(hi)) << 16);
-    }
-    lut[i] = value;
+    if (i >= 256 * 32) return;
+    const uint32_t v = i >> 5;
+    const __half lo = __float2half_rn(kNf4Codebook[v & 15u]);
+    const __half hi = __float2half_rn(kNf4Codebook[v >> 4]);
+    lut[i] = static_cast<uint32_t>(__half_as_ushort(lo)) | (static_cast<uint32_t>(__half_as_ushort(hi)) << 16);
 }
 
-template <int MT, int WR>
-int32_t launch_config(const DeviceContext& ctx, GemvParams p, uint32_t ksplit, cudaStream_t stream) {
-    using S = Smem<MT, WR>;
-    auto kernel = nf4_gemv_kernel<MT, WR>;
-    B2_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal));
-    p.row_tiles = static_cast<uint32_t>((p.w.out_features + S::kRowsTile - 1) / S::kRowsTile);
-    uint32_t clusters = static_cast<uint32_t>(ctx.sm_count) / ksplit;
-    if (clusters > p.row_tiles) clusters = p.row_tiles;
-    if (clusters == 0) clusters = 1;
+template <int MT>
+int32_t launch_config(const DeviceContext& ctx, const GemvParams& p, uint32_t ksplit, cudaStream_t stream) {
+    (void)ctx;
+    using S = Smem<MT>;
+    auto kernel = nf4_gemv_kernel<MT>;
+    static bool configured = false;  // per template instance
+    if (!configured) {
+        B2_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal));
+        configured = true;
+    }
+    const uint32_t row_tiles = static_cast<uint32_t>((p.w.out_features + kRowsTile - 1) / kRowsTile);
     cudaLaunchConfig_t config = {};
-    config.gridDim = dim3(clusters * ksplit);
+    config.gridDim = dim3(row_tiles * ksplit);
     config.blockDim = dim3(kThreads);
     config.dynamicSmemBytes = S::kTotal;
     config.stream = stream;
@@ -343,22 +340,11 @@ int32_t launch_config(const DeviceContext& ctx, GemvParams p, uint32_t ksplit, c
     return B2_STATUS_OK;
 }
 
-template <int MT>
-int32_t launch_mt(const DeviceContext& ctx, const GemvParams& p, uint32_t wr, uint32_t ksplit,
-                  cudaStream_t stream) {
-    switch (wr) {
-    case 1: return launch_config<MT, 1>(ctx, p, ksplit, stream);
-    case 2: return launch_config<MT, 2>(ctx, p, ksplit, stream);
-    case 4: return launch_config<MT, 4>(ctx, p, ksplit, stream);
-    default: return launch_config<MT, 8>(ctx, p, ksplit, stream);
-    }
-}
-
 }  // namespace
 
 int32_t init_gemv_lut(DeviceContext* ctx) {
-    B2_CUDA_TRY(cudaMalloc(&ctx->gemv_lut, kLutBytes));
-    gemv_lut_init_kernel<<<64, 256>>>(ctx->gemv_lut);
+    B2_CUDA_TRY(cudaMalloc(&ctx->gemv_lut, 256 * 32 * 4));
+    gemv_lut_init_kernel<<<32, 256>>>(ctx->gemv_lut);
     B2_CUDA_TRY(cudaGetLastError());
     B2_CUDA_TRY(cudaDeviceSynchronize());
     return B2_STATUS_OK;
@@ -369,11 +355,10 @@ bool nf4_gemv_supported(const WeightView& w, const float* x, const float* y, uin
     return rows >= 1 && rows <= 32 && w.in_features % kStepK == 0 && w.block_size >= kStepK &&
            (reinterpret_cast<uintptr_t>(w.codes) & 7u) == 0 &&
            (reinterpret_cast<uintptr_t>(x) & 15u) == 0 && w.in_features / kStepK <= 0xFFFFFFFFull &&
-           w.out_features <= 0x7FFFFFFFull;
+           w.out_features <= 0x3FFFFFFFull;
 }
 
-// Tunable through the environment for experiments: B2_GEMV_WR (rows per CTA /
-// 16) and B2_GEMV_KSPLIT (cluster size along the contraction).
+// B2_GEMV_KSPLIT (1..8) overrides the cluster size along the contraction, for experiments.
 int32_t launch_nf4_gemv(const DeviceContext& ctx, const WeightView& w, const float* x, float* y,
                         uint64_t rows, cudaStream_t stream) {
     GemvParams p;
@@ -383,35 +368,19 @@ int32_t launch_nf4_gemv(const DeviceContext& ctx, const WeightView& w, const flo
     p.rows = static_cast<uint32_t>(rows);
     p.steps_total = static_cast<uint32_t>(w.in_features / kStepK);
     p.lut = ctx.gemv_lut;
-    p.row_tiles = 0;
-
-    // One chunk (32 steps = 2048 inputs) per cluster rank where the cluster
-    // limit of 8 allows it; longer contractions take several chunks per rank.
-    const uint32_t chunk = rows > 16 ? chunk_steps_for<4>() : chunk_steps_for<1>();
+    const uint32_t chunk = rows <= 8 ? chunk_steps_for<1>() : rows <= 16 ? chunk_steps_for<2>() : chunk_steps_for<4>();
+    // One chunk per cluster rank where the portable cluster limit of 8 allows.
     uint32_t ksplit = (p.steps_total + chunk - 1) / chunk;
     if (ksplit > 8) ksplit = 8;
-    if (ksplit < 1) ksplit = 1;
-    // Rows per CTA: as large as still leaves every SM at least one tile.
-    uint32_t wr = 8;
-    while (wr > 1 && (w.out_features + 16 * wr - 1) / (16 * wr) * ksplit <
-                         static_cast<uint64_t>(ctx.sm_count)) {
-        wr >>= 1;
-    }
-    static const char* env_wr = getenv("B2_GEMV_WR");
     static const char* env_ks = getenv("B2_GEMV_KSPLIT");
-    if (env_wr != nullptr) {
-        const int v = atoi(env_wr);
-        if (v == 1 || v == 2 || v == 4 || v == 8) wr = static_cast<uint32_t>(v);
-    }
     if (env_ks != nullptr) {
         const int v = atoi(env_ks);
         if (v >= 1 && v <= 8) ksplit = static_cast<uint32_t>(v);
     }
     p.steps_per_cta = (p.steps_total + ksplit - 1) / ksplit;
-
-    if (rows <= 8) return launch_mt<1>(ctx, p, wr, ksplit, stream);
-    if (rows <= 16) return launch_mt<2>(ctx, p, wr, ksplit, stream);
-    return launch_mt<4>(ctx, p, wr, ksplit, stream);
+    if (rows <= 8) return launch_config<1>(ctx, p, ksplit, stream);
+    if (rows <= 16) return launch_config<2>(ctx, p, ksplit, stream);
+    return launch_config<4>(ctx, p, ksplit, stream);
 }
 
 }  // namespace b2
