@@ -179,6 +179,32 @@ B2_API size_t b2_paged_decode_workspace_bytes(uint32_t n_seq, uint32_t q_heads,
                                        uint32_t head_width, uint32_t block_size,
                                        uint32_t max_seq_len);
 
+/*
+ * The same attention as b2_paged_decode_attention for callers that must not
+ * allocate device memory: an engine whose memory is entirely owned by its own
+ * pool, or a call site where cudaMalloc / cudaFree are unwelcome because they
+ * synchronise the whole device. It has no counterpart in the reference. The
+ * split-K scratch is a fixed B2_NOALLOC_SCRATCH_BYTES array inside the library
+ * (each GPU that loads the library holds it until the process exits), and the
+ * call itself performs no cudaMalloc, cudaFree or other allocating routine.
+ *  - Limit: the call is rejected with B2_STATUS_INVALID_ARGUMENT when
+ *    b2_paged_decode_workspace_bytes(...) for its shape exceeds
+ *    B2_NOALLOC_SCRATCH_BYTES (head_width 128 / block_size 16: n_seq * q_heads *
+ *    ceil(max_seq_len / 256) * 520 bytes, 0 when max_seq_len <= 256).
+ *  - The first call on each device looks up the array's device address; make
+ *    that first call outside any stream capture.
+ *  - All calls on a device share the one array. Nothing in it has to start at
+ *    zero (every partial result is written before it is read), but two calls
+ *    whose kernels overlap on the GPU - different streams, or threads - race on
+ *    it: order them on one stream.
+ */
+#define B2_NOALLOC_SCRATCH_BYTES (8u * 1024u * 1024u)
+B2_API int32_t b2_paged_decode_attention_noalloc(
+    const float* q, const float* k_pages, const float* v_pages, const uint32_t* block_tables,
+    const uint32_t* seq_lens, float* ctx, uint32_t n_seq, uint32_t q_heads, uint32_t kv_heads,
+    uint32_t head_width, uint32_t block_size, uint64_t physical_blocks, uint32_t max_blocks,
+    uint32_t max_seq_len, uint32_t* status, void* stream);
+
 /* ---- host-buffer seam --------------------------------------------------- */
 /*
  * The reference adapter contract is synchronous over host-visible storage

@@ -21,6 +21,7 @@
 #include "b2_kernels.h"
 
 #include <cmath>
+#include <mutex>
 
 namespace b2 {
 namespace {
@@ -384,3 +385,104 @@ int32_t launch_paged_decode(const DeviceContext&, const PagedDecodeArgs& a, void
 }
 
 }  // namespace b2
+
+// ---- entry point that allocates nothing ---------------------------------------------
+//
+// Some callers may not allocate device memory at the point where they run
+// attention: an engine that has handed all of its memory to a pool it manages
+// itself, or code running inside a region where cudaMalloc / cudaFree are not
+// allowed because they synchronise the device. For them the split-K scratch of
+// the decode kernel lives in the fixed-size array below, which every GPU that
+// loads this library holds from load until exit.
+namespace b2 {
+namespace {
+
+constexpr size_t kStaticScratchBytes = B2_NOALLOC_SCRATCH_BYTES;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+constexpr int kMaxScratchDevices = 64;
+std::mutex g_scratch_mutex;
+void* g_scratch_address[kMaxScratchDevices];  // device address of g_static_scratch, per device
+bool g_scratch_ready[kMaxScratchDevices];
+
+// In host code `g_static_scratch` names a host-side shadow, not device memory;
+// the device address has to be asked for once per device, with that device
+// current. Nothing here allocates.
+int32_t static_scratch_pointer(void** out) {
+    int device = -1;
+    cudaError_t err = cudaGetDevice(&device);
+    if (err != cudaSuccess || device < 0 || device >= kMaxScratchDevices) {
+        cudaGetLastError();
+        return fail(B2_STATUS_BACKEND_UNAVAILABLE, "CUDA backend unavailable: %s",
+                    err != cudaSuccess ? cudaGetErrorString(err) : "device index out of range");
+    }
+    std::lock_guard<std::mutex> lock(g_scratch_mutex);
+    if (!g_scratch_ready[device]) {
+        int major = 0;
+        err = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device);
+        if (err != cudaSuccess || major != 10) {
+            cudaGetLastError();
+            return fail(B2_STATUS_BACKEND_UNAVAILABLE,
+                        "CUDA backend unavailable: this library is built for sm_100a only");
+        }
+        void* address = nullptr;
+        err = cudaGetSymbolAddress(&address, g_static_scratch);
+        if (err != cudaSuccess || address == nullptr) {
+            return fail_cuda(err != cudaSuccess ? err : cudaErrorInvalidSymbol,
+                             "cudaGetSymbolAddress(static attention scratch)");
+        }
+        g_scratch_address[device] = address;
+        g_scratch_ready[device] = true;
+    }
+    *out = g_scratch_address[device];
+    return B2_STATUS_OK;
+}
+
+}  // namespace
+}  // namespace b2
+
+extern "C" int32_t b2_paged_decode_attention_noalloc(
+    const float* q, const float* k_pages, const float* v_pages, const uint32_t* block_tables,
+    const uint32_t* seq_lens, float* ctx, uint32_t n_seq, uint32_t q_heads, uint32_t kv_heads,
+    uint32_t head_width, uint32_t block_size, uint64_t physical_blocks, uint32_t max_blocks,
+    uint32_t max_seq_len, uint32_t* status, void* stream) {
+    using namespace b2;
+    clear_error();
+    if (n_seq == 0 || q_heads == 0 || kv_heads == 0 || head_width == 0 || block_size == 0 ||
+        physical_blocks == 0 || max_seq_len == 0 || max_blocks == 0) {
+        return fail(B2_STATUS_INVALID_ARGUMENT, "paged decode attention dimensions must be positive");
+    }
+    if (physical_blocks - 1 > 0xFFFFFFFFull) {
+        return fail(B2_STATUS_OVERFLOW, "paged decode attention physical block IDs exceed uint32_t");
+    }
+    if (q_heads % kv_heads != 0) {
+        return fail(B2_STATUS_INVALID_ARGUMENT,
+                    "paged decode attention query heads must be a multiple of KV heads");
+    }
+    if ((static_cast<uint64_t>(max_seq_len) - 1) / block_size + 1 > max_blocks) {
+        return fail(B2_STATUS_INVALID_ARGUMENT,
+                    "paged decode attention block table size does not match the sequence");
+    }
+    if (q == nullptr || k_pages == nullptr || v_pages == nullptr || block_tables == nullptr ||
+        seq_lens == nullptr || ctx == nullptr) {
+        return fail(B2_STATUS_INVALID_ARGUMENT, "paged decode attention pointers must not be null");
+    }
+    if (ctx == q || ctx == k_pages || ctx == v_pages) {
+        return fail(B2_STATUS_INVALID_ARGUMENT, "paged decode attention output must not alias an input");
+    }
+    const size_t need = paged_decode_workspace_bytes(n_seq, q_heads, head_width, block_size, max_seq_len);
+    if (need > kStaticScratchBytes) {
+        return fail(B2_STATUS_INVALID_ARGUMENT,
+                    "paged decode attention needs %zu bytes of scratch but the allocation-free entry point "
+                    "has a fixed %zu: lower n_seq * q_heads * ceil(max_seq_len / 256), or call "
+                    "b2_paged_decode_attention with a workspace",
+                    need, kStaticScratchBytes);
+    }
+    void* scratch = nullptr;
+    B2_TRY(static_scratch_pointer(&scratch));
+    PagedDecodeArgs args{q, k_pages, v_pages, block_tables, seq_lens, ctx,
+                         n_seq, q_heads, kv_heads, head_width, block_size, max_blocks, max_seq_len,
+                         physical_blocks, status};
+    DeviceContext unused;  // the launcher does not read it
+    return launch_paged_decode(unused, args, scratch, kStaticScratchBytes, static_cast<cudaStream_t>(stream));
+}
