@@ -205,6 +205,51 @@ B2_API int32_t b2_paged_decode_attention_noalloc(
     uint32_t head_width, uint32_t block_size, uint64_t physical_blocks, uint32_t max_blocks,
     uint32_t max_seq_len, uint32_t* status, void* stream);
 
+/* ---- decode-step glue ---------------------------------------------------- */
+/*
+ * The small operators either side of the linears and the attention in one
+ * decode step of a Llama-shaped decoder, so the whole step can stay on the
+ * device. All pointers are device pointers; calls only enqueue.
+ */
+
+/* y[r,:] = x[r,:] * (1 / sqrt(mean(x[r,:]^2) + eps)) * scale (rms_norm,
+ * src/nn/rms_norm.cpp:39-73). With delta != NULL the residual stream is
+ * updated first: x_out = x + delta, and the norm is taken of x_out (x_out may
+ * equal x). With delta == NULL x_out is ignored. */
+B2_API int32_t b2_rmsnorm(const float* x, const float* delta, float* x_out, const float* scale,
+                          float* y, uint64_t rows, uint64_t width, float eps, void* stream);
+
+/* Split-half rotary embedding of the new token of every sequence, in place on
+ * q [n_seq, q_heads, d] and while copying k [n_seq, kv_heads, d] into its page
+ * slot; v [n_seq, kv_heads, d] is copied unchanged. positions[s] is the token's
+ * position (= its slot in the sequence's pages). RoPE: rotate_forward,
+ * src/model/rotary_embedding.cpp:64-117 (pairs (c, c + d/2), angle =
+ * position * theta^(-2c/d) in double). Page write: copy_token_to_page,
+ * src/stages/serving/cache/page_table_cache.cpp:44-77. A block id outside the
+ * pool is not written and sets B2_ATTN_STATUS_BAD_BLOCK in *status. */
+B2_API int32_t b2_rope_append_kv(float* q, const float* k, const float* v, const uint32_t* positions,
+                                 const uint32_t* block_tables, float* k_pages, float* v_pages,
+                                 uint32_t n_seq, uint32_t q_heads, uint32_t kv_heads,
+                                 uint32_t head_width, uint32_t block_size, uint64_t physical_blocks,
+                                 uint32_t max_blocks, float theta, uint32_t* status, void* stream);
+
+/* out = silu(gate) * up, silu as silu_forward (src/nn/activations.cpp:38-58);
+ * the product is SwiGLU's hidden state (src/model/swiglu.cpp:27-29). */
+B2_API int32_t b2_silu_mul(const float* gate, const float* up, float* out, uint64_t n, void* stream);
+
+/* out = a + b (residual add). */
+B2_API int32_t b2_add(const float* a, const float* b, float* out, uint64_t n, void* stream);
+
+/* out[r,:] = table[ids[r],:] (embedding lookup; gather_rows of the reference's
+ * IndexingCapability, src/core/backend/nn/capability.hpp). An id >= vocab reads
+ * row 0 and sets bit 0 of *status. */
+B2_API int32_t b2_gather_rows(const float* table, const uint32_t* ids, float* out, uint32_t rows,
+                              uint32_t width, uint32_t vocab, uint32_t* status, void* stream);
+
+/* out[r] = index of the first maximum of logits[r,:] (greedy sampling,
+ * src/stages/serving/generation.cpp:100-120). */
+B2_API int32_t b2_argmax(const float* logits, uint32_t* out, uint32_t rows, uint32_t width, void* stream);
+
 /* ---- host-buffer seam --------------------------------------------------- */
 /*
  * The reference adapter contract is synchronous over host-visible storage

@@ -65,6 +65,13 @@ SIGNATURES = {
     "b2_paged_decode_workspace_bytes": (_sz, [_u32, _u32, _u32, _u32, _u32]),
     "b2_paged_decode_attention_noalloc": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u32,
                                                  _u64, _u32, _u32, _vp, _vp]),
+    "b2_rmsnorm": (_i32, [_vp, _vp, _vp, _vp, _vp, _u64, _u64, C.c_float, _vp]),
+    "b2_rope_append_kv": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u32, _u64, _u32,
+                                 C.c_float, _vp, _vp]),
+    "b2_silu_mul": (_i32, [_vp, _vp, _vp, _u64, _vp]),
+    "b2_add": (_i32, [_vp, _vp, _vp, _u64, _vp]),
+    "b2_gather_rows": (_i32, [_vp, _vp, _vp, _u32, _u32, _u32, _vp, _vp]),
+    "b2_argmax": (_i32, [_vp, _vp, _u32, _u32, _vp]),
     "b2_host_nf4_linear_forward": (_i32, [_W, _vp, _vp, _u64, _vp]),
     "b2_host_nf4_linear_input_backward": (_i32, [_W, _vp, _vp, _u64, _vp]),
     "b2_host_paged_decode_attention": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32,

@@ -396,6 +396,97 @@ int32_t b2_paged_decode_attention(const float* q, const float* k_pages, const fl
     return launch_paged_decode(*ctx, args, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
 }
 
+// ---- decode-step glue ------------------------------------------------------------
+
+int32_t b2_rmsnorm(const float* x, const float* delta, float* x_out, const float* scale, float* y,
+                   uint64_t rows, uint64_t width, float eps, void* stream) {
+    clear_error();
+    int32_t status = B2_STATUS_OK;
+    if (device_context(&status) == nullptr) return status;
+    if (x == nullptr || scale == nullptr || y == nullptr || (delta != nullptr && x_out == nullptr)) {
+        return fail(B2_STATUS_INVALID_ARGUMENT, "RMS normalization pointers must not be null");
+    }
+    if (rows == 0 || width == 0 || rows > 0x7FFFFFFFull || width > 0xFFFFFFFFull) {
+        return fail(B2_STATUS_INVALID_ARGUMENT, "RMS normalization requires positive dimensions");
+    }
+    if (!std::isfinite(eps) || eps <= 0.0f) {
+        return fail(B2_STATUS_INVALID_ARGUMENT, "RMS normalization epsilon must be finite and positive");
+    }
+    return launch_rmsnorm(x, delta, x_out, scale, y, rows, static_cast<uint32_t>(width), eps,
+                          static_cast<cudaStream_t>(stream));
+}
+
+int32_t b2_rope_append_kv(float* q, const float* k, const float* v, const uint32_t* positions,
+                          const uint32_t* block_tables, float* k_pages, float* v_pages, uint32_t n_seq,
+                          uint32_t q_heads, uint32_t kv_heads, uint32_t head_width, uint32_t block_size,
+                          uint64_t physical_blocks, uint32_t max_blocks, float theta, uint32_t* status_word,
+                          void* stream) {
+    clear_error();
+    int32_t status = B2_STATUS_OK;
+    if (device_context(&status) == nullptr) return status;
+    if (q == nullptr || k == nullptr || v == nullptr || positions == nullptr || block_tables == nullptr ||
+        k_pages == nullptr || v_pages == nullptr) {
+        return fail(B2_STATUS_INVALID_ARGUMENT, "rotary/append pointers must not be null");
+    }
+    if (n_seq == 0 || q_heads == 0 || kv_heads == 0 || head_width == 0 || block_size == 0 ||
+        physical_blocks == 0 || max_blocks == 0) {
+        return fail(B2_STATUS_INVALID_ARGUMENT, "rotary/append dimensions must be positive");
+    }
+    if (head_width % 2 != 0) {
+        return fail(B2_STATUS_INVALID_ARGUMENT, "rotary embedding requires an even head width");
+    }
+    if (!std::isfinite(theta) || theta <= 0.0f) {
+        return fail(B2_STATUS_INVALID_ARGUMENT, "rotary theta must be finite and positive");
+    }
+    return launch_rope_append(q, k, v, positions, block_tables, k_pages, v_pages, n_seq, q_heads, kv_heads,
+                              head_width, block_size, physical_blocks, max_blocks, theta, status_word,
+                              static_cast<cudaStream_t>(stream));
+}
+
+int32_t b2_silu_mul(const float* gate, const float* up, float* out, uint64_t n, void* stream) {
+    clear_error();
+    int32_t status = B2_STATUS_OK;
+    DeviceContext* ctx = device_context(&status);
+    if (ctx == nullptr) return status;
+    if (gate == nullptr || up == nullptr || out == nullptr || n == 0) {
+        return fail(B2_STATUS_INVALID_ARGUMENT, "silu_mul needs non-null pointers and a positive size");
+    }
+    return launch_silu_mul(*ctx, gate, up, out, n, static_cast<cudaStream_t>(stream));
+}
+
+int32_t b2_add(const float* a, const float* b, float* out, uint64_t n, void* stream) {
+    clear_error();
+    int32_t status = B2_STATUS_OK;
+    DeviceContext* ctx = device_context(&status);
+    if (ctx == nullptr) return status;
+    if (a == nullptr || b == nullptr || out == nullptr || n == 0) {
+        return fail(B2_STATUS_INVALID_ARGUMENT, "add needs non-null pointers and a positive size");
+    }
+    return launch_add(*ctx, a, b, out, n, static_cast<cudaStream_t>(stream));
+}
+
+int32_t b2_gather_rows(const float* table, const uint32_t* ids, float* out, uint32_t rows, uint32_t width,
+                       uint32_t vocab, uint32_t* status_word, void* stream) {
+    clear_error();
+    int32_t status = B2_STATUS_OK;
+    if (device_context(&status) == nullptr) return status;
+    if (table == nullptr || ids == nullptr || out == nullptr || rows == 0 || width == 0 || vocab == 0) {
+        return fail(B2_STATUS_INVALID_ARGUMENT, "gather_rows needs non-null pointers and positive sizes");
+    }
+    return launch_gather_rows(table, ids, out, rows, width, vocab, status_word,
+                              static_cast<cudaStream_t>(stream));
+}
+
+int32_t b2_argmax(const float* logits, uint32_t* out, uint32_t rows, uint32_t width, void* stream) {
+    clear_error();
+    int32_t status = B2_STATUS_OK;
+    if (device_context(&status) == nullptr) return status;
+    if (logits == nullptr || out == nullptr || rows == 0 || width == 0) {
+        return fail(B2_STATUS_INVALID_ARGUMENT, "argmax needs non-null pointers and positive sizes");
+    }
+    return launch_argmax(logits, out, rows, width, static_cast<cudaStream_t>(stream));
+}
+
 // ---- host-buffer seam ---------------------------------------------------------
 
 static int32_t host_linear(const b2_nf4_weight* weight, const float* src_host, float* dst_host,

@@ -47,4 +47,21 @@ size_t paged_decode_workspace_bytes(uint32_t n_seq, uint32_t q_heads, uint32_t h
 int32_t launch_paged_decode(const DeviceContext& ctx, const PagedDecodeArgs& args, void* workspace,
                             size_t workspace_bytes, cudaStream_t stream);
 
+
+// decode_glue.cu
+int32_t launch_rmsnorm(const float* x, const float* delta, float* x_out, const float* scale, float* y,
+                       uint64_t rows, uint32_t width, float eps, cudaStream_t stream);
+int32_t launch_rope_append(float* q, const float* k, const float* v, const uint32_t* positions,
+                           const uint32_t* block_tables, float* k_pages, float* v_pages, uint32_t n_seq,
+                           uint32_t q_heads, uint32_t kv_heads, uint32_t d, uint32_t block_size,
+                           uint64_t physical_blocks, uint32_t max_blocks, float theta, uint32_t* status,
+                           cudaStream_t stream);
+int32_t launch_silu_mul(const DeviceContext& ctx, const float* gate, const float* up, float* out, uint64_t n,
+                        cudaStream_t stream);
+int32_t launch_add(const DeviceContext& ctx, const float* a, const float* b, float* out, uint64_t n,
+                   cudaStream_t stream);
+int32_t launch_gather_rows(const float* table, const uint32_t* ids, float* out, uint32_t rows, uint32_t width,
+                           uint32_t vocab, uint32_t* status, cudaStream_t stream);
+int32_t launch_argmax(const float* logits, uint32_t* out, uint32_t rows, uint32_t width, cudaStream_t stream);
+
 }  // namespace b2

@@ -1,0 +1,242 @@
+// Small memory-bound kernels that sit between the packed-NF4 linears and the
+// paged attention in a decode step of a Llama-shaped decoder: RMSNorm (with an
+// optional fused residual add), split-half RoPE fused with the KV-page append,
+// SiLU(gate)*up, embedding gather and greedy argmax. Each restates a reference
+// primitive (cited at the kernel); none of them is on the roofline-critical
+// path, they exist so a whole decode step stays on the device and in one graph.
+#include "b2_common.cuh"
+#include "b2_kernels.h"
+
+#include <cmath>
+
+namespace b2 {
+namespace {
+
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
+    const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    const uint32_t warps = blockDim.x >> 5;
+    float total = 0.0f;
+    for (uint32_t w = 0; w < warps; ++w) total += scratch[w];
+    __syncthreads();
+    return total;
+}
+
+// y = x * (1 / sqrt(mean(x^2) + eps)) * scale, one CTA per row
+// (src/nn/rms_norm.cpp:39-73). With `delta`, first x_out = x + delta (the
+// residual stream update) and the norm is taken of x_out.
+__global__ void __launch_bounds__(256)
+rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ delta, float* __restrict__ x_out,
+               const float* __restrict__ scale, float* __restrict__ y, uint32_t width, float eps) {
+    __shared__ float scratch[8];
+    const uint64_t row = blockIdx.x;
+    const float* xr = x + row * width;
+    float ss = 0.0f;
+    for (uint32_t c = threadIdx.x; c < width; c += blockDim.x) {
+        float v = xr[c];
+        if (delta != nullptr) {
+            v += delta[row * width + c];
+            x_out[row * width + c] = v;
+        }
+        ss = fmaf(v, v, ss);
+    }
+    const float mean_square = block_sum(ss, scratch) / static_cast<float>(width);
+    const float inv = 1.0f / sqrtf(mean_square + eps);
+    const float* src = delta != nullptr ? x_out + row * width : xr;
+    for (uint32_t c = threadIdx.x; c < width; c += blockDim.x) {
+        y[row * width + c] = src[c] * inv * scale[c];
+    }
+}
+
+// Split-half rotary embedding of the new token's q and k (pairs (c, c + d/2),
+// angle = position * theta^(-2c/d) evaluated in double,
+// src/model/rotary_embedding.cpp:64-117), then k and v are written into their
+// page slot (copy_token_to_page, src/stages/serving/cache/page_table_cache.cpp:44-77).
+// One CTA per sequence; thread = (head, channel pair).
+__global__ void __launch_bounds__(256)
+rope_append_kernel(float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
+                   const uint32_t* __restrict__ positions, const uint32_t* __restrict__ block_tables,
+                   float* __restrict__ k_pages, float* __restrict__ v_pages, uint32_t q_heads,
+                   uint32_t kv_heads, uint32_t d, uint32_t block_size, uint64_t physical_blocks,
+                   uint32_t max_blocks, float theta, uint32_t* status) {
+    const uint32_t seq = blockIdx.x;
+    const uint32_t pos = positions[seq];
+    const uint32_t half = d / 2;
+    uint64_t phys = block_tables[static_cast<uint64_t>(seq) * max_blocks + pos / block_size];
+    bool bad = false;
+    if (phys >= physical_blocks) {
+        bad = true;
+        phys = 0;
+    }
+    if (bad && threadIdx.x == 0 && status != nullptr) atomicOr(status, B2_ATTN_STATUS_BAD_BLOCK);
+    const uint32_t slot = pos % block_size;
+    const uint32_t pairs = (q_heads + kv_heads) * half;
+    for (uint32_t i = threadIdx.x; i < pairs; i += blockDim.x) {
+        const uint32_t head = i / half, c = i % half;
+        const double angle = static_cast<double>(pos) *
+                             pow(static_cast<double>(theta), -2.0 * static_cast<double>(c) / static_cast<double>(d));
+        const float cs = static_cast<float>(cos(angle)), sn = static_cast<float>(sin(angle));
+        if (head < q_heads) {
+            float* p = q + (static_cast<uint64_t>(seq) * q_heads + head) * d;
+            const float a = p[c], b = p[c + half];
+            p[c] = __fsub_rn(__fmul_rn(a, cs), __fmul_rn(b, sn));
+            p[c + half] = __fadd_rn(__fmul_rn(b, cs), __fmul_rn(a, sn));
+        } else if (!bad) {
+            const uint32_t kh = head - q_heads;
+            const float* p = k + (static_cast<uint64_t>(seq) * kv_heads + kh) * d;
+            const float a = p[c], b = p[c + half];
+            float* dst = k_pages + ((phys * kv_heads + kh) * block_size + slot) * d;
+            dst[c] = __fsub_rn(__fmul_rn(a, cs), __fmul_rn(b, sn));
+            dst[c + half] = __fadd_rn(__fmul_rn(b, cs), __fmul_rn(a, sn));
+        }
+    }
+    if (!bad) {
+        for (uint32_t i = threadIdx.x; i < kv_heads * d; i += blockDim.x) {
+            const uint32_t kh = i / d, c = i % d;
+            v_pages[((phys * kv_heads + kh) * block_size + slot) * d + c] =
+                v[(static_cast<uint64_t>(seq) * kv_heads + kh) * d + c];
+        }
+    }
+}
+
+// value * sigmoid(value) with the numerically stable sigmoid of
+// src/nn/activations.cpp:38-58, times `up` (src/model/swiglu.cpp:27-29).
+__device__ __forceinline__ float silu_ref(float value) {
+    if (value == -INFINITY) return -0.0f;
+    float s;
+    if (value >= 0.0f) {
+        s = 1.0f / (1.0f + expf(-value));
+    } else {
+        const float e = expf(value);
+        s = e / (1.0f + e);
+    }
+    return value * s;
+}
+
+__global__ void __launch_bounds__(256)
+silu_mul_kernel(const float* __restrict__ gate, const float* __restrict__ up, float* __restrict__ out,
+                uint64_t n) {
+    const uint64_t stride = static_cast<uint64_t>(gridDim.x) * blockDim.x;
+    for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
+        out[i] = silu_ref(gate[i]) * up[i];
+    }
+}
+
+__global__ void __launch_bounds__(256)
+add_kernel(const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ out, uint64_t n) {
+    const uint64_t stride = static_cast<uint64_t>(gridDim.x) * blockDim.x;
+    for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
+        out[i] = a[i] + b[i];
+    }
+}
+
+// Embedding rows for a batch of token ids (gather_rows in the reference,
+// src/core/backend/nn/reference/operations.cpp). An id >= vocab sets bit 0 of status.
+__global__ void __launch_bounds__(256)
+gather_rows_kernel(const float* __restrict__ table, const uint32_t* __restrict__ ids, float* __restrict__ out,
+                   uint32_t width, uint32_t vocab, uint32_t* status) {
+    const uint32_t row = blockIdx.x;
+    uint32_t id = ids[row];
+    if (id >= vocab) {
+        if (threadIdx.x == 0 && status != nullptr) atomicOr(status, 1u);
+        id = 0;
+    }
+    for (uint32_t c = threadIdx.x; c < width; c += blockDim.x) {
+        out[static_cast<uint64_t>(row) * width + c] = table[static_cast<uint64_t>(id) * width + c];
+    }
+}
+
+// Greedy sampling: index of the first maximum of each row
+// (src/stages/serving/generation.cpp:100-120 keeps the lowest index on ties).
+__global__ void __launch_bounds__(256)
+argmax_kernel(const float* __restrict__ logits, uint32_t* __restrict__ out, uint32_t width) {
+    __shared__ float s_val[256];
+    __shared__ uint32_t s_idx[256];
+    const float* r = logits + static_cast<uint64_t>(blockIdx.x) * width;
+    float best = -INFINITY;
+    uint32_t best_i = 0xFFFFFFFFu;
+    for (uint32_t c = threadIdx.x; c < width; c += blockDim.x) {
+        const float v = r[c];
+        if (v > best || best_i == 0xFFFFFFFFu) {
+            best = v;
+            best_i = c;
+        }
+    }
+    s_val[threadIdx.x] = best;
+    s_idx[threadIdx.x] = best_i;
+    __syncthreads();
+    for (uint32_t s = blockDim.x / 2; s > 0; s >>= 1) {
+        if (threadIdx.x < s) {
+            const float ov = s_val[threadIdx.x + s];
+            const uint32_t oi = s_idx[threadIdx.x + s];
+            const float mv = s_val[threadIdx.x];
+            const uint32_t mi = s_idx[threadIdx.x];
+            if (oi != 0xFFFFFFFFu && (mi == 0xFFFFFFFFu || ov > mv || (ov == mv && oi < mi))) {
+                s_val[threadIdx.x] = ov;
+                s_idx[threadIdx.x] = oi;
+            }
+        }
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) out[blockIdx.x] = s_idx[0];
+}
+
+unsigned grid_for(uint64_t n, int sm_count) {
+    uint64_t blocks = (n + 255) / 256;
+    const uint64_t cap = static_cast<uint64_t>(sm_count > 0 ? sm_count : 148) * 8;
+    if (blocks > cap) blocks = cap;
+    return static_cast<unsigned>(blocks == 0 ? 1 : blocks);
+}
+
+}  // namespace
+
+int32_t launch_rmsnorm(const float* x, const float* delta, float* x_out, const float* scale, float* y,
+                       uint64_t rows, uint32_t width, float eps, cudaStream_t stream) {
+    rmsnorm_kernel<<<static_cast<unsigned>(rows), 256, 0, stream>>>(x, delta, x_out, scale, y, width, eps);
+    B2_CUDA_TRY(cudaGetLastError());
+    return B2_STATUS_OK;
+}
+
+int32_t launch_rope_append(float* q, const float* k, const float* v, const uint32_t* positions,
+                           const uint32_t* block_tables, float* k_pages, float* v_pages, uint32_t n_seq,
+                           uint32_t q_heads, uint32_t kv_heads, uint32_t d, uint32_t block_size,
+                           uint64_t physical_blocks, uint32_t max_blocks, float theta, uint32_t* status,
+                           cudaStream_t stream) {
+    rope_append_kernel<<<n_seq, 256, 0, stream>>>(q, k, v, positions, block_tables, k_pages, v_pages, q_heads,
+                                                  kv_heads, d, block_size, physical_blocks, max_blocks, theta,
+                                                  status);
+    B2_CUDA_TRY(cudaGetLastError());
+    return B2_STATUS_OK;
+}
+
+int32_t launch_silu_mul(const DeviceContext& ctx, const float* gate, const float* up, float* out, uint64_t n,
+                        cudaStream_t stream) {
+    silu_mul_kernel<<<grid_for(n, ctx.sm_count), 256, 0, stream>>>(gate, up, out, n);
+    B2_CUDA_TRY(cudaGetLastError());
+    return B2_STATUS_OK;
+}
+
+int32_t launch_add(const DeviceContext& ctx, const float* a, const float* b, float* out, uint64_t n,
+                   cudaStream_t stream) {
+    add_kernel<<<grid_for(n, ctx.sm_count), 256, 0, stream>>>(a, b, out, n);
+    B2_CUDA_TRY(cudaGetLastError());
+    return B2_STATUS_OK;
+}
+
+int32_t launch_gather_rows(const float* table, const uint32_t* ids, float* out, uint32_t rows, uint32_t width,
+                           uint32_t vocab, uint32_t* status, cudaStream_t stream) {
+    gather_rows_kernel<<<rows, 256, 0, stream>>>(table, ids, out, width, vocab, status);
+    B2_CUDA_TRY(cudaGetLastError());
+    return B2_STATUS_OK;
+}
+
+int32_t launch_argmax(const float* logits, uint32_t* out, uint32_t rows, uint32_t width, cudaStream_t stream) {
+    argmax_kernel<<<rows, 256, 0, stream>>>(logits, out, width);
+    B2_CUDA_TRY(cudaGetLastError());
+    return B2_STATUS_OK;
+}
+
+}  // namespace b2

@@ -1,0 +1,269 @@
+"""One decode step of a Llama-shaped decoder assembled from the hot-path
+operators: packed-NF4 linears, RMSNorm, split-half RoPE + KV-page append, paged
+grouped-query attention, SwiGLU, greedy argmax.
+
+The reference has no incremental decode for its Llama/Mistral model
+(include/riftco_transformer/model/llama_mistral_transformer.hpp:77-79); the
+step below strings together the reference's primitives in the order of its
+full-sequence forward (src/model/llama_mistral_transformer.cpp) and of
+DecoderOnlyTransformer::decode_token (src/model/decoder_only_transformer.cpp:368-460):
+per layer  x += Wo·attn(rope(Wq·n1), rope(Wk·n1), Wv·n1),  x += Wdown·(silu(Wgate·n2) * Wup·n2)
+with n = RMSNorm(x); bias-free linears; final RMSNorm and LM head.
+
+Multi-GPU (one process per GPU): every linear is sharded by output rows, the
+attention by KV head; ranks exchange activations with an all-gather at the four
+layer boundaries where the next operator needs the full width. There is no
+reduction: no linear is split along its contraction.
+
+The step is written against a small `ops` interface so that the same
+orchestration (sharding arithmetic, buffer flow, gathers) is exercised by CPU
+tests with a checker backend; the product backend is `CudaOps`, which calls the
+C ABI and has no CPU fallback.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+
+import torch
+
+from . import _lib
+from ._lib import lib
+from .backend import PackedNf4Weight, PagedKvPool, _check, _stream_ptr
+
+
+@dataclass
+class DecoderConfig:
+    layers: int = 32
+    d_model: int = 4096
+    q_heads: int = 32
+    kv_heads: int = 8
+    head_dim: int = 128
+    ffn: int = 14336
+    vocab: int = 32000
+    eps: float = 1e-5
+    theta: float = 1e4
+    block_size: int = 16
+
+    def shard_check(self, world: int) -> None:
+        for name, v in (("q_heads", self.q_heads), ("kv_heads", self.kv_heads), ("d_model", self.d_model),
+                        ("ffn", self.ffn), ("vocab", self.vocab)):
+            if v % world != 0:
+                raise ValueError(f"{name}={v} does not divide over {world} ranks")
+
+
+LAYER_WEIGHTS = ("wq", "wk", "wv", "wo", "w_gate", "w_up", "w_down")
+
+
+def weight_shapes(cfg: DecoderConfig) -> dict[str, tuple[int, int]]:
+    """(out, in) of every linear of one layer, plus the LM head."""
+    d, hd = cfg.d_model, cfg.head_dim
+    return {
+        "wq": (cfg.q_heads * hd, d), "wk": (cfg.kv_heads * hd, d), "wv": (cfg.kv_heads * hd, d),
+        "wo": (d, cfg.q_heads * hd), "w_gate": (cfg.ffn, d), "w_up": (cfg.ffn, d), "w_down": (d, cfg.ffn),
+        "lm_head": (cfg.vocab, d),
+    }
+
+
+class CudaOps:
+    """Product backend: torch tensors for memory, the C ABI for arithmetic,
+    torch.distributed (NCCL) for the all-gather."""
+
+    def __init__(self, device, group=None) -> None:
+        self.device = device
+        self.group = group
+        self.world = 1 if group is None else torch.distributed.get_world_size(group)
+        self.launches = 0
+
+    def empty(self, shape, dtype=torch.float32):
+        return torch.empty(shape, dtype=dtype, device=self.device)
+
+    def linear(self, x, w: PackedNf4Weight, out) -> None:
+        ws = w.struct()
+        _check(lib.b2_nf4_linear_forward(C.byref(ws), x.data_ptr(), out.data_ptr(), x.shape[0], None, 0,
+                                         _stream_ptr(None)))
+        self.launches += 1
+
+    def rmsnorm(self, x, delta, x_out, scale, y, eps: float) -> None:
+        _check(lib.b2_rmsnorm(x.data_ptr(), None if delta is None else delta.data_ptr(),
+                              None if x_out is None else x_out.data_ptr(), scale.data_ptr(), y.data_ptr(),
+                              x.shape[0], x.shape[1], eps, _stream_ptr(None)))
+        self.launches += 1
+
+    def rope_append(self, q, k, v, positions, tables, pool: PagedKvPool, theta: float, status) -> None:
+        n_seq, q_heads, d = q.shape
+        _check(lib.b2_rope_append_kv(q.data_ptr(), k.data_ptr(), v.data_ptr(), positions.data_ptr(),
+                                     tables.data_ptr(), pool.key_pages.data_ptr(), pool.value_pages.data_ptr(),
+                                     n_seq, q_heads, k.shape[1], d, pool.block_size, pool.physical_blocks,
+                                     tables.shape[1], theta, status.data_ptr(), _stream_ptr(None)))
+        self.launches += 1
+
+    def attention(self, q, pool: PagedKvPool, tables, seq_lens, ctx, max_seq_len: int, status, workspace) -> None:
+        n_seq, q_heads, d = q.shape
+        _check(lib.b2_paged_decode_attention(
+            q.data_ptr(), pool.key_pages.data_ptr(), pool.value_pages.data_ptr(), tables.data_ptr(),
+            seq_lens.data_ptr(), ctx.data_ptr(), n_seq, q_heads, pool.kv_heads, d, pool.block_size,
+            pool.physical_blocks, tables.shape[1], max_seq_len,
+            None if workspace is None else workspace.data_ptr(),
+            0 if workspace is None else workspace.numel() * workspace.element_size(), status.data_ptr(),
+            _stream_ptr(None)))
+        self.launches += 2 if max_seq_len > 256 else 1
+
+    def attention_workspace(self, n_seq, q_heads, d, block_size, max_seq_len):
+        need = lib.b2_paged_decode_workspace_bytes(n_seq, q_heads, d, block_size, max_seq_len)
+        return torch.empty(max(need, 16), dtype=torch.uint8, device=self.device)
+
+    def silu_mul(self, gate, up, out) -> None:
+        _check(lib.b2_silu_mul(gate.data_ptr(), up.data_ptr(), out.data_ptr(), out.numel(), _stream_ptr(None)))
+        self.launches += 1
+
+    def gather_rows(self, table, ids, out, status) -> None:
+        _check(lib.b2_gather_rows(table.data_ptr(), ids.data_ptr(), out.data_ptr(), out.shape[0], out.shape[1],
+                                  table.shape[0], status.data_ptr(), _stream_ptr(None)))
+        self.launches += 1
+
+    def argmax(self, logits, out) -> None:
+        _check(lib.b2_argmax(logits.data_ptr(), out.data_ptr(), logits.shape[0], logits.shape[1],
+                             _stream_ptr(None)))
+        self.launches += 1
+
+    def all_gather_columns(self, local, gathered, full) -> None:
+        """local [B, n] on every rank -> full [B, world*n] (rank r's columns at
+        r*n). `gathered` is a [world, B, n] staging buffer."""
+        if self.world == 1:
+            raise RuntimeError("all_gather_columns is only used with more than one rank")
+        torch.distributed.all_gather_into_tensor(gathered.view(-1, local.shape[1]), local, group=self.group)
+        full.view(local.shape[0], self.world, local.shape[1]).copy_(gathered.permute(1, 0, 2))
+
+
+class DecodeStep:
+    """Holds one rank's weight shards, KV pools and activation buffers and runs
+    decode steps for a fixed batch."""
+
+    def __init__(self, cfg: DecoderConfig, ops, weights: dict, norms: dict, embedding, pools: list,
+                 tables, batch: int, max_seq_len: int, rank: int = 0, world: int = 1) -> None:
+        cfg.shard_check(world)
+        self.cfg, self.ops, self.rank, self.world = cfg, ops, rank, world
+        self.w, self.norms, self.embedding, self.pools, self.tables = weights, norms, embedding, pools, tables
+        self.batch, self.max_seq_len = batch, max_seq_len
+        d, hd = cfg.d_model, cfg.head_dim
+        self.hq, self.hkv = cfg.q_heads // world, cfg.kv_heads // world
+        e = ops.empty
+        B = batch
+        self.x = e((B, d))
+        self.n = e((B, d))
+        self.q = e((B, self.hq, hd))
+        self.k = e((B, self.hkv, hd))
+        self.v = e((B, self.hkv, hd))
+        self.ctx_local = e((B, self.hq, hd))
+        self.ctx = e((B, cfg.q_heads * hd)) if world > 1 else None
+        self.o_local = e((B, d // world))
+        self.o = e((B, d)) if world > 1 else None
+        self.gate = e((B, cfg.ffn // world))
+        self.up = e((B, cfg.ffn // world))
+        self.h_local = e((B, cfg.ffn // world))
+        self.h = e((B, cfg.ffn)) if world > 1 else None
+        self.down_local = e((B, d // world))
+        self.down = e((B, d)) if world > 1 else None
+        self.logits_local = e((B, cfg.vocab // world))
+        self.logits = e((B, cfg.vocab)) if world > 1 else None
+        self.next_tokens = e((B,), dtype=torch.int32)
+        self.status = ops.empty((1,), dtype=torch.int32)
+        self.workspace = ops.attention_workspace(B, self.hq, hd, cfg.block_size, max_seq_len)
+        if world > 1:
+            widths = {cfg.q_heads * hd // world, d // world, cfg.ffn // world, cfg.vocab // world}
+            self.stage = {n_: e((world, B, n_)) for n_ in widths}
+
+    def _gather(self, local, full):
+        if self.world == 1:
+            return local.view(local.shape[0], -1)
+        flat = local.view(local.shape[0], -1)
+        self.ops.all_gather_columns(flat, self.stage[flat.shape[1]], full)
+        return full
+
+    def step(self, tokens, positions, seq_lens):
+        """tokens int32 [B]; positions uint32/int32 [B] = index of the new token;
+        seq_lens = positions + 1. Returns (next_tokens [B], logits [B, vocab])."""
+        cfg, ops = self.cfg, self.ops
+        ops.gather_rows(self.embedding, tokens, self.x, self.status)
+        pending = None  # residual delta not yet added to x
+        for layer in range(cfg.layers):
+            w, nm = self.w[layer], self.norms[layer]
+            ops.rmsnorm(self.x, pending, self.x, nm["attn"], self.n, cfg.eps)
+            ops.linear(self.n, w["wq"], self.q.view(self.batch, -1))
+            ops.linear(self.n, w["wk"], self.k.view(self.batch, -1))
+            ops.linear(self.n, w["wv"], self.v.view(self.batch, -1))
+            ops.rope_append(self.q, self.k, self.v, positions, self.tables, self.pools[layer], cfg.theta,
+                            self.status)
+            ops.attention(self.q, self.pools[layer], self.tables, seq_lens, self.ctx_local, self.max_seq_len,
+                          self.status, self.workspace)
+            ctx = self._gather(self.ctx_local, self.ctx)
+            ops.linear(ctx, w["wo"], self.o_local)
+            o = self._gather(self.o_local, self.o)
+            ops.rmsnorm(self.x, o, self.x, nm["ffn"], self.n, cfg.eps)
+            ops.linear(self.n, w["w_gate"], self.gate)
+            ops.linear(self.n, w["w_up"], self.up)
+            ops.silu_mul(self.gate, self.up, self.h_local)
+            h = self._gather(self.h_local, self.h)
+            ops.linear(h, w["w_down"], self.down_local)
+            pending = self._gather(self.down_local, self.down)
+        ops.rmsnorm(self.x, pending, self.x, self.norms["final"], self.n, cfg.eps)
+        ops.linear(self.n, self.w["lm_head"], self.logits_local)
+        logits = self._gather(self.logits_local, self.logits)
+        ops.argmax(logits, self.next_tokens)
+        return self.next_tokens, logits
+
+    # ---- accounting ---------------------------------------------------------------
+    def weight_bytes(self) -> int:
+        total = 0
+        for layer in range(self.cfg.layers):
+            total += sum(self.w[layer][k].resident_payload_bytes() for k in LAYER_WEIGHTS)
+        return total + self.w["lm_head"].resident_payload_bytes()
+
+
+def synthetic_step(cfg: DecoderConfig, batch: int, context: int, rank: int = 0, world: int = 1, device="cuda",
+                   group=None, seed: int = 1234) -> tuple[DecodeStep, dict]:
+    """A DecodeStep over seeded synthetic shards for benchmarking: packed weights
+    drawn in the packed domain at the shard's own shape, KV pools ~ N(0,1) holding
+    `context` tokens per sequence, permuted block tables shared by all layers."""
+    from . import synth
+    cfg.shard_check(world)
+    ops = CudaOps(device, group)
+    shapes = weight_shapes(cfg)
+    weights: dict = {}
+    for layer in range(cfg.layers):
+        weights[layer] = {}
+        for i, name in enumerate(LAYER_WEIGHTS):
+            out_f, in_f = shapes[name]
+            weights[layer][name] = synth.packed_weight(out_f // world, in_f, device=device,
+                                                       seed=seed + 1000 * layer + 10 * i + rank)
+    out_f, in_f = shapes["lm_head"]
+    weights["lm_head"] = synth.packed_weight(out_f // world, in_f, device=device, seed=seed + 999983 + rank)
+    g = torch.Generator(device=device)
+    g.manual_seed(seed + 7)
+    norms = {layer: {"attn": 1.0 + 0.1 * torch.randn(cfg.d_model, device=device, generator=g),
+                     "ffn": 1.0 + 0.1 * torch.randn(cfg.d_model, device=device, generator=g)}
+             for layer in range(cfg.layers)}
+    norms["final"] = 1.0 + 0.1 * torch.randn(cfg.d_model, device=device, generator=g)
+    embedding = 0.02 * torch.randn((cfg.vocab, cfg.d_model), device=device, generator=g)
+    # One spare slot per sequence for the token this step appends.
+    lens = [context + 1] * batch
+    blocks = -(-(context + 1) // cfg.block_size)
+    total = blocks * batch
+    perm = torch.randperm(total, device=device, generator=g).to(torch.int32)
+    tables = perm.view(batch, blocks).contiguous()
+    pools = []
+    hkv = cfg.kv_heads // world
+    for layer in range(cfg.layers):
+        shape = (total, hkv, cfg.block_size, cfg.head_dim)
+        pools.append(PagedKvPool(torch.randn(shape, device=device, generator=g),
+                                 torch.randn(shape, device=device, generator=g)))
+    step = DecodeStep(cfg, ops, weights, norms, embedding, pools, tables, batch, context + 1, rank, world)
+    inputs = {
+        "tokens": torch.randint(0, cfg.vocab, (batch,), device=device, generator=g, dtype=torch.int32),
+        "positions": torch.full((batch,), context, dtype=torch.int32, device=device),
+        "seq_lens": torch.full((batch,), context + 1, dtype=torch.int32, device=device),
+        "kv_bytes_per_step": cfg.layers * batch * (context + 1) * hkv * cfg.head_dim * 4 * 2,
+        "lens": lens,
+    }
+    return step, inputs

@@ -1,0 +1,106 @@
+"""The decode step on the GPU (CudaOps, C ABI) against the same step run with
+the CPU checker backend, plus the glue operators one by one."""
+import numpy as np
+import pytest
+import torch
+
+import decode_cases
+from conftest import rel_l2
+from oracle import decode_ref
+
+pytestmark = pytest.mark.gpu
+
+
+def cuda_step(model):
+    import riftco_transformer_b200 as b2
+    from riftco_transformer_b200.decode import LAYER_WEIGHTS, CudaOps, DecodeStep
+    cfg = decode_cases.CFG
+    dev = torch.device("cuda", 0)
+    ops = CudaOps(dev)
+    weights = {layer: {n: b2.PackedNf4Weight.from_host(model["weights"][layer][n]) for n in LAYER_WEIGHTS}
+               for layer in range(cfg.layers)}
+    weights["lm_head"] = b2.PackedNf4Weight.from_host(model["weights"]["lm_head"])
+    norms = {k: ({a: torch.from_numpy(b).to(dev) for a, b in v.items()} if isinstance(v, dict)
+                 else torch.from_numpy(v).to(dev)) for k, v in model["norms"].items()}
+    pools = [b2.PagedKvPool(torch.from_numpy(k).to(dev), torch.from_numpy(v).to(dev)) for k, v in model["pools"]]
+    return DecodeStep(cfg, ops, weights, norms, torch.from_numpy(model["embedding"]).to(dev), pools,
+                      torch.from_numpy(model["tables"]).to(dev), decode_cases.BATCH,
+                      int(model["lens"].max()) + 1)
+
+
+def test_decode_step_matches_checker():
+    model = decode_cases.host_model()
+    want_next, want_logits = decode_cases.run(decode_cases.checker_step(model), model)
+    step = cuda_step(model)
+    got_next, got_logits = decode_cases.run(step, model)
+    torch.cuda.synchronize()
+    assert int(step.status.item()) == 0
+    assert np.isfinite(got_logits).all()
+    assert rel_l2(got_logits, want_logits) <= 5e-3   # two layers of 2e-3 operators compounded
+    assert (got_next == want_next).all()
+    # the appended K/V slots hold the rotated key and the value bit for bit (pure copies / exact formulas aside)
+    ref = decode_cases.checker_step(model)
+    decode_cases.run(ref, model)
+    for layer in range(decode_cases.CFG.layers):
+        assert rel_l2(step.pools[layer].key_pages.cpu().numpy(), ref.pools[layer].key_pages.numpy()) <= 5e-3
+        assert rel_l2(step.pools[layer].value_pages.cpu().numpy(), ref.pools[layer].value_pages.numpy()) <= 5e-3
+
+
+def test_glue_operators():
+    from riftco_transformer_b200.decode import CudaOps
+    import riftco_transformer_b200 as b2
+    dev = torch.device("cuda", 0)
+    ops = CudaOps(dev)
+    rng = np.random.default_rng(5)
+    x = rng.standard_normal((5, 4096)).astype(np.float32)
+    delta = rng.standard_normal((5, 4096)).astype(np.float32)
+    scale = (1 + 0.1 * rng.standard_normal(4096)).astype(np.float32)
+    tx, td, ts = (torch.from_numpy(a).to(dev) for a in (x, delta, scale))
+    y = torch.empty_like(tx)
+    ops.rmsnorm(tx, None, None, ts, y, 1e-5)
+    assert rel_l2(y.cpu().numpy(), decode_ref.rms_norm(x, scale, 1e-5)) <= 1e-6
+    xo = torch.empty_like(tx)
+    ops.rmsnorm(tx, td, xo, ts, y, 1e-5)
+    assert (xo.cpu().numpy() == x + delta).all()
+    assert rel_l2(y.cpu().numpy(), decode_ref.rms_norm(x + delta, scale, 1e-5)) <= 1e-6
+
+    g = rng.standard_normal((7, 1000)).astype(np.float32) * 4
+    g[0, 0] = -np.inf
+    u = rng.standard_normal((7, 1000)).astype(np.float32)
+    out = torch.empty((7, 1000), device=dev)
+    ops.silu_mul(torch.from_numpy(g).to(dev), torch.from_numpy(u).to(dev), out)
+    want = decode_ref.silu(g) * u
+    want[0, 0] = -0.0 * u[0, 0]
+    assert np.allclose(out.cpu().numpy(), want, rtol=2e-6, atol=1e-7)
+
+    logits = rng.standard_normal((4, 32000)).astype(np.float32)
+    logits[1, 77] = logits[1, 9000] = 50.0   # tie: lowest index wins
+    idx = torch.empty(4, dtype=torch.int32, device=dev)
+    ops.argmax(torch.from_numpy(logits).to(dev), idx)
+    assert (idx.cpu().numpy() == np.argmax(logits, axis=1)).all() and int(idx[1]) == 77
+
+    # RoPE + append at several positions, including position 0 and a page boundary
+    hq, hkv, d, bs = 4, 2, 128, 16
+    positions = np.array([0, 15, 16, 301], np.int32)
+    P = 40
+    tables = rng.permutation(P)[:4 * 20].reshape(4, 20).astype(np.int32) if P >= 80 else \
+        np.stack([rng.permutation(P)[:20] for _ in range(4)]).astype(np.int32)
+    q = rng.standard_normal((4, hq, d)).astype(np.float32)
+    k = rng.standard_normal((4, hkv, d)).astype(np.float32)
+    v = rng.standard_normal((4, hkv, d)).astype(np.float32)
+    pool = b2.PagedKvPool(torch.zeros((P, hkv, bs, d), device=dev), torch.zeros((P, hkv, bs, d), device=dev))
+    tq = torch.from_numpy(q).to(dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    # distinct pages per sequence so the slots do not collide
+    tables = np.arange(80, dtype=np.int32).reshape(4, 20) % P
+    tables[1] = (tables[1] + 7) % P
+    ops.rope_append(tq, torch.from_numpy(k).to(dev), torch.from_numpy(v).to(dev), torch.from_numpy(positions).to(dev),
+                    torch.from_numpy(tables).to(dev), pool, 1e4, status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    for s, pos in enumerate(positions):
+        assert np.allclose(tq[s].cpu().numpy(), decode_ref.rotate(q[s], int(pos), 1e4), rtol=1e-6, atol=1e-6)
+    s = 3
+    page, slot = tables[s, positions[s] // bs], positions[s] % bs
+    assert np.allclose(pool.key_pages[page, :, slot].cpu().numpy(), decode_ref.rotate(k[s], 301, 1e4), rtol=1e-6, atol=1e-6)
+    assert (pool.value_pages[page, :, slot].cpu().numpy() == v[s]).all()
