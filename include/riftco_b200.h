@@ -250,6 +250,14 @@ B2_API int32_t b2_gather_rows(const float* table, const uint32_t* ids, float* ou
  * src/stages/serving/generation.cpp:100-120). */
 B2_API int32_t b2_argmax(const float* logits, uint32_t* out, uint32_t rows, uint32_t width, void* stream);
 
+/* Synchronises the device and reports (then clears) sticky device-side error
+ * flags of earlier asynchronous calls: today, a bounded barrier wait inside the
+ * tensor-core GEMM that gave up (B2_STATUS_RUNTIME_ERROR). Kernels never trap or
+ * spin forever; this is how such a failure reaches the host. The reference
+ * reads a device status word the same way after its kernels
+ * (src/core/backend/attention/cuda/common.cuh:124-133). */
+B2_API int32_t b2_check_device_errors(void);
+
 /* ---- host-buffer seam --------------------------------------------------- */
 /*
  * The reference adapter contract is synchronous over host-visible storage

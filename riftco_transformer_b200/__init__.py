@@ -11,6 +11,7 @@ _EXPORTS = (
     "BackendUnavailable",
     "PackedNf4Weight",
     "PagedKvPool",
+    "check_device_errors",
     "dequantize",
     "dispatch_paged_decode_attention_forward",
     "dispatch_quantized_linear_forward",

@@ -72,6 +72,7 @@ SIGNATURES = {
     "b2_add": (_i32, [_vp, _vp, _vp, _u64, _vp]),
     "b2_gather_rows": (_i32, [_vp, _vp, _vp, _u32, _u32, _u32, _vp, _vp]),
     "b2_argmax": (_i32, [_vp, _vp, _u32, _u32, _vp]),
+    "b2_check_device_errors": (_i32, []),
     "b2_host_nf4_linear_forward": (_i32, [_W, _vp, _vp, _u64, _vp]),
     "b2_host_nf4_linear_input_backward": (_i32, [_W, _vp, _vp, _u64, _vp]),
     "b2_host_paged_decode_attention": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32,

@@ -73,6 +73,11 @@ def unavailability_reason() -> str:
     return lib.b2_unavailability_reason().decode()
 
 
+def check_device_errors() -> None:
+    """Synchronises and raises if an earlier asynchronous call flagged a device-side failure."""
+    _check(lib.b2_check_device_errors())
+
+
 def _stream_ptr(stream) -> int:
     if stream is None:
         stream = torch.cuda.current_stream()

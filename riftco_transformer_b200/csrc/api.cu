@@ -88,7 +88,8 @@ DeviceContext* device_context(int32_t* status) {
         ctx.device = device;
         ctx.sm_count = prop.multiProcessorCount;
         ctx.cc_major = prop.major;
-        const int32_t s = init_gemv_lut(&ctx);
+        int32_t s = init_gemv_lut(&ctx);
+        if (s == B2_STATUS_OK) s = init_gemm_lut(&ctx);
         if (s != B2_STATUS_OK) {
             g_context_status[device] = s;
             g_context_error[device] = g_last_error;
@@ -219,7 +220,7 @@ bool aliases_weight(const b2_nf4_weight* weight, const void* p) {
 }
 
 int32_t linear_forward_impl(const b2_nf4_weight* weight, const float* x, float* y, uint64_t rows,
-                            void*, size_t, cudaStream_t stream) {
+                            void* workspace, size_t workspace_bytes, cudaStream_t stream) {
     int32_t status = B2_STATUS_OK;
     DeviceContext* ctx = device_context(&status);
     if (ctx == nullptr) return status;
@@ -242,6 +243,16 @@ int32_t linear_forward_impl(const b2_nf4_weight* weight, const float* x, float* 
             return launch_nf4_gemv_stream(*ctx, w, x, y, rows, spw, ksplit, stream);
         }
         return launch_nf4_gemv(*ctx, w, x, y, rows, stream);
+    }
+    static const char* gemm_off = getenv("B2_DISABLE_TENSOR_GEMM");
+    if (gemm_off == nullptr && nf4_gemm_supported(w, x, rows, false)) {
+        const size_t need = nf4_gemm_workspace_bytes(w, rows, false);
+        if (workspace == nullptr) {
+            B2_TRY(reserve_arena(ctx, need));
+            workspace = ctx->arena;
+            workspace_bytes = ctx->arena_bytes;
+        }
+        return launch_nf4_gemm(*ctx, w, x, y, rows, false, workspace, workspace_bytes, stream);
     }
     return launch_nf4_linear_forward_generic(*ctx, w, x, y, rows, stream);
 }
@@ -356,7 +367,13 @@ int32_t b2_nf4_linear_input_backward(const b2_nf4_weight* weight, const float* d
                                 static_cast<cudaStream_t>(stream));
 }
 
-size_t b2_nf4_linear_workspace_bytes(const b2_nf4_weight*, uint64_t, int32_t) { return 0; }
+size_t b2_nf4_linear_workspace_bytes(const b2_nf4_weight* weight, uint64_t rows, int32_t backward) {
+    WeightView w;
+    if (make_weight_view(weight, &w) != B2_STATUS_OK) return 0;
+    clear_error();
+    if (!nf4_gemm_supported(w, reinterpret_cast<const float*>(16), rows, backward != 0)) return 0;
+    return nf4_gemm_workspace_bytes(w, rows, backward != 0);
+}
 
 size_t b2_paged_decode_workspace_bytes(uint32_t n_seq, uint32_t q_heads, uint32_t head_width,
                                        uint32_t block_size, uint32_t max_seq_len) {
@@ -489,6 +506,21 @@ int32_t b2_argmax(const float* logits, uint32_t* out, uint32_t rows, uint32_t wi
 
 // ---- host-buffer seam ---------------------------------------------------------
 
+int32_t b2_check_device_errors(void) {
+    int32_t status = B2_STATUS_OK;
+    DeviceContext* ctx = device_context(&status);
+    if (ctx == nullptr) return status;
+    uint32_t word = 0;
+    B2_CUDA_TRY(cudaMemcpy(&word, ctx->gemm_error, sizeof(word), cudaMemcpyDeviceToHost));
+    if (word != 0) {
+        B2_CUDA_TRY(cudaMemset(ctx->gemm_error, 0, sizeof(word)));
+        return fail(B2_STATUS_RUNTIME_ERROR,
+                    "a bounded wait inside the tensor-core NF4 GEMM timed out (flags 0x%x); its output is invalid",
+                    word);
+    }
+    return B2_STATUS_OK;
+}
+
 static int32_t host_linear(const b2_nf4_weight* weight, const float* src_host, float* dst_host,
                            uint64_t rows, bool backward, cudaStream_t stream) {
     int32_t status = B2_STATUS_OK;
@@ -521,7 +553,7 @@ static int32_t host_linear(const b2_nf4_weight* weight, const float* src_host, f
     }
     B2_CUDA_TRY(cudaMemcpyAsync(dst_host, d_dst, dst_bytes, cudaMemcpyDeviceToHost, stream));
     B2_CUDA_TRY(cudaStreamSynchronize(stream));
-    return B2_STATUS_OK;
+    return b2_check_device_errors();
 }
 
 int32_t b2_host_nf4_linear_forward(const b2_nf4_weight* weight, const float* x_host, float* y_host,

@@ -46,6 +46,10 @@ struct DeviceContext {
     // 256 rows of 256 bytes; row v holds, for each of 32 lanes at byte 4*lane,
     // the two fp16 codebook values of packed byte v (low nibble in the low half).
     uint32_t* gemv_lut = nullptr;
+    // Same table with bf16 pairs, compact [256][32] words, for the prefill GEMM.
+    uint32_t* gemm_lut = nullptr;
+    // Device word the GEMM sets when a bounded barrier wait gives up.
+    uint32_t* gemm_error = nullptr;
     // Library-owned scratch arena used when a caller passes no workspace.
     void* arena = nullptr;
     size_t arena_bytes = 0;

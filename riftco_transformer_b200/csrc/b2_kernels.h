@@ -30,6 +30,13 @@ bool nf4_gemv_stream_plan(const DeviceContext& ctx, const WeightView& w, uint64_
 int32_t launch_nf4_gemv_stream(const DeviceContext& ctx, const WeightView& w, const float* x, float* y,
                                uint64_t rows, uint32_t spw, uint32_t ksplit, cudaStream_t stream);
 
+// nf4_gemm_sm100.cu - tcgen05 prefill GEMM, rows > 32.
+int32_t init_gemm_lut(DeviceContext* ctx);
+bool nf4_gemm_supported(const WeightView& w, const float* x, uint64_t rows, bool backward);
+size_t nf4_gemm_workspace_bytes(const WeightView& w, uint64_t rows, bool backward);
+int32_t launch_nf4_gemm(const DeviceContext& ctx, const WeightView& w, const float* x, float* y, uint64_t rows,
+                        bool backward, void* workspace, size_t workspace_bytes, cudaStream_t stream);
+
 // paged_decode.cu
 struct PagedDecodeArgs {
     const float* q;

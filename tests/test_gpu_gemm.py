@@ -1,0 +1,61 @@
+"""The tensor-core (tcgen05) prefill path of the packed-NF4 linear against the
+FP32 CPU oracle. Tolerance: relative L2 <= 1e-2 (bf16 operands, FP32 accumulate)."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import rel_l2
+
+pytestmark = pytest.mark.gpu
+
+GEMM_TOL = 1e-2
+
+
+@pytest.fixture(scope="module")
+def b2():
+    import riftco_transformer_b200 as pkg
+    assert pkg.is_available(), pkg.unavailability_reason()
+    return pkg
+
+
+def forward(b2, w, x):
+    rows = x.shape[0]
+    y = torch.empty((rows, w.out_features), dtype=torch.float32, device="cuda")
+    b2.dispatch_quantized_linear_forward(x, w, y, (rows, w.in_features, w.out_features, w.block_size))
+    b2.check_device_errors()
+    return y.cpu().numpy()
+
+
+@pytest.mark.parametrize("rows,out_f,in_f,block,dq", [
+    (256, 256, 64, 64, False),      # one tile, one k-block
+    (300, 512, 256, 64, True),      # ragged M, several k-blocks (ring wraps)
+    (257, 300, 1024, 128, True),    # ragged M and N, block 128
+    (64, 1000, 4096, 64, False),    # fewer rows than a tile, FP32 scales, long K
+])
+def test_gemm_small_shapes(b2, port, rows, out_f, in_f, block, dq):
+    rng = np.random.default_rng(rows + out_f)
+    W = (rng.standard_normal((out_f, in_f)) * 0.02).astype(np.float32)
+    host = port.quantize_nf4_double_quantized(W, block, 32) if dq else port.quantize_nf4(W, block)
+    x = rng.standard_normal((rows, in_f)).astype(np.float32)
+    y = forward(b2, b2.PackedNf4Weight.from_host(host), torch.from_numpy(x).cuda())
+    want = port.linear_forward(host, x)
+    assert np.isfinite(y).all()
+    assert rel_l2(y, want) <= GEMM_TOL
+    for r in (0, rows // 2, rows - 1):
+        assert rel_l2(y[r], want[r]) <= GEMM_TOL
+
+
+def test_gemm_config3_sampled_rows(b2, port):
+    # baseline configuration 3, forward: M = 4096 tokens through 4096 -> 14336, checked on 24 rows
+    rng = np.random.default_rng(1234)
+    W = (rng.standard_normal((14336, 4096)) * 0.02).astype(np.float32)
+    host = port.quantize_nf4_double_quantized(W, 64, 256)
+    x = rng.standard_normal((4096, 4096)).astype(np.float32)
+    y = forward(b2, b2.PackedNf4Weight.from_host(host), torch.from_numpy(x).cuda())
+    idx = np.r_[0:8, 2000:2008, 4088:4096]
+    want = port.linear_forward(host, x[idx])
+    assert rel_l2(y[idx], want) <= GEMM_TOL
+    assert np.isfinite(y).all()
+    # linearity in the activations
+    y2 = forward(b2, b2.PackedNf4Weight.from_host(host), torch.from_numpy(2.0 * x[:64]).cuda())
+    assert rel_l2(y2, 2.0 * y[:64]) <= 1e-6
