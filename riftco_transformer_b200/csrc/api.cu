@@ -258,7 +258,7 @@ int32_t linear_forward_impl(const b2_nf4_weight* weight, const float* x, float* 
 }
 
 int32_t linear_backward_impl(const b2_nf4_weight* weight, const float* dy, float* dx, uint64_t rows,
-                             void*, size_t, cudaStream_t stream) {
+                             void* workspace, size_t workspace_bytes, cudaStream_t stream) {
     int32_t status = B2_STATUS_OK;
     DeviceContext* ctx = device_context(&status);
     if (ctx == nullptr) return status;
@@ -275,6 +275,16 @@ int32_t linear_backward_impl(const b2_nf4_weight* weight, const float* dy, float
     }
     if (aliases_weight(weight, dx)) {
         return fail(B2_STATUS_INVALID_ARGUMENT, "quantized linear weight and output storage must not alias");
+    }
+    static const char* gemm_off = getenv("B2_DISABLE_TENSOR_GEMM");
+    if (gemm_off == nullptr && nf4_gemm_supported(w, dy, rows, true)) {
+        const size_t need = nf4_gemm_workspace_bytes(w, rows, true);
+        if (workspace == nullptr) {
+            B2_TRY(reserve_arena(ctx, need));
+            workspace = ctx->arena;
+            workspace_bytes = ctx->arena_bytes;
+        }
+        return launch_nf4_gemm(*ctx, w, dy, dx, rows, true, workspace, workspace_bytes, stream);
     }
     return launch_nf4_linear_input_backward_generic(*ctx, w, dy, dx, rows, stream);
 }

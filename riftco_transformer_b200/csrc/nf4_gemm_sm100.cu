@@ -129,10 +129,44 @@ __device__ __forceinline__ void dequant_forward(const GemmParams& p, const Forwa
     }
 }
 
+// Backward: the B tile is W[o0 .. o0+64, n0 .. n0+256] read "transposed": shared-memory row n holds
+// the 64 contraction values (output rows o) of input column n. Lane (kg = lane % 8, cgl = lane / 8)
+// of dequant warp w owns the 8 x 8 sub-block rows o0 + 8*kg .. +8, columns n0 + 8*(4*w + cgl) .. +8:
+// it loads one packed word (8 columns) per output row, pairs the words of two consecutive rows
+// nibble by nibble into byte indices, so one table lookup yields the (o, o+1) bf16 pair of one
+// column - already in K order - and stores one 16-byte chunk per column. The 8 lanes that share
+// a column group fill one whole 128-byte row per store instruction (no bank conflicts).
+struct BackwardState {
+    uint32_t words[8];   // packed word of each of the 8 output rows (8 input columns each)
+    float scale;         // scale this thread decodes for the CTA: (o = r % 64, in-block = r / 64)
+};
+
+__device__ __forceinline__ void backward_fetch(const GemmParams& p, uint32_t kb, uint32_t n0, uint32_t r,
+                                               uint32_t kg, uint32_t cg, BackwardState& st) {
+    const uint64_t in = p.w.in_features;
+    const uint32_t col = n0 + 8u * cg;
+    const uint64_t o_base = static_cast<uint64_t>(kb) * kBK + 8u * kg;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        st.words[i] = 0x77777777u;
+        if (col < p.n) {
+            st.words[i] = __ldg(reinterpret_cast<const uint32_t*>(p.w.codes + (((o_base + i) * in + col) >> 1)));
+        }
+    }
+    const uint32_t so = r & 63u, sib = r >> 6;
+    st.scale = 0.0f;
+    if (n0 + 64u * sib < p.n) {
+        const uint64_t flat = (static_cast<uint64_t>(kb) * kBK + so) * in + n0 + 64u * sib;
+        st.scale = decode_block_scale(p.w, flat >> p.w.block_shift);
+    }
+}
+
+template <bool kBackward>
 __global__ void __launch_bounds__(kThreads, 1)
-nf4_gemm_forward_kernel(const __grid_constant__ CUtensorMap map_a, const GemmParams p) {
+nf4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const GemmParams p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     __shared__ __align__(8) Barriers bars;
+    __shared__ __align__(16) __nv_bfloat16 s_scales[2][4][64];   // backward: [parity][in-block][output row]
     const uint32_t raw32 = smem_u32(smem_raw);
     const uint32_t base32 = (raw32 + 1023u) & ~1023u;
     const uint32_t a32 = base32;
@@ -210,36 +244,89 @@ nf4_gemm_forward_kernel(const __grid_constant__ CUtensorMap map_a, const GemmPar
     } else {
         // ---- dequantisation warps, then epilogue ----
         const uint32_t r = tid - 64u;
-        const uint32_t n = n0 + r;
         const uint32_t lut_lane = lut32 | (lane * 4u);
-        ForwardRow row;
-        row.codes = n < p.n ? p.w.codes + static_cast<uint64_t>(n) * (p.k >> 1) : nullptr;
-        row.flat0 = static_cast<uint64_t>(n) * p.k;
-        uint4 c0 = make_uint4(0, 0, 0, 0), c1 = c0;
-        float scale = 0.0f;
-        if (row.codes != nullptr) {
-            c0 = ldg_u4(row.codes);
-            c1 = ldg_u4(row.codes + 16);
-            scale = decode_block_scale(p.w, row.flat0 >> p.w.block_shift);
-        }
-        for (uint32_t kb = 0; kb < num_kb; ++kb) {
-            const uint32_t j = kb % kStagesB;
-            // next k-block's codes and scale while this one is expanded
-            uint4 n0c = make_uint4(0, 0, 0, 0), n1c = n0c;
-            float nscale = 0.0f;
-            if (row.codes != nullptr && kb + 1 < num_kb) {
-                n0c = ldg_u4(row.codes + (kb + 1) * 32u);
-                n1c = ldg_u4(row.codes + (kb + 1) * 32u + 16);
-                nscale = decode_block_scale(p.w, (row.flat0 + static_cast<uint64_t>(kb + 1) * kBK) >> p.w.block_shift);
+        if (!kBackward) {
+            const uint32_t n = n0 + r;
+            ForwardRow row;
+            row.codes = n < p.n ? p.w.codes + static_cast<uint64_t>(n) * (p.k >> 1) : nullptr;
+            row.flat0 = static_cast<uint64_t>(n) * p.k;
+            uint4 c0 = make_uint4(0, 0, 0, 0), c1 = c0;
+            float scale = 0.0f;
+            if (row.codes != nullptr) {
+                c0 = ldg_u4(row.codes);
+                c1 = ldg_u4(row.codes + 16);
+                scale = decode_block_scale(p.w, row.flat0 >> p.w.block_shift);
             }
-            if (kb >= kStagesB) mbar_wait(&bars.empty_b[j], ((kb / kStagesB) - 1u) & 1u, abort);
-            dequant_forward(p, row, r, c0, c1, scale, b32 + j * kStageBBytes, lut_lane);
-            fence_proxy_async_smem();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&bars.full_b[j]);
-            c0 = n0c;
-            c1 = n1c;
-            scale = nscale;
+            for (uint32_t kb = 0; kb < num_kb; ++kb) {
+                const uint32_t j = kb % kStagesB;
+                // next k-block's codes and scale while this one is expanded
+                uint4 n0c = make_uint4(0, 0, 0, 0), n1c = n0c;
+                float nscale = 0.0f;
+                if (row.codes != nullptr && kb + 1 < num_kb) {
+                    n0c = ldg_u4(row.codes + (kb + 1) * 32u);
+                    n1c = ldg_u4(row.codes + (kb + 1) * 32u + 16);
+                    nscale = decode_block_scale(p.w, (row.flat0 + static_cast<uint64_t>(kb + 1) * kBK) >> p.w.block_shift);
+                }
+                if (kb >= kStagesB) mbar_wait(&bars.empty_b[j], ((kb / kStagesB) - 1u) & 1u, abort);
+                dequant_forward(p, row, r, c0, c1, scale, b32 + j * kStageBBytes, lut_lane);
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&bars.full_b[j]);
+                c0 = n0c;
+                c1 = n1c;
+                scale = nscale;
+            }
+        } else {
+            const uint32_t kg = lane & 7u, cg = 4u * (warp - 2u) + (lane >> 3);
+            const uint32_t my_ib = cg >> 3;   // in-block (64 columns) of this thread's 8 columns
+            BackwardState cur, nxt;
+            backward_fetch(p, 0, n0, r, kg, cg, cur);
+            for (uint32_t kb = 0; kb < num_kb; ++kb) {
+                const uint32_t j = kb % kStagesB, par = kb & 1u;
+                if (kb + 1 < num_kb) backward_fetch(p, kb + 1, n0, r, kg, cg, nxt);
+                // publish this k-block's 256 decoded scales, then every thread reads its 8 (4 pairs)
+                s_scales[par][r >> 6][r & 63u] = __float2bfloat16_rn(cur.scale);
+                asm volatile("bar.sync 1, 256;" ::: "memory");
+                const uint4 sc = *reinterpret_cast<const uint4*>(&s_scales[par][my_ib][8u * kg]);
+                const uint32_t sc2[4] = {sc.x, sc.y, sc.z, sc.w};
+                uint4 even[4], odd[4];   // [row pair] -> columns (0,2,4,6) / (1,3,5,7), each a (o, o+1) pair
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const uint32_t wa = cur.words[2 * i], wb = cur.words[2 * i + 1];
+                    const uint32_t idx_e = (wa & 0x0F0F0F0Fu) | ((wb << 4) & 0xF0F0F0F0u);
+                    const uint32_t idx_o = ((wa >> 4) & 0x0F0F0F0Fu) | (wb & 0xF0F0F0F0u);
+                    even[i] = expand_word(idx_e, lut_lane, sc2[i]);
+                    odd[i] = expand_word(idx_o, lut_lane, sc2[i]);
+                }
+                if (kb >= kStagesB) mbar_wait(&bars.empty_b[j], ((kb / kStagesB) - 1u) & 1u, abort);
+                const uint32_t stage32 = b32 + j * kStageBBytes;
+                const bool live = n0 + 8u * cg < p.n;
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    // column c of this thread: pairs from the four row pairs
+                    uint4 v;
+                    if ((c & 1) == 0) {
+                        const int q = c >> 1;
+                        v.x = q == 0 ? even[0].x : q == 1 ? even[0].y : q == 2 ? even[0].z : even[0].w;
+                        v.y = q == 0 ? even[1].x : q == 1 ? even[1].y : q == 2 ? even[1].z : even[1].w;
+                        v.z = q == 0 ? even[2].x : q == 1 ? even[2].y : q == 2 ? even[2].z : even[2].w;
+                        v.w = q == 0 ? even[3].x : q == 1 ? even[3].y : q == 2 ? even[3].z : even[3].w;
+                    } else {
+                        const int q = c >> 1;
+                        v.x = q == 0 ? odd[0].x : q == 1 ? odd[0].y : q == 2 ? odd[0].z : odd[0].w;
+                        v.y = q == 0 ? odd[1].x : q == 1 ? odd[1].y : q == 2 ? odd[1].z : odd[1].w;
+                        v.z = q == 0 ? odd[2].x : q == 1 ? odd[2].y : q == 2 ? odd[2].z : odd[2].w;
+                        v.w = q == 0 ? odd[3].x : q == 1 ? odd[3].y : q == 2 ? odd[3].z : odd[3].w;
+                    }
+                    if (!live) v = make_uint4(0u, 0u, 0u, 0u);
+                    const uint32_t nrow = 8u * cg + static_cast<uint32_t>(c);
+                    sts_u4(stage32 + nrow * 128u + ((kg ^ (nrow & 7u)) << 4), v);
+                }
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&bars.full_b[j]);
+                cur = nxt;
+            }
         }
         // epilogue: TMEM -> registers -> global
         mbar_wait(&bars.acc_full, 0u, abort);
@@ -334,7 +421,7 @@ int32_t init_gemm_lut(DeviceContext* ctx) {
 // straddle a scale block, whole bytes per weight row and 16-byte aligned rows.
 bool nf4_gemm_supported(const WeightView& w, const float* x, uint64_t rows, bool backward) {
     if (rows <= 32) return false;
-    if (backward) return false;  // input-backward tiles are not built yet
+    if (backward && (w.out_features % kBK != 0 || (reinterpret_cast<uintptr_t>(w.codes) & 3u) != 0)) return false;
     const uint64_t k = backward ? w.out_features : w.in_features;
     return k % kBK == 0 && w.in_features % 64 == 0 && w.block_size >= 64 &&
            (reinterpret_cast<uintptr_t>(w.codes) & 15u) == 0 && (reinterpret_cast<uintptr_t>(x) & 15u) == 0 &&
@@ -368,7 +455,9 @@ int32_t launch_nf4_gemm(const DeviceContext& ctx, const WeightView& w, const flo
     B2_TRY(make_operand_map(&map, workspace, rows, k));
     static bool configured = false;
     if (!configured) {
-        B2_CUDA_TRY(cudaFuncSetAttribute(nf4_gemm_forward_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        B2_CUDA_TRY(cudaFuncSetAttribute(nf4_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         kSmemBytes));
+        B2_CUDA_TRY(cudaFuncSetAttribute(nf4_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          kSmemBytes));
         configured = true;
     }
@@ -381,7 +470,11 @@ int32_t launch_nf4_gemm(const DeviceContext& ctx, const WeightView& w, const flo
     p.error = ctx.gemm_error;
     p.lut = ctx.gemm_lut;
     const dim3 grid(static_cast<unsigned>((n + kBN - 1) / kBN), static_cast<unsigned>((rows + kBM - 1) / kBM));
-    nf4_gemm_forward_kernel<<<grid, kThreads, kSmemBytes, stream>>>(map, p);
+    if (backward) {
+        nf4_gemm_kernel<true><<<grid, kThreads, kSmemBytes, stream>>>(map, p);
+    } else {
+        nf4_gemm_kernel<false><<<grid, kThreads, kSmemBytes, stream>>>(map, p);
+    }
     B2_CUDA_TRY(cudaGetLastError());
     return B2_STATUS_OK;
 }

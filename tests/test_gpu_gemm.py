@@ -59,3 +59,43 @@ def test_gemm_config3_sampled_rows(b2, port):
     # linearity in the activations
     y2 = forward(b2, b2.PackedNf4Weight.from_host(host), torch.from_numpy(2.0 * x[:64]).cuda())
     assert rel_l2(y2, 2.0 * y[:64]) <= 1e-6
+
+
+def backward(b2, w, dy):
+    rows = dy.shape[0]
+    dx = torch.empty((rows, w.in_features), dtype=torch.float32, device="cuda")
+    b2.dispatch_quantized_linear_input_backward(dy, w, dx, (rows, w.in_features, w.out_features, w.block_size))
+    b2.check_device_errors()
+    return dx.cpu().numpy()
+
+
+@pytest.mark.parametrize("rows,out_f,in_f,block,dq", [
+    (256, 64, 256, 64, False),      # one tile, one k-block
+    (300, 256, 512, 64, True),      # ragged M, ring wraps
+    (100, 1024, 320, 64, True),     # ragged N (320 = 256 + 64), in-blocks past the edge
+    (257, 512, 1024, 256, False),   # block 256: four 64-wide column groups share a scale
+])
+def test_input_backward_tensor_core(b2, port, rows, out_f, in_f, block, dq):
+    rng = np.random.default_rng(rows * 3 + in_f)
+    W = (rng.standard_normal((out_f, in_f)) * 0.02).astype(np.float32)
+    host = port.quantize_nf4_double_quantized(W, block, 32) if dq else port.quantize_nf4(W, block)
+    dy = (rng.standard_normal((rows, out_f)) * 0.01).astype(np.float32)
+    dx = backward(b2, b2.PackedNf4Weight.from_host(host), torch.from_numpy(dy).cuda())
+    want = port.linear_input_backward(host, dy)
+    assert np.isfinite(dx).all()
+    assert rel_l2(dx, want) <= GEMM_TOL
+    for r in (0, rows - 1):
+        assert rel_l2(dx[r], want[r]) <= GEMM_TOL
+
+
+def test_input_backward_config3_sampled_rows(b2, port):
+    # baseline configuration 3, backward: dY [4096, 14336] ~ N(0, 1e-4) -> dX [4096, 4096]
+    rng = np.random.default_rng(4321)
+    W = (rng.standard_normal((14336, 4096)) * 0.02).astype(np.float32)
+    host = port.quantize_nf4_double_quantized(W, 64, 256)
+    dy = (rng.standard_normal((4096, 14336)) * 0.01).astype(np.float32)
+    dx = backward(b2, b2.PackedNf4Weight.from_host(host), torch.from_numpy(dy).cuda())
+    idx = np.r_[0:4, 2047:2051, 4092:4096]
+    want = port.linear_input_backward(host, dy[idx])
+    assert rel_l2(dx[idx], want) <= GEMM_TOL
+    assert np.isfinite(dx).all()
