@@ -242,6 +242,18 @@ int32_t linear_forward_impl(const b2_nf4_weight* weight, const float* x, float* 
             nf4_gemv_stream_plan(*ctx, w, rows, &spw, &ksplit)) {
             return launch_nf4_gemv_stream(*ctx, w, x, y, rows, spw, ksplit, stream);
         }
+        // 17..32 rows: two passes of the streaming kernel over 16 rows each. The second pass finds
+        // the packed weight in L2 (a 7B-class layer is at most ~30 MB), so HBM is still read once.
+        if ((impl == nullptr || strcmp(impl, "tile") != 0) && rows > 16 &&
+            nf4_gemv_stream_plan(*ctx, w, 16, &spw, &ksplit)) {
+            B2_TRY(launch_nf4_gemv_stream(*ctx, w, x, y, 16, spw, ksplit, stream));
+            const uint64_t rest = rows - 16;
+            uint32_t spw2 = 0, ks2 = 0;
+            if (nf4_gemv_stream_plan(*ctx, w, rest, &spw2, &ks2)) {
+                return launch_nf4_gemv_stream(*ctx, w, x + 16 * w.in_features, y + 16 * w.out_features, rest,
+                                              spw2, ks2, stream);
+            }
+        }
         return launch_nf4_gemv(*ctx, w, x, y, rows, stream);
     }
     static const char* gemm_off = getenv("B2_DISABLE_TENSOR_GEMM");
