@@ -238,6 +238,23 @@ int32_t linear_forward_impl(const b2_nf4_weight* weight, const float* x, float* 
         // B2_GEMV_IMPL=tile forces the non-persistent kernel (for A/B measurements).
         static const char* impl = getenv("B2_GEMV_IMPL");
         uint32_t spw = 0, ksplit = 0;
+        // Default: the TMA-fed kernel (rows <= 16; 17..32 as two passes). B2_GEMV_IMPL=stream / tile
+        // select the register-pipelined and the tiled kernels for A/B measurements.
+        if (impl == nullptr || strcmp(impl, "tma") == 0) {
+            uint32_t per = 0;
+            if (nf4_gemv_tma_plan(*ctx, w, x, rows, &ksplit, &per)) {
+                return launch_nf4_gemv_tma(*ctx, w, x, y, rows, ksplit, per, stream);
+            }
+            if (rows > 16 && nf4_gemv_tma_plan(*ctx, w, x, 16, &ksplit, &per)) {
+                B2_TRY(launch_nf4_gemv_tma(*ctx, w, x, y, 16, ksplit, per, stream));
+                uint32_t ks2 = 0, per2 = 0;
+                if (nf4_gemv_tma_plan(*ctx, w, x + 16 * w.in_features, rows - 16, &ks2, &per2)) {
+                    return launch_nf4_gemv_tma(*ctx, w, x + 16 * w.in_features, y + 16 * w.out_features,
+                                               rows - 16, ks2, per2, stream);
+                }
+                return fail(B2_STATUS_RUNTIME_ERROR, "internal: TMA decode plan failed for the second pass");
+            }
+        }
         if ((impl == nullptr || strcmp(impl, "tile") != 0) &&
             nf4_gemv_stream_plan(*ctx, w, rows, &spw, &ksplit)) {
             return launch_nf4_gemv_stream(*ctx, w, x, y, rows, spw, ksplit, stream);

@@ -30,6 +30,12 @@ bool nf4_gemv_stream_plan(const DeviceContext& ctx, const WeightView& w, uint64_
 int32_t launch_nf4_gemv_stream(const DeviceContext& ctx, const WeightView& w, const float* x, float* y,
                                uint64_t rows, uint32_t spw, uint32_t ksplit, cudaStream_t stream);
 
+// nf4_gemv_tma.cu - TMA-fed decode kernel, rows <= 16.
+bool nf4_gemv_tma_plan(const DeviceContext& ctx, const WeightView& w, const float* x, uint64_t rows,
+                       uint32_t* ksplit_out, uint32_t* steps_per_cta_out);
+int32_t launch_nf4_gemv_tma(const DeviceContext& ctx, const WeightView& w, const float* x, float* y,
+                            uint64_t rows, uint32_t ksplit, uint32_t steps_per_cta, cudaStream_t stream);
+
 // nf4_gemm_sm100.cu - tcgen05 prefill GEMM, rows > 32.
 int32_t init_gemm_lut(DeviceContext* ctx);
 bool nf4_gemm_supported(const WeightView& w, const float* x, uint64_t rows, bool backward);

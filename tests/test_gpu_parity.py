@@ -108,8 +108,8 @@ def test_linear_config1_against_reference_rows(b2, port, golden):
     for dq, key in ((False, "c1_forward_rows0_8"), (True, "c1_dq_forward_rows0_8")):
         host = port.quantize_nf4_double_quantized(c["W1"], 64, 256) if dq else port.quantize_nf4(c["W1"], 64)
         w = b2.PackedNf4Weight.from_host(host)
-        y = forward(b2, w, dev(c["X1"]))  # 64 rows: generic kernel
-        assert rel_l2(y[:8], golden[key]) <= 1e-5
+        y = forward(b2, w, dev(c["X1"]))  # 64 rows: tensor-core path (bf16 operands)
+        assert rel_l2(y[:8], golden[key]) <= 1e-2
         y8 = forward(b2, w, dev(c["X1"][:8]))  # 8 rows: decode kernel
         assert rel_l2(y8, golden[key]) <= GEMV_TOL
         if dq:
