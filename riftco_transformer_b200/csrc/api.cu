@@ -554,7 +554,8 @@ int32_t b2_check_device_errors(void) {
     if (word != 0) {
         B2_CUDA_TRY(cudaMemset(ctx->gemm_error, 0, sizeof(word)));
         return fail(B2_STATUS_RUNTIME_ERROR,
-                    "a bounded wait inside the tensor-core NF4 GEMM timed out (flags 0x%x); its output is invalid",
+                    "a device-side check of an earlier NF4 kernel failed (flags 0x%x: 1 GEMM barrier timeout, 2 decode kernel "
+                    "shared-memory layout, 4 decode kernel barrier timeout); that call's output is invalid",
                     word);
     }
     return B2_STATUS_OK;

@@ -34,6 +34,7 @@ constexpr int kWarps = 16;                       // consumer warps
 constexpr int kThreads = (kWarps + 1) * 32;      // + one producer warp
 constexpr int kStepK = 64;
 constexpr int kTileRows = 16;
+constexpr int kRedRow = kTileRows + 4;           // padded row of the [n][row] partial-sum layout
 constexpr int kBoxBytes = kTileRows * 128;       // one TMA box: 16 rows x 128 bytes (4 steps)
 constexpr int kLutBytes = 256 * 256;
 constexpr int kRingBytes = 96 * 1024;
@@ -42,12 +43,12 @@ constexpr int kSmemBytes = 65536 /* bytes below the 64 KB-aligned table */ + kLu
 template <int MT>
 struct Layout {
     static constexpr int NB = 8 * MT;
-    static constexpr int kMaxTiles = MT == 1 ? 48 : 24;
+    static constexpr int kMaxTiles = MT == 1 ? 48 : 16;
     // offsets from the first 16-byte aligned address of the dynamic allocation (below the table)
     static constexpr int kBarOff = 0;                                   // full[12], empty[12], abort
     static constexpr int kFactorOff = 256;                              // 256 floats
     static constexpr int kRedOff = kFactorOff + 1024;                   // [2][16 warps][16 rows][NB]
-    static constexpr int kRedBytes = 2 * kWarps * kTileRows * NB * 4;
+    static constexpr int kRedBytes = 2 * kWarps * (kTileRows + 4) * NB * 4;
     static constexpr int kOutOff = kRedOff + kRedBytes;                 // [tile][16 rows][NB]
     static constexpr int kOutBytes = kMaxTiles * kTileRows * NB * 4;
     static constexpr int kLowBytes = kOutOff + kOutBytes;
@@ -201,24 +202,33 @@ nf4_gemv_tma_kernel(const __grid_constant__ CUtensorMap map_w, const TmaParams p
         const uint32_t tile_stride_rows = n_clusters * kTileRows;
 
         RawScale sraw[2][NSC];
+        // Hoisted weight-view fields and this lane's running scale-block index: rows are block
+        // aligned and tiles are whole (the launcher checks both), so the index of (row, step) is
+        // base + slot * stride.
+        const float* const fp32_ptr = w.fp32_scales;
+        const uint8_t* const code_ptr = w.scale_codes;
+        const float* const second_ptr = w.second_level;
+        const uint32_t sshift = w.scale_block_shift;
+        const uint32_t fbase = static_cast<uint32_t>(w.flat_block_base);
+        const float dq_offset = w.offset;
+        uint32_t blk0[NSC];
+#pragma unroll
+        for (int k = 0; k < NSC; ++k) {
+            blk0[k] = (cluster_id * kTileRows + g + 8u * scale_row_half(k)) * blocks_per_row +
+                      (((step0 + scale_step) * static_cast<uint32_t>(kStepK)) >> w.block_shift);
+        }
+        const uint32_t blk_stride = tile_stride_rows * blocks_per_row;
         auto fetch_scales = [&](int d, uint32_t slot) {
             if (slot < my_tiles && warp_active) {
-                const uint64_t row0 = static_cast<uint64_t>(cluster_id + slot * n_clusters) * kTileRows;
 #pragma unroll
                 for (int k = 0; k < NSC; ++k) {
-                    const uint64_t row = min(row0 + g + 8 * scale_row_half(k), out - 1);
-                    uint64_t block;
-                    if (blocks_per_row != 0) {
-                        block = row * blocks_per_row + (((step0 + scale_step) * static_cast<uint32_t>(kStepK)) >> w.block_shift);
-                    } else {
-                        block = (row * in + static_cast<uint64_t>(step0 + scale_step) * kStepK) >> w.block_shift;
-                    }
+                    const uint32_t block = blk0[k] + slot * blk_stride;
                     if (fp32_scales) {
-                        sraw[d][k].bits = __float_as_uint(__ldg(w.fp32_scales + block));
+                        sraw[d][k].bits = __float_as_uint(__ldg(fp32_ptr + block));
                         sraw[d][k].second = 0.0f;
                     } else {
-                        sraw[d][k].bits = __ldg(w.scale_codes + block);
-                        sraw[d][k].second = __ldg(w.second_level + ((w.flat_block_base + block) >> w.scale_block_shift));
+                        sraw[d][k].bits = __ldg(code_ptr + block);
+                        sraw[d][k].second = __ldg(second_ptr + ((fbase + block) >> sshift));
                     }
                 }
             }
@@ -263,6 +273,12 @@ nf4_gemv_tma_kernel(const __grid_constant__ CUtensorMap map_w, const TmaParams p
             frag_off[u] = g * 128u + (((2u * st + (t >> 1)) ^ g) << 4) + (t & 1u) * 8u;
         }
 
+        // reducing threads (tid < 16 * NB): output element (n = tid / 16, r = tid % 16) of every tile
+        const uint32_t red_n = tid / kTileRows, red_r = tid % kTileRows;
+        float* y_run = p.y + static_cast<uint64_t>(red_n) * out + static_cast<uint64_t>(cluster_id) * kTileRows + red_r;
+        const uint64_t y_stride = static_cast<uint64_t>(tile_stride_rows);
+        const bool red_store = tid < kTileRows * NB && red_n < p.rows;
+
         uint32_t parity = 0;
         for (uint32_t base = 0; base < my_tiles; base += 2) {
 #pragma unroll
@@ -299,7 +315,7 @@ nf4_gemv_tma_kernel(const __grid_constant__ CUtensorMap map_w, const TmaParams p
 #pragma unroll
                         for (int k = 0; k < NSC; ++k) {
                             sc[k] = fp32_scales ? __uint_as_float(sraw[d][k].bits)
-                                                : dq_finish(s_factor[sraw[d][k].bits], sraw[d][k].second, w.offset);
+                                                : dq_finish(s_factor[sraw[d][k].bits], sraw[d][k].second, dq_offset);
                         }
 #pragma unroll
                         for (int u = 0; u < SPW; ++u) {
@@ -339,24 +355,27 @@ nf4_gemv_tma_kernel(const __grid_constant__ CUtensorMap map_w, const TmaParams p
                             }
                         }
                     }
-                    float* red = s_red + (parity * kWarps + warp) * kTileRows * NB;
+                    // partial tile as [n][row] with rows padded to 20 words: conflict-free scalar stores
+                    // here, contiguous reads by the reducing threads below
+                    float* red = s_red + (parity * kWarps + warp) * (NB * kRedRow);
 #pragma unroll
                     for (int m = 0; m < MT; ++m) {
-                        *reinterpret_cast<float2*>(red + g * NB + m * 8 + 2 * t) = make_float2(acc[m][0], acc[m][1]);
-                        *reinterpret_cast<float2*>(red + (g + 8) * NB + m * 8 + 2 * t) = make_float2(acc[m][2], acc[m][3]);
+                        float* q = red + (m * 8 + 2 * t) * kRedRow;
+                        q[g] = acc[m][0];
+                        q[kRedRow + g] = acc[m][1];
+                        q[g + 8] = acc[m][2];
+                        q[kRedRow + g + 8] = acc[m][3];
                     }
                     asm volatile("bar.sync 1, 512;" ::: "memory");
                     if (tid < kTileRows * NB) {
-                        const float* src = s_red + parity * kWarps * kTileRows * NB + tid;
+                        const float* src = s_red + parity * kWarps * (NB * kRedRow) + red_n * kRedRow + red_r;
                         float v = 0.0f;
 #pragma unroll
-                        for (int k = 0; k < kWarps; ++k) v += src[k * kTileRows * NB];
+                        for (int k = 0; k < kWarps; ++k) v += src[k * (NB * kRedRow)];
                         if (ksplit == 1) {
-                            const uint32_t r = tid / NB, n = tid % NB;
-                            const uint64_t row = static_cast<uint64_t>(cluster_id + slot * n_clusters) * kTileRows + r;
-                            if (n < p.rows && row < out) p.y[static_cast<uint64_t>(n) * out + row] = v;
+                            if (red_store) y_run[slot * y_stride] = v;
                         } else {
-                            s_out[slot * kTileRows * NB + tid] = v;
+                            s_out[slot * kTileRows * NB + red_r * NB + red_n] = v;
                         }
                     }
                     parity ^= 1u;
@@ -400,15 +419,48 @@ EncodeTiledFn encode_tiled() {
     return fn;
 }
 
+// Clusters of `ksplit` CTAs of this kernel the device can hold at once (GPC packing), cached.
+template <int MT, int SPW>
+int32_t max_active_clusters(const DeviceContext& ctx, uint32_t ksplit, uint32_t* out) {
+    auto kernel = nf4_gemv_tma_kernel<MT, SPW>;
+    static bool configured = false;
+    static int cached[9] = {0};
+    if (!configured) {
+        B2_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+        configured = true;
+    }
+    if (cached[ksplit] == 0) {
+        cudaLaunchConfig_t config = {};
+        config.blockDim = dim3(kThreads);
+        config.dynamicSmemBytes = kSmemBytes;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = ksplit;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        config.attrs = attr;
+        config.numAttrs = 1;
+        config.gridDim = dim3(static_cast<unsigned>(ctx.sm_count / ksplit) * ksplit);
+        int n = 0;
+        B2_CUDA_TRY(cudaOccupancyMaxActiveClusters(&n, kernel, &config));
+        cached[ksplit] = n > 0 ? n : 1;
+    }
+    uint32_t clusters = static_cast<uint32_t>(cached[ksplit]);
+    const uint32_t by_sm = static_cast<uint32_t>(ctx.sm_count) / ksplit;
+    *out = clusters < by_sm ? clusters : by_sm;
+    return B2_STATUS_OK;
+}
+
 template <int MT, int SPW>
 int32_t launch_tma(const DeviceContext& ctx, const CUtensorMap& map, TmaParams p, uint32_t ksplit,
                    cudaStream_t stream) {
     auto kernel = nf4_gemv_tma_kernel<MT, SPW>;
-    static bool configured = false;
-    static int max_clusters[9] = {0};
-    if (!configured) {
-        B2_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
-        configured = true;
+    uint32_t clusters = 0;
+    B2_TRY((max_active_clusters<MT, SPW>(ctx, ksplit, &clusters)));
+    if (clusters > p.row_tiles) clusters = p.row_tiles;
+    if (clusters == 0) clusters = 1;
+    if ((p.row_tiles + clusters - 1) / clusters > static_cast<uint32_t>(Layout<MT>::kMaxTiles)) {
+        return fail(B2_STATUS_RUNTIME_ERROR, "internal: NF4 TMA decode kernel tile budget exceeded");
     }
     cudaLaunchConfig_t config = {};
     config.blockDim = dim3(kThreads);
@@ -421,20 +473,6 @@ int32_t launch_tma(const DeviceContext& ctx, const CUtensorMap& map, TmaParams p
     attr[0].val.clusterDim.z = 1;
     config.attrs = attr;
     config.numAttrs = 1;
-    if (max_clusters[ksplit] == 0) {
-        config.gridDim = dim3(static_cast<unsigned>(ctx.sm_count / ksplit) * ksplit);
-        int n = 0;
-        B2_CUDA_TRY(cudaOccupancyMaxActiveClusters(&n, kernel, &config));
-        max_clusters[ksplit] = n > 0 ? n : 1;
-    }
-    uint32_t clusters = static_cast<uint32_t>(max_clusters[ksplit]);
-    const uint32_t by_sm = static_cast<uint32_t>(ctx.sm_count) / ksplit;
-    if (clusters > by_sm) clusters = by_sm;
-    if (clusters > p.row_tiles) clusters = p.row_tiles;
-    if (clusters == 0) clusters = 1;
-    if ((p.row_tiles + clusters - 1) / clusters > static_cast<uint32_t>(Layout<MT>::kMaxTiles)) {
-        return fail(B2_STATUS_RUNTIME_ERROR, "internal: NF4 TMA decode kernel tile budget exceeded");
-    }
     config.gridDim = dim3(clusters * ksplit);
     B2_CUDA_TRY(cudaLaunchKernelEx(&config, kernel, map, p));
     return B2_STATUS_OK;
@@ -448,19 +486,27 @@ bool nf4_gemv_tma_plan(const DeviceContext& ctx, const WeightView& w, const floa
     if (rows < 1 || rows > 16 || w.in_features % kStepK != 0 || w.block_size < kStepK) return false;
     if ((reinterpret_cast<uintptr_t>(w.codes) & 15u) != 0 || (reinterpret_cast<uintptr_t>(x) & 15u) != 0) return false;
     if (encode_tiled() == nullptr) return false;
+    if (w.in_features % w.block_size != 0 || w.out_features % kTileRows != 0) return false;
     const uint64_t steps = w.in_features / kStepK;
     const uint64_t row_tiles = (w.out_features + kTileRows - 1) / kTileRows;
     if (steps > 0xFFFFFFull || row_tiles > 0x7FFFFFFull || w.out_features > 0x7FFFFFFFull) return false;
-    if ((w.out_features + 2048) * (w.in_features / w.block_size + 1) > 0xFFFFFFFFull) return false;
+    if ((w.out_features + 2048) * (w.in_features / w.block_size + 1) + w.flat_block_base > 0xFFFFFFFFull) return false;
     const uint64_t cap = rows <= 8 ? 64 : 32;   // steps one CTA covers (16 warps x 4 or 2)
     uint64_t ks = (steps + cap - 1) / cap;
     if (ks > 8) return false;
     uint64_t per = (steps + ks - 1) / ks;
     per = (per + 3) / 4 * 4;
     if (per > cap) return false;
-    const uint64_t clusters = static_cast<uint64_t>(ctx.sm_count) / ks;
+    uint32_t active = 0;
+    const int32_t st = rows <= 8 ? max_active_clusters<1, 4>(ctx, static_cast<uint32_t>(ks), &active)
+                                 : max_active_clusters<2, 2>(ctx, static_cast<uint32_t>(ks), &active);
+    if (st != B2_STATUS_OK) {
+        clear_error();
+        return false;
+    }
+    const uint64_t clusters = active;
     if (clusters == 0) return false;
-    const uint64_t max_tiles = rows <= 8 ? 48 : 24;
+    const uint64_t max_tiles = rows <= 8 ? 48 : 16;
     if ((row_tiles + clusters - 1) / clusters > max_tiles) return false;
     *ksplit_out = static_cast<uint32_t>(ks);
     *steps_per_cta_out = static_cast<uint32_t>(per);
