@@ -431,7 +431,12 @@ def run_b200(args) -> None:
         }
         print(json.dumps(line))
     if world > 1:
-        dist.destroy_process_group()
+        # Tearing the NCCL group down while CUDA graphs that captured its collectives are alive hangs;
+        # every rank has finished its work here, so leave without the teardown.
+        sys.stdout.flush()
+        dist.barrier()
+        torch.cuda.synchronize()
+        os._exit(0)
 
 
 def main() -> None:
