@@ -7,7 +7,7 @@
 // tensor memory (all 512 TMEM columns). The left operand (activations, first
 // converted to bf16 by a streaming pre-pass into caller scratch) arrives by TMA
 // in 128-byte-swizzled K-major tiles; the packed weights are read straight from
-// global memory by eight dequantisation warps, expanded through a per-lane
+// global memory by sixteen dequantisation warps, expanded through a per-lane
 // replicated byte -> bf16x2 table, multiplied by their block scale and written
 // to shared memory in the same swizzled K-major layout, so the weights exist
 // as bf16 only inside the SM. One thread issues tcgen05.mma (M128 N256 K16,
@@ -35,7 +35,7 @@ constexpr int kStagesA = 3, kStagesB = 2;
 constexpr int kStageABytes = kBM * kBK * 2;   // 32 KB
 constexpr int kStageBBytes = kBN * kBK * 2;   // 32 KB
 constexpr int kLutBytes = 256 * 128;          // byte -> bf16x2, one copy per lane (128-byte rows)
-constexpr int kDequantWarps = 8;
+constexpr int kDequantWarps = 16;
 constexpr int kThreads = (2 + kDequantWarps) * 32;
 constexpr int kSmemBytes = kStagesA * kStageABytes + kStagesB * kStageBBytes + kLutBytes + 32768 /* table alignment */;
 constexpr uint32_t kTmemColumns = 512;
@@ -115,17 +115,17 @@ struct ForwardRow {
     uint64_t flat0;         // flat index of the row's first weight
 };
 
-__device__ __forceinline__ void dequant_forward(const GemmParams& p, const ForwardRow& row, uint32_t r,
-                                                uint4 c0, uint4 c1, float scale, uint32_t b_stage32,
-                                                uint32_t lut_lane) {
+// Two threads per weight row: thread (row, hf) expands chunks 4*hf .. 4*hf+3 (32 weights).
+__device__ __forceinline__ void dequant_forward(const ForwardRow& row, uint32_t trow, uint32_t hf, uint4 c0,
+                                                float scale, uint32_t b_stage32, uint32_t lut_lane) {
     const uint32_t s2 = scale_pair(scale);
-    const uint32_t words[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
-    const uint32_t row32 = b_stage32 + r * 128u;
+    const uint32_t words[4] = {c0.x, c0.y, c0.z, c0.w};
+    const uint32_t row32 = b_stage32 + trow * 128u;
 #pragma unroll
-    for (int c = 0; c < 8; ++c) {
+    for (int c = 0; c < 4; ++c) {
         uint4 v = make_uint4(0u, 0u, 0u, 0u);
         if (row.codes != nullptr) v = expand_word(words[c], lut_lane, s2);
-        sts_u4(row32 + ((static_cast<uint32_t>(c) ^ (r & 7u)) << 4), v);
+        sts_u4(row32 + (((4u * hf + static_cast<uint32_t>(c)) ^ (trow & 7u)) << 4), v);
     }
 }
 
@@ -137,27 +137,29 @@ __device__ __forceinline__ void dequant_forward(const GemmParams& p, const Forwa
 // column - already in K order - and stores one 16-byte chunk per column. The 8 lanes that share
 // a column group fill one whole 128-byte row per store instruction (no bank conflicts).
 struct BackwardState {
-    uint32_t words[8];   // packed word of each of the 8 output rows (8 input columns each)
-    float scale;         // scale this thread decodes for the CTA: (o = r % 64, in-block = r / 64)
+    uint32_t words[4];   // packed word of each of this thread's 4 output rows (8 input columns each)
+    float scale;         // scale this thread decodes for the CTA: (o = r % 64, in-block = r / 64), r < 256
 };
 
 __device__ __forceinline__ void backward_fetch(const GemmParams& p, uint32_t kb, uint32_t n0, uint32_t r,
-                                               uint32_t kg, uint32_t cg, BackwardState& st) {
+                                               uint32_t kg, uint32_t hf, uint32_t cg, BackwardState& st) {
     const uint64_t in = p.w.in_features;
     const uint32_t col = n0 + 8u * cg;
-    const uint64_t o_base = static_cast<uint64_t>(kb) * kBK + 8u * kg;
+    const uint64_t o_base = static_cast<uint64_t>(kb) * kBK + 8u * kg + 4u * hf;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
+    for (int i = 0; i < 4; ++i) {
         st.words[i] = 0x77777777u;
         if (col < p.n) {
             st.words[i] = __ldg(reinterpret_cast<const uint32_t*>(p.w.codes + (((o_base + i) * in + col) >> 1)));
         }
     }
-    const uint32_t so = r & 63u, sib = r >> 6;
     st.scale = 0.0f;
-    if (n0 + 64u * sib < p.n) {
-        const uint64_t flat = (static_cast<uint64_t>(kb) * kBK + so) * in + n0 + 64u * sib;
-        st.scale = decode_block_scale(p.w, flat >> p.w.block_shift);
+    if (r < 256u) {
+        const uint32_t so = r & 63u, sib = r >> 6;
+        if (n0 + 64u * sib < p.n) {
+            const uint64_t flat = (static_cast<uint64_t>(kb) * kBK + so) * in + n0 + 64u * sib;
+            st.scale = decode_block_scale(p.w, flat >> p.w.block_shift);
+        }
     }
 }
 
@@ -246,52 +248,53 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const GemmParams p) {
         const uint32_t r = tid - 64u;
         const uint32_t lut_lane = lut32 | (lane * 4u);
         if (!kBackward) {
-            const uint32_t n = n0 + r;
+            const uint32_t trow = r >> 1, hf = r & 1u;
+            const uint32_t n = n0 + trow;
             ForwardRow row;
-            row.codes = n < p.n ? p.w.codes + static_cast<uint64_t>(n) * (p.k >> 1) : nullptr;
+            row.codes = n < p.n ? p.w.codes + static_cast<uint64_t>(n) * (p.k >> 1) + hf * 16u : nullptr;
             row.flat0 = static_cast<uint64_t>(n) * p.k;
-            uint4 c0 = make_uint4(0, 0, 0, 0), c1 = c0;
+            uint4 c0 = make_uint4(0, 0, 0, 0);
             float scale = 0.0f;
             if (row.codes != nullptr) {
                 c0 = ldg_u4(row.codes);
-                c1 = ldg_u4(row.codes + 16);
                 scale = decode_block_scale(p.w, row.flat0 >> p.w.block_shift);
             }
             for (uint32_t kb = 0; kb < num_kb; ++kb) {
                 const uint32_t j = kb % kStagesB;
                 // next k-block's codes and scale while this one is expanded
-                uint4 n0c = make_uint4(0, 0, 0, 0), n1c = n0c;
+                uint4 n0c = make_uint4(0, 0, 0, 0);
                 float nscale = 0.0f;
                 if (row.codes != nullptr && kb + 1 < num_kb) {
                     n0c = ldg_u4(row.codes + (kb + 1) * 32u);
-                    n1c = ldg_u4(row.codes + (kb + 1) * 32u + 16);
                     nscale = decode_block_scale(p.w, (row.flat0 + static_cast<uint64_t>(kb + 1) * kBK) >> p.w.block_shift);
                 }
                 if (kb >= kStagesB) mbar_wait(&bars.empty_b[j], ((kb / kStagesB) - 1u) & 1u, abort);
-                dequant_forward(p, row, r, c0, c1, scale, b32 + j * kStageBBytes, lut_lane);
+                dequant_forward(row, trow, hf, c0, scale, b32 + j * kStageBBytes, lut_lane);
                 fence_proxy_async_smem();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&bars.full_b[j]);
                 c0 = n0c;
-                c1 = n1c;
                 scale = nscale;
             }
         } else {
-            const uint32_t kg = lane & 7u, cg = 4u * (warp - 2u) + (lane >> 3);
+            // lane (kg = lane % 8, cgl = lane / 8) of dequant warp e: column group 4*(e % 8) + cgl,
+            // output rows 8*kg + 4*(e / 8) .. +4 of the k-block
+            const uint32_t e = warp - 2u;
+            const uint32_t kg = lane & 7u, hf = e >> 3, cg = 4u * (e & 7u) + (lane >> 3);
             const uint32_t my_ib = cg >> 3;   // in-block (64 columns) of this thread's 8 columns
             BackwardState cur, nxt;
-            backward_fetch(p, 0, n0, r, kg, cg, cur);
+            backward_fetch(p, 0, n0, r, kg, hf, cg, cur);
             for (uint32_t kb = 0; kb < num_kb; ++kb) {
                 const uint32_t j = kb % kStagesB, par = kb & 1u;
-                if (kb + 1 < num_kb) backward_fetch(p, kb + 1, n0, r, kg, cg, nxt);
-                // publish this k-block's 256 decoded scales, then every thread reads its 8 (4 pairs)
-                s_scales[par][r >> 6][r & 63u] = __float2bfloat16_rn(cur.scale);
-                asm volatile("bar.sync 1, 256;" ::: "memory");
-                const uint4 sc = *reinterpret_cast<const uint4*>(&s_scales[par][my_ib][8u * kg]);
-                const uint32_t sc2[4] = {sc.x, sc.y, sc.z, sc.w};
-                uint4 even[4], odd[4];   // [row pair] -> columns (0,2,4,6) / (1,3,5,7), each a (o, o+1) pair
+                if (kb + 1 < num_kb) backward_fetch(p, kb + 1, n0, r, kg, hf, cg, nxt);
+                // publish this k-block's 256 decoded scales, then every thread reads its 4 (2 pairs)
+                if (r < 256u) s_scales[par][r >> 6][r & 63u] = __float2bfloat16_rn(cur.scale);
+                asm volatile("bar.sync 1, 512;" ::: "memory");
+                const uint2 sc = *reinterpret_cast<const uint2*>(&s_scales[par][my_ib][8u * kg + 4u * hf]);
+                const uint32_t sc2[2] = {sc.x, sc.y};
+                uint4 even[2], odd[2];   // [row pair] -> columns (0,2,4,6) / (1,3,5,7), each an (o, o+1) pair
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
+                for (int i = 0; i < 2; ++i) {
                     const uint32_t wa = cur.words[2 * i], wb = cur.words[2 * i + 1];
                     const uint32_t idx_e = (wa & 0x0F0F0F0Fu) | ((wb << 4) & 0xF0F0F0F0u);
                     const uint32_t idx_o = ((wa >> 4) & 0x0F0F0F0Fu) | (wb & 0xF0F0F0F0u);
@@ -303,24 +306,16 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const GemmParams p) {
                 const bool live = n0 + 8u * cg < p.n;
 #pragma unroll
                 for (int c = 0; c < 8; ++c) {
-                    // column c of this thread: pairs from the four row pairs
-                    uint4 v;
-                    if ((c & 1) == 0) {
-                        const int q = c >> 1;
-                        v.x = q == 0 ? even[0].x : q == 1 ? even[0].y : q == 2 ? even[0].z : even[0].w;
-                        v.y = q == 0 ? even[1].x : q == 1 ? even[1].y : q == 2 ? even[1].z : even[1].w;
-                        v.z = q == 0 ? even[2].x : q == 1 ? even[2].y : q == 2 ? even[2].z : even[2].w;
-                        v.w = q == 0 ? even[3].x : q == 1 ? even[3].y : q == 2 ? even[3].z : even[3].w;
-                    } else {
-                        const int q = c >> 1;
-                        v.x = q == 0 ? odd[0].x : q == 1 ? odd[0].y : q == 2 ? odd[0].z : odd[0].w;
-                        v.y = q == 0 ? odd[1].x : q == 1 ? odd[1].y : q == 2 ? odd[1].z : odd[1].w;
-                        v.z = q == 0 ? odd[2].x : q == 1 ? odd[2].y : q == 2 ? odd[2].z : odd[2].w;
-                        v.w = q == 0 ? odd[3].x : q == 1 ? odd[3].y : q == 2 ? odd[3].z : odd[3].w;
-                    }
-                    if (!live) v = make_uint4(0u, 0u, 0u, 0u);
+                    const int q = c >> 1;
+                    const uint4& s0 = (c & 1) ? odd[0] : even[0];
+                    const uint4& s1 = (c & 1) ? odd[1] : even[1];
+                    uint32_t vx = q == 0 ? s0.x : q == 1 ? s0.y : q == 2 ? s0.z : s0.w;
+                    uint32_t vy = q == 0 ? s1.x : q == 1 ? s1.y : q == 2 ? s1.z : s1.w;
+                    if (!live) vx = vy = 0u;
                     const uint32_t nrow = 8u * cg + static_cast<uint32_t>(c);
-                    sts_u4(stage32 + nrow * 128u + ((kg ^ (nrow & 7u)) << 4), v);
+                    asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(stage32 + nrow * 128u + ((kg ^ (nrow & 7u)) << 4) + hf * 8u),
+                                 "r"(vx), "r"(vy)
+                                 : "memory");
                 }
                 fence_proxy_async_smem();
                 __syncwarp();
@@ -331,9 +326,9 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const GemmParams p) {
         // epilogue: TMEM -> registers -> global
         mbar_wait(&bars.acc_full, 0u, abort);
         tcgen05_fence_after_sync();
-        const uint32_t quarter = warp & 3u, half = (warp - 2u) >> 2;
+        const uint32_t quarter = warp & 3u, half = ((warp - 2u) >> 2) & 1u, col_half = (warp - 2u) >> 3;
         const uint32_t row_out = m0 + half * 128u + quarter * 32u + lane;
-        for (uint32_t c = 0; c < kBN / 32; ++c) {
+        for (uint32_t c = col_half * (kBN / 64); c < (col_half + 1u) * (kBN / 64); ++c) {
             uint32_t v[32];
             tmem_ld_32x32(tmem_base + ((quarter * 32u) << 16) + half * 256u + c * 32u, v);
             tmem_ld_wait();
