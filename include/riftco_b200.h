@@ -164,6 +164,7 @@ B2_API size_t b2_nf4_linear_workspace_bytes(const b2_nf4_weight* weight, uint64_
  * dereferenced and sets bit 4 of the status word.
  */
 #define B2_ATTN_STATUS_BAD_BLOCK 4u
+#define B2_ATTN_STATUS_TIMEOUT 8u          /* a bounded wait for a page copy gave up */
 B2_API int32_t b2_paged_decode_attention(const float* q, const float* k_pages,
                                   const float* v_pages, const uint32_t* block_tables,
                                   const uint32_t* seq_lens, float* ctx,

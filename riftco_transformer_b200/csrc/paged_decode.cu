@@ -19,8 +19,11 @@
 // block id outside the pool (which is then not dereferenced).
 #include "b2_common.cuh"
 #include "b2_kernels.h"
+#include "sm100_ptx.cuh"
 
 #include <cmath>
+#include <cstdlib>
+#include <cstring>
 #include <mutex>
 
 namespace b2 {
@@ -225,6 +228,242 @@ paged_decode_fast_kernel(const PagedDecodeArgs a, float* __restrict__ partials, 
     }
 }
 
+// Same arithmetic as paged_decode_fast_kernel, but the K and V chunks of a page (8 KB each,
+// contiguous in the pool) are brought into shared memory by cp.async.bulk: every warp owns a ring
+// of three 8 KB slots and keeps the next K, V and K chunks in flight while it works on one, so
+// 24 KB per warp (up to 192 KB per SM) are outstanding without holding them in registers.
+// The mbarrier waits are bounded; a timeout sets bit 3 of the status word.
+constexpr int kBulkSlots = 3;
+constexpr int kChunkBytes = kPage * kD * 4;   // 8 KB: one (page, kv head) of K or of V
+constexpr int kBulkSmemBytes = kFastWarps * kBulkSlots * kChunkBytes;
+
+__device__ __forceinline__ void bulk_load(uint32_t dst32, const void* src, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst32), "l"(src), "r"(bytes), "r"(sm100::smem_u32(bar))
+                 : "memory");
+}
+__device__ __forceinline__ float4 lds_f4(uint32_t a) {
+    float4 v;
+    asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(a));
+    return v;
+}
+
+template <int REP>
+__global__ void __launch_bounds__(kFastWarps * 32)
+paged_decode_bulk_kernel(const PagedDecodeArgs a, float* __restrict__ partials, uint32_t max_splits) {
+    using namespace sm100;
+    const uint32_t split = blockIdx.x, kvh = blockIdx.y, seq = blockIdx.z;
+    const uint32_t len = __ldg(a.seq_lens + seq);
+    const uint32_t n_splits = (len + kTokensPerCta - 1) / kTokensPerCta;
+    if (split >= n_splits) return;
+
+    extern __shared__ __align__(1024) uint8_t ring_raw[];
+    __shared__ __align__(8) uint64_t bars[kFastWarps][kBulkSlots];
+    __shared__ uint32_t s_abort;
+    __shared__ __align__(16) float s_p[kFastWarps][kPage][REP];
+    __shared__ float s_m[kFastWarps][REP], s_l[kFastWarps][REP];
+
+    const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
+    const uint32_t grp = lane >> 3, sub = lane & 7u;
+    const float scale = 1.0f / sqrtf(static_cast<float>(kD));
+    const uint32_t ring32 = smem_u32(ring_raw) + warp * (kBulkSlots * kChunkBytes);
+    volatile uint32_t* abort = &s_abort;
+
+    if (threadIdx.x == 0) s_abort = 0;
+    if (lane == 0) {
+        for (int i = 0; i < kBulkSlots; ++i) mbar_init(&bars[warp][i], 1);
+        mbar_fence_init();
+    }
+    __syncthreads();
+
+    float4 q[REP][4];
+    const float* qbase = a.q + (static_cast<uint64_t>(seq) * a.q_heads + kvh * REP) * kD;
+#pragma unroll
+    for (int h = 0; h < REP; ++h)
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+            q[h][j] = __ldg(reinterpret_cast<const float4*>(qbase + h * kD + 4 * sub + 32 * j));
+
+    float m[REP], l[REP];
+    float4 acc[REP];
+#pragma unroll
+    for (int h = 0; h < REP; ++h) {
+        m[h] = -INFINITY;
+        l[h] = 0.0f;
+        acc[h] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    uint32_t flags = 0;
+
+    const uint32_t tok_begin = split * kTokensPerCta;
+    const uint32_t tok_end = min(tok_begin + kTokensPerCta, len);
+    const uint32_t page_begin = tok_begin / kPage;
+    const uint32_t page_end = (tok_end + kPage - 1) / kPage;
+    const uint32_t* table = a.block_tables + static_cast<uint64_t>(seq) * a.max_blocks;
+    const uint64_t page_stride = static_cast<uint64_t>(a.kv_heads) * kPage * kD;
+    // pages of this warp: page_begin + warp, + kFastWarps, ...
+    const uint32_t first = page_begin + warp;
+    const uint32_t my_pages = first < page_end ? (page_end - first + kFastWarps - 1) / kFastWarps : 0u;
+    const uint32_t units = 2u * my_pages;   // unit 2i = K of page i, 2i + 1 = V of page i
+
+    auto issue_unit = [&](uint32_t u) {   // lane 0 only
+        const uint32_t pg = first + (u >> 1) * kFastWarps;
+        uint64_t phys = __ldg(table + pg);
+        if (phys >= a.physical_blocks) phys = 0;   // flagged where the page is consumed
+        const float* src = ((u & 1u) ? a.v_pages : a.k_pages) + phys * page_stride +
+                           static_cast<uint64_t>(kvh) * kPage * kD;
+        const uint32_t slot = u % kBulkSlots;
+        fence_proxy_async_smem();
+        mbar_expect_tx(&bars[warp][slot], kChunkBytes);
+        bulk_load(ring32 + slot * kChunkBytes, src, kChunkBytes, &bars[warp][slot]);
+    };
+    if (lane == 0) {
+        for (uint32_t u = 0; u < kBulkSlots && u < units; ++u) issue_unit(u);
+    }
+
+    for (uint32_t i = 0; i < my_pages; ++i) {
+        const uint32_t pg = first + i * kFastWarps;
+        if (__ldg(table + pg) >= a.physical_blocks) flags |= B2_ATTN_STATUS_BAD_BLOCK;
+        const uint32_t valid = min(static_cast<uint32_t>(kPage), len - pg * kPage);
+        const uint32_t uk = 2u * i, uv = uk + 1u;
+
+        // ---- scores from the K slot ----
+        mbar_wait(&bars[warp][uk % kBulkSlots], (uk / kBulkSlots) & 1u, abort);
+        const uint32_t k32 = ring32 + (uk % kBulkSlots) * kChunkBytes;
+        float sc[4][REP];
+#pragma unroll
+        for (int ps = 0; ps < 4; ++ps) {
+            float4 kreg[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) kreg[j] = lds_f4(k32 + ((4 * ps + grp) * kD + 4 * sub + 32 * j) * 4u);
+#pragma unroll
+            for (int h = 0; h < REP; ++h) {
+                float d = 0.0f;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    d = fmaf(q[h][j].x, kreg[j].x, d);
+                    d = fmaf(q[h][j].y, kreg[j].y, d);
+                    d = fmaf(q[h][j].z, kreg[j].z, d);
+                    d = fmaf(q[h][j].w, kreg[j].w, d);
+                }
+                d += __shfl_xor_sync(0xFFFFFFFFu, d, 1);
+                d += __shfl_xor_sync(0xFFFFFFFFu, d, 2);
+                d += __shfl_xor_sync(0xFFFFFFFFu, d, 4);
+                d *= scale;
+                const bool in_range = static_cast<uint32_t>(4 * ps + grp) < valid;
+                if (in_range && (isnan(d) || d == INFINITY)) flags |= B2_ATTN_STATUS_NAN_OR_POS_INF;
+                sc[ps][h] = in_range ? d : -INFINITY;
+            }
+        }
+        __syncwarp();   // every lane has read the K slot: refill it with the unit three ahead
+        if (lane == 0 && uk + kBulkSlots < units) issue_unit(uk + kBulkSlots);
+
+        // ---- online softmax update (all lanes keep identical m, l) ----
+        float rescale[REP];
+#pragma unroll
+        for (int h = 0; h < REP; ++h) {
+            float pm = fmaxf(fmaxf(sc[0][h], sc[1][h]), fmaxf(sc[2][h], sc[3][h]));
+            pm = fmaxf(pm, __shfl_xor_sync(0xFFFFFFFFu, pm, 8));
+            pm = fmaxf(pm, __shfl_xor_sync(0xFFFFFFFFu, pm, 16));
+            const float m_new = fmaxf(m[h], pm);
+            const bool dead = (m_new == -INFINITY) || isnan(m_new);
+            rescale[h] = dead ? 1.0f : __expf(m[h] - m_new);
+            float ps_sum = 0.0f;
+#pragma unroll
+            for (int ps = 0; ps < 4; ++ps) {
+                const float e = dead ? 0.0f : __expf(sc[ps][h] - m_new);
+                sc[ps][h] = e;
+                ps_sum += e;
+            }
+            ps_sum += __shfl_xor_sync(0xFFFFFFFFu, ps_sum, 8);
+            ps_sum += __shfl_xor_sync(0xFFFFFFFFu, ps_sum, 16);
+            l[h] = l[h] * rescale[h] + ps_sum;
+            m[h] = dead ? m[h] : m_new;
+        }
+        __syncwarp();
+        if (sub < REP) {
+#pragma unroll
+            for (int ps = 0; ps < 4; ++ps) {
+                float v = sc[ps][0];
+#pragma unroll
+                for (int h = 1; h < REP; ++h) v = (sub == static_cast<uint32_t>(h)) ? sc[ps][h] : v;
+                s_p[warp][4 * ps + grp][sub] = v;
+            }
+        }
+        __syncwarp();
+
+        // ---- values from the V slot: lane owns dims 4*lane .. 4*lane+3 for every head ----
+#pragma unroll
+        for (int h = 0; h < REP; ++h) {
+            acc[h].x *= rescale[h];
+            acc[h].y *= rescale[h];
+            acc[h].z *= rescale[h];
+            acc[h].w *= rescale[h];
+        }
+        mbar_wait(&bars[warp][uv % kBulkSlots], (uv / kBulkSlots) & 1u, abort);
+        const uint32_t v32 = ring32 + (uv % kBulkSlots) * kChunkBytes;
+#pragma unroll 4
+        for (uint32_t tk = 0; tk < valid; ++tk) {
+            const float4 v = lds_f4(v32 + (tk * kD + 4 * lane) * 4u);
+#pragma unroll
+            for (int h = 0; h < REP; ++h) {
+                const float pr = s_p[warp][tk][h];
+                acc[h].x = fmaf(pr, v.x, acc[h].x);
+                acc[h].y = fmaf(pr, v.y, acc[h].y);
+                acc[h].z = fmaf(pr, v.z, acc[h].z);
+                acc[h].w = fmaf(pr, v.w, acc[h].w);
+            }
+        }
+        __syncwarp();
+        if (lane == 0 && uv + kBulkSlots < units) issue_unit(uv + kBulkSlots);
+    }
+
+    // ---- combine the warps of the CTA (the ring is free now: reuse it for the accumulators) ----
+    if (lane == 0 && *abort != 0) flags |= 8u;
+    if (flags != 0 && a.status != nullptr) atomicOr(a.status, flags);
+    __syncthreads();
+    float* s_acc = reinterpret_cast<float*>(ring_raw);   // [warp][REP][kD]
+#pragma unroll
+    for (int h = 0; h < REP; ++h) {
+        if (lane == 0) {
+            s_m[warp][h] = m[h];
+            s_l[warp][h] = l[h];
+        }
+        *reinterpret_cast<float4*>(&s_acc[(warp * REP + h) * kD + 4 * lane]) = acc[h];
+    }
+    __syncthreads();
+
+    const uint32_t c = threadIdx.x;
+#pragma unroll
+    for (int h = 0; h < REP; ++h) {
+        float mm = -INFINITY;
+#pragma unroll
+        for (int wv = 0; wv < kFastWarps; ++wv) mm = fmaxf(mm, s_m[wv][h]);
+        float ll = 0.0f, o = 0.0f;
+#pragma unroll
+        for (int wv = 0; wv < kFastWarps; ++wv) {
+            const float f = (s_m[wv][h] == -INFINITY) ? 0.0f : __expf(s_m[wv][h] - mm);
+            ll = fmaf(s_l[wv][h], f, ll);
+            o = fmaf(s_acc[(wv * REP + h) * kD + c], f, o);
+        }
+        const uint64_t head = static_cast<uint64_t>(seq) * a.q_heads + kvh * REP + h;
+        if (n_splits == 1) {
+            if (mm == -INFINITY) {
+                if (c == 0 && a.status != nullptr) atomicOr(a.status, B2_ATTN_STATUS_ALL_NEG_INF);
+                a.ctx[head * kD + c] = 0.0f;
+            } else {
+                a.ctx[head * kD + c] = o / ll;
+            }
+        } else {
+            float* dst = partials + (head * max_splits + split) * kPartialStride;
+            if (c == 0) {
+                dst[0] = mm;
+                dst[1] = ll;
+            }
+            dst[2 + c] = o;
+        }
+    }
+}
+
 // Combines the split partials of every (sequence, query head) that was split.
 __global__ void __launch_bounds__(kD)
 paged_decode_merge_kernel(const PagedDecodeArgs a, const float* __restrict__ partials,
@@ -362,11 +601,30 @@ int32_t launch_paged_decode(const DeviceContext&, const PagedDecodeArgs& a, void
         if (splits > 65535) return fail(B2_STATUS_OVERFLOW, "paged decode sequence too long");
         const dim3 grid(splits, a.kv_heads, a.n_seq);
         float* partials = static_cast<float*>(workspace);
-        switch (a.q_heads / a.kv_heads) {
-        case 1: paged_decode_fast_kernel<1><<<grid, kFastWarps * 32, 0, stream>>>(a, partials, splits); break;
-        case 2: paged_decode_fast_kernel<2><<<grid, kFastWarps * 32, 0, stream>>>(a, partials, splits); break;
-        case 4: paged_decode_fast_kernel<4><<<grid, kFastWarps * 32, 0, stream>>>(a, partials, splits); break;
-        default: paged_decode_fast_kernel<8><<<grid, kFastWarps * 32, 0, stream>>>(a, partials, splits); break;
+        static const char* impl = getenv("B2_ATTN_IMPL");   // "ldg" selects the register-load kernel
+        const bool bulk = impl == nullptr || strcmp(impl, "ldg") != 0;
+        if (bulk) {
+            static bool configured = false;
+            if (!configured) {
+                B2_CUDA_TRY(cudaFuncSetAttribute(paged_decode_bulk_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBulkSmemBytes));
+                B2_CUDA_TRY(cudaFuncSetAttribute(paged_decode_bulk_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBulkSmemBytes));
+                B2_CUDA_TRY(cudaFuncSetAttribute(paged_decode_bulk_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBulkSmemBytes));
+                B2_CUDA_TRY(cudaFuncSetAttribute(paged_decode_bulk_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBulkSmemBytes));
+                configured = true;
+            }
+            switch (a.q_heads / a.kv_heads) {
+            case 1: paged_decode_bulk_kernel<1><<<grid, kFastWarps * 32, kBulkSmemBytes, stream>>>(a, partials, splits); break;
+            case 2: paged_decode_bulk_kernel<2><<<grid, kFastWarps * 32, kBulkSmemBytes, stream>>>(a, partials, splits); break;
+            case 4: paged_decode_bulk_kernel<4><<<grid, kFastWarps * 32, kBulkSmemBytes, stream>>>(a, partials, splits); break;
+            default: paged_decode_bulk_kernel<8><<<grid, kFastWarps * 32, kBulkSmemBytes, stream>>>(a, partials, splits); break;
+            }
+        } else {
+            switch (a.q_heads / a.kv_heads) {
+            case 1: paged_decode_fast_kernel<1><<<grid, kFastWarps * 32, 0, stream>>>(a, partials, splits); break;
+            case 2: paged_decode_fast_kernel<2><<<grid, kFastWarps * 32, 0, stream>>>(a, partials, splits); break;
+            case 4: paged_decode_fast_kernel<4><<<grid, kFastWarps * 32, 0, stream>>>(a, partials, splits); break;
+            default: paged_decode_fast_kernel<8><<<grid, kFastWarps * 32, 0, stream>>>(a, partials, splits); break;
+            }
         }
         B2_CUDA_TRY(cudaGetLastError());
         if (splits > 1) {
