@@ -63,9 +63,11 @@ __device__ __forceinline__ uint32_t bf16x2_mul(uint32_t a, uint32_t b) {
     return *reinterpret_cast<uint32_t*>(&r);
 }
 
+// Table read (the table is constant after the kernel's first barrier): not volatile, so the
+// lookups of later chunks can be scheduled ahead of the stores of earlier ones.
 __device__ __forceinline__ uint32_t lds_u32(uint32_t shared_addr) {
     uint32_t v;
-    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(shared_addr));
+    asm("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(shared_addr));
     return v;
 }
 __device__ __forceinline__ void sts_u4(uint32_t shared_addr, uint4 v) {

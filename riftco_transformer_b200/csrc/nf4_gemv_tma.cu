@@ -1,4 +1,4 @@
-// Decode kernel for the packed-NF4 linear, batch rows <= 16, fed by TMA:
+// Decode kernel for the packed-NF4 linear, batch rows <= 32, fed by TMA:
 // y[r,o] = sum_i x[r,i] * W[o,i].
 //
 // Same arithmetic as nf4_gemv_stream.cu (W as the 16-row A operand of
@@ -31,27 +31,37 @@ namespace {
 using namespace sm100;
 
 constexpr int kWarps = 16;                       // consumer warps
-constexpr int kThreads = (kWarps + 1) * 32;      // + one producer warp
+constexpr int kThreadsProducerWarp = (kWarps + 1) * 32;   // consumer warps + one producer warp
 constexpr int kStepK = 64;
 constexpr int kTileRows = 16;
 constexpr int kRedRow = kTileRows + 4;           // padded row of the [n][row] partial-sum layout
 constexpr int kBoxBytes = kTileRows * 128;       // one TMA box: 16 rows x 128 bytes (4 steps)
 constexpr int kLutBytes = 256 * 256;
-constexpr int kRingBytes = 96 * 1024;
-constexpr int kSmemBytes = 65536 /* bytes below the 64 KB-aligned table */ + kLutBytes + kRingBytes;
 
 template <int MT>
 struct Layout {
     static constexpr int NB = 8 * MT;
     static constexpr int kMaxTiles = MT == 1 ? 48 : 16;
+    // 32 batch rows: one partial-sum buffer (two barriers per tile), a 64 KB ring, and the
+    // split-K output tiles behind the ring instead of below the table.
+    // With 17 warps a scheduler partition holds 5 of them and the register file caps a thread at
+    // 96 registers; the 32-row variant needs more, so it runs 16 warps (128 registers) and
+    // thread 0 refills a stage itself once the CTA barrier shows every warp has read it.
+    static constexpr bool kInlineProducer = MT == 4;
+    static constexpr int kThreads = kInlineProducer ? kWarps * 32 : kThreadsProducerWarp;
+    static constexpr int kRedParities = MT == 4 ? 1 : 2;
+    static constexpr bool kOutBehindRing = MT == 4;
+    static constexpr int kRingBytes = MT == 4 ? 64 * 1024 : 96 * 1024;
     // offsets from the first 16-byte aligned address of the dynamic allocation (below the table)
     static constexpr int kBarOff = 0;                                   // full[12], empty[12], abort
     static constexpr int kFactorOff = 256;                              // 256 floats
-    static constexpr int kRedOff = kFactorOff + 1024;                   // [2][16 warps][16 rows][NB]
-    static constexpr int kRedBytes = 2 * kWarps * (kTileRows + 4) * NB * 4;
-    static constexpr int kOutOff = kRedOff + kRedBytes;                 // [tile][16 rows][NB]
-    static constexpr int kOutBytes = kMaxTiles * kTileRows * NB * 4;
-    static constexpr int kLowBytes = kOutOff + kOutBytes;
+    static constexpr int kRedOff = kFactorOff + 1024;                   // [parity][16 warps][NB][20]
+    static constexpr int kRedBytes = kRedParities * kWarps * (kTileRows + 4) * NB * 4;
+    static constexpr int kOutBytes = kMaxTiles * kTileRows * NB * 4;    // [tile][16 rows][NB]
+    static constexpr int kOutOff = kRedOff + kRedBytes;                 // when it lives below the table
+    static constexpr int kLowBytes = kOutOff + (kOutBehindRing ? 0 : kOutBytes);
+    static constexpr int kSmemBytes = 65536 /* bytes below the 64 KB-aligned table */ + kLutBytes + kRingBytes +
+                                      (kOutBehindRing ? kOutBytes : 0);
 };
 
 struct TmaParams {
@@ -69,7 +79,7 @@ struct TmaParams {
 
 __device__ __forceinline__ void mma_f16_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
                                               uint32_t a3, uint32_t b0, uint32_t b1) {
-    asm volatile(
+    asm(
         "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
         "{%8,%9}, {%0,%1,%2,%3};\n"
         : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
@@ -77,15 +87,17 @@ __device__ __forceinline__ void mma_f16_16816(float (&d)[4], uint32_t a0, uint32
 }
 __device__ __forceinline__ void mma_f16_16816_zero(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
                                                    uint32_t a3, uint32_t b0, uint32_t b1) {
-    asm volatile(
+    asm(
         "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
         "{%8,%9}, {%10,%10,%10,%10};\n"
         : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.0f));
 }
+// Table read: the table is constant once the kernel's first barrier has passed, so this load is
+// not volatile and the compiler may hoist a whole step's lookups ahead of the MMAs.
 __device__ __forceinline__ uint32_t lds_u32(uint32_t a) {
     uint32_t v;
-    asm volatile("ld.shared.u32 %0, [%1];\n" : "=r"(v) : "r"(a));
+    asm("ld.shared.u32 %0, [%1];\n" : "=r"(v) : "r"(a));
     return v;
 }
 __device__ __forceinline__ uint2 lds_u2(uint32_t a) {
@@ -103,15 +115,16 @@ struct RawScale {
 };
 
 template <int MT, int SPW>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(Layout<MT>::kThreads, 1)
 nf4_gemv_tma_kernel(const __grid_constant__ CUtensorMap map_w, const TmaParams p) {
     using L = Layout<MT>;
     constexpr int NB = L::NB;
+    constexpr uint32_t kThreads = L::kThreads;
     constexpr int NSC = (2 * SPW) / 4;                       // scales decoded per lane per tile
     constexpr int kWarpsPerBox = 4 / SPW;                    // SPW 4: one warp per box, SPW 2: two
     constexpr uint32_t kMaxBoxes = kWarps / kWarpsPerBox;    // boxes per stage at most
     constexpr uint32_t kStageBytes = kMaxBoxes * kBoxBytes;  // 32 KB or 16 KB
-    constexpr uint32_t NS = kRingBytes / kStageBytes;        // 3 or 6 stages
+    constexpr uint32_t NS = L::kRingBytes / kStageBytes;     // 3, 6 or 4 stages
 
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     const uint32_t raw32 = smem_u32(smem_raw);
@@ -124,7 +137,8 @@ nf4_gemv_tma_kernel(const __grid_constant__ CUtensorMap map_w, const TmaParams p
     volatile uint32_t* abort = reinterpret_cast<volatile uint32_t*>(low + L::kBarOff + 200);
     const float* s_factor = reinterpret_cast<const float*>(low + L::kFactorOff);
     float* s_red = reinterpret_cast<float*>(low + L::kRedOff);
-    float* s_out = reinterpret_cast<float*>(low + L::kOutOff);
+    float* s_out = L::kOutBehindRing ? reinterpret_cast<float*>(smem_raw + (ring32 - raw32) + L::kRingBytes)
+                                     : reinterpret_cast<float*>(low + L::kOutOff);
 
     cg::cluster_group cluster = cg::this_cluster();
     const uint32_t ksplit = cluster.num_blocks();
@@ -171,22 +185,30 @@ nf4_gemv_tma_kernel(const __grid_constant__ CUtensorMap map_w, const TmaParams p
     asm volatile("cp.async.wait_group 0;\n" ::);
     __syncthreads();
 
-    if (warp == kWarps) {
-        // ---- producer: one thread streams this CTA's boxes of every tile ----
+    // Streams the boxes of tile `slot` of this CTA into its ring stage (one thread).
+    auto issue_tile = [&](uint32_t slot) {
+        const uint32_t s = slot % NS;
+        mbar_expect_tx(&full[s], n_boxes * kBoxBytes);
+        const int x0 = static_cast<int>(slice_begin * 32u);
+        const int y = static_cast<int>((cluster_id + slot * n_clusters) * kTileRows);
+        for (uint32_t b = 0; b < n_boxes; ++b) {
+            tma_load_2d(smem_raw + (ring32 - raw32) + s * kStageBytes + b * kBoxBytes, &map_w,
+                        x0 + static_cast<int>(b * 128u), y, &full[s]);
+        }
+    };
+
+    if (!L::kInlineProducer && warp == kWarps) {
+        // ---- producer warp: one thread streams this CTA's boxes of every tile ----
         if (lane == 0) {
-            const int x0 = static_cast<int>(slice_begin * 32u);
             for (uint32_t slot = 0; slot < my_tiles; ++slot) {
-                const uint32_t s = slot % NS;
-                if (slot >= NS) mbar_wait(&empty[s], ((slot / NS) - 1u) & 1u, abort);
-                mbar_expect_tx(&full[s], n_boxes * kBoxBytes);
-                const int y = static_cast<int>((cluster_id + slot * n_clusters) * kTileRows);
-                for (uint32_t b = 0; b < n_boxes; ++b) {
-                    tma_load_2d(smem_raw + (ring32 - raw32) + s * kStageBytes + b * kBoxBytes, &map_w,
-                                x0 + static_cast<int>(b * 128u), y, &full[s]);
-                }
+                if (slot >= NS) mbar_wait(&empty[slot % NS], ((slot / NS) - 1u) & 1u, abort);
+                issue_tile(slot);
             }
         }
     } else {
+        if (L::kInlineProducer && tid == 0) {
+            for (uint32_t slot = 0; slot < my_tiles && slot < NS; ++slot) issue_tile(slot);
+        }
         // ---- consumers ----
         const uint32_t box = warp / kWarpsPerBox;
         const uint32_t sub0 = (warp % kWarpsPerBox) * SPW;           // first step of this warp inside its box
@@ -305,7 +327,7 @@ nf4_gemv_tma_kernel(const __grid_constant__ CUtensorMap map_w, const TmaParams p
                     __syncwarp();
                     // Release the stage once this warp's fragment reads have RETURNED: the arrive
                     // takes the last loaded register as a (dummy) operand, so it cannot issue earlier.
-                    if (lane == 0) {
+                    if (!L::kInlineProducer && lane == 0) {
                         const uint32_t dep = warp_active ? wb[SPW - 1].y : 0u;
                         asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0]; // %1" ::"r"(smem_u32(&empty[s])), "r"(dep)
                                      : "memory");
@@ -357,6 +379,12 @@ nf4_gemv_tma_kernel(const __grid_constant__ CUtensorMap map_w, const TmaParams p
                     }
                     // partial tile as [n][row] with rows padded to 20 words: conflict-free scalar stores
                     // here, contiguous reads by the reducing threads below
+                    if (L::kRedParities == 1) {
+                        // every warp has read its fragments of this stage and the reducers of the
+                        // previous tile are done
+                        asm volatile("bar.sync 1, 512;" ::: "memory");
+                        if (L::kInlineProducer && tid == 0 && slot + NS < my_tiles) issue_tile(slot + NS);
+                    }
                     float* red = s_red + (parity * kWarps + warp) * (NB * kRedRow);
 #pragma unroll
                     for (int m = 0; m < MT; ++m) {
@@ -378,7 +406,7 @@ nf4_gemv_tma_kernel(const __grid_constant__ CUtensorMap map_w, const TmaParams p
                             s_out[slot * kTileRows * NB + red_r * NB + red_n] = v;
                         }
                     }
-                    parity ^= 1u;
+                    if (L::kRedParities == 2) parity ^= 1u;
                 }
             }
         }
@@ -426,13 +454,13 @@ int32_t max_active_clusters(const DeviceContext& ctx, uint32_t ksplit, uint32_t*
     static bool configured = false;
     static int cached[9] = {0};
     if (!configured) {
-        B2_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+        B2_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Layout<MT>::kSmemBytes));
         configured = true;
     }
     if (cached[ksplit] == 0) {
         cudaLaunchConfig_t config = {};
-        config.blockDim = dim3(kThreads);
-        config.dynamicSmemBytes = kSmemBytes;
+        config.blockDim = dim3(Layout<MT>::kThreads);
+        config.dynamicSmemBytes = Layout<MT>::kSmemBytes;
         cudaLaunchAttribute attr[1];
         attr[0].id = cudaLaunchAttributeClusterDimension;
         attr[0].val.clusterDim.x = ksplit;
@@ -463,8 +491,8 @@ int32_t launch_tma(const DeviceContext& ctx, const CUtensorMap& map, TmaParams p
         return fail(B2_STATUS_RUNTIME_ERROR, "internal: NF4 TMA decode kernel tile budget exceeded");
     }
     cudaLaunchConfig_t config = {};
-    config.blockDim = dim3(kThreads);
-    config.dynamicSmemBytes = kSmemBytes;
+    config.blockDim = dim3(Layout<MT>::kThreads);
+    config.dynamicSmemBytes = Layout<MT>::kSmemBytes;
     config.stream = stream;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -483,7 +511,7 @@ int32_t launch_tma(const DeviceContext& ctx, const CUtensorMap& map, TmaParams p
 // Shapes the TMA decode kernel takes: whole 128-byte boxes per CTA slice, 16-byte aligned rows.
 bool nf4_gemv_tma_plan(const DeviceContext& ctx, const WeightView& w, const float* x, uint64_t rows,
                        uint32_t* ksplit_out, uint32_t* steps_per_cta_out) {
-    if (rows < 1 || rows > 16 || w.in_features % kStepK != 0 || w.block_size < kStepK) return false;
+    if (rows < 1 || rows > 32 || w.in_features % kStepK != 0 || w.block_size < kStepK) return false;
     if ((reinterpret_cast<uintptr_t>(w.codes) & 15u) != 0 || (reinterpret_cast<uintptr_t>(x) & 15u) != 0) return false;
     if (encode_tiled() == nullptr) return false;
     if (w.in_features % w.block_size != 0 || w.out_features % kTileRows != 0) return false;
@@ -498,8 +526,9 @@ bool nf4_gemv_tma_plan(const DeviceContext& ctx, const WeightView& w, const floa
     per = (per + 3) / 4 * 4;
     if (per > cap) return false;
     uint32_t active = 0;
-    const int32_t st = rows <= 8 ? max_active_clusters<1, 4>(ctx, static_cast<uint32_t>(ks), &active)
-                                 : max_active_clusters<2, 2>(ctx, static_cast<uint32_t>(ks), &active);
+    const int32_t st = rows <= 8    ? max_active_clusters<1, 4>(ctx, static_cast<uint32_t>(ks), &active)
+                       : rows <= 16 ? max_active_clusters<2, 2>(ctx, static_cast<uint32_t>(ks), &active)
+                                    : max_active_clusters<4, 2>(ctx, static_cast<uint32_t>(ks), &active);
     if (st != B2_STATUS_OK) {
         clear_error();
         return false;
@@ -536,7 +565,8 @@ int32_t launch_nf4_gemv_tma(const DeviceContext& ctx, const WeightView& w, const
     p.lut = ctx.gemv_lut;
     p.error = ctx.gemm_error;
     if (rows <= 8) return launch_tma<1, 4>(ctx, map, p, ksplit, stream);
-    return launch_tma<2, 2>(ctx, map, p, ksplit, stream);
+    if (rows <= 16) return launch_tma<2, 2>(ctx, map, p, ksplit, stream);
+    return launch_tma<4, 2>(ctx, map, p, ksplit, stream);
 }
 
 }  // namespace b2

@@ -82,7 +82,7 @@ class CudaOps:
         ws = w.struct()
         _check(lib.b2_nf4_linear_forward(C.byref(ws), x.data_ptr(), out.data_ptr(), x.shape[0], None, 0,
                                          _stream_ptr(None)))
-        self.launches += 2 if 16 < x.shape[0] <= 32 else 1   # 17..32 rows run as two streaming passes
+        self.launches += 1
 
     def rmsnorm(self, x, delta, x_out, scale, y, eps: float) -> None:
         _check(lib.b2_rmsnorm(x.data_ptr(), None if delta is None else delta.data_ptr(),

@@ -130,7 +130,7 @@ def c2_weights(port):
 
 
 @pytest.mark.parametrize("shape", [(4096, 4096), (14336, 4096), (4096, 14336)])
-@pytest.mark.parametrize("rows", [1, 4, 16, 32])
+@pytest.mark.parametrize("rows", [1, 4, 16, 23, 32])
 def test_gemv_config2(b2, port, c2_weights, shape, rows):
     host = c2_weights[shape]
     w = b2.PackedNf4Weight.from_host(host)
