@@ -6,6 +6,7 @@
 // path, they exist so a whole decode step stays on the device and in one graph.
 #include "b2_common.cuh"
 #include "b2_kernels.h"
+#include "sm100_ptx.cuh"
 
 #include <cmath>
 
@@ -31,6 +32,7 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
 __global__ void __launch_bounds__(256)
 rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ delta, float* __restrict__ x_out,
                const float* __restrict__ scale, float* __restrict__ y, uint32_t width, float eps) {
+    sm100::pdl_launch_dependents();   // a following decode GEMV may start its set-up now
     __shared__ float scratch[8];
     const uint64_t row = blockIdx.x;
     const float* xr = x + row * width;
@@ -62,6 +64,7 @@ rope_append_kernel(float* __restrict__ q, const float* __restrict__ k, const flo
                    float* __restrict__ k_pages, float* __restrict__ v_pages, uint32_t q_heads,
                    uint32_t kv_heads, uint32_t d, uint32_t block_size, uint64_t physical_blocks,
                    uint32_t max_blocks, float theta, uint32_t* status) {
+    sm100::pdl_launch_dependents();   // a following decode GEMV may start its set-up now
     const uint32_t seq = blockIdx.x;
     const uint32_t pos = positions[seq];
     const uint32_t half = d / 2;
@@ -119,6 +122,7 @@ __device__ __forceinline__ float silu_ref(float value) {
 __global__ void __launch_bounds__(256)
 silu_mul_kernel(const float* __restrict__ gate, const float* __restrict__ up, float* __restrict__ out,
                 uint64_t n) {
+    sm100::pdl_launch_dependents();   // a following decode GEMV may start its set-up now
     const uint64_t stride = static_cast<uint64_t>(gridDim.x) * blockDim.x;
     for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
         out[i] = silu_ref(gate[i]) * up[i];
@@ -127,6 +131,7 @@ silu_mul_kernel(const float* __restrict__ gate, const float* __restrict__ up, fl
 
 __global__ void __launch_bounds__(256)
 add_kernel(const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ out, uint64_t n) {
+    sm100::pdl_launch_dependents();   // a following decode GEMV may start its set-up now
     const uint64_t stride = static_cast<uint64_t>(gridDim.x) * blockDim.x;
     for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
         out[i] = a[i] + b[i];
@@ -138,6 +143,7 @@ add_kernel(const float* __restrict__ a, const float* __restrict__ b, float* __re
 __global__ void __launch_bounds__(256)
 gather_rows_kernel(const float* __restrict__ table, const uint32_t* __restrict__ ids, float* __restrict__ out,
                    uint32_t width, uint32_t vocab, uint32_t* status) {
+    sm100::pdl_launch_dependents();   // a following decode GEMV may start its set-up now
     const uint32_t row = blockIdx.x;
     uint32_t id = ids[row];
     if (id >= vocab) {

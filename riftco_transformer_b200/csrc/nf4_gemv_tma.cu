@@ -21,6 +21,7 @@
 #include <cooperative_groups.h>
 #include <cuda_fp16.h>
 
+#include <cstdlib>
 #include <mutex>
 
 namespace cg = cooperative_groups;
@@ -30,38 +31,52 @@ namespace {
 
 using namespace sm100;
 
-constexpr int kWarps = 16;                       // consumer warps
-constexpr int kThreadsProducerWarp = (kWarps + 1) * 32;   // consumer warps + one producer warp
+constexpr int kWarps = 16;
+constexpr int kThreads = kWarps * 32;
 constexpr int kStepK = 64;
 constexpr int kTileRows = 16;
 constexpr int kRedRow = kTileRows + 4;           // padded row of the [n][row] partial-sum layout
 constexpr int kBoxBytes = kTileRows * 128;       // one TMA box: 16 rows x 128 bytes (4 steps)
 constexpr int kLutBytes = 256 * 256;
+// Per ring stage, the tile's raw scales: a [16 rows x kScaleBoxU8 bytes] box of scale codes
+// (or [16 x kScaleBoxF32] floats) and 32 second-level values.
+constexpr int kScaleBoxU8 = 64 + 16;             // blocks of the widest CTA slice + alignment slack
+constexpr int kScaleBoxF32 = 64 + 4;
+constexpr int kScaleBoxBytesU8 = kTileRows * kScaleBoxU8;          // 1280
+constexpr int kScaleBoxBytesF32 = kTileRows * kScaleBoxF32 * 4;    // 4352
+constexpr int kSecondOff = kScaleBoxBytesF32;
+constexpr int kSecondBox = 32;                   // floats
+constexpr int kScaleStageBytes = 4608;           // 4352 + 128, rounded to 128
 
+// MT = batch rows / 8. Sixteen warps share the contraction range of the CTA, SPW steps of 64
+// each; thread 0 is also the producer: it refills a ring stage once a CTA barrier has shown that
+// every warp is done with it. (A seventeenth, dedicated producer warp would put five warps on
+// one scheduler partition and cap every thread at 96 registers.)
 template <int MT>
 struct Layout {
     static constexpr int NB = 8 * MT;
-    static constexpr int kMaxTiles = MT == 1 ? 48 : 16;
-    // 32 batch rows: one partial-sum buffer (two barriers per tile), a 64 KB ring, and the
-    // split-K output tiles behind the ring instead of below the table.
-    // With 17 warps a scheduler partition holds 5 of them and the register file caps a thread at
-    // 96 registers; the 32-row variant needs more, so it runs 16 warps (128 registers) and
-    // thread 0 refills a stage itself once the CTA barrier shows every warp has read it.
-    static constexpr bool kInlineProducer = MT == 4;
-    static constexpr int kThreads = kInlineProducer ? kWarps * 32 : kThreadsProducerWarp;
-    static constexpr int kRedParities = MT == 4 ? 1 : 2;
-    static constexpr bool kOutBehindRing = MT == 4;
+    static constexpr int SPW = MT == 4 ? 2 : 4;
+    static constexpr int kWarpsPerBox = 4 / SPW;
+    static constexpr int kBoxesPerStage = kWarps / kWarpsPerBox;
+    static constexpr int kStageBytes = kBoxesPerStage * kBoxBytes;      // 32 KB or 16 KB
     static constexpr int kRingBytes = MT == 4 ? 64 * 1024 : 96 * 1024;
-    // offsets from the first 16-byte aligned address of the dynamic allocation (below the table)
-    static constexpr int kBarOff = 0;                                   // full[12], empty[12], abort
+    static constexpr int NS = kRingBytes / kStageBytes;                 // 3 or 4 stages
+    static constexpr int kMaxTiles = MT == 1 ? 48 : 16;
+    // One partial-sum buffer costs a second CTA barrier per tile; 8 batch rows can afford two.
+    static constexpr int kRedParities = MT == 1 ? 2 : 1;
+    static constexpr bool kOutBehindRing = MT == 4;
+    // offsets from the first 128-byte aligned address of the dynamic allocation (below the table)
+    static constexpr int kBarOff = 0;                                   // full[8], abort
     static constexpr int kFactorOff = 256;                              // 256 floats
-    static constexpr int kRedOff = kFactorOff + 1024;                   // [parity][16 warps][NB][20]
-    static constexpr int kRedBytes = kRedParities * kWarps * (kTileRows + 4) * NB * 4;
+    static constexpr int kScaleOff = 1280;                              // [stage] raw scales
+    static constexpr int kRedOff = kScaleOff + NS * kScaleStageBytes;   // [parity][16 warps][NB][20]
+    static constexpr int kRedBytes = kRedParities * kWarps * kRedRow * NB * 4;
     static constexpr int kOutBytes = kMaxTiles * kTileRows * NB * 4;    // [tile][16 rows][NB]
     static constexpr int kOutOff = kRedOff + kRedBytes;                 // when it lives below the table
     static constexpr int kLowBytes = kOutOff + (kOutBehindRing ? 0 : kOutBytes);
     static constexpr int kSmemBytes = 65536 /* bytes below the 64 KB-aligned table */ + kLutBytes + kRingBytes +
                                       (kOutBehindRing ? kOutBytes : 0);
+    static_assert(kLowBytes <= 65536 - 2048, "region below the table too large");
 };
 
 struct TmaParams {
@@ -71,8 +86,8 @@ struct TmaParams {
     uint32_t rows;            // batch rows M
     uint32_t steps_total;     // in / 64
     uint32_t steps_per_cta;   // multiple of 4, <= 16 * SPW
-    uint32_t row_tiles;       // ceil(out / 16)
-    uint32_t blocks_per_row;  // in / block_size when rows are block aligned, else 0
+    uint32_t row_tiles;       // out / 16
+    uint32_t blocks_per_row;  // in / block_size
     const uint32_t* lut;      // compact [256][32] words of fp16 pairs
     uint32_t* error;
 };
@@ -105,35 +120,51 @@ __device__ __forceinline__ uint2 lds_u2(uint32_t a) {
     asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];\n" : "=r"(v.x), "=r"(v.y) : "r"(a));
     return v;
 }
+__device__ __forceinline__ float lds_f32(uint32_t a) {
+    float v;
+    asm volatile("ld.shared.f32 %0, [%1];\n" : "=f"(v) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds_u8(uint32_t a) {
+    uint32_t v;
+    asm volatile("ld.shared.u8 %0, [%1];\n" : "=r"(v) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ void tma_load_1d(uint32_t dst32, const CUtensorMap* map, int x, uint64_t* bar) {
+    asm volatile("cp.async.bulk.tensor.1d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2}], [%3];"
+                 ::"r"(dst32), "l"(map), "r"(x), "r"(smem_u32(bar))
+                 : "memory");
+}
+__device__ __forceinline__ void tma_load_2d_at(uint32_t dst32, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst32), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
+        : "memory");
+}
 __device__ __forceinline__ void cp_async_16(uint32_t dst32, const void* gmem_src) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 16;\n" ::"r"(dst32), "l"(gmem_src));
 }
 
-struct RawScale {
-    uint32_t bits;
-    float second;
-};
-
-template <int MT, int SPW>
-__global__ void __launch_bounds__(Layout<MT>::kThreads, 1)
-nf4_gemv_tma_kernel(const __grid_constant__ CUtensorMap map_w, const TmaParams p) {
+template <int MT>
+__global__ void __launch_bounds__(kThreads, 1)
+nf4_gemv_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_s,
+                    const __grid_constant__ CUtensorMap map_2, const TmaParams p) {
     using L = Layout<MT>;
     constexpr int NB = L::NB;
-    constexpr uint32_t kThreads = L::kThreads;
+    constexpr int SPW = L::SPW;
     constexpr int NSC = (2 * SPW) / 4;                       // scales decoded per lane per tile
-    constexpr int kWarpsPerBox = 4 / SPW;                    // SPW 4: one warp per box, SPW 2: two
-    constexpr uint32_t kMaxBoxes = kWarps / kWarpsPerBox;    // boxes per stage at most
-    constexpr uint32_t kStageBytes = kMaxBoxes * kBoxBytes;  // 32 KB or 16 KB
-    constexpr uint32_t NS = L::kRingBytes / kStageBytes;     // 3, 6 or 4 stages
+    constexpr uint32_t kWarpsPerBox = L::kWarpsPerBox;
+    constexpr uint32_t kStageBytes = L::kStageBytes;
+    constexpr uint32_t NS = L::NS;
 
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     const uint32_t raw32 = smem_u32(smem_raw);
-    const uint32_t low32 = (raw32 + 15u) & ~15u;
+    const uint32_t low32 = (raw32 + 127u) & ~127u;
     const uint32_t lut32 = (raw32 + 65535u) & ~65535u;
     const uint32_t ring32 = lut32 + kLutBytes;
+    const uint32_t scale32 = low32 + L::kScaleOff;
     uint8_t* low = smem_raw + (low32 - raw32);
     uint64_t* full = reinterpret_cast<uint64_t*>(low + L::kBarOff);
-    uint64_t* empty = full + 12;
     volatile uint32_t* abort = reinterpret_cast<volatile uint32_t*>(low + L::kBarOff + 200);
     const float* s_factor = reinterpret_cast<const float*>(low + L::kFactorOff);
     float* s_red = reinterpret_cast<float*>(low + L::kRedOff);
@@ -155,7 +186,7 @@ nf4_gemv_tma_kernel(const __grid_constant__ CUtensorMap map_w, const TmaParams p
     const WeightView& w = p.w;
     const uint64_t in = w.in_features, out = w.out_features;
 
-    // The region below the table must hold barriers, factor table and reduction buffers.
+    // The region below the table must hold barriers, factor table, scales and reduction buffers.
     if (lut32 - low32 < static_cast<uint32_t>(L::kLowBytes)) {
         if (tid == 0 && p.error != nullptr) atomicOr(p.error, 2u);
         return;
@@ -167,96 +198,80 @@ nf4_gemv_tma_kernel(const __grid_constant__ CUtensorMap map_w, const TmaParams p
     const uint32_t my_tiles =
         cluster_id < p.row_tiles ? (p.row_tiles - cluster_id + n_clusters - 1) / n_clusters : 0u;
 
-    if (tid == 0) {
-        for (uint32_t s = 0; s < NS; ++s) {
-            mbar_init(&full[s], 1);
-            mbar_init(&empty[s], kWarps);
+    // Scale blocks of this CTA's slice: first block column, rounded down to the 16-byte
+    // granularity a TMA coordinate needs; running block index of the first tile's first row.
+    const bool fp32_scales = w.encoding == B2_SCALES_FLOAT32;
+    const uint32_t blocks_per_row = p.blocks_per_row;
+    const uint32_t b_begin = (slice_begin * static_cast<uint32_t>(kStepK)) >> w.block_shift;
+    const uint32_t scale_x0 = fp32_scales ? (b_begin & ~3u) : (b_begin & ~15u);
+    const uint32_t sshift = w.scale_block_shift;
+    const uint32_t fbase = static_cast<uint32_t>(w.flat_block_base);
+    const uint32_t tile_stride_rows = n_clusters * kTileRows;
+    const uint32_t blk_stride = tile_stride_rows * blocks_per_row;
+    const uint32_t tile_blk0 = cluster_id * kTileRows * blocks_per_row + b_begin;   // + slot * blk_stride
+    const uint32_t tx_bytes = n_boxes * kBoxBytes +
+                              (fp32_scales ? kScaleBoxBytesF32 : kScaleBoxBytesU8 + kSecondBox * 4);
+
+    // Streams tile `slot` of this CTA into its ring stage: packed codes, raw scales and, for
+    // double-quantised weights, the second-level values the tile's blocks refer to (one thread).
+    auto issue_tile = [&](uint32_t slot) {
+        const uint32_t s = slot % NS;
+        mbar_expect_tx(&full[s], tx_bytes);
+        const int x0 = static_cast<int>(slice_begin * 32u);
+        const int y = static_cast<int>((cluster_id + slot * n_clusters) * kTileRows);
+        for (uint32_t b = 0; b < n_boxes; ++b) {
+            tma_load_2d_at(ring32 + s * kStageBytes + b * kBoxBytes, &map_w, x0 + static_cast<int>(b * 128u), y,
+                           &full[s]);
         }
+        const uint32_t sdst = scale32 + s * kScaleStageBytes;
+        tma_load_2d_at(sdst, &map_s, static_cast<int>(scale_x0), y, &full[s]);
+        if (!fp32_scales) {
+            const uint32_t first = (fbase + tile_blk0 + slot * blk_stride) >> sshift;
+            tma_load_1d(sdst + kSecondOff, &map_2, static_cast<int>(first & ~3u), &full[s]);
+        }
+    };
+
+    // Set-up that touches no tensor of the caller (barriers, the byte table, the factor table)
+    // runs before the dependency wait, so it overlaps the tail of the previous kernel in the
+    // stream; weights, scales and activations are only read after it.
+    if (tid == 0) {
+        for (uint32_t s = 0; s < NS; ++s) mbar_init(&full[s], 1);
         *abort = 0;
         mbar_fence_init();
-        tma_prefetch_descriptor(&map_w);
     }
-    // byte table (used half of each 256-byte row) and scale factor table
     for (uint32_t i = tid; i < 256 * 8; i += kThreads) {
         cp_async_16(lut32 + (i >> 3) * 256u + (i & 7u) * 16u, p.lut + i * 4);
     }
     asm volatile("cp.async.commit_group;\n" ::);
     if (tid < 256) reinterpret_cast<float*>(low + L::kFactorOff)[tid] = dq_factor(tid);
-    asm volatile("cp.async.wait_group 0;\n" ::);
-    __syncthreads();
+    pdl_launch_dependents();
+    pdl_wait();
+    if (tid == 0) {
+        for (uint32_t slot = 0; slot < my_tiles && slot < NS; ++slot) issue_tile(slot);
+    }
 
-    // Streams the boxes of tile `slot` of this CTA into its ring stage (one thread).
-    auto issue_tile = [&](uint32_t slot) {
-        const uint32_t s = slot % NS;
-        mbar_expect_tx(&full[s], n_boxes * kBoxBytes);
-        const int x0 = static_cast<int>(slice_begin * 32u);
-        const int y = static_cast<int>((cluster_id + slot * n_clusters) * kTileRows);
-        for (uint32_t b = 0; b < n_boxes; ++b) {
-            tma_load_2d(smem_raw + (ring32 - raw32) + s * kStageBytes + b * kBoxBytes, &map_w,
-                        x0 + static_cast<int>(b * 128u), y, &full[s]);
-        }
-    };
-
-    if (!L::kInlineProducer && warp == kWarps) {
-        // ---- producer warp: one thread streams this CTA's boxes of every tile ----
-        if (lane == 0) {
-            for (uint32_t slot = 0; slot < my_tiles; ++slot) {
-                if (slot >= NS) mbar_wait(&empty[slot % NS], ((slot / NS) - 1u) & 1u, abort);
-                issue_tile(slot);
-            }
-        }
-    } else {
-        if (L::kInlineProducer && tid == 0) {
-            for (uint32_t slot = 0; slot < my_tiles && slot < NS; ++slot) issue_tile(slot);
-        }
-        // ---- consumers ----
+    {
         const uint32_t box = warp / kWarpsPerBox;
         const uint32_t sub0 = (warp % kWarpsPerBox) * SPW;           // first step of this warp inside its box
         const uint32_t step0 = slice_begin + warp * SPW;
         const uint32_t my_steps = step0 < slice_end ? min(static_cast<uint32_t>(SPW), slice_end - step0) : 0u;
         const bool warp_active = my_steps > 0;                       // warp-uniform
 
+        // This lane decodes NSC scales per tile: SPW 4 -> (row g, step t) and (row g+8, step t);
+        // SPW 2 -> (row g + 8*(t/2), step t%2). Quad shuffles hand them to the lanes that use them.
         const uint32_t scale_step_raw = SPW == 4 ? t : (t & 1u);
         const uint32_t scale_step = warp_active ? min(scale_step_raw, my_steps - 1) : 0u;
-        auto scale_row_half = [&](int k) -> uint32_t { return SPW == 4 ? static_cast<uint32_t>(k) : (t >> 1); };
-        const bool fp32_scales = w.encoding == B2_SCALES_FLOAT32;
-        const uint32_t blocks_per_row = p.blocks_per_row;
-        const uint32_t tile_stride_rows = n_clusters * kTileRows;
-
-        RawScale sraw[2][NSC];
-        // Hoisted weight-view fields and this lane's running scale-block index: rows are block
-        // aligned and tiles are whole (the launcher checks both), so the index of (row, step) is
-        // base + slot * stride.
-        const float* const fp32_ptr = w.fp32_scales;
-        const uint8_t* const code_ptr = w.scale_codes;
-        const float* const second_ptr = w.second_level;
-        const uint32_t sshift = w.scale_block_shift;
-        const uint32_t fbase = static_cast<uint32_t>(w.flat_block_base);
         const float dq_offset = w.offset;
-        uint32_t blk0[NSC];
+        const uint32_t lane_block = ((step0 + scale_step) * static_cast<uint32_t>(kStepK)) >> w.block_shift;
+        uint32_t scale_addr[NSC];   // shared-memory byte offset of this lane's raw scale inside a stage
+        uint32_t blk0[NSC];         // its block index relative to the tile's first block
 #pragma unroll
         for (int k = 0; k < NSC; ++k) {
-            blk0[k] = (cluster_id * kTileRows + g + 8u * scale_row_half(k)) * blocks_per_row +
-                      (((step0 + scale_step) * static_cast<uint32_t>(kStepK)) >> w.block_shift);
+            const uint32_t row = g + 8u * (SPW == 4 ? static_cast<uint32_t>(k) : (t >> 1));
+            scale_addr[k] = fp32_scales ? (row * kScaleBoxF32 + (lane_block - scale_x0)) * 4u
+                                        : row * kScaleBoxU8 + (lane_block - scale_x0);
+            blk0[k] = row * blocks_per_row + (lane_block - b_begin);
         }
-        const uint32_t blk_stride = tile_stride_rows * blocks_per_row;
-        auto fetch_scales = [&](int d, uint32_t slot) {
-            if (slot < my_tiles && warp_active) {
-#pragma unroll
-                for (int k = 0; k < NSC; ++k) {
-                    const uint32_t block = blk0[k] + slot * blk_stride;
-                    if (fp32_scales) {
-                        sraw[d][k].bits = __float_as_uint(__ldg(fp32_ptr + block));
-                        sraw[d][k].second = 0.0f;
-                    } else {
-                        sraw[d][k].bits = __ldg(code_ptr + block);
-                        sraw[d][k].second = __ldg(second_ptr + ((fbase + block) >> sshift));
-                    }
-                }
-            }
-        };
-        (void)tile_stride_rows;
-        fetch_scales(0, 0);
 
         // Activations of this warp's steps as fp16 B fragments (registers for the whole kernel).
         uint4 xf[MT][SPW][2];
@@ -292,122 +307,131 @@ nf4_gemv_tma_kernel(const __grid_constant__ CUtensorMap map_w, const TmaParams p
 #pragma unroll
         for (int u = 0; u < SPW; ++u) {
             const uint32_t st = min(sub0 + static_cast<uint32_t>(u), sub0 + (warp_active ? my_steps - 1u : 0u));
-            frag_off[u] = g * 128u + (((2u * st + (t >> 1)) ^ g) << 4) + (t & 1u) * 8u;
+            frag_off[u] = box * kBoxBytes + g * 128u + (((2u * st + (t >> 1)) ^ g) << 4) + (t & 1u) * 8u;
         }
 
         // reducing threads (tid < 16 * NB): output element (n = tid / 16, r = tid % 16) of every tile
         const uint32_t red_n = tid / kTileRows, red_r = tid % kTileRows;
         float* y_run = p.y + static_cast<uint64_t>(red_n) * out + static_cast<uint64_t>(cluster_id) * kTileRows + red_r;
-        const uint64_t y_stride = static_cast<uint64_t>(tile_stride_rows);
-        const bool red_store = tid < kTileRows * NB && red_n < p.rows;
+        const bool red_thread = tid < kTileRows * NB;
+        const bool red_store = red_thread && red_n < p.rows;
+        float* const my_red = s_red + warp * (NB * kRedRow);
+        const float* const red_src = s_red + red_n * kRedRow + red_r;
+        float* out_run = s_out + red_r * NB + red_n;
 
-        uint32_t parity = 0;
-        for (uint32_t base = 0; base < my_tiles; base += 2) {
+        asm volatile("cp.async.wait_group 0;\n" ::);
+        __syncthreads();   // tables and barrier initialisation visible to every thread
+
+        uint32_t parity_off = 0;          // float offset of the partial-sum buffer in use
+        uint32_t stage = 0, phase = 0;    // ring position of the current tile
+        uint32_t tile_first = fbase + tile_blk0;   // flat index of the tile's first scale block
+        for (uint32_t slot = 0; slot < my_tiles; ++slot) {
+            const uint32_t stage_ring = ring32 + stage * kStageBytes;
+            const uint32_t stage_scale = scale32 + stage * kScaleStageBytes;
+            mbar_wait(&full[stage], phase, abort);
+            float acc[MT][4];
 #pragma unroll
-            for (int d = 0; d < 2; ++d) {
-                const uint32_t slot = base + d;
-                if (slot < my_tiles) {   // CTA-uniform
-                    fetch_scales(d ^ 1, slot + 1);
-                    const uint32_t s = slot % NS;
-                    float acc[MT][4];
+            for (int m = 0; m < MT; ++m)
 #pragma unroll
-                    for (int m = 0; m < MT; ++m)
+                for (int e = 0; e < 4; ++e) acc[m][e] = 0.0f;
+            if (warp_active) {
+                uint2 wa[SPW], wb[SPW];
 #pragma unroll
-                        for (int e = 0; e < 4; ++e) acc[m][e] = 0.0f;
-                    mbar_wait(&full[s], (slot / NS) & 1u, abort);
-                    uint2 wa[SPW], wb[SPW];
-                    if (warp_active) {
-                        const uint32_t box32 = ring32 + s * kStageBytes + box * kBoxBytes;
+                for (int u = 0; u < SPW; ++u) {
+                    wa[u] = lds_u2(stage_ring + frag_off[u]);
+                    wb[u] = lds_u2(stage_ring + frag_off[u] + 1024u);
+                }
+                float sc[NSC];
 #pragma unroll
-                        for (int u = 0; u < SPW; ++u) {
-                            wa[u] = lds_u2(box32 + frag_off[u]);
-                            wb[u] = lds_u2(box32 + frag_off[u] + 1024u);
-                        }
+                for (int k = 0; k < NSC; ++k) {
+                    if (fp32_scales) {
+                        sc[k] = lds_f32(stage_scale + scale_addr[k]);
+                    } else {
+                        const uint32_t code = lds_u8(stage_scale + scale_addr[k]);
+                        const uint32_t idx = ((tile_first + blk0[k]) >> sshift) - ((tile_first >> sshift) & ~3u);
+                        const float second = lds_f32(stage_scale + kSecondOff + idx * 4u);
+                        sc[k] = dq_finish(s_factor[code], second, dq_offset);
                     }
-                    __syncwarp();
-                    // Release the stage once this warp's fragment reads have RETURNED: the arrive
-                    // takes the last loaded register as a (dummy) operand, so it cannot issue earlier.
-                    if (!L::kInlineProducer && lane == 0) {
-                        const uint32_t dep = warp_active ? wb[SPW - 1].y : 0u;
-                        asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0]; // %1" ::"r"(smem_u32(&empty[s])), "r"(dep)
-                                     : "memory");
-                    }
-                    if (warp_active) {
-                        float sc[NSC];
+                }
 #pragma unroll
-                        for (int k = 0; k < NSC; ++k) {
-                            sc[k] = fp32_scales ? __uint_as_float(sraw[d][k].bits)
-                                                : dq_finish(s_factor[sraw[d][k].bits], sraw[d][k].second, dq_offset);
-                        }
+                for (int u = 0; u < SPW; ++u) {
+                    const float sA = __shfl_sync(0xFFFFFFFFu, sc[0], quad_base + u);
+                    const float sB = SPW == 4 ? __shfl_sync(0xFFFFFFFFu, sc[NSC - 1], quad_base + u)
+                                              : __shfl_sync(0xFFFFFFFFu, sc[0], quad_base + 2 + u);
+                    float part[MT][4];
+                    const uint32_t wwa[2] = {wa[u].x, wa[u].y};
+                    const uint32_t wwb[2] = {wb[u].x, wb[u].y};
 #pragma unroll
-                        for (int u = 0; u < SPW; ++u) {
-                            const float sA = __shfl_sync(0xFFFFFFFFu, sc[0], quad_base + u);
-                            const float sB = SPW == 4 ? __shfl_sync(0xFFFFFFFFu, sc[NSC - 1], quad_base + u)
-                                                      : __shfl_sync(0xFFFFFFFFu, sc[0], quad_base + 2 + u);
-                            float part[MT][4];
-                            const uint32_t wwa[2] = {wa[u].x, wa[u].y};
-                            const uint32_t wwb[2] = {wb[u].x, wb[u].y};
+                    for (int i = 0; i < 4; ++i) {
+                        const uint32_t word_a = wwa[i >> 1], word_b = wwb[i >> 1];
+                        const uint32_t sel0 = (i & 1) ? 0x7624u : 0x7604u;
+                        const uint32_t sel1 = (i & 1) ? 0x7634u : 0x7614u;
+                        const uint32_t a0 = lds_u32(__byte_perm(word_a, lut_lane, sel0));
+                        const uint32_t a2 = lds_u32(__byte_perm(word_a, lut_lane, sel1));
+                        const uint32_t a1 = lds_u32(__byte_perm(word_b, lut_lane, sel0));
+                        const uint32_t a3 = lds_u32(__byte_perm(word_b, lut_lane, sel1));
 #pragma unroll
-                            for (int i = 0; i < 4; ++i) {
-                                const uint32_t word_a = wwa[i >> 1], word_b = wwb[i >> 1];
-                                const uint32_t sel0 = (i & 1) ? 0x7624u : 0x7604u;
-                                const uint32_t sel1 = (i & 1) ? 0x7634u : 0x7614u;
-                                const uint32_t a0 = lds_u32(__byte_perm(word_a, lut_lane, sel0));
-                                const uint32_t a2 = lds_u32(__byte_perm(word_a, lut_lane, sel1));
-                                const uint32_t a1 = lds_u32(__byte_perm(word_b, lut_lane, sel0));
-                                const uint32_t a3 = lds_u32(__byte_perm(word_b, lut_lane, sel1));
-#pragma unroll
-                                for (int m = 0; m < MT; ++m) {
-                                    const uint4& xv = xf[m][u][i >> 1];
-                                    const uint32_t b0 = (i & 1) ? xv.z : xv.x;
-                                    const uint32_t b1 = (i & 1) ? xv.w : xv.y;
-                                    if (i == 0) {
-                                        mma_f16_16816_zero(part[m], a0, a1, a2, a3, b0, b1);
-                                    } else {
-                                        mma_f16_16816(part[m], a0, a1, a2, a3, b0, b1);
-                                    }
-                                }
-                            }
-#pragma unroll
-                            for (int m = 0; m < MT; ++m) {
-                                acc[m][0] = fmaf(sA, part[m][0], acc[m][0]);
-                                acc[m][1] = fmaf(sA, part[m][1], acc[m][1]);
-                                acc[m][2] = fmaf(sB, part[m][2], acc[m][2]);
-                                acc[m][3] = fmaf(sB, part[m][3], acc[m][3]);
+                        for (int m = 0; m < MT; ++m) {
+                            const uint4& xv = xf[m][u][i >> 1];
+                            const uint32_t b0 = (i & 1) ? xv.z : xv.x;
+                            const uint32_t b1 = (i & 1) ? xv.w : xv.y;
+                            if (i == 0) {
+                                mma_f16_16816_zero(part[m], a0, a1, a2, a3, b0, b1);
+                            } else {
+                                mma_f16_16816(part[m], a0, a1, a2, a3, b0, b1);
                             }
                         }
                     }
-                    // partial tile as [n][row] with rows padded to 20 words: conflict-free scalar stores
-                    // here, contiguous reads by the reducing threads below
-                    if (L::kRedParities == 1) {
-                        // every warp has read its fragments of this stage and the reducers of the
-                        // previous tile are done
-                        asm volatile("bar.sync 1, 512;" ::: "memory");
-                        if (L::kInlineProducer && tid == 0 && slot + NS < my_tiles) issue_tile(slot + NS);
-                    }
-                    float* red = s_red + (parity * kWarps + warp) * (NB * kRedRow);
 #pragma unroll
                     for (int m = 0; m < MT; ++m) {
-                        float* q = red + (m * 8 + 2 * t) * kRedRow;
-                        q[g] = acc[m][0];
-                        q[kRedRow + g] = acc[m][1];
-                        q[g + 8] = acc[m][2];
-                        q[kRedRow + g + 8] = acc[m][3];
+                        acc[m][0] = fmaf(sA, part[m][0], acc[m][0]);
+                        acc[m][1] = fmaf(sA, part[m][1], acc[m][1]);
+                        acc[m][2] = fmaf(sB, part[m][2], acc[m][2]);
+                        acc[m][3] = fmaf(sB, part[m][3], acc[m][3]);
                     }
-                    asm volatile("bar.sync 1, 512;" ::: "memory");
-                    if (tid < kTileRows * NB) {
-                        const float* src = s_red + parity * kWarps * (NB * kRedRow) + red_n * kRedRow + red_r;
-                        float v = 0.0f;
-#pragma unroll
-                        for (int k = 0; k < kWarps; ++k) v += src[k * (NB * kRedRow)];
-                        if (ksplit == 1) {
-                            if (red_store) y_run[slot * y_stride] = v;
-                        } else {
-                            s_out[slot * kTileRows * NB + red_r * NB + red_n] = v;
-                        }
-                    }
-                    if (L::kRedParities == 2) parity ^= 1u;
                 }
+            }
+            if (L::kRedParities == 1) {
+                // every warp is done with this ring stage, and the reducers of the previous tile
+                // are done with the partial-sum buffer
+                __syncthreads();
+                if (tid == 0 && slot + NS < my_tiles) issue_tile(slot + NS);
+            }
+            // partial tile as [n][row] with rows padded to 20 words: conflict-free scalar stores
+            // here, contiguous reads by the reducing threads below
+            {
+                float* red = my_red + parity_off;
+#pragma unroll
+                for (int m = 0; m < MT; ++m) {
+                    float* q = red + (m * 8 + 2 * t) * kRedRow;
+                    q[g] = acc[m][0];
+                    q[kRedRow + g] = acc[m][1];
+                    q[g + 8] = acc[m][2];
+                    q[kRedRow + g + 8] = acc[m][3];
+                }
+            }
+            __syncthreads();
+            if (L::kRedParities == 2) {
+                if (tid == 0 && slot + NS < my_tiles) issue_tile(slot + NS);
+            }
+            if (red_thread) {
+                const float* src = red_src + parity_off;
+                float v = 0.0f;
+#pragma unroll
+                for (int k = 0; k < kWarps; ++k) v += src[k * (NB * kRedRow)];
+                if (ksplit == 1) {
+                    if (red_store) *y_run = v;
+                } else {
+                    *out_run = v;
+                }
+            }
+            y_run += tile_stride_rows;
+            out_run += kTileRows * NB;
+            tile_first += blk_stride;
+            if (L::kRedParities == 2) parity_off ^= static_cast<uint32_t>(kWarps * NB * kRedRow);
+            if (++stage == NS) {
+                stage = 0;
+                phase ^= 1u;
             }
         }
     }
@@ -448,9 +472,9 @@ EncodeTiledFn encode_tiled() {
 }
 
 // Clusters of `ksplit` CTAs of this kernel the device can hold at once (GPC packing), cached.
-template <int MT, int SPW>
+template <int MT>
 int32_t max_active_clusters(const DeviceContext& ctx, uint32_t ksplit, uint32_t* out) {
-    auto kernel = nf4_gemv_tma_kernel<MT, SPW>;
+    auto kernel = nf4_gemv_tma_kernel<MT>;
     static bool configured = false;
     static int cached[9] = {0};
     if (!configured) {
@@ -459,7 +483,7 @@ int32_t max_active_clusters(const DeviceContext& ctx, uint32_t ksplit, uint32_t*
     }
     if (cached[ksplit] == 0) {
         cudaLaunchConfig_t config = {};
-        config.blockDim = dim3(Layout<MT>::kThreads);
+        config.blockDim = dim3(kThreads);
         config.dynamicSmemBytes = Layout<MT>::kSmemBytes;
         cudaLaunchAttribute attr[1];
         attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -479,57 +503,88 @@ int32_t max_active_clusters(const DeviceContext& ctx, uint32_t ksplit, uint32_t*
     return B2_STATUS_OK;
 }
 
-template <int MT, int SPW>
-int32_t launch_tma(const DeviceContext& ctx, const CUtensorMap& map, TmaParams p, uint32_t ksplit,
-                   cudaStream_t stream) {
-    auto kernel = nf4_gemv_tma_kernel<MT, SPW>;
+int32_t active_clusters_for(const DeviceContext& ctx, uint64_t rows, uint32_t ksplit, uint32_t* out) {
+    if (rows <= 8) return max_active_clusters<1>(ctx, ksplit, out);
+    if (rows <= 16) return max_active_clusters<2>(ctx, ksplit, out);
+    return max_active_clusters<4>(ctx, ksplit, out);
+}
+
+template <int MT>
+int32_t launch_tma(const DeviceContext& ctx, const CUtensorMap& map_w, const CUtensorMap& map_s,
+                   const CUtensorMap& map_2, TmaParams p, uint32_t ksplit, cudaStream_t stream) {
+    auto kernel = nf4_gemv_tma_kernel<MT>;
     uint32_t clusters = 0;
-    B2_TRY((max_active_clusters<MT, SPW>(ctx, ksplit, &clusters)));
+    B2_TRY((max_active_clusters<MT>(ctx, ksplit, &clusters)));
     if (clusters > p.row_tiles) clusters = p.row_tiles;
     if (clusters == 0) clusters = 1;
     if ((p.row_tiles + clusters - 1) / clusters > static_cast<uint32_t>(Layout<MT>::kMaxTiles)) {
         return fail(B2_STATUS_RUNTIME_ERROR, "internal: NF4 TMA decode kernel tile budget exceeded");
     }
     cudaLaunchConfig_t config = {};
-    config.blockDim = dim3(Layout<MT>::kThreads);
+    config.blockDim = dim3(kThreads);
     config.dynamicSmemBytes = Layout<MT>::kSmemBytes;
     config.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = ksplit;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
+    // Programmatic stream serialisation: the kernel may start while its predecessor drains; it
+    // calls griddepcontrol.wait before it reads or writes any caller tensor. B2_DISABLE_PDL=1
+    // restores plain stream order.
+    static const bool pdl = getenv("B2_DISABLE_PDL") == nullptr;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     config.attrs = attr;
-    config.numAttrs = 1;
+    config.numAttrs = pdl ? 2 : 1;
     config.gridDim = dim3(clusters * ksplit);
-    B2_CUDA_TRY(cudaLaunchKernelEx(&config, kernel, map, p));
+    B2_CUDA_TRY(cudaLaunchKernelEx(&config, kernel, map_w, map_s, map_2, p));
+    return B2_STATUS_OK;
+}
+
+int32_t encode(const char* what, CUtensorMap* map, CUtensorMapDataType type, uint32_t rank, const void* base,
+               const cuuint64_t* dims, const cuuint64_t* strides, const cuuint32_t* box, CUtensorMapSwizzle swizzle) {
+    const cuuint32_t elem[2] = {1, 1};
+    const CUresult r = encode_tiled()(map, type, rank, const_cast<void*>(base), dims, strides, box, elem,
+                                      CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        return fail(B2_STATUS_RUNTIME_ERROR, "cuTensorMapEncodeTiled failed (%d) for the %s map", static_cast<int>(r), what);
+    }
     return B2_STATUS_OK;
 }
 
 }  // namespace
 
-// Shapes the TMA decode kernel takes: whole 128-byte boxes per CTA slice, 16-byte aligned rows.
+// Shapes the TMA decode kernel takes: whole 16-row tiles, rows made of whole scale blocks, every
+// array 16-byte aligned with 16-byte aligned row pitches (what a TMA descriptor needs), and few
+// enough second-level values per tile to fit the 32-float box.
 bool nf4_gemv_tma_plan(const DeviceContext& ctx, const WeightView& w, const float* x, uint64_t rows,
                        uint32_t* ksplit_out, uint32_t* steps_per_cta_out) {
     if (rows < 1 || rows > 32 || w.in_features % kStepK != 0 || w.block_size < kStepK) return false;
     if ((reinterpret_cast<uintptr_t>(w.codes) & 15u) != 0 || (reinterpret_cast<uintptr_t>(x) & 15u) != 0) return false;
     if (encode_tiled() == nullptr) return false;
     if (w.in_features % w.block_size != 0 || w.out_features % kTileRows != 0) return false;
+    const uint64_t blocks_per_row = w.in_features / w.block_size;
+    if (w.encoding == B2_SCALES_FLOAT32) {
+        if ((reinterpret_cast<uintptr_t>(w.fp32_scales) & 15u) != 0 || blocks_per_row % 4 != 0) return false;
+    } else {
+        if ((reinterpret_cast<uintptr_t>(w.scale_codes) & 15u) != 0 || blocks_per_row % 16 != 0) return false;
+        if ((reinterpret_cast<uintptr_t>(w.second_level) & 15u) != 0) return false;
+        if (((kTileRows * blocks_per_row) >> w.scale_block_shift) + 5 > static_cast<uint64_t>(kSecondBox)) return false;
+    }
     const uint64_t steps = w.in_features / kStepK;
-    const uint64_t row_tiles = (w.out_features + kTileRows - 1) / kTileRows;
+    const uint64_t row_tiles = w.out_features / kTileRows;
     if (steps > 0xFFFFFFull || row_tiles > 0x7FFFFFFull || w.out_features > 0x7FFFFFFFull) return false;
-    if ((w.out_features + 2048) * (w.in_features / w.block_size + 1) + w.flat_block_base > 0xFFFFFFFFull) return false;
-    const uint64_t cap = rows <= 8 ? 64 : 32;   // steps one CTA covers (16 warps x 4 or 2)
+    if ((w.out_features + 2048) * (blocks_per_row + 1) + w.flat_block_base > 0xFFFFFFFFull) return false;
+    const uint64_t cap = rows <= 16 ? 64 : 32;   // steps one CTA covers (16 warps x 4 or 2)
     uint64_t ks = (steps + cap - 1) / cap;
     if (ks > 8) return false;
     uint64_t per = (steps + ks - 1) / ks;
     per = (per + 3) / 4 * 4;
     if (per > cap) return false;
     uint32_t active = 0;
-    const int32_t st = rows <= 8    ? max_active_clusters<1, 4>(ctx, static_cast<uint32_t>(ks), &active)
-                       : rows <= 16 ? max_active_clusters<2, 2>(ctx, static_cast<uint32_t>(ks), &active)
-                                    : max_active_clusters<4, 2>(ctx, static_cast<uint32_t>(ks), &active);
-    if (st != B2_STATUS_OK) {
+    if (active_clusters_for(ctx, rows, static_cast<uint32_t>(ks), &active) != B2_STATUS_OK) {
         clear_error();
         return false;
     }
@@ -544,15 +599,35 @@ bool nf4_gemv_tma_plan(const DeviceContext& ctx, const WeightView& w, const floa
 
 int32_t launch_nf4_gemv_tma(const DeviceContext& ctx, const WeightView& w, const float* x, float* y,
                             uint64_t rows, uint32_t ksplit, uint32_t steps_per_cta, cudaStream_t stream) {
-    CUtensorMap map;
-    const cuuint64_t dims[2] = {w.in_features / 2, w.out_features};
-    const cuuint64_t strides[1] = {w.in_features / 2};
-    const cuuint32_t box[2] = {128, kTileRows};
-    const cuuint32_t elem[2] = {1, 1};
-    const CUresult r = encode_tiled()(&map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t*>(w.codes), dims,
-                                      strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                                      CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return fail(B2_STATUS_RUNTIME_ERROR, "cuTensorMapEncodeTiled failed (%d)", static_cast<int>(r));
+    const uint64_t blocks_per_row = w.in_features / w.block_size;
+    CUtensorMap map_w, map_s, map_2;
+    {
+        const cuuint64_t dims[2] = {w.in_features / 2, w.out_features};
+        const cuuint64_t strides[1] = {w.in_features / 2};
+        const cuuint32_t box[2] = {128, kTileRows};
+        B2_TRY(encode("codes", &map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, w.codes, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B));
+    }
+    if (w.encoding == B2_SCALES_FLOAT32) {
+        const cuuint64_t dims[2] = {blocks_per_row, w.out_features};
+        const cuuint64_t strides[1] = {blocks_per_row * 4};
+        const cuuint32_t box[2] = {kScaleBoxF32, kTileRows};
+        B2_TRY(encode("fp32 scales", &map_s, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, w.fp32_scales, dims, strides, box,
+                      CU_TENSOR_MAP_SWIZZLE_NONE));
+        map_2 = map_s;   // never used for this encoding
+    } else {
+        const cuuint64_t dims[2] = {blocks_per_row, w.out_features};
+        const cuuint64_t strides[1] = {blocks_per_row};
+        const cuuint32_t box[2] = {kScaleBoxU8, kTileRows};
+        B2_TRY(encode("scale codes", &map_s, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, w.scale_codes, dims, strides, box,
+                      CU_TENSOR_MAP_SWIZZLE_NONE));
+        // second-level values this view's blocks refer to: indices [0, last] of the shared array
+        const uint64_t last = (w.flat_block_base + w.out_features * blocks_per_row - 1) >> w.scale_block_shift;
+        const cuuint64_t dims2[1] = {last + 1};
+        const cuuint64_t strides2[1] = {0};   // rank 1 has no strides; the pointer must still be valid
+        const cuuint32_t box2[1] = {kSecondBox};
+        B2_TRY(encode("second-level", &map_2, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 1, w.second_level, dims2, strides2, box2,
+                      CU_TENSOR_MAP_SWIZZLE_NONE));
+    }
     TmaParams p;
     p.w = w;
     p.x = x;
@@ -560,13 +635,13 @@ int32_t launch_nf4_gemv_tma(const DeviceContext& ctx, const WeightView& w, const
     p.rows = static_cast<uint32_t>(rows);
     p.steps_total = static_cast<uint32_t>(w.in_features / kStepK);
     p.steps_per_cta = steps_per_cta;
-    p.row_tiles = static_cast<uint32_t>((w.out_features + kTileRows - 1) / kTileRows);
-    p.blocks_per_row = w.in_features % w.block_size == 0 ? static_cast<uint32_t>(w.in_features / w.block_size) : 0u;
+    p.row_tiles = static_cast<uint32_t>(w.out_features / kTileRows);
+    p.blocks_per_row = static_cast<uint32_t>(blocks_per_row);
     p.lut = ctx.gemv_lut;
     p.error = ctx.gemm_error;
-    if (rows <= 8) return launch_tma<1, 4>(ctx, map, p, ksplit, stream);
-    if (rows <= 16) return launch_tma<2, 2>(ctx, map, p, ksplit, stream);
-    return launch_tma<4, 2>(ctx, map, p, ksplit, stream);
+    if (rows <= 8) return launch_tma<1>(ctx, map_w, map_s, map_2, p, ksplit, stream);
+    if (rows <= 16) return launch_tma<2>(ctx, map_w, map_s, map_2, p, ksplit, stream);
+    return launch_tma<4>(ctx, map_w, map_s, map_2, p, ksplit, stream);
 }
 
 }  // namespace b2

@@ -46,6 +46,7 @@ __device__ __forceinline__ float4 ldg_stream_f4(const float* p) {
 template <int REP>
 __global__ void __launch_bounds__(kFastWarps * 32)
 paged_decode_fast_kernel(const PagedDecodeArgs a, float* __restrict__ partials, uint32_t max_splits) {
+    sm100::pdl_launch_dependents();   // a following decode GEMV may start its set-up now
     const uint32_t split = blockIdx.x, kvh = blockIdx.y, seq = blockIdx.z;
     const uint32_t len = __ldg(a.seq_lens + seq);
     const uint32_t n_splits = (len + kTokensPerCta - 1) / kTokensPerCta;
@@ -251,6 +252,7 @@ __device__ __forceinline__ float4 lds_f4(uint32_t a) {
 template <int REP>
 __global__ void __launch_bounds__(kFastWarps * 32)
 paged_decode_bulk_kernel(const PagedDecodeArgs a, float* __restrict__ partials, uint32_t max_splits) {
+    sm100::pdl_launch_dependents();   // a following decode GEMV may start its set-up now
     using namespace sm100;
     const uint32_t split = blockIdx.x, kvh = blockIdx.y, seq = blockIdx.z;
     const uint32_t len = __ldg(a.seq_lens + seq);
@@ -468,6 +470,7 @@ paged_decode_bulk_kernel(const PagedDecodeArgs a, float* __restrict__ partials, 
 __global__ void __launch_bounds__(kD)
 paged_decode_merge_kernel(const PagedDecodeArgs a, const float* __restrict__ partials,
                           uint32_t max_splits) {
+    sm100::pdl_launch_dependents();   // a following decode GEMV may start its set-up now
     const uint32_t h = blockIdx.x, seq = blockIdx.y, c = threadIdx.x;
     const uint32_t len = __ldg(a.seq_lens + seq);
     const uint32_t n_splits = (len + kTokensPerCta - 1) / kTokensPerCta;

@@ -54,6 +54,20 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
     return false;
 }
 
+// ---- programmatic dependent launch ---------------------------------------------------------
+
+// Lets the next kernel in the stream start its prologue while this grid is still running (it only
+// takes effect when that kernel was launched with programmatic stream serialisation).
+__device__ __forceinline__ void pdl_launch_dependents() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+// Blocks until every kernel this grid depends on has completed and its writes are visible. A
+// kernel launched with programmatic stream serialisation must call this before it reads anything
+// an earlier kernel may have written, and before its own first global write.
+__device__ __forceinline__ void pdl_wait() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
 // ---- proxies and fences --------------------------------------------------------------
 
 // Makes generic-proxy shared-memory writes visible to the async proxy (TMA, tcgen05).
