@@ -289,7 +289,7 @@ def kernel_measurements(torch, b2, synth, peaks) -> dict:
     us = time_graph(torch, lambda: b2.paged_decode_attention(q, pool, tables, dlens, ctx, mx, status=status,
                                                              workspace=ws), 10, 1)
     kv_bytes = int(lens.sum()) * 8 * 128 * 4 * 2
-    out["paged_decode_c4"] = {"kernel": "paged_decode_fast_kernel(+merge)", "bound": "hbm", "unit": "GB/s",
+    out["paged_decode_c4"] = {"kernel": "paged_decode_bulk_kernel(+merge)", "bound": "hbm", "unit": "GB/s",
                               "us": round(us, 1), "kv_bytes": kv_bytes, "gbps": round(kv_bytes / us / 1e3, 1),
                               "frac": round(kv_bytes / us / 1e3 / peaks["hbm_gbs"], 4),
                               "status": int(status.item())}
@@ -400,7 +400,7 @@ def run_b200(args) -> None:
     attn_us = max_over_ranks(time_graph(torch, attention_all_layers, 5, cfg.layers))
     kv_bytes_launch = inputs["kv_bytes_per_step"] / cfg.layers
     achieved = kv_bytes_launch / attn_us / 1e3
-    roofline = {"kernel": "paged_decode_fast_kernel(+merge)", "bound": "hbm", "achieved": achieved,
+    roofline = {"kernel": "paged_decode_bulk_kernel(+merge)", "bound": "hbm", "achieved": achieved,
                 "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
                 "peak_source": peak_kind, "traffic": None, "us_per_launch": attn_us,
                 "share_of_step": attn_us * cfg.layers / 1e3 / ms_per_step}
