@@ -234,6 +234,26 @@ int32_t linear_forward_impl(const b2_nf4_weight* weight, const float* x, float* 
     if (aliases_weight(weight, y)) {
         return fail(B2_STATUS_INVALID_ARGUMENT, "quantized linear weight and output storage must not alias");
     }
+    static const char* gemm_off = getenv("B2_DISABLE_TENSOR_GEMM");
+    // 33..128 batch rows: the skinny tcgen05 kernel. 17..32 rows prefer the decode GEMV below (it
+    // measures faster there) and fall back to the skinny kernel for shapes the GEMV's TMA plan does
+    // not take. B2_DISABLE_SKINNY_GEMM=1 sends everything above 32 rows to the 256 x 256 tile kernel.
+    static const char* skinny_off = getenv("B2_DISABLE_SKINNY_GEMM");
+    const bool skinny_ok = gemm_off == nullptr && skinny_off == nullptr && nf4_skinny_supported(w, x, rows);
+    bool take_skinny = skinny_ok && rows > 32;
+    if (skinny_ok && rows <= 32) {
+        uint32_t ks = 0, per = 0;
+        take_skinny = !(nf4_gemv_supported(w, x, y, rows) &&
+                        (nf4_gemv_tma_plan(*ctx, w, x, rows, &ks, &per) || nf4_gemv_tma_plan(*ctx, w, x, 16, &ks, &per)));
+    }
+    if (take_skinny) {
+        if (workspace == nullptr) {
+            B2_TRY(reserve_arena(ctx, nf4_skinny_workspace_bytes(w, rows)));
+            workspace = ctx->arena;
+            workspace_bytes = ctx->arena_bytes;
+        }
+        return launch_nf4_skinny(*ctx, w, x, y, rows, workspace, workspace_bytes, stream);
+    }
     if (nf4_gemv_supported(w, x, y, rows)) {
         // B2_GEMV_IMPL=tile forces the non-persistent kernel (for A/B measurements).
         static const char* impl = getenv("B2_GEMV_IMPL");
@@ -273,7 +293,6 @@ int32_t linear_forward_impl(const b2_nf4_weight* weight, const float* x, float* 
         }
         return launch_nf4_gemv(*ctx, w, x, y, rows, stream);
     }
-    static const char* gemm_off = getenv("B2_DISABLE_TENSOR_GEMM");
     if (gemm_off == nullptr && nf4_gemm_supported(w, x, rows, false)) {
         const size_t need = nf4_gemm_workspace_bytes(w, rows, false);
         if (workspace == nullptr) {
@@ -410,6 +429,9 @@ size_t b2_nf4_linear_workspace_bytes(const b2_nf4_weight* weight, uint64_t rows,
     WeightView w;
     if (make_weight_view(weight, &w) != B2_STATUS_OK) return 0;
     clear_error();
+    if (backward == 0 && nf4_skinny_supported(w, reinterpret_cast<const float*>(16), rows)) {
+        return nf4_skinny_workspace_bytes(w, rows);
+    }
     if (!nf4_gemm_supported(w, reinterpret_cast<const float*>(16), rows, backward != 0)) return 0;
     return nf4_gemm_workspace_bytes(w, rows, backward != 0);
 }

@@ -38,6 +38,11 @@ int32_t launch_nf4_gemv_tma(const DeviceContext& ctx, const WeightView& w, const
 
 // nf4_gemm_sm100.cu - tcgen05 prefill GEMM, rows > 32.
 int32_t init_gemm_lut(DeviceContext* ctx);
+// Skinny forward (17..128 batch rows): weight rows as the N operand, one or two waves of CTAs.
+bool nf4_skinny_supported(const WeightView& w, const float* x, uint64_t rows);
+size_t nf4_skinny_workspace_bytes(const WeightView& w, uint64_t rows);
+int32_t launch_nf4_skinny(const DeviceContext& ctx, const WeightView& w, const float* x, float* y, uint64_t rows,
+                          void* workspace, size_t workspace_bytes, cudaStream_t stream);
 bool nf4_gemm_supported(const WeightView& w, const float* x, uint64_t rows, bool backward);
 size_t nf4_gemm_workspace_bytes(const WeightView& w, uint64_t rows, bool backward);
 int32_t launch_nf4_gemm(const DeviceContext& ctx, const WeightView& w, const float* x, float* y, uint64_t rows,

@@ -45,6 +45,33 @@ def test_gemm_small_shapes(b2, port, rows, out_f, in_f, block, dq):
         assert rel_l2(y[r], want[r]) <= GEMM_TOL
 
 
+@pytest.mark.parametrize("rows,out_f,in_f,block,dq", [
+    (17, 4096, 4096, 64, True),      # 32-row tiles, one TMEM quarter
+    (32, 14336, 4096, 64, True),     # 112-row tiles, 128 CTAs
+    (32, 4096, 14336, 64, True),     # long contraction
+    (33, 1000, 256, 64, True),       # ragged last tile, second TMEM quarter with one row
+    (64, 4096, 4096, 128, False),    # FP32 scales, block 128
+    (128, 1024, 512, 64, True),      # every TMEM lane, 16-row tiles
+    (100, 32000, 1024, 64, True),    # two waves of tiles
+])
+def test_skinny_batches(b2, port, rows, out_f, in_f, block, dq):
+    """17..128 batch rows: the weight tile is the N operand, the batch the M operand."""
+    rng = np.random.default_rng(rows * 11 + out_f)
+    W = (rng.standard_normal((out_f, in_f)) * 0.02).astype(np.float32)
+    host = port.quantize_nf4_double_quantized(W, block, 256) if dq else port.quantize_nf4(W, block)
+    x = rng.standard_normal((rows, in_f)).astype(np.float32)
+    w = b2.PackedNf4Weight.from_host(host)
+    y = forward(b2, w, torch.from_numpy(x).cuda())
+    want = port.linear_forward(host, x)
+    assert np.isfinite(y).all()
+    assert rel_l2(y, want) <= GEMM_TOL
+    for r in range(rows):
+        assert rel_l2(y[r], want[r]) <= GEMM_TOL
+    # same bits on a second run
+    y2 = forward(b2, w, torch.from_numpy(x).cuda())
+    assert (y.view(np.uint32) == y2.view(np.uint32)).all()
+
+
 def test_gemm_config3_sampled_rows(b2, port):
     # baseline configuration 3, forward: M = 4096 tokens through 4096 -> 14336, checked on 24 rows
     rng = np.random.default_rng(1234)

@@ -138,10 +138,12 @@ def test_gemv_config2(b2, port, c2_weights, shape, rows):
     y = forward(b2, w, dev(x))
     want = port.linear_forward(host, x)
     assert np.isfinite(y).all()
-    assert rel_l2(y, want) <= GEMV_TOL
+    # up to 16 rows: fp16 operands, FP32 block scales (2e-3); above, the bf16 tensor-core path (1e-2)
+    tol = GEMV_TOL if rows <= 16 else 1e-2
+    assert rel_l2(y, want) <= tol
     # every row separately, so a wrong batch row cannot hide in the norm
     for r in range(rows):
-        assert rel_l2(y[r], want[r]) <= GEMV_TOL
+        assert rel_l2(y[r], want[r]) <= tol
 
 
 @pytest.mark.parametrize("out_f,in_f,block,rows,dq", [
