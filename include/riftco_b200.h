@@ -247,6 +247,26 @@ B2_API int32_t b2_add(const float* a, const float* b, float* out, uint64_t n, vo
 B2_API int32_t b2_gather_rows(const float* table, const uint32_t* ids, float* out, uint32_t rows,
                               uint32_t width, uint32_t vocab, uint32_t* status, void* stream);
 
+/* All-gather of column shards over NVLink peer memory (tensor-parallel decode:
+ * the reference keeps activations whole and shards nothing, so this call has no
+ * reference counterpart; it joins the row-sharded outputs of b2_nf4_linear_forward,
+ * src/core/backend/nn/quantized_linear/reference/operations.cpp:49-81, across GPUs).
+ * local[rows, cols] holds this rank's columns rank*cols .. of the full activation;
+ * the kernel stores them into full[rows, world*cols] of EVERY rank and returns
+ * once every rank's columns have arrived here.
+ *   peer_full   device array [world] of addresses: each rank's full buffer
+ *   peer_flags  device array [world] of addresses: each rank's uint32[world] flag array
+ *   state       local device uint32[2], zero before the first call (epoch, CTA counter)
+ *   status      local device word; B2_PEER_STATUS_TIMEOUT is set when a peer did not
+ *               arrive within two seconds (the kernel then returns, it never hangs)
+ * Buffers must be peer-mapped (e.g. CUDA IPC / symmetric memory), cols a multiple
+ * of 4, and consecutive gathers must not reuse the same full buffer. Every rank
+ * must issue the same sequence of gathers. */
+#define B2_PEER_STATUS_TIMEOUT 16u
+B2_API int32_t b2_peer_all_gather_columns(const float* local, uint64_t rows, uint64_t cols,
+                                          const uint64_t* peer_full, const uint64_t* peer_flags, uint32_t rank,
+                                          uint32_t world, uint32_t* state, uint32_t* status, void* stream);
+
 /* out[r] = index of the first maximum of logits[r,:] (greedy sampling,
  * src/stages/serving/generation.cpp:100-120). */
 B2_API int32_t b2_argmax(const float* logits, uint32_t* out, uint32_t rows, uint32_t width, void* stream);

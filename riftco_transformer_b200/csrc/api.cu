@@ -565,6 +565,31 @@ int32_t b2_argmax(const float* logits, uint32_t* out, uint32_t rows, uint32_t wi
     return launch_argmax(logits, out, rows, width, static_cast<cudaStream_t>(stream));
 }
 
+int32_t b2_peer_all_gather_columns(const float* local, uint64_t rows, uint64_t cols, const uint64_t* peer_full,
+                                   const uint64_t* peer_flags, uint32_t rank, uint32_t world, uint32_t* state,
+                                   uint32_t* status_word, void* stream) {
+    clear_error();
+    int32_t status = B2_STATUS_OK;
+    DeviceContext* ctx = device_context(&status);
+    if (ctx == nullptr) return status;
+    if (local == nullptr || peer_full == nullptr || peer_flags == nullptr || state == nullptr ||
+        status_word == nullptr) {
+        return fail(B2_STATUS_INVALID_ARGUMENT, "peer all-gather needs non-null pointers");
+    }
+    if (rows == 0 || cols == 0 || cols % 4 != 0 || world == 0 || world > 64 || rank >= world) {
+        return fail(B2_STATUS_INVALID_ARGUMENT,
+                    "peer all-gather needs positive sizes, cols a multiple of 4 and rank < world <= 64");
+    }
+    if ((reinterpret_cast<uintptr_t>(local) & 15u) != 0) {
+        return fail(B2_STATUS_INVALID_ARGUMENT, "peer all-gather shard must be 16-byte aligned");
+    }
+    if (rows * cols * world > 0xFFFFFFFFull || rows > 0xFFFFFFFFull || cols > 0xFFFFFFFFull) {
+        return fail(B2_STATUS_OVERFLOW, "peer all-gather activation too large");
+    }
+    return launch_peer_gather(*ctx, local, rows, cols, peer_full, peer_flags, rank, world, state, status_word,
+                              static_cast<cudaStream_t>(stream));
+}
+
 // ---- host-buffer seam ---------------------------------------------------------
 
 int32_t b2_check_device_errors(void) {

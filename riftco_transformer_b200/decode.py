@@ -23,6 +23,7 @@ C ABI and has no CPU fallback.
 from __future__ import annotations
 
 import ctypes as C
+import os
 from dataclasses import dataclass
 
 import torch
@@ -66,17 +67,57 @@ def weight_shapes(cfg: DecoderConfig) -> dict[str, tuple[int, int]]:
 
 
 class CudaOps:
-    """Product backend: torch tensors for memory, the C ABI for arithmetic,
-    torch.distributed (NCCL) for the all-gather."""
+    """Product backend: torch tensors for memory, the C ABI for arithmetic.
+
+    With more than one rank the activations are joined by the library's own
+    peer-store all-gather kernel: the gathered buffers live in symmetric memory
+    (torch.distributed._symmetric_memory exchanges the peer mappings, nothing
+    else), every rank stores its shard straight into every rank's buffer over
+    NVLink and waits, with a time limit, for the others. ``B2_PEER_GATHER=0``
+    selects the NCCL all-gather (plus a layout copy) instead."""
 
     def __init__(self, device, group=None) -> None:
         self.device = device
         self.group = group
         self.world = 1 if group is None else torch.distributed.get_world_size(group)
+        self.rank = 0 if group is None else torch.distributed.get_rank(group)
         self.launches = 0
+        self.peer = (self.world > 1 and torch.device(device).type == "cuda"
+                     and os.environ.get("B2_PEER_GATHER", "1") != "0")
+        self._peer_ptrs: dict = {}
+        if self.peer:
+            import torch.distributed._symmetric_memory as symm
+            self._symm = symm
+            # flag array (one slot per rank), local epoch / CTA counter, status word
+            self._flags = symm.empty((64,), dtype=torch.int32, device=self.device)
+            self._flags.zero_()
+            handle = symm.rendezvous(self._flags, self.group)
+            self._flag_handle = handle
+            self._flag_ptrs = torch.tensor([int(p) for p in handle.buffer_ptrs], dtype=torch.int64,
+                                           device=self.device)
+            self._peer_state = torch.zeros((2,), dtype=torch.int32, device=self.device)
+            self.peer_status = torch.zeros((1,), dtype=torch.int32, device=self.device)
+            torch.cuda.synchronize(self.device)
+            torch.distributed.barrier(group=self.group)
 
     def empty(self, shape, dtype=torch.float32):
         return torch.empty(shape, dtype=dtype, device=self.device)
+
+    def gathered_buffer(self, shape):
+        """Buffer that receives an all-gather: peer-mapped when the peer-store gather is in use."""
+        if not self.peer:
+            return self.empty(shape)
+        t = self._symm.empty(tuple(shape), dtype=torch.float32, device=self.device)
+        handle = self._symm.rendezvous(t, self.group)
+        ptrs = torch.tensor([int(p) for p in handle.buffer_ptrs], dtype=torch.int64, device=self.device)
+        self._peer_ptrs[t.data_ptr()] = (handle, ptrs)
+        return t
+
+    def check_peer_status(self) -> None:
+        """Raises if a peer-store gather gave up waiting for another rank."""
+        if self.peer and int(self.peer_status.item()) != 0:
+            raise RuntimeError("peer all-gather timed out waiting for another rank "
+                               f"(status {int(self.peer_status.item())})")
 
     def linear(self, x, w: PackedNf4Weight, out) -> None:
         ws = w.struct()
@@ -132,6 +173,16 @@ class CudaOps:
         r*n). `gathered` is a [world, B, n] staging buffer."""
         if self.world == 1:
             raise RuntimeError("all_gather_columns is only used with more than one rank")
+        if self.peer:
+            entry = self._peer_ptrs.get(full.data_ptr())
+            if entry is None:
+                raise RuntimeError("peer all-gather target was not allocated with gathered_buffer()")
+            _check(lib.b2_peer_all_gather_columns(local.data_ptr(), local.shape[0], local.shape[1],
+                                                  entry[1].data_ptr(), self._flag_ptrs.data_ptr(), self.rank,
+                                                  self.world, self._peer_state.data_ptr(),
+                                                  self.peer_status.data_ptr(), _stream_ptr(None)))
+            self.launches += 1
+            return
         torch.distributed.all_gather_into_tensor(gathered.view(-1, local.shape[1]), local, group=self.group)
         full.view(local.shape[0], self.world, local.shape[1]).copy_(gathered.permute(1, 0, 2))
 
@@ -149,6 +200,7 @@ class DecodeStep:
         d, hd = cfg.d_model, cfg.head_dim
         self.hq, self.hkv = cfg.q_heads // world, cfg.kv_heads // world
         e = ops.empty
+        g = getattr(ops, "gathered_buffer", ops.empty)   # peer-mapped where the backend gathers by peer stores
         B = batch
         self.x = e((B, d))
         self.n = e((B, d))
@@ -156,17 +208,17 @@ class DecodeStep:
         self.k = e((B, self.hkv, hd))
         self.v = e((B, self.hkv, hd))
         self.ctx_local = e((B, self.hq, hd))
-        self.ctx = e((B, cfg.q_heads * hd)) if world > 1 else None
+        self.ctx = g((B, cfg.q_heads * hd)) if world > 1 else None
         self.o_local = e((B, d // world))
-        self.o = e((B, d)) if world > 1 else None
+        self.o = g((B, d)) if world > 1 else None
         self.gate = e((B, cfg.ffn // world))
         self.up = e((B, cfg.ffn // world))
         self.h_local = e((B, cfg.ffn // world))
-        self.h = e((B, cfg.ffn)) if world > 1 else None
+        self.h = g((B, cfg.ffn)) if world > 1 else None
         self.down_local = e((B, d // world))
-        self.down = e((B, d)) if world > 1 else None
+        self.down = g((B, d)) if world > 1 else None
         self.logits_local = e((B, cfg.vocab // world))
-        self.logits = e((B, cfg.vocab)) if world > 1 else None
+        self.logits = g((B, cfg.vocab)) if world > 1 else None
         self.next_tokens = e((B,), dtype=torch.int32)
         self.status = ops.empty((1,), dtype=torch.int32)
         self.workspace = ops.attention_workspace(B, self.hq, hd, cfg.block_size, max_seq_len)
