@@ -221,7 +221,8 @@ def workload_config(world: int) -> dict:
     return {"workload": "7b_decode_step", "layers": N_LAYERS, "d_model": 4096, "q_heads": 32, "kv_heads": 8,
             "head_dim": 128, "ffn": 14336, "vocab": 32000, "batch": BATCH, "context": CONTEXT,
             "weights": "nf4 block 64, double-quantised scales (u8 + f32 per 256)", "kv": "f32 pages of 16",
-            "sharding": f"output rows / kv heads over {world} gpu(s), nccl all-gather at layer boundaries",
+            "sharding": f"output rows / kv heads over {world} gpu(s); activations joined at layer boundaries by the "
+                        "library's peer-store all-gather kernel over NVLink (B2_PEER_GATHER=0: NCCL all-gather)",
             "l2": "each step reads ~21 GB of weights and KV, far larger than L2"}
 
 
@@ -363,6 +364,9 @@ def run_b200(args) -> None:
             graph.replay()
         torch.cuda.synchronize()
     clocks = sampler.summary()
+    # a bounded wait that ran out (barrier, peer all-gather) invalidates the measurement
+    b2.check_device_errors()
+    step.ops.check_peer_status()
     elapsed_ms = max_over_ranks(elapsed_ms)
     ms_per_step = elapsed_ms / args.steps
     value = BATCH / (ms_per_step / 1e3)
