@@ -231,8 +231,9 @@ class Reference:
 
     kind = "reference"
 
-    def __init__(self) -> None:
-        path = _build.build_reference()
+    def __init__(self, path=None) -> None:
+        if path is None:
+            path = _build.build_reference()
         if path is None or not Path(path).exists():
             raise FileNotFoundError("oracle/_ref/libriftco_ref.so is not built and no reference checkout is present")
         self.lib = C.CDLL(str(path))
@@ -375,6 +376,21 @@ def ref() -> Reference:
     if _ref is None:
         _ref = Reference()
     return _ref
+
+
+def ref_with_b200_adapter() -> Reference:
+    """The reference's core linked with the product's CUDA adapter
+    (riftco_transformer_b200/adapter/cuda_b200_adapter.cpp) and switched to
+    ExecutionBackend::Cuda: the reference's own dispatch layer in front of the
+    B200 kernels. Test infrastructure, like everything in this package."""
+    path = _build.build_reference_with_b200_adapter()
+    if path is None or not Path(path).exists():
+        raise FileNotFoundError("oracle/_ref/libriftco_ref_b200.so is not built and no reference checkout is present")
+    r = Reference(path)
+    r.lib.ref_set_backend.argtypes = [C.c_int]
+    if r.lib.ref_set_backend(2) != 0:
+        raise RuntimeError("the CUDA backend is not available behind the reference's dispatch layer")
+    return r
 
 
 def ref_available() -> bool:

@@ -29,6 +29,7 @@ BUILD_DIR = HERE / "_build"
 REF_DIR = HERE / "_ref"
 ORACLE_LIB = BUILD_DIR / "libriftco_oracle.so"
 REF_LIB = REF_DIR / "libriftco_ref.so"
+REF_B200_LIB = REF_DIR / "libriftco_ref_b200.so"
 
 DEFAULT_REFERENCE_DIR = "/root/reference"
 
@@ -131,10 +132,47 @@ def build_reference(force: bool = False) -> Path | None:
     return REF_LIB
 
 
+def build_reference_with_b200_adapter(force: bool = False) -> Path | None:
+    """The reference's core with its CUDA seam defined by
+    riftco_transformer_b200/adapter/cuda_b200_adapter.cpp instead of adapters/cuda/stub.cpp,
+    linked against the product library: lets the tests drive the reference's own
+    dispatch layer on ExecutionBackend::Cuda. None without a checkout or without
+    the product library."""
+    root = reference_dir()
+    product = HERE.parent / "riftco_transformer_b200" / "lib" / "libriftco_b200.so"
+    if root is None or not product.exists():
+        return REF_B200_LIB if REF_B200_LIB.exists() else None
+    if build_reference(force) is None:
+        return None
+    adapter = HERE.parent / "riftco_transformer_b200" / "adapter" / "cuda_b200_adapter.cpp"
+    stub = root / "src/core/backend/adapters/cuda/stub.cpp"
+    sources = [root / s for s in REFERENCE_SOURCES if (root / s) != stub] + [HERE / "ref_bridge.cpp"]
+    if not force and _newer(REF_B200_LIB, sources + [adapter, product]):
+        return REF_B200_LIB
+    obj_dir = REF_DIR / "obj"
+    cuda = Path(os.environ.get("CUDA_HOME", "/usr/local/cuda"))
+    includes = ["-I", str(root / "include"), "-I", str(root / "src"), "-I", str(HERE.parent / "include"),
+                "-I", str(cuda / "include")]
+    adapter_obj = obj_dir / "cuda_b200_adapter.o"
+    _run(["g++", *CXXFLAGS, *includes, "-c", str(adapter), "-o", str(adapter_obj)])
+    objects = []
+    for src in sources:   # compiled by build_reference() above
+        tag = hashlib.sha1(str(src).encode()).hexdigest()[:12]
+        objects.append(obj_dir / f"{src.stem}-{tag}.o")
+    _run([
+        "g++", "-shared", "-pthread", "-o", str(REF_B200_LIB), *map(str, objects), str(adapter_obj),
+        "-L", str(product.parent), "-lriftco_b200", "-L", str(cuda / "lib64"), "-lcudart",
+        "-Wl,-rpath,$ORIGIN/../../riftco_transformer_b200/lib", "-Wl,-rpath," + str(cuda / "lib64"),
+        "-Wl,--no-undefined",
+    ])
+    return REF_B200_LIB
+
+
 def main() -> None:
     force = "--force" in sys.argv
     print("oracle:", build_oracle(force))
     print("reference:", build_reference(force))
+    print("reference + B200 adapter:", build_reference_with_b200_adapter(force))
 
 
 if __name__ == "__main__":

@@ -15,7 +15,9 @@
 //                                  (src/core/backend/attention/dispatch.cpp:440-509)
 //   dispatch_materialized_causal_attention_forward (used by the reference's own
 //   paged-decode test as its expected value, tests/core/backend/test_nn_backend.cpp:2079-2216)
-// all on ExecutionBackend::Cpu.
+// on ExecutionBackend::Cpu unless ref_set_backend() selected another one (the
+// library variant linked with riftco_transformer_b200/adapter/cuda_b200_adapter.cpp
+// uses it to drive the reference's dispatch layer on ExecutionBackend::Cuda).
 #include "core/backend/attention/dispatch.hpp"
 #include "core/backend/nn/quantized_linear/dispatch.hpp"
 #include "core/quantization/nf4.hpp"
@@ -42,6 +44,14 @@ using riftco_transformer::Tensor;
 namespace backend = riftco_transformer::backend_detail;
 
 thread_local std::string g_error;
+ExecutionBackend g_backend = ExecutionBackend::Cpu;
+
+// Quantisation and dequantisation are host algorithms: they always run on the CPU backend.
+struct CpuScope {
+    ExecutionBackend saved = g_backend;
+    CpuScope() { g_backend = ExecutionBackend::Cpu; }
+    ~CpuScope() { g_backend = saved; }
+};
 
 // Same numeric codes as rt_status (include/riftco_transformer/c_api.h:41-49)
 // with the mapping of src/c_api/internal/error.hpp; domain_error gets its own
@@ -95,7 +105,7 @@ private:
 
 Tensor tensor_from(const float* p, std::size_t rows, std::size_t cols) {
     return Tensor({rows, cols}, std::vector<float>(p, p + rows * cols),
-                  ExecutionBackend::Cpu);
+                  g_backend);
 }
 
 QuantizedWeight weight_from(const std::uint8_t* codes, const float* fp32_scales,
@@ -119,7 +129,7 @@ QuantizedWeight weight_from(const std::uint8_t* codes, const float* fp32_scales,
         payload.double_quantized_scales = std::move(nested);
     }
     return QuantizedWeight::from_packed_nf4({out, in}, block, std::move(payload),
-                                            ExecutionBackend::Cpu);
+                                            g_backend);
 }
 
 }  // namespace
@@ -127,6 +137,14 @@ QuantizedWeight weight_from(const std::uint8_t* codes, const float* fp32_scales,
 extern "C" {
 
 const char* ref_last_error() { return g_error.c_str(); }
+
+// 0 = Cpu (default), 2 = Cuda; returns 1 when the backend is not available in this build.
+int ref_set_backend(int backend) {
+    const ExecutionBackend b = static_cast<ExecutionBackend>(backend);
+    if (!riftco_transformer::execution_backend_available(b)) return 1;
+    g_backend = b;
+    return 0;
+}
 
 void ref_codebook(float* out16) {
     const auto cb = riftco_transformer::quantization::nf4_codebook();
@@ -141,6 +159,7 @@ std::uint8_t ref_nearest_nf4_code(float v) {
 // scales: ceil(n/block) floats.
 int ref_quantize_nf4(const float* values, std::uint64_t out, std::uint64_t in,
                      std::uint64_t block, std::uint8_t* codes, float* scales) {
+    const CpuScope cpu_only;
     return guarded([&] {
         const auto payload =
             QuantizedWeight::quantize_nf4(tensor_from(values, out, in), block)
@@ -156,6 +175,7 @@ int ref_quantize_nf4_double_quantized(const float* values, std::uint64_t out,
                                       std::uint8_t* codes,
                                       std::uint8_t* scale_codes, float* second,
                                       float* offset) {
+    const CpuScope cpu_only;
     return guarded([&] {
         const auto payload = QuantizedWeight::quantize_nf4_double_quantized(
                                  tensor_from(values, out, in), block, scale_block)
@@ -174,6 +194,7 @@ int ref_dequantize(const std::uint8_t* codes, const float* fp32_scales,
                    std::uint64_t scale_block, float offset, std::uint32_t encoding,
                    std::uint64_t block, std::uint64_t out, std::uint64_t in,
                    float* values) {
+    const CpuScope cpu_only;
     return guarded([&] {
         const Tensor dense = weight_from(codes, fp32_scales, scale_codes, second,
                                          scale_block, offset, encoding, block,
@@ -195,10 +216,10 @@ int ref_linear_forward(const std::uint8_t* codes, const float* fp32_scales,
                                               second, scale_block, offset,
                                               encoding, block, out, in);
         const Tensor input = tensor_from(x, rows, in);
-        Tensor output({rows, out}, ExecutionBackend::Cpu);
+        Tensor output({rows, out}, g_backend);
         const Stopwatch watch(seconds);
         backend::dispatch_quantized_linear_forward(
-            ExecutionBackend::Cpu,
+            g_backend,
             {backend::tensor_storage(input), backend::quantized_weight_storage(w),
              backend::tensor_storage(output), {rows, in, out, block}});
         const auto data = output.data();
@@ -218,10 +239,10 @@ int ref_linear_input_backward(const std::uint8_t* codes, const float* fp32_scale
                                               second, scale_block, offset,
                                               encoding, block, out, in);
         const Tensor upstream = tensor_from(dy, rows, out);
-        Tensor gradient({rows, in}, ExecutionBackend::Cpu);
+        Tensor gradient({rows, in}, g_backend);
         const Stopwatch watch(seconds);
         backend::dispatch_quantized_linear_input_backward(
-            ExecutionBackend::Cpu,
+            g_backend,
             {backend::tensor_storage(upstream),
              backend::quantized_weight_storage(w),
              backend::tensor_storage(gradient), {rows, in, out, block}});
@@ -242,17 +263,17 @@ int ref_paged_decode(const float* q, const float* key_pages,
         const std::size_t pool = physical_blocks * heads * block_size * width;
         const Tensor queries({heads, width},
                              std::vector<float>(q, q + heads * width),
-                             ExecutionBackend::Cpu);
+                             g_backend);
         const Tensor keys({physical_blocks, heads, block_size, width},
                           std::vector<float>(key_pages, key_pages + pool),
-                          ExecutionBackend::Cpu);
+                          g_backend);
         const Tensor values({physical_blocks, heads, block_size, width},
                             std::vector<float>(value_pages, value_pages + pool),
-                            ExecutionBackend::Cpu);
-        Tensor context({heads, width}, ExecutionBackend::Cpu);
+                            g_backend);
+        Tensor context({heads, width}, g_backend);
         const Stopwatch watch(seconds);
         backend::dispatch_paged_decode_attention_forward(
-            ExecutionBackend::Cpu,
+            g_backend,
             {backend::tensor_storage(queries), backend::tensor_storage(keys),
              backend::tensor_storage(values),
              std::span<const std::uint32_t>(table, table_len),
