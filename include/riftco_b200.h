@@ -309,6 +309,39 @@ B2_API int32_t b2_host_paged_decode_attention(const float* q_host, const float* 
                                        uint32_t block_size, uint64_t physical_blocks,
                                        uint32_t max_blocks, void* stream);
 
+/* ---- packed model state (RTNF4S1) -------------------------------------------------------
+ * The reference's canonical stream of packed NF4 linear weights
+ * (packed_model_state_bytes / parse_packed_model_state, src/c_api/model_state.cpp:27-113,
+ * 165-297): magic "RTNF4S1\0", u64 weight count, then per weight
+ *   u64 rank (= 2), u64 block_size, u64 n_codes, u64 n_fp32_scales, u64 n_scale_codes,
+ *   u64 n_second, u64 scale_block_size, f32 offset, u32 flags (1 = double-quantised),
+ *   u64 dims[2], packed codes, f32 block scales, [u8 scale codes, f32 second-level scales],
+ * everything little-endian. b2_rtnf4_index walks a stream held in host memory, applies the
+ * reference parser's checks (truncation, unknown magic or flags, rank != 2, inconsistent scale
+ * metadata, trailing bytes -> INVALID_ARGUMENT; sizes past the address space -> OVERFLOW) and
+ * reports where each array lies, so a loader can copy row shards of codes and scales straight
+ * from the stream into device memory without an FP32 detour. Writes at most `capacity`
+ * entries; *count receives the number of weights in the stream. No GPU is needed. */
+typedef struct b2_rtnf4_entry {
+    uint64_t block_size;
+    uint64_t out_features;       /* dims[0] */
+    uint64_t in_features;        /* dims[1] */
+    uint64_t n_codes;            /* packed bytes */
+    uint64_t n_fp32_scales;      /* FP32 block scales (flags 0) */
+    uint64_t n_scale_codes;      /* u8 scale codes (flags 1) */
+    uint64_t n_second;           /* FP32 second-level scales (flags 1) */
+    uint64_t scale_block_size;
+    float offset;
+    uint32_t double_quantized;   /* flags */
+    uint64_t codes_offset;       /* byte offsets from the start of the stream */
+    uint64_t fp32_scales_offset;
+    uint64_t scale_codes_offset;
+    uint64_t second_offset;
+} b2_rtnf4_entry;
+
+B2_API int32_t b2_rtnf4_index(const uint8_t* stream, uint64_t bytes, b2_rtnf4_entry* entries,
+                              uint64_t capacity, uint64_t* count);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,87 @@
+"""RTNF4S1 packed-model-state streams: the C parser's index against streams
+written with the layout of packed_model_state_bytes
+(src/c_api/model_state.cpp:27-113), and the malformed-stream cases of
+parse_packed_model_state (model_state.cpp:165-297) with the reference's
+messages. No golden stream of the reference is available for this format, so
+parity of the layout rests on restating the serializer field by field."""
+import struct
+
+import numpy as np
+import pytest
+
+
+@pytest.fixture(scope="module")
+def payloads(port):
+    rng = np.random.default_rng(77)
+    a = port.quantize_nf4_double_quantized((rng.standard_normal((48, 128)) * 0.02).astype(np.float32), 64, 16)
+    b = port.quantize_nf4((rng.standard_normal((10, 96)) * 0.5).astype(np.float32), 32)
+    c = port.quantize_nf4_double_quantized((rng.standard_normal((7, 33))).astype(np.float32), 64, 256)
+    return [a, b, c]
+
+
+def test_index_matches_what_was_written(payloads):
+    from riftco_transformer_b200 import rtnf4
+    stream = rtnf4.dumps(payloads)
+    assert stream[:8] == b"RTNF4S1\0"
+    entries = rtnf4.index(stream)
+    assert len(entries) == len(payloads)
+    raw = np.frombuffer(stream, np.uint8)
+    for e, p in zip(entries, payloads):
+        assert (e.out_features, e.in_features, e.block_size) == (p.out_features, p.in_features, p.block_size)
+        assert np.array_equal(raw[e.codes_offset:e.codes_offset + e.n_codes], p.codes)
+        if p.fp32_scales is not None:
+            assert not e.double_quantized and e.n_scale_codes == 0 and e.n_second == 0 and e.offset == 0.0
+            got = raw[e.fp32_scales_offset:e.fp32_scales_offset + 4 * e.n_fp32_scales].view("<f4")
+            assert np.array_equal(got.view(np.uint32), np.asarray(p.fp32_scales, np.float32).view(np.uint32))
+        else:
+            assert e.double_quantized and e.n_fp32_scales == 0
+            assert e.scale_block_size == p.scale_block_size and e.offset == np.float32(p.offset)
+            assert np.array_equal(raw[e.scale_codes_offset:e.scale_codes_offset + e.n_scale_codes], p.scale_codes)
+            got = raw[e.second_offset:e.second_offset + 4 * e.n_second].view("<f4")
+            assert np.array_equal(got.view(np.uint32), np.asarray(p.second_level, np.float32).view(np.uint32))
+    # entries are laid out back to back and the last one ends the stream
+    last = entries[-1]
+    end = (last.second_offset + 4 * last.n_second) if last.double_quantized else \
+        (last.fp32_scales_offset + 4 * last.n_fp32_scales)
+    assert end == len(stream)
+
+
+def test_accepts_buffers_of_any_kind(payloads):
+    from riftco_transformer_b200 import rtnf4
+    stream = rtnf4.dumps(payloads[:1])
+    for view in (stream, bytearray(stream), memoryview(stream), np.frombuffer(stream, np.uint8)):
+        assert len(rtnf4.index(view)) == 1
+
+
+def _header(rank=2, block=64, n_codes=4, n_fp32=1, n_sc=0, n_second=0, sbs=0, offset_bits=0, flags=0, dims=(1, 8)):
+    return struct.pack("<QQQQQQQII", rank, block, n_codes, n_fp32, n_sc, n_second, sbs, offset_bits, flags) + \
+        b"".join(struct.pack("<Q", d) for d in dims)
+
+
+@pytest.mark.parametrize("stream,message", [
+    (b"RTNF4S", "truncated packed model state: magic"),
+    (b"RTNF4S2\0" + struct.pack("<Q", 1) + bytes(96), "unknown packed model state format"),
+    (b"RTNF4S1\0" + struct.pack("<Q", 0), "weight count is inconsistent"),
+    (b"RTNF4S1\0" + struct.pack("<Q", 3) + bytes(100), "weight count is inconsistent"),
+    (b"RTNF4S1\0" + struct.pack("<Q", 1) + _header(rank=3, dims=(1, 2, 4)) + bytes(8), "must have rank two"),
+    (b"RTNF4S1\0" + struct.pack("<Q", 1) + _header(flags=2) + bytes(8), "unknown flags"),
+    (b"RTNF4S1\0" + struct.pack("<Q", 1) + _header(offset_bits=1) + bytes(8), "inconsistent NF4 scale metadata"),
+    (b"RTNF4S1\0" + struct.pack("<Q", 1) + _header(n_sc=1) + bytes(9), "inconsistent NF4 scale metadata"),
+    (b"RTNF4S1\0" + struct.pack("<Q", 1) + _header(flags=1, n_fp32=1, n_sc=1, n_second=1, sbs=4) + bytes(13),
+     "inconsistent NF4 scale metadata"),
+    (b"RTNF4S1\0" + struct.pack("<Q", 1) + _header(flags=1, n_fp32=0, n_sc=1, n_second=1, sbs=0) + bytes(9),
+     "inconsistent NF4 scale metadata"),
+    (b"RTNF4S1\0" + struct.pack("<Q", 1) + _header() + bytes(7), "truncated packed model state: weight payload"),
+    (b"RTNF4S1\0" + struct.pack("<Q", 1) + _header() + bytes(9), "trailing bytes"),
+])
+def test_malformed_streams_are_rejected_like_the_reference(stream, message):
+    from riftco_transformer_b200 import rtnf4
+    with pytest.raises(ValueError, match=message):
+        rtnf4.index(stream)
+
+
+def test_sizes_past_the_address_space_overflow():
+    from riftco_transformer_b200 import rtnf4
+    stream = b"RTNF4S1\0" + struct.pack("<Q", 1) + _header(n_codes=2 ** 64 - 8, n_fp32=2 ** 62) + bytes(8)
+    with pytest.raises(OverflowError, match="exceeds addressable memory"):
+        rtnf4.index(stream)
