@@ -235,6 +235,20 @@ int32_t linear_forward_impl(const b2_nf4_weight* weight, const float* x, float* 
         return fail(B2_STATUS_INVALID_ARGUMENT, "quantized linear weight and output storage must not alias");
     }
     static const char* gemm_off = getenv("B2_DISABLE_TENSOR_GEMM");
+    // B2_LINEAR_IMPL=tmem: every batch size through the kernel that keeps the expanded weight tile
+    // in tensor memory (A/B measurements).
+    static const char* linear_impl = getenv("B2_LINEAR_IMPL");
+    if (gemm_off == nullptr && linear_impl != nullptr && strcmp(linear_impl, "tmem") == 0 &&
+        nf4_gemm_tmem_supported(w, x, rows)) {
+        const size_t need = static_cast<size_t>(rows) * w.in_features * 2;
+        if (workspace == nullptr || workspace_bytes < need) {
+            B2_TRY(reserve_arena(ctx, need));
+            workspace = ctx->arena;
+            workspace_bytes = ctx->arena_bytes;
+        }
+        B2_TRY(launch_f32_to_bf16(*ctx, x, workspace, rows * w.in_features, stream));
+        return launch_nf4_gemm_tmem(*ctx, w, workspace, y, rows, stream);
+    }
     // 33..128 batch rows: the skinny tcgen05 kernel. 17..32 rows prefer the decode GEMV below (it
     // measures faster there) and fall back to the skinny kernel for shapes the GEMV's TMA plan does
     // not take. B2_DISABLE_SKINNY_GEMM=1 sends everything above 32 rows to the 256 x 256 tile kernel.

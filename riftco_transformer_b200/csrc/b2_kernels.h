@@ -43,6 +43,11 @@ bool nf4_skinny_supported(const WeightView& w, const float* x, uint64_t rows);
 size_t nf4_skinny_workspace_bytes(const WeightView& w, uint64_t rows);
 int32_t launch_nf4_skinny(const DeviceContext& ctx, const WeightView& w, const float* x, float* y, uint64_t rows,
                           void* workspace, size_t workspace_bytes, cudaStream_t stream);
+// nf4_gemm_tmem.cu - forward GEMM with the expanded weight tile as a tensor-memory operand.
+int32_t launch_f32_to_bf16(const DeviceContext& ctx, const float* src, void* dst, uint64_t count, cudaStream_t stream);
+bool nf4_gemm_tmem_supported(const WeightView& w, const float* x, uint64_t rows);
+int32_t launch_nf4_gemm_tmem(const DeviceContext& ctx, const WeightView& w, const void* x_bf16, float* y,
+                             uint64_t rows, cudaStream_t stream);
 bool nf4_gemm_supported(const WeightView& w, const float* x, uint64_t rows, bool backward);
 size_t nf4_gemm_workspace_bytes(const WeightView& w, uint64_t rows, bool backward);
 int32_t launch_nf4_gemm(const DeviceContext& ctx, const WeightView& w, const float* x, float* y, uint64_t rows,

@@ -24,6 +24,7 @@
 #include <cuda_bf16.h>
 
 #include <cstdlib>
+#include <cstring>
 #include <mutex>
 
 namespace b2 {
@@ -753,6 +754,17 @@ bool nf4_skinny_supported(const WeightView& w, const float* x, uint64_t rows) {
            w.out_features <= 0x7FFFFFFFull && w.in_features <= 0x7FFFFFFFull;
 }
 
+// fp32 -> bf16 copy of `count` values (a multiple of 4) on `stream`.
+int32_t launch_f32_to_bf16(const DeviceContext& ctx, const float* src, void* dst, uint64_t count, cudaStream_t stream) {
+    const uint64_t n4 = count / 4;
+    uint64_t blocks = (n4 + 255) / 256;
+    if (blocks > static_cast<uint64_t>(ctx.sm_count) * 16) blocks = static_cast<uint64_t>(ctx.sm_count) * 16;
+    if (blocks == 0) blocks = 1;
+    f32_to_bf16_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(src, static_cast<__nv_bfloat16*>(dst), n4);
+    B2_CUDA_TRY(cudaGetLastError());
+    return B2_STATUS_OK;
+}
+
 size_t nf4_skinny_workspace_bytes(const WeightView& w, uint64_t rows) {
     return static_cast<size_t>(rows) * w.in_features * 2;   // bf16 copy of the activations
 }
@@ -845,6 +857,13 @@ int32_t launch_nf4_gemm(const DeviceContext& ctx, const WeightView& w, const flo
     f32_to_bf16_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
         x, static_cast<__nv_bfloat16*>(workspace), n4);
     B2_CUDA_TRY(cudaGetLastError());
+
+    // Forward, B2_GEMM_IMPL=tmem: the kernel that keeps the expanded weight tile in tensor memory
+    // (not bound by the shared-memory port) instead of the shared-memory kernel below.
+    static const char* impl = getenv("B2_GEMM_IMPL");
+    if (!backward && impl != nullptr && strcmp(impl, "tmem") == 0 && nf4_gemm_tmem_supported(w, x, rows)) {
+        return launch_nf4_gemm_tmem(ctx, w, workspace, y, rows, stream);
+    }
 
     CUtensorMap map;
     B2_TRY(make_operand_map(&map, workspace, rows, k));
