@@ -235,38 +235,29 @@ int32_t linear_forward_impl(const b2_nf4_weight* weight, const float* x, float* 
         return fail(B2_STATUS_INVALID_ARGUMENT, "quantized linear weight and output storage must not alias");
     }
     static const char* gemm_off = getenv("B2_DISABLE_TENSOR_GEMM");
-    // B2_LINEAR_IMPL=tmem: every batch size through the kernel that keeps the expanded weight tile
-    // in tensor memory (A/B measurements).
+    // More than 16 batch rows: the tcgen05 kernel that keeps the expanded weight tile in tensor
+    // memory (decode batches of 17+ rows, speculative / chunked prefill, full prefill).
+    // B2_GEMM_IMPL=smem sends 17..32 rows to the decode GEMV and the rest to the shared-memory
+    // tcgen05 kernel instead; B2_LINEAR_IMPL=tmem sends every batch size here (A/B measurements).
+    static const char* gemm_impl = getenv("B2_GEMM_IMPL");
     static const char* linear_impl = getenv("B2_LINEAR_IMPL");
-    if (gemm_off == nullptr && linear_impl != nullptr && strcmp(linear_impl, "tmem") == 0 &&
-        nf4_gemm_tmem_supported(w, x, rows)) {
-        const size_t need = static_cast<size_t>(rows) * w.in_features * 2;
-        if (workspace == nullptr || workspace_bytes < need) {
+    const bool tmem_all = linear_impl != nullptr && strcmp(linear_impl, "tmem") == 0;
+    const bool tmem_off = gemm_impl != nullptr && strcmp(gemm_impl, "smem") == 0;
+    if (gemm_off == nullptr && !tmem_off && (rows > 16 || tmem_all) && nf4_gemm_tmem_supported(w, x, rows)) {
+        const size_t need = nf4_gemm_tmem_workspace_bytes(w, rows);
+        if (workspace == nullptr) {
             B2_TRY(reserve_arena(ctx, need));
             workspace = ctx->arena;
             workspace_bytes = ctx->arena_bytes;
         }
+        if (workspace_bytes < need) {
+            return fail(B2_STATUS_INVALID_ARGUMENT, "NF4 GEMM workspace too small: need %zu bytes", need);
+        }
+        if ((reinterpret_cast<uintptr_t>(workspace) & 15u) != 0) {
+            return fail(B2_STATUS_INVALID_ARGUMENT, "NF4 GEMM workspace must be 16-byte aligned");
+        }
         B2_TRY(launch_f32_to_bf16(*ctx, x, workspace, rows * w.in_features, stream));
         return launch_nf4_gemm_tmem(*ctx, w, workspace, y, rows, stream);
-    }
-    // 33..128 batch rows: the skinny tcgen05 kernel. 17..32 rows prefer the decode GEMV below (it
-    // measures faster there) and fall back to the skinny kernel for shapes the GEMV's TMA plan does
-    // not take. B2_DISABLE_SKINNY_GEMM=1 sends everything above 32 rows to the 256 x 256 tile kernel.
-    static const char* skinny_off = getenv("B2_DISABLE_SKINNY_GEMM");
-    const bool skinny_ok = gemm_off == nullptr && skinny_off == nullptr && nf4_skinny_supported(w, x, rows);
-    bool take_skinny = skinny_ok && rows > 32;
-    if (skinny_ok && rows <= 32) {
-        uint32_t ks = 0, per = 0;
-        take_skinny = !(nf4_gemv_supported(w, x, y, rows) &&
-                        (nf4_gemv_tma_plan(*ctx, w, x, rows, &ks, &per) || nf4_gemv_tma_plan(*ctx, w, x, 16, &ks, &per)));
-    }
-    if (take_skinny) {
-        if (workspace == nullptr) {
-            B2_TRY(reserve_arena(ctx, nf4_skinny_workspace_bytes(w, rows)));
-            workspace = ctx->arena;
-            workspace_bytes = ctx->arena_bytes;
-        }
-        return launch_nf4_skinny(*ctx, w, x, y, rows, workspace, workspace_bytes, stream);
     }
     if (nf4_gemv_supported(w, x, y, rows)) {
         // B2_GEMV_IMPL=tile forces the non-persistent kernel (for A/B measurements).
@@ -443,8 +434,8 @@ size_t b2_nf4_linear_workspace_bytes(const b2_nf4_weight* weight, uint64_t rows,
     WeightView w;
     if (make_weight_view(weight, &w) != B2_STATUS_OK) return 0;
     clear_error();
-    if (backward == 0 && nf4_skinny_supported(w, reinterpret_cast<const float*>(16), rows)) {
-        return nf4_skinny_workspace_bytes(w, rows);
+    if (backward == 0 && rows > 16 && nf4_gemm_tmem_supported(w, reinterpret_cast<const float*>(16), rows)) {
+        return nf4_gemm_tmem_workspace_bytes(w, rows);
     }
     if (!nf4_gemm_supported(w, reinterpret_cast<const float*>(16), rows, backward != 0)) return 0;
     return nf4_gemm_workspace_bytes(w, rows, backward != 0);

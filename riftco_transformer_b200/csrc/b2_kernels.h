@@ -38,14 +38,9 @@ int32_t launch_nf4_gemv_tma(const DeviceContext& ctx, const WeightView& w, const
 
 // nf4_gemm_sm100.cu - tcgen05 prefill GEMM, rows > 32.
 int32_t init_gemm_lut(DeviceContext* ctx);
-// Skinny forward (17..128 batch rows): weight rows as the N operand, one or two waves of CTAs.
-bool nf4_skinny_supported(const WeightView& w, const float* x, uint64_t rows);
-size_t nf4_skinny_workspace_bytes(const WeightView& w, uint64_t rows);
-int32_t launch_nf4_skinny(const DeviceContext& ctx, const WeightView& w, const float* x, float* y, uint64_t rows,
-                          void* workspace, size_t workspace_bytes, cudaStream_t stream);
-// nf4_gemm_tmem.cu - forward GEMM with the expanded weight tile as a tensor-memory operand.
 int32_t launch_f32_to_bf16(const DeviceContext& ctx, const float* src, void* dst, uint64_t count, cudaStream_t stream);
 bool nf4_gemm_tmem_supported(const WeightView& w, const float* x, uint64_t rows);
+size_t nf4_gemm_tmem_workspace_bytes(const WeightView& w, uint64_t rows);
 int32_t launch_nf4_gemm_tmem(const DeviceContext& ctx, const WeightView& w, const void* x_bf16, float* y,
                              uint64_t rows, cudaStream_t stream);
 bool nf4_gemm_supported(const WeightView& w, const float* x, uint64_t rows, bool backward);

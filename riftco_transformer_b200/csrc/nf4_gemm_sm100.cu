@@ -1,6 +1,8 @@
-// Prefill / training packed-NF4 linear on the 5th-generation tensor cores:
-//   forward   Y[M, out] = X[M, in] * W[out, in]^T
-//   backward  dX[M, in] = dY[M, out] * W[out, in]
+// Packed-NF4 linear on the 5th-generation tensor cores with the expanded weight tile in SHARED
+// memory:
+//   backward  dX[M, in] = dY[M, out] * W[out, in]      (the kernel in use for rows > 32)
+//   forward   Y[M, out] = X[M, in] * W[out, in]^T      (B2_GEMM_IMPL=smem; the default forward
+//                                                      kernel is nf4_gemm_tmem.cu)
 // (reference loops: src/core/backend/nn/quantized_linear/reference/operations.cpp:49-115).
 //
 // One CTA owns a 256 x 256 output tile as two 128 x 256 FP32 accumulators in
@@ -15,8 +17,10 @@
 // tcgen05.commit. Every mbarrier wait is bounded and reports a timeout in a
 // status word instead of spinning.
 //
-// Tensor-pipe bound in principle: 2*M*out*in flops per launch. In this
-// single-CTA form the dequantisation warps are the practical limit.
+// Tensor-pipe bound in principle: 2*M*out*in flops per launch. In practice the 128 B/clk
+// shared-memory port (weight tile written, then read twice by the MMAs, plus the activation tile
+// and the table lookups) and the issuing thread's two waits and two commits per k-block set the
+// pace: about half of the tensor peak.
 #include "b2_common.cuh"
 #include "b2_kernels.h"
 #include "sm100_ptx.cuh"
@@ -414,272 +418,6 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const GemmParams p) {
     }
 }
 
-// ---- skinny forward: 17..128 batch rows ------------------------------------------------------------
-//
-// For a handful of batch rows the 256 x 256 tile above leaves most SMs idle, so this kernel turns
-// the problem around: every CTA owns `tile_n` weight rows (chosen so that one or two waves of CTAs
-// cover all rows) and the whole contraction. The weight tile is the N operand of tcgen05.mma
-// (M128, N = tile rows, K16), expanded in the SM exactly as above; the activations - at most 128
-// rows, converted to bf16 by the streaming pre-pass - are the M operand and arrive by TMA in boxes
-// of 32, 64 or 128 rows. The MMA always reads 128 operand rows; the rows past the box are whatever
-// follows in shared memory, and only feed accumulator lanes that are never read back. Nothing but
-// the packed codes streams from HBM; the FP32 accumulator lives in 128 TMEM columns.
-constexpr int kSkBK = 128;                         // contraction elements per stage (two 64-wide sub-tiles)
-constexpr int kSkMaxStages = 4;                    // weight stages (expanded in the SM)
-constexpr int kSkMaxStagesA = 16;                  // activation stages (TMA): deep, the ring hides L2 latency
-constexpr int kSkThreads = (kDequantWarps + 2) * 32;
-constexpr int kSkSmemBytes = 221 * 1024;   // 227 KB less the static barriers and scale pairs
-constexpr int kSkStageBudget = kSkSmemBytes - kLutBytes - 32768 /* table alignment */ - 16384 /* operand read window */;
-constexpr uint32_t kSkTmemColumns = 128;
-
-struct SkinnyParams {
-    WeightView w;
-    float* y;            // [m, n] fp32
-    uint32_t m, n, k;
-    uint32_t tile_n;     // weight rows per CTA: multiple of 16, <= 128
-    uint32_t m_box;      // activation rows per TMA box: 32, 64 or 128
-    uint32_t stages;     // weight stages, 2 .. kSkMaxStages
-    uint32_t stages_a;   // activation stages, 2 .. kSkMaxStagesA
-    uint32_t* error;
-    const uint32_t* lut;
-};
-
-struct SkinnyBarriers {
-    uint64_t full_a[kSkMaxStagesA];
-    uint64_t empty_a[kSkMaxStagesA];
-    uint64_t full_b[kSkMaxStages];
-    uint64_t empty[kSkMaxStages];
-    uint64_t acc_full;
-    uint32_t tmem_base;
-    uint32_t abort;
-};
-
-__device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&r)[16]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-        : "r"(taddr)
-        : "memory");
-}
-
-__global__ void __launch_bounds__(kSkThreads, 1)
-nf4_skinny_kernel(const __grid_constant__ CUtensorMap map_a, const SkinnyParams p) {
-    extern __shared__ __align__(1024) uint8_t smem_raw[];
-    __shared__ __align__(8) SkinnyBarriers bars;
-    __shared__ __align__(16) uint32_t s_scale[kSkMaxStages][128][2];   // bf16 pairs: [stage][tile row][64-wide half]
-    __shared__ float s_factor[256];                                    // scale code -> (code - 128) / 127
-    const uint32_t raw32 = smem_u32(smem_raw);
-    const uint32_t lut32 = (raw32 + 32767u) & ~32767u;
-    const uint32_t tile_n = p.tile_n, stages = p.stages, stages_a = p.stages_a;
-    const uint32_t a_sub = p.m_box * 128u, a_stage_bytes = 2u * a_sub;
-    const uint32_t b_sub = tile_n * 128u, b_stage_bytes = 2u * b_sub;
-    const uint32_t a32 = lut32 + kLutBytes;
-    const uint32_t b32 = a32 + stages_a * a_stage_bytes;
-
-    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
-    const uint32_t n0 = blockIdx.x * tile_n;
-    const uint32_t num_kb = p.k / kSkBK;
-    volatile uint32_t* abort = &bars.abort;
-
-    if (warp == kDequantWarps) {
-        if (lane == 0) {
-            for (uint32_t s = 0; s < stages_a; ++s) {
-                mbar_init(&bars.full_a[s], 1);
-                mbar_init(&bars.empty_a[s], 1);
-            }
-            for (uint32_t s = 0; s < stages; ++s) {
-                mbar_init(&bars.full_b[s], kDequantWarps);
-                mbar_init(&bars.empty[s], 1);
-            }
-            mbar_init(&bars.acc_full, 1);
-            bars.abort = 0;
-            mbar_fence_init();
-            tma_prefetch_descriptor(&map_a);
-        }
-        __syncwarp();
-        tmem_alloc(&bars.tmem_base, kSkTmemColumns);
-    }
-    for (uint32_t i = tid; i < kLutBytes / 16; i += kSkThreads) {
-        sts_u4(lut32 + i * 16u, __ldg(reinterpret_cast<const uint4*>(p.lut) + i));
-    }
-    if (tid < 256) s_factor[tid] = dq_factor(tid);
-    tcgen05_fence_before_sync();
-    __syncthreads();
-    tcgen05_fence_after_sync();
-    const uint32_t tmem_base = bars.tmem_base;
-    // Everything above touched only this CTA's shared and tensor memory; the caller's tensors are
-    // read and written below, after the kernels this launch depends on have completed.
-    pdl_launch_dependents();
-    pdl_wait();
-
-    if (warp == kDequantWarps + 1) {
-        // ---- TMA producer: activation boxes ----
-        if (lane == 0) {
-            for (uint32_t kb = 0; kb < num_kb; ++kb) {
-                const uint32_t s = kb % stages_a;
-                if (kb >= stages_a) mbar_wait(&bars.empty_a[s], ((kb / stages_a) - 1u) & 1u, abort);
-                mbar_expect_tx(&bars.full_a[s], a_stage_bytes);
-                uint8_t* dst = smem_raw + (a32 - raw32) + s * a_stage_bytes;
-                tma_load_2d(dst, &map_a, static_cast<int>(kb * kSkBK), 0, &bars.full_a[s]);
-                tma_load_2d(dst + a_sub, &map_a, static_cast<int>(kb * kSkBK + 64u), 0, &bars.full_a[s]);
-            }
-        }
-    } else if (warp == kDequantWarps) {
-        // ---- MMA issuer ----
-        if (lane == 0) {
-            const uint32_t idesc = umma_idesc_bf16_f32(128, tile_n);
-            // one descriptor per operand, offsets added to its start-address field (address / 16)
-            const uint64_t da0 = umma_desc_k_major_sw128(a32), db0 = umma_desc_k_major_sw128(b32);
-            const uint32_t a_step = a_stage_bytes >> 4, b_step = b_stage_bytes >> 4;
-            const uint32_t a_sub16 = a_sub >> 4, b_sub16 = b_sub >> 4;
-            uint32_t s = 0, sa = 0, pa = 0, pb = 0;
-            for (uint32_t kb = 0; kb < num_kb; ++kb) {
-                mbar_wait(&bars.full_a[sa], pa, abort);
-                mbar_wait(&bars.full_b[s], pb, abort);
-                tcgen05_fence_after_sync();
-                const uint64_t da_s = da0 + sa * a_step, db_s = db0 + s * b_step;
-#pragma unroll
-                for (uint32_t sub = 0; sub < 2; ++sub) {
-#pragma unroll
-                    for (uint32_t kk = 0; kk < 4; ++kk) {
-                        umma_bf16(tmem_base, da_s + (sub * a_sub16 + kk * 2u), db_s + (sub * b_sub16 + kk * 2u), idesc,
-                                  (kb | sub | kk) != 0u ? 1u : 0u);
-                    }
-                }
-                umma_commit(&bars.empty_a[sa]);
-                umma_commit(&bars.empty[s]);
-                if (++sa == stages_a) {
-                    sa = 0;
-                    pa ^= 1u;
-                }
-                if (++s == stages) {
-                    s = 0;
-                    pb ^= 1u;
-                }
-            }
-            umma_commit(&bars.acc_full);
-        }
-    } else {
-        // ---- expansion warps: the weight tile of every stage, then the epilogue ----
-        const uint32_t r = tid;                       // 0 .. 511
-        const uint32_t lut_lane = lut32 | (lane * 4u);
-        const uint32_t w_items = tile_n * 16u;        // (row, 8-weight chunk) pairs per stage
-        const uint64_t row_bytes = p.k >> 1;
-
-        // this thread's items: i = r + 512 j -> row i / 16, chunk i % 16
-        const uint8_t* code_ptr[4];
-        uint32_t w_dst[4];       // byte offset inside a weight stage
-        uint32_t w_scale[4];     // index of the item's scale pair inside s_scale[stage]
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const uint32_t i = r + 512u * j;
-            const uint32_t row = i >> 4, chunk = i & 15u;
-            w_scale[j] = row * 2u + (chunk >> 3);
-            w_dst[j] = (chunk >> 3) * b_sub + row * 128u + (((chunk & 7u) ^ (row & 7u)) << 4);
-            code_ptr[j] = (i < w_items && n0 + row < p.n)
-                              ? p.w.codes + static_cast<uint64_t>(n0 + row) * row_bytes + chunk * 4u
-                              : nullptr;
-        }
-        // scale decoded by this thread for the CTA: (tile row r / 2, half r % 2)
-        const bool scale_thread = r < 2u * tile_n && n0 + (r >> 1) < p.n;
-        const uint64_t scale_flat0 = static_cast<uint64_t>(n0 + (r >> 1)) * p.k + (r & 1u) * 64u;
-
-        // Packed words and raw scales are fetched kSkAhead stages ahead into a register ring: one
-        // stage of expansion is much shorter than a trip to HBM.
-        constexpr int kSkAhead = 4;
-        uint32_t words[kSkAhead][4];
-        RawScale raw[kSkAhead];
-        auto fetch_stage = [&](int d, uint32_t kb) {
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                words[d][j] = 0u;
-                if (kb < num_kb && code_ptr[j] != nullptr) {
-                    words[d][j] = __ldg(reinterpret_cast<const uint32_t*>(code_ptr[j] + static_cast<uint64_t>(kb) * (kSkBK / 2)));
-                }
-            }
-            raw[d].bits = 0u;
-            raw[d].second = 0.0f;
-            if (kb < num_kb && scale_thread) {
-                raw[d] = fetch_raw_scale(p.w, (scale_flat0 + static_cast<uint64_t>(kb) * kSkBK) >> p.w.block_shift);
-            }
-        };
-#pragma unroll
-        for (int d = 0; d < kSkAhead; ++d) fetch_stage(d, static_cast<uint32_t>(d));
-
-        uint32_t s = 0, phase = 0;   // ring stage of k-block kb, parity of its use
-        for (uint32_t kb0 = 0; kb0 < num_kb; kb0 += kSkAhead) {
-#pragma unroll
-            for (int d = 0; d < kSkAhead; ++d) {
-                const uint32_t kb = kb0 + d;
-                if (kb < num_kb) {   // CTA-uniform
-                    if (kb >= stages) mbar_wait(&bars.empty[s], phase ^ 1u, abort);
-                    if (r < 2u * tile_n) {
-                        float sc = 0.0f;
-                        if (scale_thread) {
-                            sc = finish_raw_scale(p.w, raw[d], s_factor);
-                        }
-                        (&s_scale[s][0][0])[r] = scale_pair(sc);
-                    }
-                    asm volatile("bar.sync 1, 512;" ::: "memory");
-                    const uint32_t b_stage = b32 + s * b_stage_bytes;
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        if (r + 512u * j < w_items) {
-                            const uint32_t s2 = (&s_scale[s][0][0])[w_scale[j]];
-                            uint4 v = make_uint4(0u, 0u, 0u, 0u);
-                            if (code_ptr[j] != nullptr) v = expand_word(words[d][j], lut_lane, s2);
-                            sts_u4(b_stage + w_dst[j], v);
-                        }
-                    }
-                    fence_proxy_async_smem();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&bars.full_b[s]);
-                    fetch_stage(d, kb + kSkAhead);
-                    if (++s == stages) {
-                        s = 0;
-                        phase ^= 1u;
-                    }
-                }
-            }
-        }
-
-        // ---- epilogue: TMEM lane = batch row, column = weight row of the tile ----
-        mbar_wait(&bars.acc_full, 0u, abort);
-        tcgen05_fence_after_sync();
-        const uint32_t quarter = warp & 3u;            // the 32 TMEM lanes this warp may read
-        const uint32_t row_out = quarter * 32u + lane;
-        if (quarter * 32u < p.m) {
-            for (uint32_t c = warp >> 2; c * 16u < tile_n; c += 4u) {
-                uint32_t v[16];
-                tmem_ld_32x16(tmem_base + ((quarter * 32u) << 16) + c * 16u, v);
-                tmem_ld_wait();
-                const uint32_t col0 = n0 + c * 16u;
-                if (row_out < p.m && col0 < p.n) {
-                    float* dst = p.y + static_cast<uint64_t>(row_out) * p.n + col0;
-                    if (col0 + 16u <= p.n && (p.n & 3u) == 0u) {
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            reinterpret_cast<float4*>(dst)[i] =
-                                make_float4(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]),
-                                            __uint_as_float(v[4 * i + 2]), __uint_as_float(v[4 * i + 3]));
-                        }
-                    } else {
-                        for (uint32_t i = 0; i < 16u && col0 + i < p.n; ++i) dst[i] = __uint_as_float(v[i]);
-                    }
-                }
-            }
-        }
-    }
-    tcgen05_fence_before_sync();
-    __syncthreads();
-    if (warp == kDequantWarps) {
-        tmem_dealloc(tmem_base, kSkTmemColumns);
-        if (lane == 0 && bars.abort != 0 && p.error != nullptr) atomicOr(p.error, 1u);
-    }
-}
-
 __global__ void gemm_lut_init_kernel(uint32_t* lut) {
     // [256][32] words: entry v (replicated for the 32 lanes) = bf16 pair of packed byte v,
     // low nibble's value in the low half.
@@ -736,24 +474,6 @@ int32_t init_gemm_lut(DeviceContext* ctx) {
     return B2_STATUS_OK;
 }
 
-// Weight rows per CTA of the skinny kernel: the smallest multiple of 16 that covers all rows in
-// whole waves of CTAs (4096 rows on 148 SMs -> 32, 14336 -> 112, 32000 -> 112 in two waves).
-uint32_t skinny_tile_rows(const DeviceContext& ctx, uint64_t out_features) {
-    const uint64_t sms = static_cast<uint64_t>(ctx.sm_count > 0 ? ctx.sm_count : 1);
-    const uint64_t waves = (out_features + 128 * sms - 1) / (128 * sms);
-    uint64_t rows = (out_features + sms * waves - 1) / (sms * waves);
-    rows = (rows + 15) / 16 * 16;
-    if (rows < 16) rows = 16;
-    if (rows > 128) rows = 128;
-    return static_cast<uint32_t>(rows);
-}
-
-bool nf4_skinny_supported(const WeightView& w, const float* x, uint64_t rows) {
-    return rows > 16 && rows <= 128 && w.in_features % kSkBK == 0 && w.block_size >= 64 &&
-           (reinterpret_cast<uintptr_t>(w.codes) & 3u) == 0 && (reinterpret_cast<uintptr_t>(x) & 15u) == 0 &&
-           w.out_features <= 0x7FFFFFFFull && w.in_features <= 0x7FFFFFFFull;
-}
-
 // fp32 -> bf16 copy of `count` values (a multiple of 4) on `stream`.
 int32_t launch_f32_to_bf16(const DeviceContext& ctx, const float* src, void* dst, uint64_t count, cudaStream_t stream) {
     const uint64_t n4 = count / 4;
@@ -765,69 +485,10 @@ int32_t launch_f32_to_bf16(const DeviceContext& ctx, const float* src, void* dst
     return B2_STATUS_OK;
 }
 
-size_t nf4_skinny_workspace_bytes(const WeightView& w, uint64_t rows) {
-    return static_cast<size_t>(rows) * w.in_features * 2;   // bf16 copy of the activations
-}
-
-int32_t launch_nf4_skinny(const DeviceContext& ctx, const WeightView& w, const float* x, float* y, uint64_t rows,
-                          void* workspace, size_t workspace_bytes, cudaStream_t stream) {
-    const size_t need = nf4_skinny_workspace_bytes(w, rows);
-    if (workspace == nullptr || workspace_bytes < need) {
-        return fail(B2_STATUS_INVALID_ARGUMENT, "NF4 GEMM workspace too small: need %zu bytes", need);
-    }
-    if ((reinterpret_cast<uintptr_t>(workspace) & 15u) != 0) {
-        return fail(B2_STATUS_INVALID_ARGUMENT, "NF4 GEMM workspace must be 16-byte aligned");
-    }
-    static bool configured = false;
-    if (!configured) {
-        B2_CUDA_TRY(cudaFuncSetAttribute(nf4_skinny_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSkSmemBytes));
-        configured = true;
-    }
-    const uint64_t n4 = rows * w.in_features / 4;
-    uint64_t blocks = (n4 + 255) / 256;
-    if (blocks > static_cast<uint64_t>(ctx.sm_count) * 16) blocks = static_cast<uint64_t>(ctx.sm_count) * 16;
-    f32_to_bf16_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(x, static_cast<__nv_bfloat16*>(workspace), n4);
-    B2_CUDA_TRY(cudaGetLastError());
-
-    SkinnyParams p;
-    p.w = w;
-    p.y = y;
-    p.m = static_cast<uint32_t>(rows);
-    p.n = static_cast<uint32_t>(w.out_features);
-    p.k = static_cast<uint32_t>(w.in_features);
-    p.tile_n = skinny_tile_rows(ctx, w.out_features);
-    p.m_box = rows <= 32 ? 32u : rows <= 64 ? 64u : 128u;
-    // Weight stages first (two to four), then as many activation stages as still fit.
-    const uint32_t a_stage = 2u * 128u * p.m_box, b_stage = 2u * 128u * p.tile_n;
-    p.stages = b_stage <= 16384u ? 4u : b_stage <= 24576u ? 3u : 2u;
-    p.stages_a = (static_cast<uint32_t>(kSkStageBudget) - p.stages * b_stage) / a_stage;
-    if (p.stages_a > static_cast<uint32_t>(kSkMaxStagesA)) p.stages_a = kSkMaxStagesA;
-    if (p.stages_a < 2) return fail(B2_STATUS_RUNTIME_ERROR, "internal: skinny NF4 GEMM stage budget");
-    p.error = ctx.gemm_error;
-    p.lut = ctx.gemm_lut;
-    CUtensorMap map;
-    B2_TRY(make_operand_map(&map, workspace, rows, w.in_features, p.m_box));
-    cudaLaunchConfig_t config = {};
-    config.gridDim = dim3(static_cast<unsigned>((w.out_features + p.tile_n - 1) / p.tile_n));
-    config.blockDim = dim3(kSkThreads);
-    config.dynamicSmemBytes = kSkSmemBytes;
-    config.stream = stream;
-    // The kernel calls griddepcontrol.wait before it touches a caller tensor, so it may be
-    // scheduled while the conversion pre-pass drains. B2_DISABLE_PDL=1 restores plain stream order.
-    static const bool pdl = getenv("B2_DISABLE_PDL") == nullptr;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    config.attrs = attr;
-    config.numAttrs = pdl ? 1 : 0;
-    B2_CUDA_TRY(cudaLaunchKernelEx(&config, nf4_skinny_kernel, map, p));
-    return B2_STATUS_OK;
-}
-
 // The tensor-core path needs whole 64-wide contraction blocks that never
 // straddle a scale block, whole bytes per weight row and 16-byte aligned rows.
 bool nf4_gemm_supported(const WeightView& w, const float* x, uint64_t rows, bool backward) {
-    if (rows <= 32) return false;   // forward rows 17..128 are taken by the skinny kernel first
+    if (rows <= 32) return false;
     if (backward && (w.out_features % kBK != 0 || (reinterpret_cast<uintptr_t>(w.codes) & 3u) != 0)) return false;
     const uint64_t k = backward ? w.out_features : w.in_features;
     return k % kBK == 0 && w.in_features % 64 == 0 && w.block_size >= 64 &&
@@ -857,13 +518,6 @@ int32_t launch_nf4_gemm(const DeviceContext& ctx, const WeightView& w, const flo
     f32_to_bf16_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
         x, static_cast<__nv_bfloat16*>(workspace), n4);
     B2_CUDA_TRY(cudaGetLastError());
-
-    // Forward, B2_GEMM_IMPL=tmem: the kernel that keeps the expanded weight tile in tensor memory
-    // (not bound by the shared-memory port) instead of the shared-memory kernel below.
-    static const char* impl = getenv("B2_GEMM_IMPL");
-    if (!backward && impl != nullptr && strcmp(impl, "tmem") == 0 && nf4_gemm_tmem_supported(w, x, rows)) {
-        return launch_nf4_gemm_tmem(ctx, w, workspace, y, rows, stream);
-    }
 
     CUtensorMap map;
     B2_TRY(make_operand_map(&map, workspace, rows, k));

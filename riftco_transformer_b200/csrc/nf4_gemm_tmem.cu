@@ -15,9 +15,14 @@
 //
 // Sixteen expansion warps form four groups of four (a group covers the 128
 // lanes); group g expands the k-blocks kb = g mod 4 into TMEM stage g, so four
-// k-blocks are in expansion at any time. One thread issues tcgen05.mma
-// (M128 N256 K16, A from TMEM); tcgen05.commit releases the activation stage
-// and the TMEM stage. Every mbarrier wait is bounded.
+// k-blocks are in expansion at any time. tcgen05.mma (M128, N = tokens of the tile,
+// K16, A from TMEM) is issued by one thread, tcgen05.commit releases the activation
+// stage and the TMEM stage. With a full 256-token tile the MMAs themselves set the
+// pace and one issuing warp is enough; with at most 64 tokens (decode batches) the
+// pace is the issuing thread's own instruction latency (~1000 cycles per k-block
+// for two waits, four MMAs and two commits), so every expansion group then issues
+// its own k-blocks into its own accumulator and the four accumulators are summed
+// in the epilogue. Every mbarrier wait is bounded.
 #include "b2_common.cuh"
 #include "b2_kernels.h"
 #include "sm100_ptx.cuh"
@@ -38,7 +43,6 @@ using namespace sm100;
 constexpr int kTileW = 128;                    // weight rows per CTA (MMA M, TMEM lanes)
 constexpr int kMaxTileT = 256;                 // tokens per CTA at most (MMA N, accumulator columns)
 constexpr int kBK = 64;
-constexpr int kMaxStagesX = 8;                 // activation stages (shared memory, TMA)
 constexpr int kGroups = 4;                     // expansion groups = weight stages in TMEM
 constexpr int kXBytes = 4 * kMaxTileT * kBK * 2;   // 128 KB of activation stages (or of partial sums)
 constexpr int kLutBytes = 256 * 128;
@@ -48,23 +52,25 @@ constexpr int kSmemBytes = kXBytes + kLutBytes + 32768 /* table alignment */ + 1
 constexpr uint32_t kTmemColumns = 512;
 constexpr uint32_t kAccColumns = kMaxTileT;    // D: columns [0, tile_t) of [0, 256)
 constexpr uint32_t kWeightColumns = kBK / 2;   // one weight stage: 64 bf16 = 32 columns
+constexpr uint32_t kMultiIssueTokens = 64;     // up to here: one accumulator (64 columns) and one issuer per group
 
 struct Params {
     WeightView w;
     float* out;          // [m, n] fp32
     uint32_t m, n, k;    // tokens, output features, contraction length
     uint32_t tile_t;     // tokens per CTA: multiple of 16, <= 256
-    uint32_t stages_x;   // activation stages: kXBytes / (tile_t * 128), at most kMaxStagesX
     uint32_t kb_per_cta; // k-blocks per CTA (the contraction is split over the cluster along z)
     uint32_t* error;
     const uint32_t* lut; // compact [256][32] words of bf16 pairs
 };
 
+// K-block i of a CTA uses slot i % 4 for both its activation stage and its weight stage, so one
+// barrier per slot says "operands ready" (the TMA's byte count plus one arrival of each of the
+// group's four warps) and one says "MMAs done" (tcgen05.commit): one wait and one commit per
+// k-block for the issuing thread, whose instruction latency paces the CTA.
 struct Barriers {
-    uint64_t full_x[kMaxStagesX];
-    uint64_t empty_x[kMaxStagesX];
-    uint64_t full_w[kGroups];
-    uint64_t empty_w[kGroups];
+    uint64_t full[kGroups];
+    uint64_t done[kGroups];
     uint64_t acc_full;
     uint32_t tmem_base;
     uint32_t abort;
@@ -154,8 +160,9 @@ nf4_gemm_tmem_kernel(const __grid_constant__ CUtensorMap map_x, const Params p) 
     const uint32_t krank = cluster.block_rank();
 
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
-    const uint32_t tile_t = p.tile_t, stages_x = p.stages_x;
+    const uint32_t tile_t = p.tile_t;
     const uint32_t stage_bytes = tile_t * (kBK * 2u);
+    const bool multi_issue = tile_t <= kMultiIssueTokens;
     const uint32_t n0 = blockIdx.x * kTileW;   // first weight row (output feature) of the tile
     const uint32_t m0 = blockIdx.y * tile_t;   // first token of the tile
     const uint32_t total_kb = p.k / kBK;
@@ -165,15 +172,11 @@ nf4_gemm_tmem_kernel(const __grid_constant__ CUtensorMap map_x, const Params p) 
 
     if (warp == 0) {
         if (lane == 0) {
-            for (uint32_t s = 0; s < stages_x; ++s) {
-                mbar_init(&bars.full_x[s], 1);
-                mbar_init(&bars.empty_x[s], 1);
-            }
             for (int g = 0; g < kGroups; ++g) {
-                mbar_init(&bars.full_w[g], 4);    // lane 0 of the group's four warps
-                mbar_init(&bars.empty_w[g], 1);
+                mbar_init(&bars.full[g], 5);      // the producer's expect_tx + lane 0 of the group's four warps
+                mbar_init(&bars.done[g], 1);
             }
-            mbar_init(&bars.acc_full, 1);
+            mbar_init(&bars.acc_full, p.tile_t <= kMultiIssueTokens ? kGroups : 1);
             bars.abort = 0;
             mbar_fence_init();
             tma_prefetch_descriptor(&map_x);
@@ -198,43 +201,32 @@ nf4_gemm_tmem_kernel(const __grid_constant__ CUtensorMap map_x, const Params p) 
     if (warp == 0) {
         // ---- TMA producer: activation tiles [tile_t tokens x 64] ----
         if (lane == 0) {
-            uint32_t s = 0, ph = 0;
             for (uint32_t i = 0; i < num_kb; ++i) {
-                if (i >= stages_x) mbar_wait(&bars.empty_x[s], ph ^ 1u, abort);
-                mbar_expect_tx(&bars.full_x[s], stage_bytes);
-                tma_load_2d(smem + s * stage_bytes, &map_x, static_cast<int>((kb_begin + i) * kBK),
-                            static_cast<int>(m0), &bars.full_x[s]);
-                if (++s == stages_x) {
-                    s = 0;
-                    ph ^= 1u;
-                }
+                const uint32_t j = i % kGroups;
+                if (i >= kGroups) mbar_wait(&bars.done[j], ((i / kGroups) - 1u) & 1u, abort);
+                mbar_expect_tx(&bars.full[j], stage_bytes);
+                tma_load_2d(smem + j * stage_bytes, &map_x, static_cast<int>((kb_begin + i) * kBK),
+                            static_cast<int>(m0), &bars.full[j]);
             }
         }
     } else if (warp == 1) {
-        // ---- MMA issuer ----
-        if (lane == 0) {
+        // ---- MMA issuer (full tiles; small tiles are issued by the expansion groups) ----
+        if (lane == 0 && !multi_issue) {
             const uint32_t idesc = umma_idesc_bf16_f32(kTileW, tile_t);
             const uint64_t dx0 = umma_desc_k_major_sw128(x32);
             const uint32_t stage16 = stage_bytes >> 4;
-            uint32_t s = 0, px = 0;
             for (uint32_t i = 0; i < num_kb; ++i) {
-                const uint32_t g = i % kGroups;
-                mbar_wait(&bars.full_x[s], px, abort);
-                mbar_wait(&bars.full_w[g], (i / kGroups) & 1u, abort);
+                const uint32_t j = i % kGroups;
+                mbar_wait(&bars.full[j], (i / kGroups) & 1u, abort);
                 tcgen05_fence_after_sync();
-                const uint64_t dx_s = dx0 + s * stage16;
+                const uint64_t dx_s = dx0 + j * stage16;
 #pragma unroll
                 for (uint32_t kk = 0; kk < kBK / 16; ++kk) {
                     // 16 contraction values = 8 columns of the weight stage, 32 bytes of an activation row
-                    umma_bf16_a_tmem(tmem_base, tmem_w + g * kWeightColumns + kk * 8u, dx_s + kk * 2u, idesc,
+                    umma_bf16_a_tmem(tmem_base, tmem_w + j * kWeightColumns + kk * 8u, dx_s + kk * 2u, idesc,
                                      (i | kk) != 0u ? 1u : 0u);
                 }
-                umma_commit(&bars.empty_x[s]);
-                umma_commit(&bars.empty_w[g]);
-                if (++s == stages_x) {
-                    s = 0;
-                    px ^= 1u;
-                }
+                umma_commit(&bars.done[j]);
             }
             umma_commit(&bars.acc_full);
         }
@@ -250,73 +242,97 @@ nf4_gemm_tmem_kernel(const __grid_constant__ CUtensorMap map_x, const Params p) 
         const uint8_t* codes = live ? p.w.codes + static_cast<uint64_t>(n) * (p.k >> 1) + kb_begin * 32u : nullptr;
         const uint64_t flat0 = static_cast<uint64_t>(n) * p.k + static_cast<uint64_t>(kb_begin) * kBK;
         const uint32_t taddr = tmem_w + g * kWeightColumns + ((quarter * 32u) << 16);
+        const bool leader = (e & 3u) == 0u;           // first warp of the group: issues the group's MMAs for small tiles
+        const uint32_t idesc = umma_idesc_bf16_f32(kTileW, tile_t);
+        const uint64_t dx0 = umma_desc_k_major_sw128(x32);
 
-        // this group's k-blocks; codes and raw scale are fetched two of them (eight k-blocks) ahead
-        uint4 c0[2] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)}, c1[2] = {c0[0], c0[0]};
-        RawScale raw0 = {0u, 0.0f}, raw1 = raw0;
-        auto fetch = [&](uint32_t i, uint4 (&c)[2], RawScale& raw) {
-            c[0] = c[1] = make_uint4(0, 0, 0, 0);
-            raw.bits = 0u;
-            raw.second = 0.0f;
+        // This group's k-blocks; codes and raw scale are fetched two of them (eight k-blocks) ahead
+        // into a ring of three register sets. The loop is unrolled by three so that every set is
+        // addressed statically: copying a set whose load is still in flight (a rotating
+        // "next = next-next") would make the thread wait for memory in every iteration.
+        uint4 c[3][2];
+        RawScale raw[3];
+        auto fetch = [&](uint32_t i, uint4 (&cc)[2], RawScale& rr) {
+            cc[0] = cc[1] = make_uint4(0, 0, 0, 0);
+            rr.bits = 0u;
+            rr.second = 0.0f;
             if (live && i < num_kb) {
-                c[0] = ldg_u4(codes + i * 32u);
-                c[1] = ldg_u4(codes + i * 32u + 16u);
-                raw = fetch_raw_scale(p.w, (flat0 + static_cast<uint64_t>(i) * kBK) >> p.w.block_shift);
+                cc[0] = ldg_u4(codes + i * 32u);
+                cc[1] = ldg_u4(codes + i * 32u + 16u);
+                rr = fetch_raw_scale(p.w, (flat0 + static_cast<uint64_t>(i) * kBK) >> p.w.block_shift);
             }
         };
-        fetch(g, c0, raw0);
-        fetch(g + kGroups, c1, raw1);
+        fetch(g, c[0], raw[0]);
+        fetch(g + kGroups, c[1], raw[1]);
         uint32_t use = 0;   // how often this group's stage has been filled
-        for (uint32_t i = g; i < num_kb; i += kGroups, ++use) {
-            uint4 c2[2];
-            RawScale raw2;
-            fetch(i + 2u * kGroups, c2, raw2);
-            if (use > 0) mbar_wait(&bars.empty_w[g], (use - 1u) & 1u, abort);
-            tcgen05_fence_after_sync();
-            const uint32_t s2 = scale_pair(live ? finish_raw_scale(p.w, raw0, s_factor) : 0.0f);
-            uint32_t v[32];
-            const uint32_t words[8] = {c0[0].x, c0[0].y, c0[0].z, c0[0].w, c0[1].x, c0[1].y, c0[1].z, c0[1].w};
+        for (uint32_t i0 = g; i0 < num_kb; i0 += 3u * kGroups) {
 #pragma unroll
-            for (int q = 0; q < 8; ++q) {
-                const uint32_t word = words[q];
-                v[4 * q + 0] = bf16x2_mul(lds_u32(((word << 7) & 0x7F80u) | lut_lane), s2);
-                v[4 * q + 1] = bf16x2_mul(lds_u32(((word >> 1) & 0x7F80u) | lut_lane), s2);
-                v[4 * q + 2] = bf16x2_mul(lds_u32(((word >> 9) & 0x7F80u) | lut_lane), s2);
-                v[4 * q + 3] = bf16x2_mul(lds_u32(((word >> 17) & 0x7F80u) | lut_lane), s2);
+            for (int j = 0; j < 3; ++j) {
+                const uint32_t i = i0 + static_cast<uint32_t>(j) * kGroups;
+                if (i < num_kb) {   // warp-uniform
+                    fetch(i + 2u * kGroups, c[(j + 2) % 3], raw[(j + 2) % 3]);
+                    if (use > 0) mbar_wait(&bars.done[g], (use - 1u) & 1u, abort);
+                    tcgen05_fence_after_sync();
+                    const uint32_t s2 = scale_pair(live ? finish_raw_scale(p.w, raw[j], s_factor) : 0.0f);
+                    uint32_t v[32];
+                    const uint32_t words[8] = {c[j][0].x, c[j][0].y, c[j][0].z, c[j][0].w,
+                                               c[j][1].x, c[j][1].y, c[j][1].z, c[j][1].w};
+#pragma unroll
+                    for (int q = 0; q < 8; ++q) {
+                        const uint32_t word = words[q];
+                        v[4 * q + 0] = bf16x2_mul(lds_u32(((word << 7) & 0x7F80u) | lut_lane), s2);
+                        v[4 * q + 1] = bf16x2_mul(lds_u32(((word >> 1) & 0x7F80u) | lut_lane), s2);
+                        v[4 * q + 2] = bf16x2_mul(lds_u32(((word >> 9) & 0x7F80u) | lut_lane), s2);
+                        v[4 * q + 3] = bf16x2_mul(lds_u32(((word >> 17) & 0x7F80u) | lut_lane), s2);
+                    }
+                    tmem_st_32x32(taddr, v);
+                    tmem_st_wait();
+                    tcgen05_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&bars.full[g]);
+                    if (multi_issue && leader && lane == 0) {
+                        // this group's k-block: slot g, its own accumulator
+                        mbar_wait(&bars.full[g], use & 1u, abort);
+                        tcgen05_fence_after_sync();
+                        const uint64_t dx_s = dx0 + g * (stage_bytes >> 4);
+#pragma unroll
+                        for (uint32_t kk = 0; kk < kBK / 16; ++kk) {
+                            umma_bf16_a_tmem(tmem_base + g * kMultiIssueTokens, tmem_w + g * kWeightColumns + kk * 8u,
+                                             dx_s + kk * 2u, idesc, (use | kk) != 0u ? 1u : 0u);
+                        }
+                        umma_commit(&bars.done[g]);
+                    }
+                    __syncwarp();
+                    ++use;
+                }
             }
-            tmem_st_32x32(taddr, v);
-            tmem_st_wait();
-            tcgen05_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&bars.full_w[g]);
-            c0[0] = c1[0];
-            c0[1] = c1[1];
-            c1[0] = c2[0];
-            c1[1] = c2[1];
-            raw0 = raw1;
-            raw1 = raw2;
         }
+        if (multi_issue && leader && lane == 0) umma_commit(&bars.acc_full);   // after this group's last MMA
 
         // ---- epilogue: lane = weight row, column = token ----
         mbar_wait(&bars.acc_full, 0u, abort);
         tcgen05_fence_after_sync();
         float* partial = reinterpret_cast<float*>(smem);   // [tile_t][128] when the contraction is split
+        const uint32_t accumulators = multi_issue ? min(static_cast<uint32_t>(kGroups), num_kb) : (num_kb > 0 ? 1u : 0u);
         for (uint32_t c = g; c * 32u < tile_t; c += kGroups) {
-            uint32_t v[32];
-            tmem_ld_32x32(tmem_base + ((quarter * 32u) << 16) + c * 32u, v);
-            tmem_ld_wait();
-            if (num_kb == 0) {
+            float acc[32];
 #pragma unroll
-                for (int i = 0; i < 32; ++i) v[i] = 0u;   // a CTA without k-blocks contributes zeros
+            for (int i = 0; i < 32; ++i) acc[i] = 0.0f;   // a CTA without k-blocks contributes zeros
+            for (uint32_t a = 0; a < accumulators; ++a) {  // warp-uniform
+                uint32_t v[32];
+                tmem_ld_32x32(tmem_base + ((quarter * 32u) << 16) + a * kMultiIssueTokens + c * 32u, v);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) acc[i] += __uint_as_float(v[i]);
             }
 #pragma unroll
             for (uint32_t i = 0; i < 32u; ++i) {
                 const uint32_t t = c * 32u + i;          // token inside the tile
                 if (t < tile_t) {
                     if (ksplit == 1) {
-                        if (live && m0 + t < p.m) p.out[static_cast<uint64_t>(m0 + t) * p.n + n] = __uint_as_float(v[i]);
+                        if (live && m0 + t < p.m) p.out[static_cast<uint64_t>(m0 + t) * p.n + n] = acc[i];
                     } else {
-                        partial[t * kTileW + row] = __uint_as_float(v[i]);
+                        partial[t * kTileW + row] = acc[i];
                     }
                 }
             }
@@ -372,6 +388,10 @@ bool nf4_gemm_tmem_supported(const WeightView& w, const float* x, uint64_t rows)
            rows <= 0x7FFFFFFFull && w.out_features <= 0x7FFFFFFFull && w.in_features <= 0x7FFFFFFFull;
 }
 
+size_t nf4_gemm_tmem_workspace_bytes(const WeightView& w, uint64_t rows) {
+    return static_cast<size_t>(rows) * w.in_features * 2;   // bf16 copy of the activations
+}
+
 // `x_bf16` is the bf16 copy of the activations (rows * in * 2 bytes), already converted.
 int32_t launch_nf4_gemm_tmem(const DeviceContext& ctx, const WeightView& w, const void* x_bf16, float* y,
                              uint64_t rows, cudaStream_t stream) {
@@ -382,8 +402,6 @@ int32_t launch_nf4_gemm_tmem(const DeviceContext& ctx, const WeightView& w, cons
     p.n = static_cast<uint32_t>(w.out_features);
     p.k = static_cast<uint32_t>(w.in_features);
     p.tile_t = rows >= kMaxTileT ? kMaxTileT : static_cast<uint32_t>((rows + 15) / 16 * 16);
-    p.stages_x = static_cast<uint32_t>(kXBytes) / (p.tile_t * kBK * 2u);
-    if (p.stages_x > static_cast<uint32_t>(kMaxStagesX)) p.stages_x = kMaxStagesX;
     const uint32_t total_kb = p.k / kBK;
     const uint64_t tiles = ((w.out_features + kTileW - 1) / kTileW) * ((rows + p.tile_t - 1) / p.tile_t);
     // Few tiles (a handful of tokens against a weight of a few thousand rows): split the

@@ -44,8 +44,18 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // Waits for the phase with the given parity, at most `budget` polls. `abort`
 // is a shared flag: once any wait in the CTA has given up every later wait
 // returns immediately, so the kernel drains in bounded time.
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{ .reg .pred p; mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+        : "=r"(done)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return done != 0;
+}
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort,
                                           uint32_t budget = 2000000u) {
+    if (mbar_test_wait(bar, parity)) return true;   // the common case on a pipeline that runs ahead
     for (uint32_t i = 0; i < budget; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((i & 1023u) == 1023u && *abort != 0) return false;

@@ -1,4 +1,5 @@
-"""The tensor-core (tcgen05) prefill path of the packed-NF4 linear against the
+"""The tensor-core (tcgen05) paths of the packed-NF4 linear - every forward with
+more than 16 batch rows and the input-backward with more than 32 - against the
 FP32 CPU oracle. Tolerance: relative L2 <= 1e-2 (bf16 operands, FP32 accumulate)."""
 import numpy as np
 import pytest
@@ -46,16 +47,19 @@ def test_gemm_small_shapes(b2, port, rows, out_f, in_f, block, dq):
 
 
 @pytest.mark.parametrize("rows,out_f,in_f,block,dq", [
-    (17, 4096, 4096, 64, True),      # 32-row tiles, one TMEM quarter
-    (32, 14336, 4096, 64, True),     # 112-row tiles, 128 CTAs
-    (32, 4096, 14336, 64, True),     # long contraction
-    (33, 1000, 256, 64, True),       # ragged last tile, second TMEM quarter with one row
-    (64, 4096, 4096, 128, False),    # FP32 scales, block 128
-    (128, 1024, 512, 64, True),      # every TMEM lane, 16-row tiles
-    (100, 32000, 1024, 64, True),    # two waves of tiles
+    (17, 4096, 4096, 64, True),      # 32-token tile, contraction split over a cluster of 4
+    (32, 14336, 4096, 64, True),     # 112 weight-row tiles, one accumulator per expansion group
+    (32, 4096, 14336, 64, True),     # long contraction, split
+    (33, 1000, 256, 64, True),       # ragged weight-row tile, 48-token tile (a half-used column chunk)
+    (64, 4096, 4096, 128, False),    # FP32 scales, block 128, the largest multi-issuer tile
+    (128, 1024, 512, 64, True),      # single issuer, 128-token tile, 8 k-blocks over a cluster of 1
+    (100, 32000, 1024, 64, True),    # two waves of tiles, ragged token tile
+    (18, 256, 64, 64, True),         # one k-block: three of the four groups have no work
+    (24, 128, 192, 64, True),        # three k-blocks
 ])
-def test_skinny_batches(b2, port, rows, out_f, in_f, block, dq):
-    """17..128 batch rows: the weight tile is the N operand, the batch the M operand."""
+def test_small_token_tiles(b2, port, rows, out_f, in_f, block, dq):
+    """17..128 batch rows on the tensor-memory kernel: up to 64 tokens every expansion group issues
+    its own MMAs into its own accumulator; few weight-row tiles split the contraction over a cluster."""
     rng = np.random.default_rng(rows * 11 + out_f)
     W = (rng.standard_normal((out_f, in_f)) * 0.02).astype(np.float32)
     host = port.quantize_nf4_double_quantized(W, block, 256) if dq else port.quantize_nf4(W, block)
@@ -85,7 +89,8 @@ def test_gemm_config3_sampled_rows(b2, port):
     assert np.isfinite(y).all()
     # linearity in the activations
     y2 = forward(b2, b2.PackedNf4Weight.from_host(host), torch.from_numpy(2.0 * x[:64]).cuda())
-    assert rel_l2(y2, 2.0 * y[:64]) <= 1e-6
+    # (64 tokens run as four partial accumulators, 4096 as one: the FP32 summation order differs)
+    assert rel_l2(y2, 2.0 * y[:64]) <= 2e-5
 
 
 def backward(b2, w, dy):

@@ -159,7 +159,8 @@ def test_gemv_edge_shapes(b2, port, out_f, in_f, block, rows, dq):
     host = port.quantize_nf4_double_quantized(W, block, 32) if dq else port.quantize_nf4(W, block)
     x = rng.standard_normal((rows, in_f)).astype(np.float32)
     y = forward(b2, b2.PackedNf4Weight.from_host(host), dev(x))
-    assert rel_l2(y, port.linear_forward(host, x)) <= GEMV_TOL
+    # up to 16 rows the fp16 decode kernel (2e-3); more rows go to the bf16 tensor-core kernel (1e-2)
+    assert rel_l2(y, port.linear_forward(host, x)) <= (GEMV_TOL if rows <= 16 else 1e-2)
 
 
 def test_gemv_is_linear_and_deterministic(b2, port, c2_weights):
