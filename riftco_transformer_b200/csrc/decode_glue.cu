@@ -28,15 +28,53 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
 
 // y = x * (1 / sqrt(mean(x^2) + eps)) * scale, one CTA per row
 // (src/nn/rms_norm.cpp:39-73). With `delta`, first x_out = x + delta (the
-// residual stream update) and the norm is taken of x_out.
-__global__ void __launch_bounds__(256)
+// residual stream update) and the norm is taken of x_out. A decode batch has few
+// rows, so a row gets up to 1024 threads, 16-byte accesses, and its values stay
+// in registers between the two passes when they fit (two float4 per thread).
+__global__ void __launch_bounds__(1024)
 rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ delta, float* __restrict__ x_out,
-               const float* __restrict__ scale, float* __restrict__ y, uint32_t width, float eps) {
-    sm100::pdl_launch_dependents();   // a following decode GEMV may start its set-up now
-    __shared__ float scratch[8];
+               const float* __restrict__ scale, float* __restrict__ y, uint32_t width, float eps, uint32_t vec4) {
+    sm100::pdl_launch_dependents();   // a following linear kernel may start its set-up now
+    __shared__ float scratch[32];
     const uint64_t row = blockIdx.x;
     const float* xr = x + row * width;
     float ss = 0.0f;
+    if (vec4 != 0u) {
+        const uint32_t n4 = width / 4;
+        const float4* x4 = reinterpret_cast<const float4*>(xr);
+        const float4* d4 = delta != nullptr ? reinterpret_cast<const float4*>(delta + row * width) : nullptr;
+        float4* o4 = delta != nullptr ? reinterpret_cast<float4*>(x_out + row * width) : nullptr;
+        auto fetch = [&](uint32_t c) {
+            float4 v = x4[c];
+            if (d4 != nullptr) {
+                const float4 dv = d4[c];
+                v = make_float4(v.x + dv.x, v.y + dv.y, v.z + dv.z, v.w + dv.w);
+                o4[c] = v;
+            }
+            ss = fmaf(v.x, v.x, ss);
+            ss = fmaf(v.y, v.y, ss);
+            ss = fmaf(v.z, v.z, ss);
+            ss = fmaf(v.w, v.w, ss);
+            return v;
+        };
+        const uint32_t c0 = threadIdx.x, c1 = threadIdx.x + blockDim.x;
+        float4 keep0 = make_float4(0.f, 0.f, 0.f, 0.f), keep1 = keep0;
+        if (c0 < n4) keep0 = fetch(c0);
+        if (c1 < n4) keep1 = fetch(c1);
+        for (uint32_t c = c1 + blockDim.x; c < n4; c += blockDim.x) (void)fetch(c);
+        const float inv = 1.0f / sqrtf(block_sum(ss, scratch) / static_cast<float>(width) + eps);
+        const float4* s4 = reinterpret_cast<const float4*>(scale);
+        const float4* src4 = d4 != nullptr ? reinterpret_cast<const float4*>(x_out + row * width) : x4;
+        float4* y4 = reinterpret_cast<float4*>(y + row * width);
+        auto emit = [&](uint32_t c, const float4& v) {
+            const float4 g = s4[c];
+            y4[c] = make_float4(v.x * inv * g.x, v.y * inv * g.y, v.z * inv * g.z, v.w * inv * g.w);
+        };
+        if (c0 < n4) emit(c0, keep0);
+        if (c1 < n4) emit(c1, keep1);
+        for (uint32_t c = c1 + blockDim.x; c < n4; c += blockDim.x) emit(c, src4[c]);
+        return;
+    }
     for (uint32_t c = threadIdx.x; c < width; c += blockDim.x) {
         float v = xr[c];
         if (delta != nullptr) {
@@ -77,11 +115,31 @@ rope_append_kernel(float* __restrict__ q, const float* __restrict__ k, const flo
     if (bad && threadIdx.x == 0 && status != nullptr) atomicOr(status, B2_ATTN_STATUS_BAD_BLOCK);
     const uint32_t slot = pos % block_size;
     const uint32_t pairs = (q_heads + kv_heads) * half;
+    // The angles depend only on (position, channel pair): evaluated once per sequence, in double,
+    // and shared by all heads (up to 256 pairs, i.e. head widths up to 512, fit the table).
+    __shared__ float s_cos[256], s_sin[256];
+    const bool tabled = half <= 256u;
+    if (tabled) {
+        for (uint32_t c = threadIdx.x; c < half; c += blockDim.x) {
+            const double angle = static_cast<double>(pos) *
+                                 pow(static_cast<double>(theta), -2.0 * static_cast<double>(c) / static_cast<double>(d));
+            s_cos[c] = static_cast<float>(cos(angle));
+            s_sin[c] = static_cast<float>(sin(angle));
+        }
+        __syncthreads();
+    }
     for (uint32_t i = threadIdx.x; i < pairs; i += blockDim.x) {
         const uint32_t head = i / half, c = i % half;
-        const double angle = static_cast<double>(pos) *
-                             pow(static_cast<double>(theta), -2.0 * static_cast<double>(c) / static_cast<double>(d));
-        const float cs = static_cast<float>(cos(angle)), sn = static_cast<float>(sin(angle));
+        float cs, sn;
+        if (tabled) {
+            cs = s_cos[c];
+            sn = s_sin[c];
+        } else {
+            const double angle = static_cast<double>(pos) *
+                                 pow(static_cast<double>(theta), -2.0 * static_cast<double>(c) / static_cast<double>(d));
+            cs = static_cast<float>(cos(angle));
+            sn = static_cast<float>(sin(angle));
+        }
         if (head < q_heads) {
             float* p = q + (static_cast<uint64_t>(seq) * q_heads + head) * d;
             const float a = p[c], b = p[c + half];
@@ -201,7 +259,17 @@ unsigned grid_for(uint64_t n, int sm_count) {
 
 int32_t launch_rmsnorm(const float* x, const float* delta, float* x_out, const float* scale, float* y,
                        uint64_t rows, uint32_t width, float eps, cudaStream_t stream) {
-    rmsnorm_kernel<<<static_cast<unsigned>(rows), 256, 0, stream>>>(x, delta, x_out, scale, y, width, eps);
+    const bool vec4 = width % 4 == 0 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y) |
+                                          reinterpret_cast<uintptr_t>(scale) | reinterpret_cast<uintptr_t>(delta) |
+                                          reinterpret_cast<uintptr_t>(x_out)) & 15u) == 0;
+    unsigned threads = 256;
+    if (vec4) {
+        threads = (width / 4 + 31) / 32 * 32;
+        if (threads > 1024) threads = 1024;
+        if (threads < 64) threads = 64;
+    }
+    rmsnorm_kernel<<<static_cast<unsigned>(rows), threads, 0, stream>>>(x, delta, x_out, scale, y, width, eps,
+                                                                       vec4 ? 1u : 0u);
     B2_CUDA_TRY(cudaGetLastError());
     return B2_STATUS_OK;
 }
