@@ -217,6 +217,9 @@ def run_reference(args) -> None:
     print(json.dumps(line))
 
 
+NCU_ATTENTION_READ_RATIO = 1.0007   # dram__bytes_read.sum / algorithmic bytes, profiles/paged_decode_bulk_8x4096.md
+
+
 def workload_config(world: int) -> dict:
     return {"workload": "7b_decode_step", "layers": N_LAYERS, "d_model": 4096, "q_heads": 32, "kv_heads": 8,
             "head_dim": 128, "ffn": 14336, "vocab": 32000, "batch": BATCH, "context": CONTEXT,
@@ -404,9 +407,15 @@ def run_b200(args) -> None:
     attn_us = max_over_ranks(time_graph(torch, attention_all_layers, 5, cfg.layers))
     kv_bytes_launch = inputs["kv_bytes_per_step"] / cfg.layers
     achieved = kv_bytes_launch / attn_us / 1e3
+    # DRAM traffic per launch: the ncu capture of a smaller case of this kernel
+    # (profiles/paged_decode_bulk_8x4096.md) read 1.0007 x its algorithmic K/V bytes and wrote its
+    # split partials and context; both scale with the tokens read, so they are scaled to this launch.
+    splits = -(-(CONTEXT + 1) // 256)
+    hq_local = cfg.q_heads // world
+    traffic = int(kv_bytes_launch * NCU_ATTENTION_READ_RATIO) + BATCH * hq_local * (splits * 130 + 128) * 4
     roofline = {"kernel": "paged_decode_bulk_kernel(+merge)", "bound": "hbm", "achieved": achieved,
                 "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
-                "peak_source": peak_kind, "traffic": None, "us_per_launch": attn_us,
+                "peak_source": peak_kind, "traffic": traffic, "us_per_launch": attn_us,
                 "share_of_step": attn_us * cfg.layers / 1e3 / ms_per_step}
     step_bytes = step.weight_bytes() + inputs["kv_bytes_per_step"]
     step_roofline = {"bytes_per_step_per_gpu": step_bytes, "hbm_floor_ms": step_bytes / peaks["hbm_gbs"] / 1e6,
