@@ -127,6 +127,18 @@ B2_API int32_t b2_nf4_linear_forward(const b2_nf4_weight* weight, const float* x
                               uint64_t rows, void* workspace, size_t workspace_bytes,
                               void* stream);
 
+/* Several packed linears of the SAME input in one call: ys[i][r,o] = sum_k x[r,k] * W_i[o,k]
+ * for `count` weights with equal in_features (the q / k / v projections of an attention block,
+ * the gate / up projections of a SwiGLU block: src/model/grouped_query_attention.cpp:61-94,
+ * src/model/swiglu.cpp:27-29 apply them one after the other to the same tensor). Results are
+ * those of `count` calls of b2_nf4_linear_forward with the same arguments; with more than 16
+ * rows and up to four weights the activations are converted once and one kernel launch covers
+ * every weight's tiles. Validation, workspace and stream rules as for b2_nf4_linear_forward
+ * (the workspace need is that of any single one of the calls). */
+B2_API int32_t b2_nf4_linear_forward_multi(const b2_nf4_weight* weights, uint32_t count, const float* x,
+                                    float* const* ys, uint64_t rows, void* workspace,
+                                    size_t workspace_bytes, void* stream);
+
 /* dx[r,i] = sum_o dy[r,o] * W[o,i]. dy: float[rows,out], dx: float[rows,in].
  * Replaces QuantizedLinearCapability::quantized_linear_input_backward
  * (capability.hpp:43-49; launch.hpp:19-20; loop reference/operations.cpp:83-115;

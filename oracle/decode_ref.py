@@ -92,6 +92,10 @@ class CheckerOps:
     def linear(self, x, w: Nf4Weight, out) -> None:
         out.copy_(torch.from_numpy(self.oracle.linear_forward(w, x.numpy(), threads=1)))
 
+    def linear_multi(self, x, weights, outs) -> None:
+        for w, out in zip(weights, outs):
+            self.linear(x, w, out)
+
     def rmsnorm(self, x, delta, x_out, scale, y, eps) -> None:
         if delta is not None:
             x_out.copy_(x + delta)

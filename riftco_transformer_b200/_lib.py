@@ -58,6 +58,7 @@ SIGNATURES = {
     "b2_unavailability_reason": (C.c_char_p, []),
     "b2_nf4_dequantize": (_i32, [_W, _vp, _vp]),
     "b2_nf4_linear_forward": (_i32, [_W, _vp, _vp, _u64, _vp, _sz, _vp]),
+    "b2_nf4_linear_forward_multi": (_i32, [_vp, _u32, _vp, _vp, _u64, _vp, _sz, _vp]),
     "b2_nf4_linear_input_backward": (_i32, [_W, _vp, _vp, _u64, _vp, _sz, _vp]),
     "b2_nf4_linear_workspace_bytes": (_sz, [_W, _u64, _i32]),
     "b2_paged_decode_attention": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u32,

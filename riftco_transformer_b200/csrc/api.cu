@@ -422,6 +422,61 @@ int32_t b2_nf4_linear_forward(const b2_nf4_weight* weight, const float* x, float
                                static_cast<cudaStream_t>(stream));
 }
 
+int32_t b2_nf4_linear_forward_multi(const b2_nf4_weight* weights, uint32_t count, const float* x, float* const* ys,
+                                    uint64_t rows, void* workspace, size_t workspace_bytes, void* stream_ptr) {
+    clear_error();
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+    if (weights == nullptr || ys == nullptr || count == 0) {
+        return fail(B2_STATUS_INVALID_ARGUMENT, "quantized linear needs at least one weight and its output");
+    }
+    for (uint32_t i = 0; i < count; ++i) {
+        for (uint32_t j = 0; j < i; ++j) {
+            if (ys[i] != nullptr && ys[i] == ys[j]) {
+                return fail(B2_STATUS_INVALID_ARGUMENT, "quantized linear outputs of one call must not alias");
+            }
+        }
+    }
+    int32_t status = B2_STATUS_OK;
+    DeviceContext* ctx = device_context(&status);
+    if (ctx == nullptr) return status;
+    // One launch when every weight can take the tensor-memory kernel on the same activations;
+    // otherwise the calls are simply made one after the other.
+    static const char* gemm_off = getenv("B2_DISABLE_TENSOR_GEMM");
+    static const char* gemm_impl = getenv("B2_GEMM_IMPL");
+    const bool tmem_off = gemm_off != nullptr || (gemm_impl != nullptr && strcmp(gemm_impl, "smem") == 0);
+    bool fused = !tmem_off && rows > 16 && count <= 4 && count > 1 && x != nullptr;
+    WeightView views[4];
+    for (uint32_t i = 0; fused && i < count; ++i) {
+        if (ys[i] == nullptr || x == ys[i] || aliases_weight(&weights[i], ys[i]) ||
+            make_weight_view(&weights[i], &views[i]) != B2_STATUS_OK ||
+            check_linear_dims(views[i], rows) != B2_STATUS_OK ||
+            views[i].in_features != views[0].in_features || !nf4_gemm_tmem_supported(views[i], x, rows)) {
+            fused = false;   // let the single-weight path produce the precise error
+        }
+    }
+    clear_error();
+    if (!fused) {
+        for (uint32_t i = 0; i < count; ++i) {
+            B2_TRY(linear_forward_impl(&weights[i], x, ys[i], rows, workspace, workspace_bytes, stream));
+        }
+        return B2_STATUS_OK;
+    }
+    const size_t need = nf4_gemm_tmem_workspace_bytes(views[0], rows);
+    if (workspace == nullptr) {
+        B2_TRY(reserve_arena(ctx, need));
+        workspace = ctx->arena;
+        workspace_bytes = ctx->arena_bytes;
+    }
+    if (workspace_bytes < need) {
+        return fail(B2_STATUS_INVALID_ARGUMENT, "NF4 GEMM workspace too small: need %zu bytes", need);
+    }
+    if ((reinterpret_cast<uintptr_t>(workspace) & 15u) != 0) {
+        return fail(B2_STATUS_INVALID_ARGUMENT, "NF4 GEMM workspace must be 16-byte aligned");
+    }
+    B2_TRY(launch_f32_to_bf16(*ctx, x, workspace, rows * views[0].in_features, stream));
+    return launch_nf4_gemm_tmem_multi(*ctx, views, ys, count, workspace, rows, stream);
+}
+
 int32_t b2_nf4_linear_input_backward(const b2_nf4_weight* weight, const float* dy, float* dx,
                                      uint64_t rows, void* workspace, size_t workspace_bytes,
                                      void* stream) {

@@ -54,10 +54,15 @@ constexpr uint32_t kAccColumns = kMaxTileT;    // D: columns [0, tile_t) of [0, 
 constexpr uint32_t kWeightColumns = kBK / 2;   // one weight stage: 64 bf16 = 32 columns
 constexpr uint32_t kMultiIssueTokens = 64;     // up to here: one accumulator (64 columns) and one issuer per group
 
+constexpr int kMaxWeights = 4;                 // weights applied to the same activations in one launch
+
 struct Params {
-    WeightView w;
-    float* out;          // [m, n] fp32
-    uint32_t m, n, k;    // tokens, output features, contraction length
+    WeightView w[kMaxWeights];
+    float* out[kMaxWeights];         // [m, n[i]] fp32
+    uint32_t n[kMaxWeights];         // output features of every weight
+    uint32_t tile_end[kMaxWeights];  // running count of 128-row tiles: weight i owns tiles [tile_end[i-1], tile_end[i])
+    uint32_t count;                  // weights in this launch
+    uint32_t m, k;                   // tokens, contraction length
     uint32_t tile_t;     // tokens per CTA: multiple of 16, <= 256
     uint32_t kb_per_cta; // k-blocks per CTA (the contraction is split over the cluster along z)
     uint32_t* error;
@@ -163,7 +168,26 @@ nf4_gemm_tmem_kernel(const __grid_constant__ CUtensorMap map_x, const Params p) 
     const uint32_t tile_t = p.tile_t;
     const uint32_t stage_bytes = tile_t * (kBK * 2u);
     const bool multi_issue = tile_t <= kMultiIssueTokens;
-    const uint32_t n0 = blockIdx.x * kTileW;   // first weight row (output feature) of the tile
+    // Which weight this CTA's tile belongs to (a launch may apply up to four weights to the same
+    // activations); the selected view is copied so that it lives in registers.
+    uint32_t wi = 0;
+#pragma unroll
+    for (int i = 1; i < kMaxWeights; ++i) {
+        if (static_cast<uint32_t>(i) < p.count && blockIdx.x >= p.tile_end[i - 1]) wi = static_cast<uint32_t>(i);
+    }
+    WeightView w = p.w[0];
+    float* out = p.out[0];
+    uint32_t n_out = p.n[0], tile0 = 0;
+#pragma unroll
+    for (int i = 1; i < kMaxWeights; ++i) {
+        if (wi == static_cast<uint32_t>(i)) {
+            w = p.w[i];
+            out = p.out[i];
+            n_out = p.n[i];
+            tile0 = p.tile_end[i - 1];
+        }
+    }
+    const uint32_t n0 = (blockIdx.x - tile0) * kTileW;   // first weight row (output feature) of the tile
     const uint32_t m0 = blockIdx.y * tile_t;   // first token of the tile
     const uint32_t total_kb = p.k / kBK;
     const uint32_t kb_begin = min(krank * p.kb_per_cta, total_kb);
@@ -238,8 +262,8 @@ nf4_gemm_tmem_kernel(const __grid_constant__ CUtensorMap map_x, const Params p) 
         const uint32_t row = quarter * 32u + lane;    // weight row of the tile = TMEM lane
         const uint32_t n = n0 + row;
         const uint32_t lut_lane = lut32 | (lane * 4u);
-        const bool live = n < p.n;
-        const uint8_t* codes = live ? p.w.codes + static_cast<uint64_t>(n) * (p.k >> 1) + kb_begin * 32u : nullptr;
+        const bool live = n < n_out;
+        const uint8_t* codes = live ? w.codes + static_cast<uint64_t>(n) * (p.k >> 1) + kb_begin * 32u : nullptr;
         const uint64_t flat0 = static_cast<uint64_t>(n) * p.k + static_cast<uint64_t>(kb_begin) * kBK;
         const uint32_t taddr = tmem_w + g * kWeightColumns + ((quarter * 32u) << 16);
         const bool leader = (e & 3u) == 0u;           // first warp of the group: issues the group's MMAs for small tiles
@@ -259,7 +283,7 @@ nf4_gemm_tmem_kernel(const __grid_constant__ CUtensorMap map_x, const Params p) 
             if (live && i < num_kb) {
                 cc[0] = ldg_u4(codes + i * 32u);
                 cc[1] = ldg_u4(codes + i * 32u + 16u);
-                rr = fetch_raw_scale(p.w, (flat0 + static_cast<uint64_t>(i) * kBK) >> p.w.block_shift);
+                rr = fetch_raw_scale(w, (flat0 + static_cast<uint64_t>(i) * kBK) >> w.block_shift);
             }
         };
         fetch(g, c[0], raw[0]);
@@ -273,7 +297,7 @@ nf4_gemm_tmem_kernel(const __grid_constant__ CUtensorMap map_x, const Params p) 
                     fetch(i + 2u * kGroups, c[(j + 2) % 3], raw[(j + 2) % 3]);
                     if (use > 0) mbar_wait(&bars.done[g], (use - 1u) & 1u, abort);
                     tcgen05_fence_after_sync();
-                    const uint32_t s2 = scale_pair(live ? finish_raw_scale(p.w, raw[j], s_factor) : 0.0f);
+                    const uint32_t s2 = scale_pair(live ? finish_raw_scale(w, raw[j], s_factor) : 0.0f);
                     uint32_t v[32];
                     const uint32_t words[8] = {c[j][0].x, c[j][0].y, c[j][0].z, c[j][0].w,
                                                c[j][1].x, c[j][1].y, c[j][1].z, c[j][1].w};
@@ -330,7 +354,7 @@ nf4_gemm_tmem_kernel(const __grid_constant__ CUtensorMap map_x, const Params p) 
                 const uint32_t t = c * 32u + i;          // token inside the tile
                 if (t < tile_t) {
                     if (ksplit == 1) {
-                        if (live && m0 + t < p.m) p.out[static_cast<uint64_t>(m0 + t) * p.n + n] = acc[i];
+                        if (live && m0 + t < p.m) out[static_cast<uint64_t>(m0 + t) * n_out + n] = acc[i];
                     } else {
                         partial[t * kTileW + row] = acc[i];
                     }
@@ -348,7 +372,7 @@ nf4_gemm_tmem_kernel(const __grid_constant__ CUtensorMap map_x, const Params p) 
             const uint32_t t = i / kTileW, row = i % kTileW;
             float v = 0.0f;
             for (uint32_t r = 0; r < ksplit; ++r) v += cluster.map_shared_rank(mine, r)[i];
-            if (n0 + row < p.n && m0 + t < p.m) p.out[static_cast<uint64_t>(m0 + t) * p.n + n0 + row] = v;
+            if (n0 + row < n_out && m0 + t < p.m) out[static_cast<uint64_t>(m0 + t) * n_out + n0 + row] = v;
         }
         cluster.sync();
     }
@@ -392,18 +416,29 @@ size_t nf4_gemm_tmem_workspace_bytes(const WeightView& w, uint64_t rows) {
     return static_cast<size_t>(rows) * w.in_features * 2;   // bf16 copy of the activations
 }
 
-// `x_bf16` is the bf16 copy of the activations (rows * in * 2 bytes), already converted.
-int32_t launch_nf4_gemm_tmem(const DeviceContext& ctx, const WeightView& w, const void* x_bf16, float* y,
-                             uint64_t rows, cudaStream_t stream) {
+// `x_bf16` is the bf16 copy of the activations (rows * in * 2 bytes), already converted. Applies
+// `count` (<= 4) weights with the same in_features to it in one launch; ys[i] is [rows, out_i].
+int32_t launch_nf4_gemm_tmem_multi(const DeviceContext& ctx, const WeightView* ws, float* const* ys, uint32_t count,
+                                   const void* x_bf16, uint64_t rows, cudaStream_t stream) {
+    if (count == 0 || count > static_cast<uint32_t>(kMaxWeights)) {
+        return fail(B2_STATUS_INVALID_ARGUMENT, "between one and four weights per launch");
+    }
     Params p;
-    p.w = w;
-    p.out = y;
+    uint64_t weight_tiles = 0;
+    for (uint32_t i = 0; i < static_cast<uint32_t>(kMaxWeights); ++i) {
+        const uint32_t src = i < count ? i : 0;
+        p.w[i] = ws[src];
+        p.out[i] = ys[src];
+        p.n[i] = static_cast<uint32_t>(ws[src].out_features);
+        if (i < count) weight_tiles += (ws[i].out_features + kTileW - 1) / kTileW;
+        p.tile_end[i] = static_cast<uint32_t>(weight_tiles);
+    }
+    p.count = count;
     p.m = static_cast<uint32_t>(rows);
-    p.n = static_cast<uint32_t>(w.out_features);
-    p.k = static_cast<uint32_t>(w.in_features);
+    p.k = static_cast<uint32_t>(ws[0].in_features);
     p.tile_t = rows >= kMaxTileT ? kMaxTileT : static_cast<uint32_t>((rows + 15) / 16 * 16);
     const uint32_t total_kb = p.k / kBK;
-    const uint64_t tiles = ((w.out_features + kTileW - 1) / kTileW) * ((rows + p.tile_t - 1) / p.tile_t);
+    const uint64_t tiles = weight_tiles * ((rows + p.tile_t - 1) / p.tile_t);
     // Few tiles (a handful of tokens against a weight of a few thousand rows): split the
     // contraction over a cluster so that most SMs take part; the ranks' partial tiles are summed
     // through distributed shared memory in rank order.
@@ -416,8 +451,8 @@ int32_t launch_nf4_gemm_tmem(const DeviceContext& ctx, const WeightView& w, cons
     p.lut = ctx.gemm_lut;
 
     CUtensorMap map;
-    const cuuint64_t dims[2] = {w.in_features, rows};
-    const cuuint64_t strides[1] = {w.in_features * 2};
+    const cuuint64_t dims[2] = {ws[0].in_features, rows};
+    const cuuint64_t strides[1] = {ws[0].in_features * 2};
     const cuuint32_t box[2] = {kBK, p.tile_t};
     const cuuint32_t elem[2] = {1, 1};
     const CUresult r = encode_tiled()(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(x_bf16), dims,
@@ -431,8 +466,8 @@ int32_t launch_nf4_gemm_tmem(const DeviceContext& ctx, const WeightView& w, cons
     }
     cudaLaunchConfig_t config = {};
     // weight-row tiles vary fastest: CTAs that run together share the activation tile in L2
-    config.gridDim = dim3(static_cast<unsigned>((w.out_features + kTileW - 1) / kTileW),
-                          static_cast<unsigned>((rows + p.tile_t - 1) / p.tile_t), ksplit);
+    config.gridDim = dim3(static_cast<unsigned>(weight_tiles), static_cast<unsigned>((rows + p.tile_t - 1) / p.tile_t),
+                          ksplit);
     config.blockDim = dim3(kThreads);
     config.dynamicSmemBytes = kSmemBytes;
     config.stream = stream;
@@ -450,6 +485,12 @@ int32_t launch_nf4_gemm_tmem(const DeviceContext& ctx, const WeightView& w, cons
     config.numAttrs = pdl ? 2 : 1;
     B2_CUDA_TRY(cudaLaunchKernelEx(&config, nf4_gemm_tmem_kernel, map, p));
     return B2_STATUS_OK;
+}
+
+int32_t launch_nf4_gemm_tmem(const DeviceContext& ctx, const WeightView& w, const void* x_bf16, float* y,
+                             uint64_t rows, cudaStream_t stream) {
+    float* ys[1] = {y};
+    return launch_nf4_gemm_tmem_multi(ctx, &w, ys, 1, x_bf16, rows, stream);
 }
 
 }  // namespace b2

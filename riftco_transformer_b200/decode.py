@@ -123,7 +123,17 @@ class CudaOps:
         ws = w.struct()
         _check(lib.b2_nf4_linear_forward(C.byref(ws), x.data_ptr(), out.data_ptr(), x.shape[0], None, 0,
                                          _stream_ptr(None)))
-        self.launches += 1
+        self.launches += 2 if x.shape[0] > 16 else 1   # above 16 rows: conversion pre-pass + tensor-core kernel
+
+    def linear_multi(self, x, weights, outs) -> None:
+        """Several packed linears of the same input (q / k / v, gate / up): one call, and above
+        16 rows one conversion and one kernel launch for all of them."""
+        n = len(weights)
+        structs = (_lib.Nf4WeightStruct * n)(*[w.struct() for w in weights])
+        ptrs = (C.c_void_p * n)(*[o.data_ptr() for o in outs])
+        _check(lib.b2_nf4_linear_forward_multi(structs, n, x.data_ptr(), ptrs, x.shape[0], None, 0,
+                                               _stream_ptr(None)))
+        self.launches += 2 if (x.shape[0] > 16 and n <= 4) else n
 
     def rmsnorm(self, x, delta, x_out, scale, y, eps: float) -> None:
         _check(lib.b2_rmsnorm(x.data_ptr(), None if delta is None else delta.data_ptr(),
@@ -242,9 +252,8 @@ class DecodeStep:
         for layer in range(cfg.layers):
             w, nm = self.w[layer], self.norms[layer]
             ops.rmsnorm(self.x, pending, self.x, nm["attn"], self.n, cfg.eps)
-            ops.linear(self.n, w["wq"], self.q.view(self.batch, -1))
-            ops.linear(self.n, w["wk"], self.k.view(self.batch, -1))
-            ops.linear(self.n, w["wv"], self.v.view(self.batch, -1))
+            ops.linear_multi(self.n, [w["wq"], w["wk"], w["wv"]],
+                             [self.q.view(self.batch, -1), self.k.view(self.batch, -1), self.v.view(self.batch, -1)])
             ops.rope_append(self.q, self.k, self.v, positions, self.tables, self.pools[layer], cfg.theta,
                             self.status)
             ops.attention(self.q, self.pools[layer], self.tables, seq_lens, self.ctx_local, self.max_seq_len,
@@ -253,8 +262,7 @@ class DecodeStep:
             ops.linear(ctx, w["wo"], self.o_local)
             o = self._gather(self.o_local, self.o)
             ops.rmsnorm(self.x, o, self.x, nm["ffn"], self.n, cfg.eps)
-            ops.linear(self.n, w["w_gate"], self.gate)
-            ops.linear(self.n, w["w_up"], self.up)
+            ops.linear_multi(self.n, [w["w_gate"], w["w_up"]], [self.gate, self.up])
             ops.silu_mul(self.gate, self.up, self.h_local)
             h = self._gather(self.h_local, self.h)
             ops.linear(h, w["w_down"], self.down_local)

@@ -131,3 +131,35 @@ def test_input_backward_config3_sampled_rows(b2, port):
     want = port.linear_input_backward(host, dy[idx])
     assert rel_l2(dx[idx], want) <= GEMM_TOL
     assert np.isfinite(dx).all()
+
+
+@pytest.mark.parametrize("rows", [4, 32, 200])
+def test_multi_weight_forward_matches_single_calls(b2, port, rows):
+    """b2_nf4_linear_forward_multi: q / k / v style projections of one input. Up to 16 rows it is a
+    loop of single calls; above, one conversion and one launch - bit-identical to the single calls."""
+    import ctypes as C
+
+    from riftco_transformer_b200 import _lib
+    from riftco_transformer_b200._lib import lib
+    from riftco_transformer_b200.backend import _check
+    rng = np.random.default_rng(rows)
+    in_f = 512
+    hosts = [port.quantize_nf4_double_quantized((rng.standard_normal((o, in_f)) * 0.02).astype(np.float32), 64, 256)
+             for o in (640, 128, 136)]
+    hosts.append(port.quantize_nf4((rng.standard_normal((256, in_f)) * 0.02).astype(np.float32), 128))
+    weights = [b2.PackedNf4Weight.from_host(h) for h in hosts]
+    x = torch.from_numpy(rng.standard_normal((rows, in_f)).astype(np.float32)).cuda()
+    singles = [forward(b2, w, x) for w in weights]
+    outs = [torch.empty((rows, w.out_features), device="cuda") for w in weights]
+    structs = (_lib.Nf4WeightStruct * len(weights))(*[w.struct() for w in weights])
+    ptrs = (C.c_void_p * len(weights))(*[o.data_ptr() for o in outs])
+    _check(lib.b2_nf4_linear_forward_multi(structs, len(weights), x.data_ptr(), ptrs, rows, None, 0, None))
+    b2.check_device_errors()
+    for host, single, out in zip(hosts, singles, outs):
+        got = out.cpu().numpy()
+        assert rel_l2(got, port.linear_forward(host, x.cpu().numpy())) <= GEMM_TOL
+        assert (got.view(np.uint32) == single.view(np.uint32)).all()
+    # an output used twice is a caller error, reported by the single-call path
+    ptrs[1] = ptrs[0]
+    with pytest.raises(ValueError):
+        _check(lib.b2_nf4_linear_forward_multi(structs, len(weights), x.data_ptr(), ptrs, rows, None, 0, None))
