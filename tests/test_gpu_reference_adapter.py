@@ -28,7 +28,7 @@ def cuda_ref():
 @pytest.mark.parametrize("rows,out_f,in_f,block,dq,tol", [
     (1, 4096, 4096, 64, True, 2e-3),       # decode GEMV
     (8, 1000, 192, 64, False, 2e-3),       # ragged rows, FP32 scales
-    (64, 1024, 512, 64, True, 1e-2),       # skinny tensor-core kernel
+    (64, 1024, 512, 64, True, 1e-2),       # tensor-memory kernel, small token tile
     (300, 512, 256, 128, True, 1e-2),      # 256 x 256 tensor-core kernel
     (5, 77, 333, 32, True, 2e-3),          # shape only the generic kernel takes
 ])
