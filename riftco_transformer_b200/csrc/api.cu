@@ -330,6 +330,19 @@ int32_t linear_backward_impl(const b2_nf4_weight* weight, const float* dy, float
         return fail(B2_STATUS_INVALID_ARGUMENT, "quantized linear weight and output storage must not alias");
     }
     static const char* gemm_off = getenv("B2_DISABLE_TENSOR_GEMM");
+    // From 512 rows: expand W once, transposed, into scratch and run a plain bf16 tcgen05 GEMM
+    // (B2_BACKWARD_IMPL=fused keeps the kernel that transposes nibbles inside the SM).
+    static const char* backward_impl = getenv("B2_BACKWARD_IMPL");
+    const bool dense_off = backward_impl != nullptr && strcmp(backward_impl, "fused") == 0;
+    if (gemm_off == nullptr && !dense_off && nf4_backward_dense_supported(w, dy, rows)) {
+        const size_t need = nf4_backward_dense_workspace_bytes(w, rows);
+        if (workspace == nullptr) {
+            B2_TRY(reserve_arena(ctx, need));
+            workspace = ctx->arena;
+            workspace_bytes = ctx->arena_bytes;
+        }
+        return launch_nf4_backward_dense(*ctx, w, dy, dx, rows, workspace, workspace_bytes, stream);
+    }
     if (gemm_off == nullptr && nf4_gemm_supported(w, dy, rows, true)) {
         const size_t need = nf4_gemm_workspace_bytes(w, rows, true);
         if (workspace == nullptr) {
@@ -491,6 +504,9 @@ size_t b2_nf4_linear_workspace_bytes(const b2_nf4_weight* weight, uint64_t rows,
     clear_error();
     if (backward == 0 && rows > 16 && nf4_gemm_tmem_supported(w, reinterpret_cast<const float*>(16), rows)) {
         return nf4_gemm_tmem_workspace_bytes(w, rows);
+    }
+    if (backward != 0 && nf4_backward_dense_supported(w, reinterpret_cast<const float*>(16), rows)) {
+        return nf4_backward_dense_workspace_bytes(w, rows);
     }
     if (!nf4_gemm_supported(w, reinterpret_cast<const float*>(16), rows, backward != 0)) return 0;
     return nf4_gemm_workspace_bytes(w, rows, backward != 0);

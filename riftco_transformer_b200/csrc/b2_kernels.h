@@ -45,6 +45,11 @@ int32_t launch_nf4_gemm_tmem(const DeviceContext& ctx, const WeightView& w, cons
                              uint64_t rows, cudaStream_t stream);
 int32_t launch_nf4_gemm_tmem_multi(const DeviceContext& ctx, const WeightView* ws, float* const* ys, uint32_t count,
                                    const void* x_bf16, uint64_t rows, cudaStream_t stream);
+// nf4_backward_dense.cu - input-backward for many rows: transposed bf16 expansion + plain tcgen05 GEMM.
+bool nf4_backward_dense_supported(const WeightView& w, const float* dy, uint64_t rows);
+size_t nf4_backward_dense_workspace_bytes(const WeightView& w, uint64_t rows);
+int32_t launch_nf4_backward_dense(const DeviceContext& ctx, const WeightView& w, const float* dy, float* dx,
+                                  uint64_t rows, void* workspace, size_t workspace_bytes, cudaStream_t stream);
 bool nf4_gemm_supported(const WeightView& w, const float* x, uint64_t rows, bool backward);
 size_t nf4_gemm_workspace_bytes(const WeightView& w, uint64_t rows, bool backward);
 int32_t launch_nf4_gemm(const DeviceContext& ctx, const WeightView& w, const float* x, float* y, uint64_t rows,

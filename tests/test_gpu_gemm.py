@@ -106,6 +106,9 @@ def backward(b2, w, dy):
     (300, 256, 512, 64, True),      # ragged M, ring wraps
     (100, 1024, 320, 64, True),     # ragged N (320 = 256 + 64), in-blocks past the edge
     (257, 512, 1024, 256, False),   # block 256: four 64-wide column groups share a scale
+    (600, 192, 320, 64, True),      # 512+ rows: transposed expansion + plain bf16 GEMM; ragged M and N tiles
+    (1000, 128, 64, 64, False),     # same path, one column tile, FP32 scales
+    (513, 320, 512, 128, True),     # same path, block 128, five k-blocks (ring wraps)
 ])
 def test_input_backward_tensor_core(b2, port, rows, out_f, in_f, block, dq):
     rng = np.random.default_rng(rows * 3 + in_f)
