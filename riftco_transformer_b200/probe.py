@@ -2,6 +2,7 @@
 for profilers and quick timing:
 
     python -m riftco_transformer_b200.probe linear --rows 1 --out 14336 --inp 4096 --launches 4
+    python -m riftco_transformer_b200.probe linear --rows 4096 --backward --launches 2
     python -m riftco_transformer_b200.probe attention --seqs 8 --context 4096 --launches 3
 
 ``linear`` runs ``--launches`` calls of the packed-NF4 forward, each on its own
@@ -28,21 +29,27 @@ def probe_linear(args) -> None:
     rows, out_f, in_f = args.rows, args.out, args.inp
     weights = [synth.packed_weight(out_f, in_f, seed=1000 + i, double_quantized=not args.fp32_scales)
                for i in range(args.launches)]
-    x = torch.randn((rows, in_f), device="cuda")
-    y = torch.empty((rows, out_f), device="cuda")
     shape = (rows, in_f, out_f, weights[0].block_size)
-    b2.dispatch_quantized_linear_forward(x, weights[0], y, shape)   # library set-up outside the timed launches
+    if args.backward:   # dX[rows, in] = dY[rows, out] * W
+        x = torch.randn((rows, out_f), device="cuda") * 0.01
+        y = torch.empty((rows, in_f), device="cuda")
+        call = b2.dispatch_quantized_linear_input_backward
+    else:               # Y[rows, out] = X[rows, in] * W^T
+        x = torch.randn((rows, in_f), device="cuda")
+        y = torch.empty((rows, out_f), device="cuda")
+        call = b2.dispatch_quantized_linear_forward
+    call(x, weights[0], y, shape)   # library set-up outside the timed launches
     torch.cuda.synchronize()
     start, stop = _events()
     start.record()
     for w in weights:
-        b2.dispatch_quantized_linear_forward(x, w, y, shape)
+        call(x, w, y, shape)
     stop.record()
     torch.cuda.synchronize()
     b2.check_device_errors()
     us = start.elapsed_time(stop) * 1e3 / args.launches
     payload = weights[0].resident_payload_bytes()
-    print(f"linear rows={rows} {in_f}->{out_f}: {us:.2f} us/launch (eager, launch gaps included), "
+    print(f"linear {'input-backward' if args.backward else 'forward'} rows={rows} {in_f}->{out_f}: {us:.2f} us/launch (eager, launch gaps included), "
           f"{payload} B of packed weight per launch = {payload / us / 1e3:.1f} GB/s, "
           f"{2.0 * rows * out_f * in_f / us / 1e6:.1f} TFLOP/s")
 
@@ -79,6 +86,7 @@ def main() -> None:
     lin.add_argument("--inp", type=int, default=4096)
     lin.add_argument("--launches", type=int, default=4)
     lin.add_argument("--fp32-scales", action="store_true")
+    lin.add_argument("--backward", action="store_true", help="time the input-backward dX = dY * W instead")
     lin.set_defaults(fn=probe_linear)
     att = sub.add_parser("attention")
     att.add_argument("--seqs", type=int, default=8)
