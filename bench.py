@@ -278,7 +278,7 @@ def kernel_measurements(torch, b2, synth, peaks) -> dict:
             sweep[f"M{m}_{i}to{o}"] = {"us": round(us, 3), "gbps": round(gbps, 1),
                                        "frac": round(gbps / peaks["hbm_gbs"], 4)}
         del ws
-    out["nf4_gemv_sweep"] = {"kernel": "nf4_gemv_stream_kernel", "bound": "hbm", "unit": "GB/s",
+    out["nf4_gemv_sweep"] = {"kernel": "nf4_gemv_tma_kernel", "bound": "hbm", "unit": "GB/s",
                              "bytes": "packed codes + scale payload per launch", "cases": sweep}
     # Paged GQA decode attention: 64 sequences, context U[512, 8192].
     lens = np.random.default_rng(91011).integers(512, 8193, size=64)
@@ -437,7 +437,7 @@ def run_b200(args) -> None:
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
-            "scaling": "strong", "vs_baseline": None, "dtype": "f32 (f16 mma operands, f32 accumulate in the linears)",
+            "scaling": "strong", "vs_baseline": None, "dtype": "f32 (batch-32 linears: bf16 tcgen05 operands, f32 accumulate; the GEMV sweep: f16 mma.sync operands, f32 accumulate)",
             "data": "synthetic", "config": workload_config(world), "roofline": roofline,
             "step_roofline": step_roofline, "kernels": kernels, "cpu_baseline": cpu_baseline, "e2e": e2e,
             "clocks": clocks, "gpu_launches": launches_per_step * args.steps,
