@@ -219,14 +219,19 @@ class DecodeStep:
         self.v = e((B, self.hkv, hd))
         self.ctx_local = e((B, self.hq, hd))
         self.ctx = g((B, cfg.q_heads * hd)) if world > 1 else None
+        # The o- and down-projections may be given whole to every rank instead of row-sharded: their
+        # inputs are gathered anyway, a [B, d] output is small, and computing it everywhere costs less
+        # than a cross-GPU handshake (two gathers per layer instead of four).
+        self.whole_o = world > 1 and weights[0]["wo"].out_features == d
+        self.whole_down = world > 1 and weights[0]["w_down"].out_features == d
         self.o_local = e((B, d // world))
-        self.o = g((B, d)) if world > 1 else None
+        self.o = (e((B, d)) if self.whole_o else g((B, d))) if world > 1 else None
         self.gate = e((B, cfg.ffn // world))
         self.up = e((B, cfg.ffn // world))
         self.h_local = e((B, cfg.ffn // world))
         self.h = g((B, cfg.ffn)) if world > 1 else None
         self.down_local = e((B, d // world))
-        self.down = g((B, d)) if world > 1 else None
+        self.down = (e((B, d)) if self.whole_down else g((B, d))) if world > 1 else None
         self.logits_local = e((B, cfg.vocab // world))
         self.logits = g((B, cfg.vocab)) if world > 1 else None
         self.next_tokens = e((B,), dtype=torch.int32)
@@ -259,14 +264,22 @@ class DecodeStep:
             ops.attention(self.q, self.pools[layer], self.tables, seq_lens, self.ctx_local, self.max_seq_len,
                           self.status, self.workspace)
             ctx = self._gather(self.ctx_local, self.ctx)
-            ops.linear(ctx, w["wo"], self.o_local)
-            o = self._gather(self.o_local, self.o)
+            if self.whole_o:
+                ops.linear(ctx, w["wo"], self.o)
+                o = self.o
+            else:
+                ops.linear(ctx, w["wo"], self.o_local)
+                o = self._gather(self.o_local, self.o)
             ops.rmsnorm(self.x, o, self.x, nm["ffn"], self.n, cfg.eps)
             ops.linear_multi(self.n, [w["w_gate"], w["w_up"]], [self.gate, self.up])
             ops.silu_mul(self.gate, self.up, self.h_local)
             h = self._gather(self.h_local, self.h)
-            ops.linear(h, w["w_down"], self.down_local)
-            pending = self._gather(self.down_local, self.down)
+            if self.whole_down:
+                ops.linear(h, w["w_down"], self.down)
+                pending = self.down
+            else:
+                ops.linear(h, w["w_down"], self.down_local)
+                pending = self._gather(self.down_local, self.down)
         ops.rmsnorm(self.x, pending, self.x, self.norms["final"], self.n, cfg.eps)
         ops.linear(self.n, self.w["lm_head"], self.logits_local)
         logits = self._gather(self.logits_local, self.logits)
@@ -279,6 +292,9 @@ class DecodeStep:
         for layer in range(self.cfg.layers):
             total += sum(self.w[layer][k].resident_payload_bytes() for k in LAYER_WEIGHTS)
         return total + self.w["lm_head"].resident_payload_bytes()
+
+
+WHOLE_ON_EVERY_RANK = ("wo", "w_down")   # see DecodeStep: replicated rather than row-sharded
 
 
 def synthetic_step(cfg: DecoderConfig, batch: int, context: int, rank: int = 0, world: int = 1, device="cuda",
@@ -295,8 +311,12 @@ def synthetic_step(cfg: DecoderConfig, batch: int, context: int, rank: int = 0, 
         weights[layer] = {}
         for i, name in enumerate(LAYER_WEIGHTS):
             out_f, in_f = shapes[name]
-            weights[layer][name] = synth.packed_weight(out_f // world, in_f, device=device,
-                                                       seed=seed + 1000 * layer + 10 * i + rank)
+            if name in WHOLE_ON_EVERY_RANK:   # the same weight on every rank
+                weights[layer][name] = synth.packed_weight(out_f, in_f, device=device,
+                                                           seed=seed + 1000 * layer + 10 * i)
+            else:
+                weights[layer][name] = synth.packed_weight(out_f // world, in_f, device=device,
+                                                           seed=seed + 1000 * layer + 10 * i + rank)
     out_f, in_f = shapes["lm_head"]
     weights["lm_head"] = synth.packed_weight(out_f // world, in_f, device=device, seed=seed + 999983 + rank)
     g = torch.Generator(device=device)

@@ -46,14 +46,16 @@ def host_model(seed=77):
                 tokens=tokens)
 
 
-def checker_step(model, rank=0, world=1, group=None):
-    """DecodeStep over CheckerOps for one rank (row / KV-head shards of the host model)."""
+def checker_step(model, rank=0, world=1, group=None, whole=()):
+    """DecodeStep over CheckerOps for one rank (row / KV-head shards of the host model; the
+    weights named in `whole` are given to every rank unsharded)."""
     from riftco_transformer_b200.decode import DecodeStep
     ops = decode_ref.CheckerOps(group)
     hkv = CFG.kv_heads // world
     weights = {}
     for layer in range(CFG.layers):
-        weights[layer] = {n: decode_ref.shard_rows(model["weights"][layer][n], rank, world) for n in LAYER_WEIGHTS}
+        weights[layer] = {n: (model["weights"][layer][n] if n in whole else
+                              decode_ref.shard_rows(model["weights"][layer][n], rank, world)) for n in LAYER_WEIGHTS}
     weights["lm_head"] = decode_ref.shard_rows(model["weights"]["lm_head"], rank, world)
     norms = {k: ({a: torch.from_numpy(b) for a, b in v.items()} if isinstance(v, dict) else torch.from_numpy(v))
              for k, v in model["norms"].items()}

@@ -18,22 +18,28 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, out_dir):
+def _worker(rank, world, port, out_dir, whole=()):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
     torch.set_num_threads(1)
     model = decode_cases.host_model()
-    step = decode_cases.checker_step(model, rank, world, dist.group.WORLD)
+    step = decode_cases.checker_step(model, rank, world, dist.group.WORLD, whole)
     nxt, logits = decode_cases.run(step, model)
     np.save(os.path.join(out_dir, f"logits{rank}.npy"), logits)
     np.save(os.path.join(out_dir, f"next{rank}.npy"), nxt)
     dist.destroy_process_group()
 
 
-def test_two_ranks_match_one_rank(tmp_path):
+import pytest
+
+
+@pytest.mark.parametrize("whole", [(), ("wo", "w_down")], ids=["all-sharded", "o-and-down-whole"])
+def test_two_ranks_match_one_rank(tmp_path, whole):
+    """Row / KV-head shards with four gathers per layer, and the variant that keeps the o- and
+    down-projections whole on every rank (two gathers per layer)."""
     model = decode_cases.host_model()
     nxt1, logits1 = decode_cases.run(decode_cases.checker_step(model), model)
-    mp.spawn(_worker, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
+    mp.spawn(_worker, args=(2, _free_port(), str(tmp_path), whole), nprocs=2, join=True)
     for rank in range(2):
         logits = np.load(tmp_path / f"logits{rank}.npy")
         nxt = np.load(tmp_path / f"next{rank}.npy")
@@ -43,7 +49,6 @@ def test_two_ranks_match_one_rank(tmp_path):
 
 
 def test_shard_check_rejects_uneven_splits():
-    import pytest
     from riftco_transformer_b200.decode import DecoderConfig
     with pytest.raises(ValueError):
         DecoderConfig(kv_heads=8).shard_check(3)
