@@ -66,10 +66,12 @@ peer_gather_kernel(const PeerGatherArgs a) {
             *reinterpret_cast<float4*>(full + dst) = v;
         }
     }
-    __threadfence_system();
+    // One system-scope fence per CTA, by the thread that then counts the CTA in: the barrier orders
+    // every thread's stores before it, and the fence is cumulative over what the barrier ordered.
     __syncthreads();
     __shared__ uint32_t s_last;
     if (threadIdx.x == 0) {
+        __threadfence_system();
         const uint32_t done = atomicAdd(&a.state[1], 1u) + 1u;
         s_last = done == gridDim.x ? 1u : 0u;
     }
