@@ -85,3 +85,29 @@ def test_sizes_past_the_address_space_overflow():
     stream = b"RTNF4S1\0" + struct.pack("<Q", 1) + _header(n_codes=2 ** 64 - 8, n_fp32=2 ** 62) + bytes(8)
     with pytest.raises(OverflowError, match="exceeds addressable memory"):
         rtnf4.index(stream)
+
+
+def test_row_shards_are_slices_of_the_stream(payloads):
+    """load_weight on the CPU device: a shard's arrays are byte ranges of the stream, the second-level
+    scales are shared, and flat_block_base keeps the parent's block numbering."""
+    from riftco_transformer_b200 import rtnf4
+    stream = rtnf4.dumps(payloads[:1])
+    entry = rtnf4.index(stream)[0]
+    host = payloads[0]                      # 48 x 128, block 64, 16 blocks per second-level scale
+    whole = rtnf4.load_weight(stream, entry, device="cpu")
+    assert np.array_equal(whole.codes.numpy(), host.codes)
+    assert np.array_equal(whole.primary.numpy(), host.scale_codes)
+    assert whole.flat_block_base == 0 and whole.out_features == 48
+    blocks_per_row = 128 // 64
+    for rank in range(4):
+        part = rtnf4.load_weight(stream, entry, device="cpu", rank=rank, world=4)
+        rows = slice(12 * rank, 12 * (rank + 1))
+        assert part.out_features == 12 and part.in_features == 128
+        assert np.array_equal(part.codes.numpy(), host.codes[rows.start * 64:rows.stop * 64])
+        assert np.array_equal(part.primary.numpy(),
+                              host.scale_codes[rows.start * blocks_per_row:rows.stop * blocks_per_row])
+        assert np.array_equal(part.secondary.numpy().view(np.uint32),
+                              np.asarray(host.second_level, np.float32).view(np.uint32))
+        assert part.flat_block_base == rows.start * blocks_per_row
+    with pytest.raises(ValueError):
+        rtnf4.load_weight(stream, entry, device="cpu", rank=0, world=5)     # 48 rows do not divide by 5
