@@ -32,6 +32,8 @@ def forward(b2, w, x):
     (300, 512, 256, 64, True),      # ragged M, several k-blocks (ring wraps)
     (257, 300, 1024, 128, True),    # ragged M and N, block 128
     (64, 1000, 4096, 64, False),    # fewer rows than a tile, FP32 scales, long K
+    (300, 256, 2048, 64, True),     # full 256-token tiles with the contraction split over a cluster of 4:
+                                    # the partial tile fills the whole activation ring
 ])
 def test_gemm_small_shapes(b2, port, rows, out_f, in_f, block, dq):
     rng = np.random.default_rng(rows + out_f)
@@ -56,6 +58,7 @@ def test_gemm_small_shapes(b2, port, rows, out_f, in_f, block, dq):
     (100, 32000, 1024, 64, True),    # two waves of tiles, ragged token tile
     (18, 256, 64, 64, True),         # one k-block: three of the four groups have no work
     (24, 128, 192, 64, True),        # three k-blocks
+    (100, 512, 4096, 64, True),      # single issuer AND a cluster of 8 over the contraction
 ])
 def test_small_token_tiles(b2, port, rows, out_f, in_f, block, dq):
     """17..128 batch rows on the tensor-memory kernel: up to 64 tokens every expansion group issues
