@@ -361,16 +361,18 @@ def run_b200(args) -> None:
             graph.replay()
         stop.record()
         barrier()
-        elapsed_ms = start.elapsed_time(stop)
-        t_end = time.perf_counter() + max(0.0, 0.6 - elapsed_ms / 1e3)
-        while time.perf_counter() < t_end:   # keep load on the GPU until the sampler has a few samples
+        elapsed_ms = max_over_ranks(start.elapsed_time(stop))
+        # Keep load on the GPU until the sampler has a few samples. Every rank must replay the step
+        # the same number of times (each replay joins the peer all-gathers), so the count comes from
+        # the reduced time, never from a local clock.
+        extra = 0 if elapsed_ms >= 600.0 else int((600.0 - elapsed_ms) / (elapsed_ms / args.steps)) + 1
+        for _ in range(extra):
             graph.replay()
         torch.cuda.synchronize()
     clocks = sampler.summary()
     # a bounded wait that ran out (barrier, peer all-gather) invalidates the measurement
     b2.check_device_errors()
     step.ops.check_peer_status()
-    elapsed_ms = max_over_ranks(elapsed_ms)
     ms_per_step = elapsed_ms / args.steps
     value = BATCH / (ms_per_step / 1e3)
 
@@ -420,6 +422,9 @@ def run_b200(args) -> None:
     step_bytes = step.weight_bytes() + inputs["kv_bytes_per_step"]
     step_roofline = {"bytes_per_step_per_gpu": step_bytes, "hbm_floor_ms": step_bytes / peaks["hbm_gbs"] / 1e6,
                      "frac": step_bytes / peaks["hbm_gbs"] / 1e6 / ms_per_step}
+
+    b2.check_device_errors()
+    step.ops.check_peer_status()
 
     kernels = None
     cpu_baseline = None
