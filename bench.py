@@ -339,6 +339,7 @@ def run_b200(args) -> None:
         return float(t.item())
 
     # Warm up eagerly (library set-up, NCCL channels), then capture the step in a graph.
+    barrier()   # ranks finish building their shards at different times; the gathers wait only so long
     step.ops.launches = 0
     step.step(tokens, positions, seq_lens)
     launches_per_step = step.ops.launches
