@@ -426,6 +426,8 @@ def run_b200(args) -> None:
 
     b2.check_device_errors()
     step.ops.check_peer_status()
+    if int(step.status.item()) != 0:
+        raise SystemExit(f"decode step reported status bits {int(step.status.item())} (bad block table or token id)")
 
     kernels = None
     cpu_baseline = None

@@ -139,6 +139,22 @@ B2_API int32_t b2_nf4_linear_forward_multi(const b2_nf4_weight* weights, uint32_
                                     float* const* ys, uint64_t rows, void* workspace,
                                     size_t workspace_bytes, void* stream);
 
+/* b2_nf4_linear_forward_multi on activations the caller already holds as bf16
+ * (x_bf16: [rows, in_features], row-major, 16-byte aligned), e.g. written by
+ * b2_rmsnorm_bf16 / b2_silu_mul_bf16. Results equal those of
+ * b2_nf4_linear_forward_multi on the FP32 values the bf16 copy was rounded
+ * from (that call rounds them the same way before its tensor-core kernel); no
+ * conversion pass is launched and no workspace is needed. Only the
+ * tensor-memory kernel takes this form: more than 16 rows, 1-4 weights of one
+ * input width. b2_nf4_linear_bf16_supported returns 1 when a call with these
+ * weights and rows would be accepted, else 0; an unsupported call fails with
+ * B2_STATUS_INVALID_ARGUMENT. */
+B2_API int32_t b2_nf4_linear_bf16_supported(const b2_nf4_weight* weights, uint32_t count,
+                                            uint64_t rows);
+B2_API int32_t b2_nf4_linear_forward_multi_bf16(const b2_nf4_weight* weights, uint32_t count,
+                                                const void* x_bf16, float* const* ys,
+                                                uint64_t rows, void* stream);
+
 /* dx[r,i] = sum_o dy[r,o] * W[o,i]. dy: float[rows,out], dx: float[rows,in].
  * Replaces QuantizedLinearCapability::quantized_linear_input_backward
  * (capability.hpp:43-49; launch.hpp:19-20; loop reference/operations.cpp:83-115;
@@ -232,6 +248,14 @@ B2_API int32_t b2_paged_decode_attention_noalloc(
 B2_API int32_t b2_rmsnorm(const float* x, const float* delta, float* x_out, const float* scale,
                           float* y, uint64_t rows, uint64_t width, float eps, void* stream);
 
+/* b2_rmsnorm that also writes y rounded to bf16 (nearest even) into y_bf16
+ * [rows, width] when it is not NULL: the activation form
+ * b2_nf4_linear_forward_multi_bf16 reads, so the linear that follows needs no
+ * conversion pass of its own. */
+B2_API int32_t b2_rmsnorm_bf16(const float* x, const float* delta, float* x_out, const float* scale,
+                               float* y, void* y_bf16, uint64_t rows, uint64_t width, float eps,
+                               void* stream);
+
 /* Split-half rotary embedding of the new token of every sequence, in place on
  * q [n_seq, q_heads, d] and while copying k [n_seq, kv_heads, d] into its page
  * slot; v [n_seq, kv_heads, d] is copied unchanged. positions[s] is the token's
@@ -249,6 +273,11 @@ B2_API int32_t b2_rope_append_kv(float* q, const float* k, const float* v, const
 /* out = silu(gate) * up, silu as silu_forward (src/nn/activations.cpp:38-58);
  * the product is SwiGLU's hidden state (src/model/swiglu.cpp:27-29). */
 B2_API int32_t b2_silu_mul(const float* gate, const float* up, float* out, uint64_t n, void* stream);
+
+/* b2_silu_mul that also writes the product rounded to bf16 into out_bf16 [n]
+ * when it is not NULL. */
+B2_API int32_t b2_silu_mul_bf16(const float* gate, const float* up, float* out, void* out_bf16,
+                                uint64_t n, void* stream);
 
 /* out = a + b (residual add). */
 B2_API int32_t b2_add(const float* a, const float* b, float* out, uint64_t n, void* stream);

@@ -59,6 +59,8 @@ SIGNATURES = {
     "b2_nf4_dequantize": (_i32, [_W, _vp, _vp]),
     "b2_nf4_linear_forward": (_i32, [_W, _vp, _vp, _u64, _vp, _sz, _vp]),
     "b2_nf4_linear_forward_multi": (_i32, [_vp, _u32, _vp, _vp, _u64, _vp, _sz, _vp]),
+    "b2_nf4_linear_bf16_supported": (_i32, [_vp, _u32, _u64]),
+    "b2_nf4_linear_forward_multi_bf16": (_i32, [_vp, _u32, _vp, _vp, _u64, _vp]),
     "b2_nf4_linear_input_backward": (_i32, [_W, _vp, _vp, _u64, _vp, _sz, _vp]),
     "b2_nf4_linear_workspace_bytes": (_sz, [_W, _u64, _i32]),
     "b2_paged_decode_attention": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u32,
@@ -67,6 +69,8 @@ SIGNATURES = {
     "b2_paged_decode_attention_noalloc": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u32,
                                                  _u64, _u32, _u32, _vp, _vp]),
     "b2_rmsnorm": (_i32, [_vp, _vp, _vp, _vp, _vp, _u64, _u64, C.c_float, _vp]),
+    "b2_rmsnorm_bf16": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _u64, _u64, C.c_float, _vp]),
+    "b2_silu_mul_bf16": (_i32, [_vp, _vp, _vp, _vp, _u64, _vp]),
     "b2_rope_append_kv": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u32, _u64, _u32,
                                  C.c_float, _vp, _vp]),
     "b2_silu_mul": (_i32, [_vp, _vp, _vp, _u64, _vp]),

@@ -550,10 +550,77 @@ int32_t b2_paged_decode_attention(const float* q, const float* k_pages, const fl
     return launch_paged_decode(*ctx, args, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
 }
 
+namespace {
+
+// Views of `count` weights that can all take the tensor-memory kernel on one bf16 activation
+// matrix of `rows` rows; false when any of them cannot.
+bool bf16_input_views(const b2_nf4_weight* weights, uint32_t count, const void* x_bf16, uint64_t rows,
+                      WeightView* views) {
+    static const char* gemm_off = getenv("B2_DISABLE_TENSOR_GEMM");
+    static const char* gemm_impl = getenv("B2_GEMM_IMPL");
+    if (gemm_off != nullptr || (gemm_impl != nullptr && strcmp(gemm_impl, "smem") == 0)) return false;
+    if (weights == nullptr || count == 0 || count > 4 || rows <= 16) return false;
+    for (uint32_t i = 0; i < count; ++i) {
+        if (make_weight_view(&weights[i], &views[i]) != B2_STATUS_OK ||
+            check_linear_dims(views[i], rows) != B2_STATUS_OK ||
+            views[i].in_features != views[0].in_features ||
+            !nf4_gemm_tmem_supported(views[i], static_cast<const float*>(x_bf16), rows)) {
+            return false;
+        }
+    }
+    return true;
+}
+
+}  // namespace
+
+int32_t b2_nf4_linear_bf16_supported(const b2_nf4_weight* weights, uint32_t count, uint64_t rows) {
+    clear_error();
+    int32_t status = B2_STATUS_OK;
+    if (device_context(&status) == nullptr) return 0;
+    WeightView views[4];
+    const bool ok = bf16_input_views(weights, count, nullptr, rows, views);
+    clear_error();
+    return ok ? 1 : 0;
+}
+
+int32_t b2_nf4_linear_forward_multi_bf16(const b2_nf4_weight* weights, uint32_t count, const void* x_bf16,
+                                         float* const* ys, uint64_t rows, void* stream_ptr) {
+    clear_error();
+    if (weights == nullptr || ys == nullptr || count == 0 || x_bf16 == nullptr) {
+        return fail(B2_STATUS_INVALID_ARGUMENT, "quantized linear needs its weights, activations and outputs");
+    }
+    for (uint32_t i = 0; i < count; ++i) {
+        if (ys[i] == nullptr || ys[i] == x_bf16 || aliases_weight(&weights[i], ys[i])) {
+            return fail(B2_STATUS_INVALID_ARGUMENT, "quantized linear output must not be null or alias an input");
+        }
+        for (uint32_t j = 0; j < i; ++j) {
+            if (ys[i] == ys[j]) {
+                return fail(B2_STATUS_INVALID_ARGUMENT, "quantized linear outputs of one call must not alias");
+            }
+        }
+    }
+    int32_t status = B2_STATUS_OK;
+    DeviceContext* ctx = device_context(&status);
+    if (ctx == nullptr) return status;
+    WeightView views[4];
+    if (!bf16_input_views(weights, count, x_bf16, rows, views)) {
+        return fail(B2_STATUS_INVALID_ARGUMENT,
+                    "bf16 activations are taken only by the tensor-memory kernel (more than 16 rows, up to 4 "
+                    "weights of one input width, 16-byte aligned rows); ask b2_nf4_linear_bf16_supported first");
+    }
+    clear_error();
+    return launch_nf4_gemm_tmem_multi(*ctx, views, ys, count, x_bf16, rows, static_cast<cudaStream_t>(stream_ptr));
+}
+
 // ---- decode-step glue ------------------------------------------------------------
 
 int32_t b2_rmsnorm(const float* x, const float* delta, float* x_out, const float* scale, float* y,
                    uint64_t rows, uint64_t width, float eps, void* stream) {
+    return b2_rmsnorm_bf16(x, delta, x_out, scale, y, nullptr, rows, width, eps, stream);
+}
+
+int32_t b2_rmsnorm_bf16(const float* x, const float* delta, float* x_out, const float* scale, float* y,
+                        void* y_bf16, uint64_t rows, uint64_t width, float eps, void* stream) {
     clear_error();
     int32_t status = B2_STATUS_OK;
     if (device_context(&status) == nullptr) return status;
@@ -566,7 +633,10 @@ int32_t b2_rmsnorm(const float* x, const float* delta, float* x_out, const float
     if (!std::isfinite(eps) || eps <= 0.0f) {
         return fail(B2_STATUS_INVALID_ARGUMENT, "RMS normalization epsilon must be finite and positive");
     }
-    return launch_rmsnorm(x, delta, x_out, scale, y, rows, static_cast<uint32_t>(width), eps,
+    if ((reinterpret_cast<uintptr_t>(y_bf16) & 1u) != 0) {
+        return fail(B2_STATUS_INVALID_ARGUMENT, "the bf16 copy must be 2-byte aligned");
+    }
+    return launch_rmsnorm(x, delta, x_out, scale, y, y_bf16, rows, static_cast<uint32_t>(width), eps,
                           static_cast<cudaStream_t>(stream));
 }
 
@@ -598,6 +668,11 @@ int32_t b2_rope_append_kv(float* q, const float* k, const float* v, const uint32
 }
 
 int32_t b2_silu_mul(const float* gate, const float* up, float* out, uint64_t n, void* stream) {
+    return b2_silu_mul_bf16(gate, up, out, nullptr, n, stream);
+}
+
+int32_t b2_silu_mul_bf16(const float* gate, const float* up, float* out, void* out_bf16, uint64_t n,
+                         void* stream) {
     clear_error();
     int32_t status = B2_STATUS_OK;
     DeviceContext* ctx = device_context(&status);
@@ -605,7 +680,10 @@ int32_t b2_silu_mul(const float* gate, const float* up, float* out, uint64_t n, 
     if (gate == nullptr || up == nullptr || out == nullptr || n == 0) {
         return fail(B2_STATUS_INVALID_ARGUMENT, "silu_mul needs non-null pointers and a positive size");
     }
-    return launch_silu_mul(*ctx, gate, up, out, n, static_cast<cudaStream_t>(stream));
+    if ((reinterpret_cast<uintptr_t>(out_bf16) & 1u) != 0) {
+        return fail(B2_STATUS_INVALID_ARGUMENT, "the bf16 copy must be 2-byte aligned");
+    }
+    return launch_silu_mul(*ctx, gate, up, out, out_bf16, n, static_cast<cudaStream_t>(stream));
 }
 
 int32_t b2_add(const float* a, const float* b, float* out, uint64_t n, void* stream) {

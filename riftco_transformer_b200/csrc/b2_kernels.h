@@ -74,15 +74,16 @@ int32_t launch_paged_decode(const DeviceContext& ctx, const PagedDecodeArgs& arg
 
 
 // decode_glue.cu
+// y_bf16 / out_bf16 (nullable): a bf16 copy of the result, the form the tensor-core linears read.
 int32_t launch_rmsnorm(const float* x, const float* delta, float* x_out, const float* scale, float* y,
-                       uint64_t rows, uint32_t width, float eps, cudaStream_t stream);
+                       void* y_bf16, uint64_t rows, uint32_t width, float eps, cudaStream_t stream);
 int32_t launch_rope_append(float* q, const float* k, const float* v, const uint32_t* positions,
                            const uint32_t* block_tables, float* k_pages, float* v_pages, uint32_t n_seq,
                            uint32_t q_heads, uint32_t kv_heads, uint32_t d, uint32_t block_size,
                            uint64_t physical_blocks, uint32_t max_blocks, float theta, uint32_t* status,
                            cudaStream_t stream);
-int32_t launch_silu_mul(const DeviceContext& ctx, const float* gate, const float* up, float* out, uint64_t n,
-                        cudaStream_t stream);
+int32_t launch_silu_mul(const DeviceContext& ctx, const float* gate, const float* up, float* out, void* out_bf16,
+                        uint64_t n, cudaStream_t stream);
 int32_t launch_add(const DeviceContext& ctx, const float* a, const float* b, float* out, uint64_t n,
                    cudaStream_t stream);
 int32_t launch_gather_rows(const float* table, const uint32_t* ids, float* out, uint32_t rows, uint32_t width,

@@ -8,10 +8,22 @@
 #include "b2_kernels.h"
 #include "sm100_ptx.cuh"
 
+#include <cuda_bf16.h>
+
 #include <cmath>
 
 namespace b2 {
 namespace {
+
+// Four values rounded to bf16 (nearest even) as one 8-byte store: the activation
+// layout the tensor-core linears read, so their conversion pre-pass can be skipped.
+__device__ __forceinline__ void store_bf16x4(__nv_bfloat16* dst, const float4& v) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+    uint2 packed;
+    packed.x = *reinterpret_cast<uint32_t*>(&lo);
+    packed.y = *reinterpret_cast<uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(dst) = packed;
+}
 
 __device__ __forceinline__ float block_sum(float v, float* scratch) {
 #pragma unroll
@@ -33,7 +45,8 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
 // in registers between the two passes when they fit (two float4 per thread).
 __global__ void __launch_bounds__(1024)
 rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ delta, float* __restrict__ x_out,
-               const float* __restrict__ scale, float* __restrict__ y, uint32_t width, float eps, uint32_t vec4) {
+               const float* __restrict__ scale, float* __restrict__ y, __nv_bfloat16* __restrict__ y16,
+               uint32_t width, float eps, uint32_t vec4) {
     sm100::pdl_launch_dependents();   // a following linear kernel may start its set-up now
     __shared__ float scratch[32];
     const uint64_t row = blockIdx.x;
@@ -68,7 +81,9 @@ rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ delta, flo
         float4* y4 = reinterpret_cast<float4*>(y + row * width);
         auto emit = [&](uint32_t c, const float4& v) {
             const float4 g = s4[c];
-            y4[c] = make_float4(v.x * inv * g.x, v.y * inv * g.y, v.z * inv * g.z, v.w * inv * g.w);
+            const float4 o = make_float4(v.x * inv * g.x, v.y * inv * g.y, v.z * inv * g.z, v.w * inv * g.w);
+            y4[c] = o;
+            if (y16 != nullptr) store_bf16x4(y16 + row * width + 4ull * c, o);
         };
         if (c0 < n4) emit(c0, keep0);
         if (c1 < n4) emit(c1, keep1);
@@ -87,7 +102,9 @@ rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ delta, flo
     const float inv = 1.0f / sqrtf(mean_square + eps);
     const float* src = delta != nullptr ? x_out + row * width : xr;
     for (uint32_t c = threadIdx.x; c < width; c += blockDim.x) {
-        y[row * width + c] = src[c] * inv * scale[c];
+        const float o = src[c] * inv * scale[c];
+        y[row * width + c] = o;
+        if (y16 != nullptr) y16[row * width + c] = __float2bfloat16_rn(o);
     }
 }
 
@@ -95,7 +112,8 @@ rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ delta, flo
 // angle = position * theta^(-2c/d) evaluated in double,
 // src/model/rotary_embedding.cpp:64-117), then k and v are written into their
 // page slot (copy_token_to_page, src/stages/serving/cache/page_table_cache.cpp:44-77).
-// One CTA per sequence; thread = (head, channel pair).
+// Grid (sequence, slice): every CTA takes an equal slice of the sequence's (head, channel pair)
+// items and of its v row, so a decode batch of a few dozen sequences still covers the SMs.
 __global__ void __launch_bounds__(256)
 rope_append_kernel(float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
                    const uint32_t* __restrict__ positions, const uint32_t* __restrict__ block_tables,
@@ -112,39 +130,38 @@ rope_append_kernel(float* __restrict__ q, const float* __restrict__ k, const flo
         bad = true;
         phys = 0;
     }
-    if (bad && threadIdx.x == 0 && status != nullptr) atomicOr(status, B2_ATTN_STATUS_BAD_BLOCK);
+    if (bad && threadIdx.x == 0 && blockIdx.y == 0 && status != nullptr) atomicOr(status, B2_ATTN_STATUS_BAD_BLOCK);
     const uint32_t slot = pos % block_size;
     const uint32_t pairs = (q_heads + kv_heads) * half;
-    // The angles depend only on (position, channel pair): evaluated once per sequence, in double,
-    // and shared by all heads (up to 256 pairs, i.e. head widths up to 512, fit the table).
-    __shared__ float s_cos[256], s_sin[256];
-    const bool tabled = half <= 256u;
-    if (tabled) {
-        // theta^(-2c/d) as exp2(-2c/d * log2(theta)): double precision like the reference's pow, within
-        // a few ulp of it (an angle error of ~1e-13 rad at position 2048, far below the FP32 result)
-        const double log2_theta = log2(static_cast<double>(theta));
-        for (uint32_t c = threadIdx.x; c < half; c += blockDim.x) {
-            const double angle = static_cast<double>(pos) *
-                                 exp2(-2.0 * static_cast<double>(c) / static_cast<double>(d) * log2_theta);
-            double sn, cs;
-            sincos(angle, &sn, &cs);
-            s_cos[c] = static_cast<float>(cs);
-            s_sin[c] = static_cast<float>(sn);
+    const uint32_t stride = blockDim.x * gridDim.y;
+    const uint32_t first = blockIdx.y * blockDim.x + threadIdx.x;
+    // The v row does not depend on the angles: its loads go out first.
+    if (!bad) {
+        for (uint32_t i = first; i < kv_heads * d; i += stride) {
+            const uint32_t kh = i / d, c = i % d;
+            v_pages[((phys * kv_heads + kh) * block_size + slot) * d + c] =
+                v[(static_cast<uint64_t>(seq) * kv_heads + kh) * d + c];
         }
-        __syncthreads();
     }
-    for (uint32_t i = threadIdx.x; i < pairs; i += blockDim.x) {
+    // angle = position * theta^(-2c/d) with theta^(-2c/d) as exp2(-2c/d * log2(theta)): double
+    // precision like the reference's pow, within a few ulp of it (an angle error of ~1e-13 rad at
+    // position 2048, far below the FP32 result). When the stride is a multiple of d/2 a thread keeps
+    // the same channel pair for all its items and evaluates its angle once.
+    const double log2_theta = log2(static_cast<double>(theta));
+    const bool fixed_channel = stride % half == 0;
+    float cs = 0.0f, sn = 0.0f;
+    auto angle_of = [&](uint32_t c) {
+        const double angle = static_cast<double>(pos) *
+                             exp2(-2.0 * static_cast<double>(c) / static_cast<double>(d) * log2_theta);
+        double s_, c_;
+        sincos(angle, &s_, &c_);
+        cs = static_cast<float>(c_);
+        sn = static_cast<float>(s_);
+    };
+    if (fixed_channel && first < pairs) angle_of(first % half);
+    for (uint32_t i = first; i < pairs; i += stride) {
         const uint32_t head = i / half, c = i % half;
-        float cs, sn;
-        if (tabled) {
-            cs = s_cos[c];
-            sn = s_sin[c];
-        } else {
-            const double angle = static_cast<double>(pos) *
-                                 pow(static_cast<double>(theta), -2.0 * static_cast<double>(c) / static_cast<double>(d));
-            cs = static_cast<float>(cos(angle));
-            sn = static_cast<float>(sin(angle));
-        }
+        if (!fixed_channel) angle_of(c);
         if (head < q_heads) {
             float* p = q + (static_cast<uint64_t>(seq) * q_heads + head) * d;
             const float a = p[c], b = p[c + half];
@@ -157,13 +174,6 @@ rope_append_kernel(float* __restrict__ q, const float* __restrict__ k, const flo
             float* dst = k_pages + ((phys * kv_heads + kh) * block_size + slot) * d;
             dst[c] = __fsub_rn(__fmul_rn(a, cs), __fmul_rn(b, sn));
             dst[c + half] = __fadd_rn(__fmul_rn(b, cs), __fmul_rn(a, sn));
-        }
-    }
-    if (!bad) {
-        for (uint32_t i = threadIdx.x; i < kv_heads * d; i += blockDim.x) {
-            const uint32_t kh = i / d, c = i % d;
-            v_pages[((phys * kv_heads + kh) * block_size + slot) * d + c] =
-                v[(static_cast<uint64_t>(seq) * kv_heads + kh) * d + c];
         }
     }
 }
@@ -184,11 +194,13 @@ __device__ __forceinline__ float silu_ref(float value) {
 
 __global__ void __launch_bounds__(256)
 silu_mul_kernel(const float* __restrict__ gate, const float* __restrict__ up, float* __restrict__ out,
-                uint64_t n) {
+                __nv_bfloat16* __restrict__ out16, uint64_t n) {
     sm100::pdl_launch_dependents();   // a following decode GEMV may start its set-up now
     const uint64_t stride = static_cast<uint64_t>(gridDim.x) * blockDim.x;
     for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
-        out[i] = silu_ref(gate[i]) * up[i];
+        const float o = silu_ref(gate[i]) * up[i];
+        out[i] = o;
+        if (out16 != nullptr) out16[i] = __float2bfloat16_rn(o);
     }
 }
 
@@ -220,19 +232,30 @@ gather_rows_kernel(const float* __restrict__ table, const uint32_t* __restrict__
 
 // Greedy sampling: index of the first maximum of each row
 // (src/stages/serving/generation.cpp:100-120 keeps the lowest index on ties).
-__global__ void __launch_bounds__(256)
-argmax_kernel(const float* __restrict__ logits, uint32_t* __restrict__ out, uint32_t width) {
-    __shared__ float s_val[256];
-    __shared__ uint32_t s_idx[256];
+__global__ void __launch_bounds__(1024)
+argmax_kernel(const float* __restrict__ logits, uint32_t* __restrict__ out, uint32_t width, uint32_t vec4) {
+    __shared__ float s_val[1024];
+    __shared__ uint32_t s_idx[1024];
     const float* r = logits + static_cast<uint64_t>(blockIdx.x) * width;
     float best = -INFINITY;
     uint32_t best_i = 0xFFFFFFFFu;
-    for (uint32_t c = threadIdx.x; c < width; c += blockDim.x) {
-        const float v = r[c];
+    auto take = [&](float v, uint32_t c) {   // columns reach a thread in increasing order
         if (v > best || best_i == 0xFFFFFFFFu) {
             best = v;
             best_i = c;
         }
+    };
+    if (vec4) {
+        const float4* r4 = reinterpret_cast<const float4*>(r);
+        for (uint32_t c = threadIdx.x; c < width / 4; c += blockDim.x) {
+            const float4 v = __ldg(r4 + c);
+            take(v.x, 4 * c);
+            take(v.y, 4 * c + 1);
+            take(v.z, 4 * c + 2);
+            take(v.w, 4 * c + 3);
+        }
+    } else {
+        for (uint32_t c = threadIdx.x; c < width; c += blockDim.x) take(r[c], c);
     }
     s_val[threadIdx.x] = best;
     s_idx[threadIdx.x] = best_i;
@@ -263,8 +286,9 @@ unsigned grid_for(uint64_t n, int sm_count) {
 }  // namespace
 
 int32_t launch_rmsnorm(const float* x, const float* delta, float* x_out, const float* scale, float* y,
-                       uint64_t rows, uint32_t width, float eps, cudaStream_t stream) {
+                       void* y_bf16, uint64_t rows, uint32_t width, float eps, cudaStream_t stream) {
     const bool vec4 = width % 4 == 0 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y) |
+                                          reinterpret_cast<uintptr_t>(y_bf16) |
                                           reinterpret_cast<uintptr_t>(scale) | reinterpret_cast<uintptr_t>(delta) |
                                           reinterpret_cast<uintptr_t>(x_out)) & 15u) == 0;
     unsigned threads = 256;
@@ -273,8 +297,8 @@ int32_t launch_rmsnorm(const float* x, const float* delta, float* x_out, const f
         if (threads > 1024) threads = 1024;
         if (threads < 64) threads = 64;
     }
-    rmsnorm_kernel<<<static_cast<unsigned>(rows), threads, 0, stream>>>(x, delta, x_out, scale, y, width, eps,
-                                                                       vec4 ? 1u : 0u);
+    rmsnorm_kernel<<<static_cast<unsigned>(rows), threads, 0, stream>>>(
+        x, delta, x_out, scale, y, static_cast<__nv_bfloat16*>(y_bf16), width, eps, vec4 ? 1u : 0u);
     B2_CUDA_TRY(cudaGetLastError());
     return B2_STATUS_OK;
 }
@@ -284,16 +308,21 @@ int32_t launch_rope_append(float* q, const float* k, const float* v, const uint3
                            uint32_t q_heads, uint32_t kv_heads, uint32_t d, uint32_t block_size,
                            uint64_t physical_blocks, uint32_t max_blocks, float theta, uint32_t* status,
                            cudaStream_t stream) {
-    rope_append_kernel<<<n_seq, 256, 0, stream>>>(q, k, v, positions, block_tables, k_pages, v_pages, q_heads,
+    // two items per thread, at most 16 slices per sequence
+    const uint32_t pairs = (q_heads + kv_heads) * (d / 2);
+    uint32_t slices = (pairs + 511u) / 512u;
+    slices = slices == 0 ? 1u : (slices > 16u ? 16u : slices);
+    rope_append_kernel<<<dim3(n_seq, slices), 256, 0, stream>>>(q, k, v, positions, block_tables, k_pages, v_pages, q_heads,
                                                   kv_heads, d, block_size, physical_blocks, max_blocks, theta,
                                                   status);
     B2_CUDA_TRY(cudaGetLastError());
     return B2_STATUS_OK;
 }
 
-int32_t launch_silu_mul(const DeviceContext& ctx, const float* gate, const float* up, float* out, uint64_t n,
-                        cudaStream_t stream) {
-    silu_mul_kernel<<<grid_for(n, ctx.sm_count), 256, 0, stream>>>(gate, up, out, n);
+int32_t launch_silu_mul(const DeviceContext& ctx, const float* gate, const float* up, float* out, void* out_bf16,
+                        uint64_t n, cudaStream_t stream) {
+    silu_mul_kernel<<<grid_for(n, ctx.sm_count), 256, 0, stream>>>(gate, up, out,
+                                                                   static_cast<__nv_bfloat16*>(out_bf16), n);
     B2_CUDA_TRY(cudaGetLastError());
     return B2_STATUS_OK;
 }
@@ -313,7 +342,10 @@ int32_t launch_gather_rows(const float* table, const uint32_t* ids, float* out, 
 }
 
 int32_t launch_argmax(const float* logits, uint32_t* out, uint32_t rows, uint32_t width, cudaStream_t stream) {
-    argmax_kernel<<<rows, 256, 0, stream>>>(logits, out, width);
+    const bool vec4 = width % 4 == 0 && (reinterpret_cast<uintptr_t>(logits) & 15u) == 0;
+    unsigned threads = 256;   // a power of two: the tree reduction halves it
+    while (threads < 1024 && static_cast<uint64_t>(threads) * (vec4 ? 8 : 2) < width) threads *= 2;
+    argmax_kernel<<<rows, threads, 0, stream>>>(logits, out, width, vec4 ? 1u : 0u);
     B2_CUDA_TRY(cudaGetLastError());
     return B2_STATUS_OK;
 }

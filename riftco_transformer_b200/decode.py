@@ -135,10 +135,27 @@ class CudaOps:
                                                _stream_ptr(None)))
         self.launches += 2 if (x.shape[0] > 16 and n <= 4) else n
 
-    def rmsnorm(self, x, delta, x_out, scale, y, eps: float) -> None:
-        _check(lib.b2_rmsnorm(x.data_ptr(), None if delta is None else delta.data_ptr(),
-                              None if x_out is None else x_out.data_ptr(), scale.data_ptr(), y.data_ptr(),
-                              x.shape[0], x.shape[1], eps, _stream_ptr(None)))
+    def linear_bf16_supported(self, weights, rows: int) -> bool:
+        """True when `linear_multi_bf16` takes these weights at this row count."""
+        n = len(weights)
+        structs = (_lib.Nf4WeightStruct * n)(*[w.struct() for w in weights])
+        return bool(lib.b2_nf4_linear_bf16_supported(structs, n, rows))
+
+    def linear_multi_bf16(self, x16, weights, outs) -> None:
+        """`linear_multi` on activations already held as bf16 (written by `rmsnorm` / `silu_mul`
+        next to their FP32 result): one kernel launch, no conversion pass."""
+        n = len(weights)
+        structs = (_lib.Nf4WeightStruct * n)(*[w.struct() for w in weights])
+        ptrs = (C.c_void_p * n)(*[o.data_ptr() for o in outs])
+        _check(lib.b2_nf4_linear_forward_multi_bf16(structs, n, x16.data_ptr(), ptrs, x16.shape[0],
+                                                    _stream_ptr(None)))
+        self.launches += 1
+
+    def rmsnorm(self, x, delta, x_out, scale, y, eps: float, y16=None) -> None:
+        _check(lib.b2_rmsnorm_bf16(x.data_ptr(), None if delta is None else delta.data_ptr(),
+                                   None if x_out is None else x_out.data_ptr(), scale.data_ptr(), y.data_ptr(),
+                                   None if y16 is None else y16.data_ptr(), x.shape[0], x.shape[1], eps,
+                                   _stream_ptr(None)))
         self.launches += 1
 
     def rope_append(self, q, k, v, positions, tables, pool: PagedKvPool, theta: float, status) -> None:
@@ -164,8 +181,9 @@ class CudaOps:
         need = lib.b2_paged_decode_workspace_bytes(n_seq, q_heads, d, block_size, max_seq_len)
         return torch.empty(max(need, 16), dtype=torch.uint8, device=self.device)
 
-    def silu_mul(self, gate, up, out) -> None:
-        _check(lib.b2_silu_mul(gate.data_ptr(), up.data_ptr(), out.data_ptr(), out.numel(), _stream_ptr(None)))
+    def silu_mul(self, gate, up, out, out16=None) -> None:
+        _check(lib.b2_silu_mul_bf16(gate.data_ptr(), up.data_ptr(), out.data_ptr(),
+                                    None if out16 is None else out16.data_ptr(), out.numel(), _stream_ptr(None)))
         self.launches += 1
 
     def gather_rows(self, table, ids, out, status) -> None:
@@ -236,10 +254,23 @@ class DecodeStep:
         self.logits = g((B, cfg.vocab)) if world > 1 else None
         self.next_tokens = e((B,), dtype=torch.int32)
         self.status = ops.empty((1,), dtype=torch.int32)
+        self.status.zero_()   # sticky error bits of the attention / append / gather kernels
         self.workspace = ops.attention_workspace(B, self.hq, hd, cfg.block_size, max_seq_len)
         if world > 1:
             widths = {cfg.q_heads * hd // world, d // world, cfg.ffn // world, cfg.vocab // world}
             self.stage = {n_: e((world, B, n_)) for n_ in widths}
+        # Where the backend's tensor-core linears read bf16 activations, the kernel that produces an
+        # activation also writes its bf16 copy and the linear skips its own conversion pass. Values
+        # are the same either way (the pass rounds the same FP32 numbers the same way).
+        self.n16 = self.h16 = None
+        takes_bf16 = getattr(ops, "linear_bf16_supported", None)
+        if takes_bf16 is not None and os.environ.get("B2_BF16_HANDOFF", "1") != "0":
+            w0 = weights[0]
+            if (takes_bf16([w0["wq"], w0["wk"], w0["wv"]], B) and takes_bf16([w0["w_gate"], w0["w_up"]], B)
+                    and takes_bf16([weights["lm_head"]], B)):
+                self.n16 = e((B, d), dtype=torch.bfloat16)
+            if world == 1 and takes_bf16([w0["w_down"]], B):
+                self.h16 = e((B, cfg.ffn), dtype=torch.bfloat16)
 
     def _gather(self, local, full):
         if self.world == 1:
@@ -247,6 +278,21 @@ class DecodeStep:
         flat = local.view(local.shape[0], -1)
         self.ops.all_gather_columns(flat, self.stage[flat.shape[1]], full)
         return full
+
+    def _norm(self, delta, scale) -> None:
+        """x += delta (when given), n = rmsnorm(x) * scale, plus n's bf16 copy where it is used."""
+        if self.n16 is not None:
+            self.ops.rmsnorm(self.x, delta, self.x, scale, self.n, self.cfg.eps, self.n16)
+        else:
+            self.ops.rmsnorm(self.x, delta, self.x, scale, self.n, self.cfg.eps)
+
+    def _linears_of_n(self, weights, outs) -> None:
+        if self.n16 is not None:
+            self.ops.linear_multi_bf16(self.n16, weights, outs)
+        elif len(weights) == 1:
+            self.ops.linear(self.n, weights[0], outs[0])
+        else:
+            self.ops.linear_multi(self.n, weights, outs)
 
     def step(self, tokens, positions, seq_lens):
         """tokens int32 [B]; positions uint32/int32 [B] = index of the new token;
@@ -256,9 +302,10 @@ class DecodeStep:
         pending = None  # residual delta not yet added to x
         for layer in range(cfg.layers):
             w, nm = self.w[layer], self.norms[layer]
-            ops.rmsnorm(self.x, pending, self.x, nm["attn"], self.n, cfg.eps)
-            ops.linear_multi(self.n, [w["wq"], w["wk"], w["wv"]],
-                             [self.q.view(self.batch, -1), self.k.view(self.batch, -1), self.v.view(self.batch, -1)])
+            self._norm(pending, nm["attn"])
+            self._linears_of_n([w["wq"], w["wk"], w["wv"]],
+                               [self.q.view(self.batch, -1), self.k.view(self.batch, -1),
+                                self.v.view(self.batch, -1)])
             ops.rope_append(self.q, self.k, self.v, positions, self.tables, self.pools[layer], cfg.theta,
                             self.status)
             ops.attention(self.q, self.pools[layer], self.tables, seq_lens, self.ctx_local, self.max_seq_len,
@@ -270,8 +317,13 @@ class DecodeStep:
             else:
                 ops.linear(ctx, w["wo"], self.o_local)
                 o = self._gather(self.o_local, self.o)
-            ops.rmsnorm(self.x, o, self.x, nm["ffn"], self.n, cfg.eps)
-            ops.linear_multi(self.n, [w["w_gate"], w["w_up"]], [self.gate, self.up])
+            self._norm(o, nm["ffn"])
+            self._linears_of_n([w["w_gate"], w["w_up"]], [self.gate, self.up])
+            if self.h16 is not None:   # one rank: the down-projection reads the bf16 copy directly
+                ops.silu_mul(self.gate, self.up, self.h_local, self.h16)
+                ops.linear_multi_bf16(self.h16, [w["w_down"]], [self.down_local])
+                pending = self.down_local
+                continue
             ops.silu_mul(self.gate, self.up, self.h_local)
             h = self._gather(self.h_local, self.h)
             if self.whole_down:
@@ -280,8 +332,8 @@ class DecodeStep:
             else:
                 ops.linear(h, w["w_down"], self.down_local)
                 pending = self._gather(self.down_local, self.down)
-        ops.rmsnorm(self.x, pending, self.x, self.norms["final"], self.n, cfg.eps)
-        ops.linear(self.n, self.w["lm_head"], self.logits_local)
+        self._norm(pending, self.norms["final"])
+        self._linears_of_n([self.w["lm_head"]], [self.logits_local])
         logits = self._gather(self.logits_local, self.logits)
         ops.argmax(logits, self.next_tokens)
         return self.next_tokens, logits

@@ -104,3 +104,120 @@ def test_glue_operators():
     page, slot = tables[s, positions[s] // bs], positions[s] % bs
     assert np.allclose(pool.key_pages[page, :, slot].cpu().numpy(), decode_ref.rotate(k[s], 301, 1e4), rtol=1e-6, atol=1e-6)
     assert (pool.value_pages[page, :, slot].cpu().numpy() == v[s]).all()
+
+
+@pytest.mark.parametrize("hq,hkv,d", [(32, 8, 128), (5, 1, 96), (3, 3, 40)])
+def test_rope_append_over_several_slices(hq, hkv, d):
+    """Head counts that spread one sequence over several CTAs, and head widths whose channel pairs
+    do not divide the CTA stride (every thread then evaluates an angle per item)."""
+    from riftco_transformer_b200.decode import CudaOps
+    import riftco_transformer_b200 as b2
+    dev = torch.device("cuda", 0)
+    ops = CudaOps(dev)
+    rng = np.random.default_rng(11)
+    n_seq, bs, P = 6, 16, 60
+    positions = np.array([0, 1, 31, 32, 77, 159], np.int32)
+    tables = np.stack([(np.arange(10) * n_seq + s) % P for s in range(n_seq)]).astype(np.int32)
+    q = rng.standard_normal((n_seq, hq, d)).astype(np.float32)
+    k = rng.standard_normal((n_seq, hkv, d)).astype(np.float32)
+    v = rng.standard_normal((n_seq, hkv, d)).astype(np.float32)
+    pool = b2.PagedKvPool(torch.zeros((P, hkv, bs, d), device=dev), torch.zeros((P, hkv, bs, d), device=dev))
+    tq = torch.from_numpy(q).to(dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    ops.rope_append(tq, torch.from_numpy(k).to(dev), torch.from_numpy(v).to(dev),
+                    torch.from_numpy(positions).to(dev), torch.from_numpy(tables).to(dev), pool, 1e4, status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    written = 0
+    for s, pos in enumerate(positions):
+        assert np.allclose(tq[s].cpu().numpy(), decode_ref.rotate(q[s], int(pos), 1e4), rtol=1e-6, atol=1e-6)
+        page, slot = tables[s, pos // bs], pos % bs
+        assert np.allclose(pool.key_pages[page, :, slot].cpu().numpy(), decode_ref.rotate(k[s], int(pos), 1e4),
+                           rtol=1e-6, atol=1e-6)
+        assert (pool.value_pages[page, :, slot].cpu().numpy() == v[s]).all()
+        written += hkv * d
+    # nothing but the six slots was touched
+    assert int((pool.value_pages != 0).sum().item()) <= written
+    assert int((pool.key_pages != 0).sum().item()) <= written
+
+
+def test_argmax_row_shapes():
+    """Widths that take the scalar path, rows shorter than the CTA, ties across threads."""
+    from riftco_transformer_b200.decode import CudaOps
+    dev = torch.device("cuda", 0)
+    ops = CudaOps(dev)
+    rng = np.random.default_rng(13)
+    for width in (1, 3, 257, 1023, 4096, 32003, 128256):
+        logits = rng.standard_normal((3, width)).astype(np.float32)
+        if width > 2:
+            logits[2, width - 1] = logits[2, width // 2] = 9.0
+        idx = torch.empty(3, dtype=torch.int32, device=dev)
+        ops.argmax(torch.from_numpy(logits).to(dev), idx)
+        assert (idx.cpu().numpy() == np.argmax(logits, axis=1)).all(), width
+
+
+def test_bf16_copies_of_the_glue_outputs():
+    """RMSNorm and SiLU*up write, next to their FP32 result, exactly its bf16 rounding."""
+    from riftco_transformer_b200.decode import CudaOps
+    dev = torch.device("cuda", 0)
+    ops = CudaOps(dev)
+    g = torch.Generator(device=dev)
+    g.manual_seed(3)
+    for width in (4096, 1000, 37):   # 16-byte rows, 8-byte rows, the scalar path
+        x = torch.randn((19, width), device=dev, generator=g)
+        delta = torch.randn((19, width), device=dev, generator=g)
+        scale = 1 + 0.1 * torch.randn(width, device=dev, generator=g)
+        y, y2, xo = torch.empty_like(x), torch.empty_like(x), torch.empty_like(x)
+        y16 = torch.empty((19, width), device=dev, dtype=torch.bfloat16)
+        ops.rmsnorm(x, delta, xo, scale, y, 1e-5, y16)
+        ops.rmsnorm(x, delta, xo, scale, y2, 1e-5)
+        assert torch.equal(y, y2) and torch.equal(y16, y.to(torch.bfloat16))
+        out, out16 = torch.empty_like(x), torch.empty((19, width), device=dev, dtype=torch.bfloat16)
+        ops.silu_mul(x, delta, out, out16)
+        assert torch.equal(out16, out.to(torch.bfloat16))
+
+
+def test_linear_on_bf16_activations_equals_the_fp32_entry():
+    from riftco_transformer_b200 import synth
+    from riftco_transformer_b200.decode import CudaOps
+    dev = torch.device("cuda", 0)
+    ops = CudaOps(dev)
+    g = torch.Generator(device=dev)
+    g.manual_seed(4)
+    ws = [synth.packed_weight(o, 512, seed=60 + i) for i, o in enumerate((512, 256, 384))]
+    for rows in (17, 32, 200):
+        assert ops.linear_bf16_supported(ws, rows)
+        x = torch.randn((rows, 512), device=dev, generator=g)
+        want = [torch.empty((rows, w.out_features), device=dev) for w in ws]
+        got = [torch.empty_like(t) for t in want]
+        ops.linear_multi(x, ws, want)
+        ops.linear_multi_bf16(x.to(torch.bfloat16), ws, got)
+        for a, b in zip(got, want):
+            assert torch.equal(a, b)
+        one = torch.empty_like(want[1])
+        ops.linear_multi_bf16(x.to(torch.bfloat16), [ws[1]], [one])
+        assert torch.equal(one, want[1])
+    assert not ops.linear_bf16_supported(ws, 16)          # the GEMV takes FP32 activations
+    assert not ops.linear_bf16_supported(ws * 2, 32)      # more than four weights
+    with pytest.raises(Exception):
+        ops.linear_multi_bf16(torch.zeros((8, 512), device=dev, dtype=torch.bfloat16), ws,
+                              [torch.empty((8, w.out_features), device=dev) for w in ws])
+
+
+def test_decode_step_with_and_without_the_bf16_handoff(monkeypatch):
+    """Batch 32 takes the tensor-core linears: the step whose producers hand bf16 copies to them
+    gives bit for bit the logits of the step that converts in a pass of its own."""
+    from riftco_transformer_b200.decode import DecoderConfig, synthetic_step
+    cfg = DecoderConfig(layers=2, d_model=512, q_heads=4, kv_heads=2, head_dim=128, ffn=1024, vocab=2048)
+    results = []
+    for flag in ("1", "0"):
+        monkeypatch.setenv("B2_BF16_HANDOFF", flag)
+        step, inputs = synthetic_step(cfg, 32, 100, device=torch.device("cuda", 0))
+        assert (step.n16 is not None) == (flag == "1") and (step.h16 is not None) == (flag == "1")
+        step.ops.launches = 0
+        nxt, logits = step.step(inputs["tokens"], inputs["positions"], inputs["seq_lens"])
+        torch.cuda.synchronize()
+        assert int(step.status.item()) == 0
+        results.append((nxt.clone(), logits.clone(), step.ops.launches))
+    assert torch.equal(results[0][1], results[1][1]) and torch.equal(results[0][0], results[1][0])
+    assert results[0][2] == results[1][2] - (3 * cfg.layers + 1)   # one pass less per q/k/v, gate/up, down, LM head
