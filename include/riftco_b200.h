@@ -308,6 +308,16 @@ B2_API int32_t b2_peer_all_gather_columns(const float* local, uint64_t rows, uin
                                           const uint64_t* peer_full, const uint64_t* peer_flags, uint32_t rank,
                                           uint32_t world, uint32_t* state, uint32_t* status, void* stream);
 
+/* b2_peer_all_gather_columns that also stores the shard rounded to bf16 (nearest
+ * even) into a second buffer of every rank: peer_full_bf16 is a device array
+ * [world] of the addresses of each rank's bf16 [rows, world*cols] buffer (8-byte
+ * aligned, peer-mapped like peer_full), or NULL for none. The linear that follows
+ * can then take b2_nf4_linear_forward_multi_bf16. */
+B2_API int32_t b2_peer_all_gather_columns_bf16(const float* local, uint64_t rows, uint64_t cols,
+                                               const uint64_t* peer_full, const uint64_t* peer_full_bf16,
+                                               const uint64_t* peer_flags, uint32_t rank, uint32_t world,
+                                               uint32_t* state, uint32_t* status, void* stream);
+
 /* out[r] = index of the first maximum of logits[r,:] (greedy sampling,
  * src/stages/serving/generation.cpp:100-120). */
 B2_API int32_t b2_argmax(const float* logits, uint32_t* out, uint32_t rows, uint32_t width, void* stream);

@@ -78,6 +78,7 @@ SIGNATURES = {
     "b2_gather_rows": (_i32, [_vp, _vp, _vp, _u32, _u32, _u32, _vp, _vp]),
     "b2_rtnf4_index": (_i32, [_vp, _u64, _vp, _u64, _vp]),
     "b2_peer_all_gather_columns": (_i32, [_vp, _u64, _u64, _vp, _vp, _u32, _u32, _vp, _vp, _vp]),
+    "b2_peer_all_gather_columns_bf16": (_i32, [_vp, _u64, _u64, _vp, _vp, _vp, _u32, _u32, _vp, _vp, _vp]),
     "b2_argmax": (_i32, [_vp, _vp, _u32, _u32, _vp]),
     "b2_check_device_errors": (_i32, []),
     "b2_host_nf4_linear_forward": (_i32, [_W, _vp, _vp, _u64, _vp]),

@@ -722,6 +722,13 @@ int32_t b2_argmax(const float* logits, uint32_t* out, uint32_t rows, uint32_t wi
 int32_t b2_peer_all_gather_columns(const float* local, uint64_t rows, uint64_t cols, const uint64_t* peer_full,
                                    const uint64_t* peer_flags, uint32_t rank, uint32_t world, uint32_t* state,
                                    uint32_t* status_word, void* stream) {
+    return b2_peer_all_gather_columns_bf16(local, rows, cols, peer_full, nullptr, peer_flags, rank, world, state,
+                                           status_word, stream);
+}
+
+int32_t b2_peer_all_gather_columns_bf16(const float* local, uint64_t rows, uint64_t cols, const uint64_t* peer_full,
+                                        const uint64_t* peer_full_bf16, const uint64_t* peer_flags, uint32_t rank,
+                                        uint32_t world, uint32_t* state, uint32_t* status_word, void* stream) {
     clear_error();
     int32_t status = B2_STATUS_OK;
     DeviceContext* ctx = device_context(&status);
@@ -740,8 +747,8 @@ int32_t b2_peer_all_gather_columns(const float* local, uint64_t rows, uint64_t c
     if (rows * cols * world > 0xFFFFFFFFull || rows > 0xFFFFFFFFull || cols > 0xFFFFFFFFull) {
         return fail(B2_STATUS_OVERFLOW, "peer all-gather activation too large");
     }
-    return launch_peer_gather(*ctx, local, rows, cols, peer_full, peer_flags, rank, world, state, status_word,
-                              static_cast<cudaStream_t>(stream));
+    return launch_peer_gather(*ctx, local, rows, cols, peer_full, peer_full_bf16, peer_flags, rank, world, state,
+                              status_word, static_cast<cudaStream_t>(stream));
 }
 
 // ---- host-buffer seam ---------------------------------------------------------

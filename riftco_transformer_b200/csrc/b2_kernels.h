@@ -90,8 +90,8 @@ int32_t launch_gather_rows(const float* table, const uint32_t* ids, float* out, 
                            uint32_t vocab, uint32_t* status, cudaStream_t stream);
 // peer_gather.cu - all-gather of column shards by peer stores.
 int32_t launch_peer_gather(const DeviceContext& ctx, const float* local, uint64_t rows, uint64_t cols,
-                           const uint64_t* peer_full, const uint64_t* peer_flags, uint32_t rank, uint32_t world,
-                           uint32_t* state, uint32_t* status, cudaStream_t stream);
+                           const uint64_t* peer_full, const uint64_t* peer_full_bf16, const uint64_t* peer_flags,
+                           uint32_t rank, uint32_t world, uint32_t* state, uint32_t* status, cudaStream_t stream);
 int32_t launch_argmax(const float* logits, uint32_t* out, uint32_t rows, uint32_t width, cudaStream_t stream);
 
 }  // namespace b2

@@ -6,7 +6,9 @@
 // included) with plain peer stores, publishes a per-rank epoch in each peer's
 // flag array once all of its stores are fenced, and returns when the local flag
 // array shows the same epoch from every rank - so the next kernel in the stream
-// sees the complete activation. No library collective, no staging copy.
+// sees the complete activation. No library collective, no staging copy. Optionally
+// the shard is also stored rounded to bf16 into a second buffer of every rank, the
+// form the tensor-core linears read.
 //
 // Every rank runs the same sequence of gathers, so "epoch" is simply the number
 // of gathers a rank has done; it lives in device memory, which keeps the kernel
@@ -20,6 +22,8 @@
 // which it issues, in stream order, after the consumer of the earlier one.
 #include "b2_common.cuh"
 #include "b2_kernels.h"
+
+#include <cuda_bf16.h>
 
 namespace b2 {
 namespace {
@@ -44,6 +48,7 @@ __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
 struct PeerGatherArgs {
     const float* local;           // [rows, cols]
     const uint64_t* peer_full;    // device array [world]: address of every rank's full[rows, world*cols]
+    const uint64_t* peer_full16;  // nullable, same for every rank's bf16 copy of full (same shape)
     const uint64_t* peer_flags;   // device array [world]: address of every rank's flag array uint32[world]
     uint32_t* state;              // local: [0] epoch of the last gather, [1] CTAs done in this launch
     uint32_t* status;             // local status word (B2_PEER_STATUS_TIMEOUT: wait budget ran out)
@@ -64,6 +69,16 @@ peer_gather_kernel(const PeerGatherArgs a) {
         for (uint32_t p = 0; p < a.world; ++p) {
             float* full = reinterpret_cast<float*>(a.peer_full[p]);
             *reinterpret_cast<float4*>(full + dst) = v;
+        }
+        if (a.peer_full16 != nullptr) {   // the form the tensor-core linears read: no conversion pass after the gather
+            __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+            uint2 packed;
+            packed.x = *reinterpret_cast<uint32_t*>(&lo);
+            packed.y = *reinterpret_cast<uint32_t*>(&hi);
+            for (uint32_t p = 0; p < a.world; ++p) {
+                __nv_bfloat16* full16 = reinterpret_cast<__nv_bfloat16*>(a.peer_full16[p]);
+                *reinterpret_cast<uint2*>(full16 + dst) = packed;
+            }
         }
     }
     // One system-scope fence per CTA, by the thread that then counts the CTA in: the barrier orders
@@ -106,11 +121,12 @@ peer_gather_kernel(const PeerGatherArgs a) {
 }  // namespace
 
 int32_t launch_peer_gather(const DeviceContext& ctx, const float* local, uint64_t rows, uint64_t cols,
-                           const uint64_t* peer_full, const uint64_t* peer_flags, uint32_t rank, uint32_t world,
-                           uint32_t* state, uint32_t* status, cudaStream_t stream) {
+                           const uint64_t* peer_full, const uint64_t* peer_full_bf16, const uint64_t* peer_flags,
+                           uint32_t rank, uint32_t world, uint32_t* state, uint32_t* status, cudaStream_t stream) {
     PeerGatherArgs a;
     a.local = local;
     a.peer_full = peer_full;
+    a.peer_full16 = peer_full_bf16;
     a.peer_flags = peer_flags;
     a.state = state;
     a.status = status;

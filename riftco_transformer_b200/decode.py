@@ -103,15 +103,29 @@ class CudaOps:
     def empty(self, shape, dtype=torch.float32):
         return torch.empty(shape, dtype=dtype, device=self.device)
 
-    def gathered_buffer(self, shape):
-        """Buffer that receives an all-gather: peer-mapped when the peer-store gather is in use."""
-        if not self.peer:
-            return self.empty(shape)
-        t = self._symm.empty(tuple(shape), dtype=torch.float32, device=self.device)
+    def _peer_mapped(self, shape, dtype):
+        t = self._symm.empty(tuple(shape), dtype=dtype, device=self.device)
         handle = self._symm.rendezvous(t, self.group)
         ptrs = torch.tensor([int(p) for p in handle.buffer_ptrs], dtype=torch.int64, device=self.device)
-        self._peer_ptrs[t.data_ptr()] = (handle, ptrs)
+        return t, handle, ptrs
+
+    def gathered_buffer(self, shape, with_bf16: bool = False):
+        """Buffer that receives an all-gather: peer-mapped when the peer-store gather is in use.
+        With `with_bf16` the gather also fills a bf16 copy of it (`bf16_of`), which every rank must
+        then ask for alike."""
+        if not self.peer:
+            return self.empty(shape)
+        t, handle, ptrs = self._peer_mapped(shape, torch.float32)
+        t16 = h16 = p16 = None
+        if with_bf16:
+            t16, h16, p16 = self._peer_mapped(shape, torch.bfloat16)
+        self._peer_ptrs[t.data_ptr()] = (handle, ptrs, t16, h16, p16)
         return t
+
+    def bf16_of(self, full):
+        """The bf16 copy the peer gather keeps of `full`, or None."""
+        entry = self._peer_ptrs.get(full.data_ptr()) if self.peer else None
+        return None if entry is None else entry[2]
 
     def check_peer_status(self) -> None:
         """Raises if a peer-store gather gave up waiting for another rank."""
@@ -205,10 +219,10 @@ class CudaOps:
             entry = self._peer_ptrs.get(full.data_ptr())
             if entry is None:
                 raise RuntimeError("peer all-gather target was not allocated with gathered_buffer()")
-            _check(lib.b2_peer_all_gather_columns(local.data_ptr(), local.shape[0], local.shape[1],
-                                                  entry[1].data_ptr(), self._flag_ptrs.data_ptr(), self.rank,
-                                                  self.world, self._peer_state.data_ptr(),
-                                                  self.peer_status.data_ptr(), _stream_ptr(None)))
+            _check(lib.b2_peer_all_gather_columns_bf16(
+                local.data_ptr(), local.shape[0], local.shape[1], entry[1].data_ptr(),
+                None if entry[4] is None else entry[4].data_ptr(), self._flag_ptrs.data_ptr(), self.rank,
+                self.world, self._peer_state.data_ptr(), self.peer_status.data_ptr(), _stream_ptr(None)))
             self.launches += 1
             return
         torch.distributed.all_gather_into_tensor(gathered.view(-1, local.shape[1]), local, group=self.group)
@@ -230,13 +244,27 @@ class DecodeStep:
         e = ops.empty
         g = getattr(ops, "gathered_buffer", ops.empty)   # peer-mapped where the backend gathers by peer stores
         B = batch
+        # Where the backend's tensor-core linears read bf16 activations, the kernel that produces an
+        # activation (RMSNorm, SiLU*up, the peer gather) also writes its bf16 copy and the linear skips
+        # its own conversion pass. Values are the same either way: the pass rounds the same FP32
+        # numbers the same way.
+        takes_bf16 = getattr(ops, "linear_bf16_supported", None)
+        if takes_bf16 is None or os.environ.get("B2_BF16_HANDOFF", "1") == "0":
+            takes_bf16 = lambda ws, rows: False   # noqa: E731
+        w0 = weights[0]
+        gather_bf16 = getattr(ops, "bf16_of", None) is not None
+
+        def gathered(shape, consumer):
+            if gather_bf16 and takes_bf16([consumer], B):
+                return g(shape, True)
+            return g(shape)
         self.x = e((B, d))
         self.n = e((B, d))
         self.q = e((B, self.hq, hd))
         self.k = e((B, self.hkv, hd))
         self.v = e((B, self.hkv, hd))
         self.ctx_local = e((B, self.hq, hd))
-        self.ctx = g((B, cfg.q_heads * hd)) if world > 1 else None
+        self.ctx = gathered((B, cfg.q_heads * hd), w0["wo"]) if world > 1 else None
         # The o- and down-projections may be given whole to every rank instead of row-sharded: their
         # inputs are gathered anyway, a [B, d] output is small, and computing it everywhere costs less
         # than a cross-GPU handshake (two gathers per layer instead of four).
@@ -247,7 +275,7 @@ class DecodeStep:
         self.gate = e((B, cfg.ffn // world))
         self.up = e((B, cfg.ffn // world))
         self.h_local = e((B, cfg.ffn // world))
-        self.h = g((B, cfg.ffn)) if world > 1 else None
+        self.h = gathered((B, cfg.ffn), w0["w_down"]) if world > 1 else None
         self.down_local = e((B, d // world))
         self.down = (e((B, d)) if self.whole_down else g((B, d))) if world > 1 else None
         self.logits_local = e((B, cfg.vocab // world))
@@ -259,18 +287,14 @@ class DecodeStep:
         if world > 1:
             widths = {cfg.q_heads * hd // world, d // world, cfg.ffn // world, cfg.vocab // world}
             self.stage = {n_: e((world, B, n_)) for n_ in widths}
-        # Where the backend's tensor-core linears read bf16 activations, the kernel that produces an
-        # activation also writes its bf16 copy and the linear skips its own conversion pass. Values
-        # are the same either way (the pass rounds the same FP32 numbers the same way).
-        self.n16 = self.h16 = None
-        takes_bf16 = getattr(ops, "linear_bf16_supported", None)
-        if takes_bf16 is not None and os.environ.get("B2_BF16_HANDOFF", "1") != "0":
-            w0 = weights[0]
-            if (takes_bf16([w0["wq"], w0["wk"], w0["wv"]], B) and takes_bf16([w0["w_gate"], w0["w_up"]], B)
-                    and takes_bf16([weights["lm_head"]], B)):
-                self.n16 = e((B, d), dtype=torch.bfloat16)
-            if world == 1 and takes_bf16([w0["w_down"]], B):
-                self.h16 = e((B, cfg.ffn), dtype=torch.bfloat16)
+        self.n16 = self.h16 = self.ctx16 = self.hfull16 = None
+        if (takes_bf16([w0["wq"], w0["wk"], w0["wv"]], B) and takes_bf16([w0["w_gate"], w0["w_up"]], B)
+                and takes_bf16([weights["lm_head"]], B)):
+            self.n16 = e((B, d), dtype=torch.bfloat16)
+        if world == 1 and takes_bf16([w0["w_down"]], B):
+            self.h16 = e((B, cfg.ffn), dtype=torch.bfloat16)
+        if world > 1 and gather_bf16:
+            self.ctx16, self.hfull16 = ops.bf16_of(self.ctx), ops.bf16_of(self.h)
 
     def _gather(self, local, full):
         if self.world == 1:
@@ -294,6 +318,12 @@ class DecodeStep:
         else:
             self.ops.linear_multi(self.n, weights, outs)
 
+    def _linear(self, x, x16, w, out) -> None:
+        if x16 is not None:
+            self.ops.linear_multi_bf16(x16, [w], [out])
+        else:
+            self.ops.linear(x, w, out)
+
     def step(self, tokens, positions, seq_lens):
         """tokens int32 [B]; positions uint32/int32 [B] = index of the new token;
         seq_lens = positions + 1. Returns (next_tokens [B], logits [B, vocab])."""
@@ -312,10 +342,10 @@ class DecodeStep:
                           self.status, self.workspace)
             ctx = self._gather(self.ctx_local, self.ctx)
             if self.whole_o:
-                ops.linear(ctx, w["wo"], self.o)
+                self._linear(ctx, self.ctx16, w["wo"], self.o)
                 o = self.o
             else:
-                ops.linear(ctx, w["wo"], self.o_local)
+                self._linear(ctx, self.ctx16, w["wo"], self.o_local)
                 o = self._gather(self.o_local, self.o)
             self._norm(o, nm["ffn"])
             self._linears_of_n([w["w_gate"], w["w_up"]], [self.gate, self.up])
@@ -327,10 +357,10 @@ class DecodeStep:
             ops.silu_mul(self.gate, self.up, self.h_local)
             h = self._gather(self.h_local, self.h)
             if self.whole_down:
-                ops.linear(h, w["w_down"], self.down)
+                self._linear(h, self.hfull16, w["w_down"], self.down)
                 pending = self.down
             else:
-                ops.linear(h, w["w_down"], self.down_local)
+                self._linear(h, self.hfull16, w["w_down"], self.down_local)
                 pending = self._gather(self.down_local, self.down)
         self._norm(pending, self.norms["final"])
         self._linears_of_n([self.w["lm_head"]], [self.logits_local])

@@ -19,7 +19,8 @@ def main() -> None:
     ops = CudaOps(dev, dist.group.WORLD)
     assert ops.peer, "peer gather not enabled"
     rows, cols = 32, 2048
-    bufs = [ops.gathered_buffer((rows, world * cols)) for _ in range(2)]
+    bufs = [ops.gathered_buffer((rows, world * cols), with_bf16=(i == 1)) for i in range(2)]
+    assert ops.bf16_of(bufs[0]) is None and ops.bf16_of(bufs[1]).dtype == torch.bfloat16
     gen = torch.Generator(device=dev)
     gen.manual_seed(100 + rank)
     stage = torch.empty((world, rows, cols), device=dev)
@@ -31,6 +32,9 @@ def main() -> None:
         want = stage.permute(1, 0, 2).reshape(rows, world * cols)
         torch.cuda.synchronize()
         assert torch.equal(full, want), f"round {it}: mismatch on rank {rank}"
+        if ops.bf16_of(full) is not None:
+            assert torch.equal(ops.bf16_of(full), want.to(torch.bfloat16)), f"round {it}: bf16 copy on rank {rank}"
+        dist.barrier()
     # graph: two gathers per replay, one per buffer
     local = torch.randn((rows, cols), device=dev, generator=gen)
     side = torch.cuda.Stream()
@@ -47,6 +51,8 @@ def main() -> None:
             want = stage.permute(1, 0, 2).reshape(rows, world * cols)
             torch.cuda.synchronize()
             assert torch.equal(bufs[0], want) and torch.equal(bufs[1], want)
+            assert torch.equal(ops.bf16_of(bufs[1]), want.to(torch.bfloat16))
+            dist.barrier()   # a replay stores into the peer's buffers at once: wait until it has compared them
     ops.check_peer_status()
     dist.barrier()
     print("PEER_GATHER_OK", flush=True)

@@ -10,6 +10,7 @@ import os
 import socket
 import subprocess
 import sys
+import time
 
 import numpy as np
 import pytest
@@ -87,6 +88,36 @@ def test_two_rank_layout_on_one_gpu(b2):
     assert status.item() == 0
 
 
+def test_two_rank_layout_with_bf16_copies(b2):
+    """The same emulation through the entry that also fills every rank's bf16 buffer."""
+    from riftco_transformer_b200._lib import lib
+    from riftco_transformer_b200.backend import _check, _stream_ptr
+    rows, cols = 8, 1024
+    full = [torch.zeros((rows, 2 * cols), device="cuda") for _ in range(2)]
+    full16 = [torch.zeros((rows, 2 * cols), device="cuda", dtype=torch.bfloat16) for _ in range(2)]
+    flags = [torch.zeros((64,), dtype=torch.int32, device="cuda") for _ in range(2)]
+    state = [torch.zeros((2,), dtype=torch.int32, device="cuda") for _ in range(2)]
+    status = torch.zeros((1,), dtype=torch.int32, device="cuda")
+    shard = [torch.randn((rows, cols), device="cuda") for _ in range(2)]
+    fp, hp, gp = _ptrs(*full), _ptrs(*full16), _ptrs(*flags)
+
+    def call(rank):
+        _check(lib.b2_peer_all_gather_columns_bf16(
+            shard[rank].data_ptr(), rows, cols, fp.data_ptr(), hp.data_ptr(), gp.data_ptr(), rank, 2,
+            state[rank].data_ptr(), status.data_ptr(), _stream_ptr(None)))
+
+    flags[1][0] = 1            # as if rank 0 had already arrived at rank 1
+    call(1)
+    torch.cuda.synchronize()
+    flags[1][0] = 0
+    call(0)
+    torch.cuda.synchronize()
+    want = torch.cat(shard, dim=1)
+    for r in range(2):
+        assert torch.equal(full[r], want) and torch.equal(full16[r], want.to(torch.bfloat16))
+    assert status.item() == 0
+
+
 def test_wait_gives_up_with_a_status_bit(b2):
     rows, cols = 4, 256
     full = [torch.zeros((rows, 2 * cols), device="cuda") for _ in range(2)]
@@ -112,26 +143,43 @@ def test_rejects_bad_arguments(b2):
         _call(t, _ptrs(t), _ptrs(z), 2, 2, z, z)          # rank >= world
 
 
-@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_two_gpus_match_nccl():
+def _run_two_ranks(worker_file: str, marker: str) -> None:
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
         port = s.getsockname()[1]
-    worker = os.path.join(os.path.dirname(__file__), "peer_gather_worker.py")
+    worker = os.path.join(os.path.dirname(__file__), worker_file)
     procs = []
     for rank in range(2):
         env = dict(os.environ, RANK=str(rank), WORLD_SIZE="2", LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1",
                    MASTER_PORT=str(port))
         procs.append(subprocess.Popen([sys.executable, worker], env=env, stdout=subprocess.PIPE,
                                       stderr=subprocess.STDOUT, text=True))
-    outs = []
+    # A rank that fails leaves the other one waiting in a collective: stop both as soon as one
+    # has exited with an error, or after two minutes.
+    deadline = time.monotonic() + 120
+    while time.monotonic() < deadline and any(p.poll() is None for p in procs):
+        if any(p.poll() not in (None, 0) for p in procs):
+            break
+        time.sleep(0.2)
     for p in procs:
-        try:
-            out, _ = p.communicate(timeout=240)
-        except subprocess.TimeoutExpired:
+        if p.poll() is None:
+            time.sleep(1.0)   # let a rank that is about to finish do so
+        if p.poll() is None:
             p.kill()
-            out, _ = p.communicate()
-        outs.append(out)
-    for rank, (p, out) in enumerate(zip(procs, outs)):
-        assert p.returncode == 0, f"rank {rank}:\n{out[-3000:]}"
-        assert "PEER_GATHER_OK" in out, out[-3000:]
+    outs = [p.communicate()[0] for p in procs]
+    report = "\n".join(f"--- rank {r} (exit {p.returncode}) ---\n{o[-2500:]}"
+                       for r, (p, o) in enumerate(zip(procs, outs)))
+    assert all(p.returncode == 0 for p in procs), report
+    assert all(marker in o for o in outs), report
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_gpus_match_nccl():
+    _run_two_ranks("peer_gather_worker.py", "PEER_GATHER_OK")
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_gpu_decode_step_variants_agree():
+    """Batch-32 decode step on two ranks: bf16 copies delivered by the gather, conversion passes
+    instead, and NCCL gathers all give the same logits bit for bit."""
+    _run_two_ranks("decode_step_worker.py", "DECODE_STEP_OK")
