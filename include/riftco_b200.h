@@ -189,10 +189,19 @@ B2_API size_t b2_nf4_linear_workspace_bytes(const b2_nf4_weight* weight, uint64_
  * caller zeroes it and reads it after synchronising, which is how the
  * reference's CUDA path reports std::domain_error (paged_decode.cu:208-214).
  * Block ids are checked on the device: an id >= physical_blocks is never
- * dereferenced and sets bit 4 of the status word.
+ * dereferenced and sets B2_ATTN_STATUS_BAD_BLOCK (value 4) in the status word.
  */
 #define B2_ATTN_STATUS_BAD_BLOCK 4u
 #define B2_ATTN_STATUS_TIMEOUT 8u          /* a bounded wait for a page copy gave up */
+
+/* The status a synchronous caller reports for a status word read back after the
+ * stream is idle, with the message in b2_last_error(): BAD_BLOCK ->
+ * B2_STATUS_OUT_OF_RANGE (std::out_of_range in the reference,
+ * src/core/backend/attention/dispatch.cpp:474-480), the two score bits ->
+ * B2_STATUS_DOMAIN_ERROR (attention/cuda/paged_decode.cu:208-214), TIMEOUT or
+ * any other bit -> B2_STATUS_RUNTIME_ERROR (the context is invalid), 0 ->
+ * B2_STATUS_OK. Needs no GPU. b2_host_paged_decode_attention applies it. */
+B2_API int32_t b2_attention_status_result(uint32_t status_bits);
 B2_API int32_t b2_paged_decode_attention(const float* q, const float* k_pages,
                                   const float* v_pages, const uint32_t* block_tables,
                                   const uint32_t* seq_lens, float* ctx,

@@ -122,6 +122,10 @@ class Port:
         L.orc_paged_decode_gqa.argtypes = (
             [_f32p, _f32p, _f32p, _u32p, _u32p, _f32p] + [C.c_size_t] * 6 + [C.c_int]
         )
+        L.orc_rms_norm.argtypes = [_f32p, _f32p, C.c_size_t, C.c_size_t, C.c_float, _f32p]
+        L.orc_silu_mul.argtypes = [_f32p, _f32p, C.c_size_t, _f32p]
+        L.orc_greedy.restype = C.c_size_t
+        L.orc_greedy.argtypes = [_f32p, C.c_size_t]
 
     # -- format ---------------------------------------------------------
     def codebook(self) -> np.ndarray:
@@ -220,6 +224,26 @@ class Port:
         return ctx
 
 
+    # -- decode-step primitives --------------------------------------------
+    def rms_norm(self, x, scale, eps: float) -> np.ndarray:
+        x, scale = _f32(x), _f32(scale)
+        out = np.empty_like(x)
+        x2 = x.reshape(-1, x.shape[-1])
+        self.lib.orc_rms_norm(_ptr(x2, _f32p), _ptr(scale, _f32p), x2.shape[0], x2.shape[1], eps, _ptr(out, _f32p))
+        return out
+
+    def silu_mul(self, gate, up=None) -> np.ndarray:
+        g = _f32(gate)
+        u = None if up is None else _f32(up)
+        out = np.empty_like(g)
+        self.lib.orc_silu_mul(_ptr(g, _f32p), _ptr(u, _f32p), g.size, _ptr(out, _f32p))
+        return out
+
+    def greedy(self, logits) -> int:
+        v = _f32(logits).ravel()
+        return int(self.lib.orc_greedy(_ptr(v, _f32p), v.size))
+
+
 class ReferenceError_(RuntimeError):
     def __init__(self, status: int, message: str) -> None:
         super().__init__(f"[status {status}] {message}")
@@ -251,6 +275,14 @@ class Reference:
         L.ref_paged_decode.argtypes = [_f32p, _f32p, _f32p, _u32p, u64, _f32p, u64, u64, u64, u64, u64,
                                        C.POINTER(C.c_double)]
         L.ref_materialized_causal_forward.argtypes = [_f32p, _f32p, _f32p, _f32p, _f32p, u64, u64, u64, u64]
+        if hasattr(L, "ref_rms_norm"):   # decode-step primitives and the packed model state
+            L.ref_rms_norm.argtypes = [_f32p, _f32p, u64, u64, C.c_float, _f32p]
+            L.ref_rope.argtypes = [_f32p, u64, u64, u64, u64, u64, C.c_float, _f32p]
+            L.ref_silu_mul.argtypes = [_f32p, _f32p, u64, _f32p]
+            L.ref_greedy.argtypes = [_f32p, u64, _u32p]
+            L.ref_paged_cache_decode.argtypes = [_f32p, _f32p, _f32p, u64, u64, u64, u64, u64, _f32p]
+            L.ref_packed_model_fixture.argtypes = [u64, u64, u64, u64, u64, u64, u64, u64, C.c_uint32,
+                                                   _u8p, u64, C.POINTER(u64), _u8p, u64, C.POINTER(u64)]
         self.last_seconds = 0.0
 
     def _check(self, rc: int) -> None:
@@ -358,6 +390,58 @@ class Reference:
         self._check(self.lib.ref_materialized_causal_forward(
             _ptr(q, _f32p), _ptr(k, _f32p), _ptr(v, _f32p), _ptr(probs, _f32p), _ptr(ctx, _f32p), b, h, t, d))
         return probs, ctx
+
+
+    # ---- decode-step primitives (reference entry points named in oracle/ref_bridge.cpp) ----
+
+    def rms_norm(self, x, scale, eps: float) -> np.ndarray:
+        x, scale = _f32(x), _f32(scale)
+        out = np.empty_like(x)
+        self._check(self.lib.ref_rms_norm(_ptr(x, _f32p), _ptr(scale, _f32p), x.shape[0], x.shape[1], eps,
+                                          _ptr(out, _f32p)))
+        return out
+
+    def rope(self, x, position_offset: int, theta: float) -> np.ndarray:
+        """x [batch, heads, time, width]; token t of the time axis is at position_offset + t."""
+        x = _f32(x)
+        out = np.empty_like(x)
+        b, h, t, w = x.shape
+        self._check(self.lib.ref_rope(_ptr(x, _f32p), b, h, t, w, position_offset, theta, _ptr(out, _f32p)))
+        return out
+
+    def silu_mul(self, gate, up=None) -> np.ndarray:
+        gate = _f32(gate).ravel()
+        up_ = None if up is None else _f32(up).ravel()
+        out = np.empty_like(gate)
+        self._check(self.lib.ref_silu_mul(_ptr(gate, _f32p), _ptr(up_, _f32p), gate.size, _ptr(out, _f32p)))
+        return out
+
+    def greedy(self, logits) -> int:
+        logits = _f32(logits).ravel()
+        token = np.zeros(1, np.uint32)
+        self._check(self.lib.ref_greedy(_ptr(logits, _f32p), logits.size, _ptr(token, _u32p)))
+        return int(token[0])
+
+    def paged_cache_decode(self, q, k, v, block_size: int, block_count: int) -> np.ndarray:
+        """q, k, v [steps, heads, width] of one sequence fed token by token through the reference's
+        paged KV cache; returns the attention context after each append."""
+        q, k, v = _f32(q), _f32(k), _f32(v)
+        steps, heads, width = q.shape
+        ctx = np.empty_like(q)
+        self._check(self.lib.ref_paged_cache_decode(_ptr(q, _f32p), _ptr(k, _f32p), _ptr(v, _f32p), steps, heads,
+                                                    width, block_size, block_count, _ptr(ctx, _f32p)))
+        return ctx
+
+    def packed_model_fixture(self, vocabulary, context, width, heads, blocks, feed_forward, block_size,
+                             scale_block_size, seed):
+        """(RTNF4S1 stream, field-by-field dump) of a small quantised decoder, both as uint8 arrays."""
+        n1, n2 = C.c_uint64(0), C.c_uint64(0)
+        args = (vocabulary, context, width, heads, blocks, feed_forward, block_size, scale_block_size, seed)
+        self._check(self.lib.ref_packed_model_fixture(*args, None, 0, C.byref(n1), None, 0, C.byref(n2)))
+        stream, dump = np.empty(n1.value, np.uint8), np.empty(n2.value, np.uint8)
+        self._check(self.lib.ref_packed_model_fixture(*args, _ptr(stream, _u8p), stream.size, C.byref(n1),
+                                                      _ptr(dump, _u8p), dump.size, C.byref(n2)))
+        return stream, dump
 
 
 _port: Port | None = None

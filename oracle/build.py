@@ -9,11 +9,15 @@ Two shared libraries come out of this script:
   together with ``ref_bridge.cpp``. Built only when such a checkout is
   present; only the binary is kept, no reference source is copied.
 
-The reference sources compiled are the ones its own build lists for the core
-library without accelerators (CMakeLists.txt:87-104,
-cmake/RiftcoTransformerBackends.cmake:1-14 plus the three accelerator stubs):
-backend registry and dispatchers, the CPU adapter, the reference loops,
-quantisation and tensor storage. They need nothing but g++ (C++20) and libm.
+The reference sources compiled are the ones its own build lists for the CPU
+library (CMakeLists.txt:87-135, cmake/RiftcoTransformerBackends.cmake:1-14) plus
+the three accelerator stubs and, for the canonical packed-model-state stream,
+the translation units of its C API (CMakeLists.txt:363-377) with the symbolic
+compiler, lowering, analysis and programmed-model sources those link against.
+They need nothing but g++ (C++20), pthreads and libm: no cmake, no generated
+code, no external library. The checkout is found through the
+RIFTCO_REFERENCE_DIR environment variable, else as a directory named
+``reference`` beside this repository.
 """
 from __future__ import annotations
 
@@ -31,9 +35,7 @@ ORACLE_LIB = BUILD_DIR / "libriftco_oracle.so"
 REF_LIB = REF_DIR / "libriftco_ref.so"
 REF_B200_LIB = REF_DIR / "libriftco_ref_b200.so"
 
-DEFAULT_REFERENCE_DIR = "/root/reference"
-
-# Paths inside the reference checkout.
+# Paths inside the reference checkout: the CPU library ...
 REFERENCE_SOURCES = [
     "src/core/backend/adapters/cpu/adapter.cpp",
     "src/core/backend/adapters/cuda/stub.cpp",
@@ -50,6 +52,11 @@ REFERENCE_SOURCES = [
     "src/core/backend/optim/adam/dispatch.cpp",
     "src/core/backend/optim/adam/reference/update.cpp",
     "src/core/backend/registry.cpp",
+    "src/artifacts/state.cpp",
+    "src/core/autograd/checkpoint.cpp",
+    "src/core/autograd/custom_gradient.cpp",
+    "src/core/autograd/graph.cpp",
+    "src/core/autograd/operations.cpp",
     "src/core/quantization/nf4.cpp",
     "src/core/quantization/quantized_weight.cpp",
     "src/core/tensor/detail/validation.cpp",
@@ -61,11 +68,49 @@ REFERENCE_SOURCES = [
     "src/core/tensor/reductions.cpp",
     "src/core/tensor/softmax.cpp",
     "src/core/tensor/storage.cpp",
+    "src/data/token_batch.cpp",
+    "src/data/tokenizer.cpp",
+    "src/model/causal_self_attention.cpp",
+    "src/model/decoder_only_transformer.cpp",
+    "src/model/feed_forward.cpp",
+    "src/model/grouped_query_attention.cpp",
+    "src/model/llama_mistral_transformer.cpp",
+    "src/model/rotary_embedding.cpp",
+    "src/model/swiglu.cpp",
+    "src/model/transformer_block.cpp",
+    "src/optim/adam.cpp",
+    "src/nn/activations.cpp",
+    "src/nn/embedding.cpp",
+    "src/nn/initialization.cpp",
+    "src/nn/layer_norm.cpp",
+    "src/nn/linear.cpp",
+    "src/nn/low_rank_adapter.cpp",
+    "src/nn/loss.cpp",
+    "src/nn/module.cpp",
+    "src/nn/parameter.cpp",
+    "src/nn/quantized_linear.cpp",
+    "src/nn/rms_norm.cpp",
+    "src/stages/serving/config.cpp",
+    "src/stages/serving/cache/contiguous_kv_cache.cpp",
+    "src/stages/serving/cache/page_storage.cpp",
+    "src/stages/serving/cache/page_table_cache.cpp",
+    "src/stages/serving/cache/paged_kv_cache.cpp",
+    "src/stages/serving/cache/validation.cpp",
+    "src/stages/serving/generation.cpp",
+    "src/stages/serving/stack.cpp",
 ]
+# ... and its C API with what that links against (every .cpp of these directories).
+REFERENCE_SOURCE_DIRS = ["src/c_api", "src/programmed", "src/compiler/cajal", "src/lowering", "src/analysis"]
+
+
+def reference_sources(root: Path) -> list[Path]:
+    extra = sorted(p for d in REFERENCE_SOURCE_DIRS for p in (root / d).glob("*.cpp"))
+    return [root / s for s in REFERENCE_SOURCES] + extra
+
 
 # -O2 is the reference's own release level; -ffp-contract=off keeps every
 # multiply and add separately rounded on any host ISA.
-CXXFLAGS = ["-std=c++20", "-O2", "-ffp-contract=off", "-fPIC", "-pthread"]
+CXXFLAGS = ["-std=c++20", "-O2", "-ffp-contract=off", "-fPIC", "-pthread", "-DRIFTCO_TRANSFORMER_C_EXPORTS"]
 
 
 def _run(cmd: list[str]) -> None:
@@ -97,7 +142,8 @@ def build_oracle(force: bool = False) -> Path:
 
 
 def reference_dir() -> Path | None:
-    root = Path(os.environ.get("RIFTCO_REFERENCE_DIR", DEFAULT_REFERENCE_DIR))
+    where = os.environ.get("RIFTCO_REFERENCE_DIR")
+    root = Path(where) if where else HERE.parent.parent / "reference"
     probe = root / "src/core/backend/nn/quantized_linear/reference/operations.cpp"
     return root if probe.exists() else None
 
@@ -108,7 +154,7 @@ def build_reference(force: bool = False) -> Path | None:
     if root is None:
         return REF_LIB if REF_LIB.exists() else None
     bridge = HERE / "ref_bridge.cpp"
-    sources = [root / s for s in REFERENCE_SOURCES] + [bridge]
+    sources = reference_sources(root) + [bridge]
     if not force and _newer(REF_LIB, sources):
         return REF_LIB
     REF_DIR.mkdir(exist_ok=True)
@@ -146,7 +192,7 @@ def build_reference_with_b200_adapter(force: bool = False) -> Path | None:
         return None
     adapter = HERE.parent / "riftco_transformer_b200" / "adapter" / "cuda_b200_adapter.cpp"
     stub = root / "src/core/backend/adapters/cuda/stub.cpp"
-    sources = [root / s for s in REFERENCE_SOURCES if (root / s) != stub] + [HERE / "ref_bridge.cpp"]
+    sources = [s for s in reference_sources(root) if s != stub] + [HERE / "ref_bridge.cpp"]
     if not force and _newer(REF_B200_LIB, sources + [adapter, product]):
         return REF_B200_LIB
     obj_dir = REF_DIR / "obj"

@@ -1,11 +1,15 @@
 """numpy restatement of the reference primitives around the hot-path operators
 in a decode step (test infrastructure, never imported by the product):
 
-  rms_norm        src/nn/rms_norm.cpp:39-73
+  rms_norm        src/nn/rms_norm.cpp:39-73                  (in riftco_oracle.c)
   rotate_forward  src/model/rotary_embedding.cpp:64-117 (split-half pairs, angle in double)
-  silu_forward    src/nn/activations.cpp:38-58 (stable sigmoid)
+  silu_forward    src/nn/activations.cpp:38-58 (stable sigmoid) (in riftco_oracle.c)
   SwiGLU          src/model/swiglu.cpp:27-29
   copy_token_to_page  src/stages/serving/cache/page_table_cache.cpp:44-77
+  GreedySampler   src/stages/serving/generation.cpp:100-110  (in riftco_oracle.c)
+
+Each of them is held bit for bit to vectors written by the reference's own code
+(tests/golden/reference_vectors.npz, tests/test_oracle_golden.py).
 
 and `CheckerOps`, an implementation of the `ops` interface of
 riftco_transformer_b200.decode.DecodeStep on CPU tensors, with the packed
@@ -22,10 +26,8 @@ from . import Nf4Weight, port
 
 
 def rms_norm(x: np.ndarray, scale: np.ndarray, eps: float) -> np.ndarray:
-    x = x.astype(np.float32)
-    mean_square = (x * x).mean(axis=-1, keepdims=True, dtype=np.float32)
-    inv = np.float32(1.0) / np.sqrt(mean_square + np.float32(eps), dtype=np.float32)
-    return (x * inv * scale).astype(np.float32)
+    """The C restatement: sequential FP32 mean like the reference's reduction."""
+    return port().rms_norm(x, scale, eps)
 
 
 def rotary_cos_sin(position: int, half: int, width: int, theta: float):
@@ -44,10 +46,8 @@ def rotate(v: np.ndarray, position: int, theta: float) -> np.ndarray:
 
 
 def silu(x: np.ndarray) -> np.ndarray:
-    x = x.astype(np.float32)
-    e_neg = np.exp(-np.abs(x)).astype(np.float32)
-    sig = np.where(x >= 0, np.float32(1.0) / (np.float32(1.0) + e_neg), e_neg / (np.float32(1.0) + e_neg))
-    return (x * sig).astype(np.float32)
+    """The C restatement (libm expf, -inf -> -0.0, as the reference)."""
+    return port().silu_mul(x)
 
 
 def shard_rows(w: Nf4Weight, rank: int, world: int) -> Nf4Weight:
@@ -121,13 +121,14 @@ class CheckerOps:
         return None
 
     def silu_mul(self, gate, up, out) -> None:
-        out.copy_(torch.from_numpy(silu(gate.numpy()) * up.numpy()))
+        out.copy_(torch.from_numpy(port().silu_mul(gate.numpy(), up.numpy())))
 
     def gather_rows(self, table, ids, out, status) -> None:
         out.copy_(table[ids.long()])
 
     def argmax(self, logits, out) -> None:
-        out.copy_(torch.from_numpy(np.argmax(logits.numpy(), axis=1).astype(np.int32)))
+        rows = logits.numpy()
+        out.copy_(torch.tensor([port().greedy(r) for r in rows], dtype=torch.int32))
 
     def all_gather_columns(self, local, gathered, full) -> None:
         torch.distributed.all_gather_into_tensor(gathered.view(-1, local.shape[1]), local.contiguous(), group=self.group)

@@ -313,3 +313,181 @@ int ref_materialized_causal_forward(const float* q, const float* k, const float*
 }
 
 }  // extern "C"
+
+// ---- decode-step primitives and the packed model state -------------------------------------
+//
+// The operators either side of the hot path in one decode step, called through the reference's
+// own public C++ entry points, so the CUDA glue kernels and the numpy restatement in
+// oracle/decode_ref.py can be held to the reference's results:
+//   rms_norm                          (src/nn/rms_norm.cpp:39-73)
+//   apply_rotary_position_embedding   (src/model/rotary_embedding.cpp:64-117, 142-193)
+//   silu and silu(gate) * up          (src/nn/activations.cpp:38-58, src/model/swiglu.cpp:27-29)
+//   GreedySampler::sample             (src/stages/serving/generation.cpp:100-110)
+//   PagedKvCachePool / DecoderKeyValueCache::append_and_attend
+//                                     (src/stages/serving/cache/page_table_cache.cpp:44-77,165-233)
+// and the canonical RTNF4S1 stream of a quantised DecoderOnlyTransformer
+//   packed_model_state_bytes          (src/c_api/model_state.cpp:27-113).
+#include "c_api/internal/model_state.hpp"
+#include "riftco_transformer/model/decoder_only_transformer.hpp"
+#include "riftco_transformer/model/rotary_embedding.hpp"
+#include "riftco_transformer/nn/activations.hpp"
+#include "riftco_transformer/nn/rms_norm.hpp"
+#include "riftco_transformer/stages/serving/generation.hpp"
+#include "riftco_transformer/stages/serving/kv_cache.hpp"
+
+#include <random>
+
+namespace {
+
+using riftco_transformer::Variable;
+
+void copy_out(const Tensor& t, float* out) {
+    const auto values = t.data();
+    std::copy(values.begin(), values.end(), out);
+}
+
+void put_u64(std::vector<std::uint8_t>& out, std::uint64_t v) {
+    for (int s = 0; s < 64; s += 8) out.push_back(static_cast<std::uint8_t>(v >> s));
+}
+
+}  // namespace
+
+extern "C" {
+
+int ref_rms_norm(const float* x, const float* scale, std::uint64_t rows, std::uint64_t width,
+                 float epsilon, float* out) {
+    return guarded([&] {
+        CpuScope cpu;
+        const Variable input(Tensor({rows, width}, std::vector<float>(x, x + rows * width), g_backend), false);
+        const Variable gain(Tensor({width}, std::vector<float>(scale, scale + width), g_backend), false);
+        copy_out(riftco_transformer::rms_norm(input, gain, epsilon).value(), out);
+    });
+}
+
+// x, out: [batch, heads, time, width]; token t of the time axis sits at position offset + t.
+int ref_rope(const float* x, std::uint64_t batch, std::uint64_t heads, std::uint64_t time,
+             std::uint64_t width, std::uint64_t position_offset, float theta, float* out) {
+    return guarded([&] {
+        CpuScope cpu;
+        const std::size_t n = batch * heads * time * width;
+        const Variable input(Tensor({batch, heads, time, width}, std::vector<float>(x, x + n), g_backend), false);
+        copy_out(riftco_transformer::apply_rotary_position_embedding(input, position_offset, theta).value(), out);
+    });
+}
+
+// out = silu(gate) (up == nullptr) or silu(gate) * up.
+int ref_silu_mul(const float* gate, const float* up, std::uint64_t n, float* out) {
+    return guarded([&] {
+        CpuScope cpu;
+        const Variable g(Tensor({n}, std::vector<float>(gate, gate + n), g_backend), false);
+        Variable result = riftco_transformer::silu(g);
+        if (up != nullptr) {
+            const Variable u(Tensor({n}, std::vector<float>(up, up + n), g_backend), false);
+            result = result * u;
+        }
+        copy_out(result.value(), out);
+    });
+}
+
+int ref_greedy(const float* logits, std::uint64_t n, std::uint32_t* token) {
+    return guarded([&] {
+        riftco_transformer::stages::serving::GreedySampler sampler;
+        *token = static_cast<std::uint32_t>(sampler.sample(std::span<const float>(logits, n)));
+    });
+}
+
+// Feeds `steps` tokens of one sequence through a paged KV cache of the reference (one layer):
+// q, k, v: [steps, heads, width] (k already rotated by the caller); ctx: [steps, heads, width] gets
+// the attention context after each append. block_count pages of block_size slots.
+int ref_paged_cache_decode(const float* q, const float* k, const float* v, std::uint64_t steps,
+                           std::uint64_t heads, std::uint64_t width, std::uint64_t block_size,
+                           std::uint64_t block_count, float* ctx) {
+    return guarded([&] {
+        CpuScope cpu;
+        riftco_transformer::TransformerDimensions dims;
+        dims.vocabulary_size = 8;
+        dims.maximum_context = block_size * block_count;
+        dims.model_width = heads * width;
+        dims.head_count = heads;
+        dims.block_count = 1;
+        dims.feed_forward_width = 4 * heads * width;
+        riftco_transformer::stages::serving::PagedKvCachePool pool(dims, ExecutionBackend::Cpu, block_size, block_count);
+        auto cache = pool.create();
+        const std::size_t n = heads * width;
+        for (std::uint64_t t = 0; t < steps; ++t) {
+            const Tensor tq({1, heads, 1, width}, std::vector<float>(q + t * n, q + (t + 1) * n), ExecutionBackend::Cpu);
+            const Tensor tk({1, heads, 1, width}, std::vector<float>(k + t * n, k + (t + 1) * n), ExecutionBackend::Cpu);
+            const Tensor tv({1, heads, 1, width}, std::vector<float>(v + t * n, v + (t + 1) * n), ExecutionBackend::Cpu);
+            cache->begin_token();
+            const Tensor context = cache->append_and_attend(0, tq, tk, tv);
+            cache->commit_token();
+            copy_out(context, ctx + t * n);
+        }
+    });
+}
+
+// Builds a small DecoderOnlyTransformer (seeded), quantises every Linear base weight to NF4
+// (scale_block_size == 0: FP32 scales, else double-quantised) and writes
+//   stream: packed_model_state_bytes(model), the canonical RTNF4S1 stream
+//   dump:   the same weights field by field straight from packed_linear_weight_state(), as
+//           u64 count, then per weight u64 {out, in, block, n_codes, n_fp32, n_scale_codes, n_second,
+//           scale_block}, f32 offset, u32 pad, codes, f32 scales, scale codes, f32 second level
+// (*_size receive the byte counts; a too-small capacity only reports the size).
+int ref_packed_model_fixture(std::uint64_t vocabulary, std::uint64_t context, std::uint64_t width,
+                             std::uint64_t heads, std::uint64_t blocks, std::uint64_t feed_forward,
+                             std::uint64_t block_size, std::uint64_t scale_block_size, std::uint32_t seed,
+                             std::uint8_t* stream, std::uint64_t stream_capacity, std::uint64_t* stream_size,
+                             std::uint8_t* dump, std::uint64_t dump_capacity, std::uint64_t* dump_size) {
+    return guarded([&] {
+        CpuScope cpu;
+        riftco_transformer::TransformerDimensions dims;
+        dims.vocabulary_size = vocabulary;
+        dims.maximum_context = context;
+        dims.model_width = width;
+        dims.head_count = heads;
+        dims.block_count = blocks;
+        dims.feed_forward_width = feed_forward;
+        std::mt19937 random(seed);
+        riftco_transformer::DecoderOnlyTransformer model(dims, random);
+        if (scale_block_size == 0) {
+            model.quantize_linear_weights_nf4(block_size);
+        } else {
+            model.quantize_linear_weights_nf4_double_quantized(block_size, scale_block_size);
+        }
+        const std::vector<std::uint8_t> bytes = riftco_transformer::c_api::detail::packed_model_state_bytes(model);
+        *stream_size = bytes.size();
+        if (stream != nullptr && stream_capacity >= bytes.size()) std::copy(bytes.begin(), bytes.end(), stream);
+        std::vector<std::uint8_t> raw;
+        const auto weights = model.packed_linear_weight_state();
+        put_u64(raw, weights.size());
+        for (const auto& w : weights) {
+            const auto& p = w.payload;
+            const bool dq = p.double_quantized_scales.has_value();
+            put_u64(raw, w.shape.at(0));
+            put_u64(raw, w.shape.at(1));
+            put_u64(raw, w.block_size);
+            put_u64(raw, p.packed_codes.size());
+            put_u64(raw, p.block_scales.size());
+            put_u64(raw, dq ? p.double_quantized_scales->scale_codes.size() : 0);
+            put_u64(raw, dq ? p.double_quantized_scales->second_level_scales.size() : 0);
+            put_u64(raw, dq ? p.double_quantized_scales->scale_block_size : 0);
+            const float offset = dq ? p.double_quantized_scales->offset : 0.0F;
+            std::uint32_t bits;
+            std::memcpy(&bits, &offset, 4);
+            put_u64(raw, bits);   // offset bits in the low half, zero padding above
+            raw.insert(raw.end(), p.packed_codes.begin(), p.packed_codes.end());
+            const auto* f = reinterpret_cast<const std::uint8_t*>(p.block_scales.data());
+            raw.insert(raw.end(), f, f + 4 * p.block_scales.size());
+            if (dq) {
+                const auto& n = *p.double_quantized_scales;
+                raw.insert(raw.end(), n.scale_codes.begin(), n.scale_codes.end());
+                const auto* s = reinterpret_cast<const std::uint8_t*>(n.second_level_scales.data());
+                raw.insert(raw.end(), s, s + 4 * n.second_level_scales.size());
+            }
+        }
+        *dump_size = raw.size();
+        if (dump != nullptr && dump_capacity >= raw.size()) std::copy(raw.begin(), raw.end(), dump);
+    });
+}
+
+}  // extern "C"

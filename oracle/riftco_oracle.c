@@ -289,3 +289,55 @@ int orc_paged_decode_gqa(const float* queries, const float* key_pages,
     }
     return rc_all;
 }
+
+/* ---- decode-step primitives either side of the hot path ---------------------- */
+
+/* rms_norm, src/nn/rms_norm.cpp:39-73: x * (1 / sqrt(mean(x * x) + eps)) * scale, where mean is
+ * the reference reduction - a sequential FP32 sum followed by one division
+ * (nn_reference_reduce, src/core/backend/nn/reference/operations.cpp:116-134) - and every
+ * product is rounded on its own. */
+void orc_rms_norm(const float* x, const float* scale, size_t rows, size_t width,
+                  float epsilon, float* out) {
+    for (size_t r = 0; r < rows; ++r) {
+        const float* xr = x + r * width;
+        float total = 0.0f;
+        for (size_t c = 0; c < width; ++c) {
+            const float square = xr[c] * xr[c];
+            total += square;
+        }
+        const float mean_square = total / (float)width;
+        const float inverse = 1.0f / sqrtf(mean_square + epsilon);
+        for (size_t c = 0; c < width; ++c) {
+            const float normalized = xr[c] * inverse;
+            out[r * width + c] = normalized * scale[c];
+        }
+    }
+}
+
+/* stable_sigmoid / silu_forward, src/nn/activations.cpp:38-58 (libm expf, as the reference),
+ * optionally times `up`: the hidden state of SwiGLU, src/model/swiglu.cpp:27-29. */
+void orc_silu_mul(const float* gate, const float* up, size_t n, float* out) {
+    for (size_t i = 0; i < n; ++i) {
+        const float value = gate[i];
+        float result;
+        if (value == -INFINITY) {
+            result = -0.0f;
+        } else if (value >= 0.0f) {
+            const float exponential = expf(-value);
+            result = value * (1.0f / (1.0f + exponential));
+        } else {
+            const float exponential = expf(value);
+            result = value * (exponential / (1.0f + exponential));
+        }
+        out[i] = up != NULL ? result * up[i] : result;
+    }
+}
+
+/* GreedySampler::sample, src/stages/serving/generation.cpp:100-110: first maximum. */
+size_t orc_greedy(const float* logits, size_t n) {
+    size_t selected = 0;
+    for (size_t i = 1; i < n; ++i) {
+        if (logits[i] > logits[selected]) selected = i;
+    }
+    return selected;
+}

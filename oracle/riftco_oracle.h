@@ -108,6 +108,13 @@ int orc_paged_decode_gqa(const float* queries, const float* key_pages,
                          size_t q_heads, size_t kv_heads, size_t head_width,
                          size_t block_size, size_t max_blocks, int threads);
 
+/* Decode-step primitives (rms_norm, SiLU / SwiGLU hidden state, greedy choice); see the .c file
+ * for the reference lines each one follows. `up` may be NULL. */
+void orc_rms_norm(const float* x, const float* scale, size_t rows, size_t width,
+                  float epsilon, float* out);
+void orc_silu_mul(const float* gate, const float* up, size_t n, float* out);
+size_t orc_greedy(const float* logits, size_t n);
+
 #ifdef __cplusplus
 }
 #endif

@@ -27,6 +27,7 @@ SCALES_DOUBLE_QUANTIZED_UINT8 = 1
 ATTN_STATUS_NAN_OR_POS_INF = 1
 ATTN_STATUS_ALL_NEG_INF = 2
 ATTN_STATUS_BAD_BLOCK = 4
+ATTN_STATUS_TIMEOUT = 8
 NOALLOC_SCRATCH_BYTES = 8 * 1024 * 1024
 
 
@@ -66,6 +67,7 @@ SIGNATURES = {
     "b2_paged_decode_attention": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u32,
                                          _u64, _u32, _u32, _vp, _sz, _vp, _vp]),
     "b2_paged_decode_workspace_bytes": (_sz, [_u32, _u32, _u32, _u32, _u32]),
+    "b2_attention_status_result": (_i32, [_u32]),
     "b2_paged_decode_attention_noalloc": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u32,
                                                  _u64, _u32, _u32, _vp, _vp]),
     "b2_rmsnorm": (_i32, [_vp, _vp, _vp, _vp, _vp, _u64, _u64, C.c_float, _vp]),

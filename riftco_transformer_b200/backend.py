@@ -312,12 +312,8 @@ def dispatch_paged_decode_attention_forward(queries: torch.Tensor, key_pages: to
     paged_decode_attention(queries.view(1, heads, head_width), pool, d_table.view(1, -1), d_len,
                            context.view(1, heads, head_width), seq_len, status=status)
     bits = int(status.item())  # synchronises, as the reference adapter contract requires
-    if bits & _lib.ATTN_STATUS_BAD_BLOCK:
-        raise IndexError("paged decode attention block table contains an invalid block")
-    if bits & _lib.ATTN_STATUS_NAN_OR_POS_INF:
-        raise DomainError("softmax rejects NaN and positive infinity")
-    if bits & _lib.ATTN_STATUS_ALL_NEG_INF:
-        raise DomainError("softmax requires one finite value per slice")
+    # bad block -> IndexError, non-finite scores -> DomainError, a page copy that timed out -> RuntimeError
+    _check(lib.b2_attention_status_result(bits))
 
 
 # ---- host-buffer seam ------------------------------------------------------------

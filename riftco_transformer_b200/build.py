@@ -46,7 +46,8 @@ def build_library(force: bool = False, verbose: bool = False, ptxas_info: bool =
     headers = sorted(CSRC.glob("*.cuh")) + sorted(CSRC.glob("*.h")) + sorted((ROOT / "include").glob("*.h"))
     newest_header = max(h.stat().st_mtime for h in headers)
     OBJ.mkdir(parents=True, exist_ok=True)
-    flags = list(NVCC_FLAGS) + (["-Xptxas", "-v"] if ptxas_info else [])
+    # B2_NVCC_EXTRA: extra nvcc flags (space separated), e.g. a -D switch for an instrumented build.
+    flags = list(NVCC_FLAGS) + (["-Xptxas", "-v"] if ptxas_info else []) + os.environ.get("B2_NVCC_EXTRA", "").split()
 
     def compile_one(src: Path) -> tuple[Path, bool]:
         obj = OBJ / (src.stem + ".o")

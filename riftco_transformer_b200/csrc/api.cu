@@ -9,6 +9,7 @@
 #include <cstring>
 #include <mutex>
 #include <string>
+#include <vector>
 
 namespace b2 {
 namespace {
@@ -16,12 +17,19 @@ namespace {
 thread_local std::string g_last_error;
 thread_local std::string g_unavailable_reason;
 
-constexpr int kMaxDevices = 64;
 DeviceContext g_contexts[kMaxDevices];
 std::once_flag g_context_once[kMaxDevices];
 int32_t g_context_status[kMaxDevices];
 std::string g_context_error[kMaxDevices];
 std::mutex g_arena_mutex;
+// Arenas that were replaced by a larger one. They are kept until the process exits: a CUDA graph
+// may have captured their address.
+std::vector<void*> g_retired_arenas;
+// The host-buffer forms share one staging buffer per device; a call holds this lock from its first
+// copy to its final synchronise.
+std::mutex g_host_mutex[kMaxDevices];
+
+constexpr uint32_t kDecodeCounterCapacity = 1u << 20;
 
 bool is_power_of_two(uint64_t v) { return v != 0 && (v & (v - 1)) == 0; }
 
@@ -90,6 +98,14 @@ DeviceContext* device_context(int32_t* status) {
         ctx.cc_major = prop.major;
         int32_t s = init_gemv_lut(&ctx);
         if (s == B2_STATUS_OK) s = init_gemm_lut(&ctx);
+        if (s == B2_STATUS_OK) {
+            cudaError_t ce = cudaMalloc(&ctx.decode_partial, nf4_decode_tmem_workspace_bytes(ctx));
+            if (ce == cudaSuccess) ce = cudaMalloc(&ctx.decode_counters, kDecodeCounterCapacity * sizeof(uint32_t));
+            if (ce == cudaSuccess) ce = cudaMemset(ctx.decode_counters, 0, kDecodeCounterCapacity * sizeof(uint32_t));
+            if (ce == cudaSuccess) ce = cudaDeviceSynchronize();
+            if (ce != cudaSuccess) s = fail_cuda(ce, "decode scratch allocation");
+            ctx.decode_counter_capacity = kDecodeCounterCapacity;
+        }
         if (s != B2_STATUS_OK) {
             g_context_status[device] = s;
             g_context_error[device] = g_last_error;
@@ -105,16 +121,36 @@ DeviceContext* device_context(int32_t* status) {
     return &g_contexts[device];
 }
 
-int32_t reserve_arena(DeviceContext* ctx, size_t bytes) {
+int32_t reserve_arena(DeviceContext* ctx, size_t bytes, cudaStream_t stream) {
     std::lock_guard<std::mutex> lock(g_arena_mutex);
     if (bytes <= ctx->arena_bytes) return B2_STATUS_OK;
-    B2_CUDA_TRY(cudaDeviceSynchronize());
-    if (ctx->arena != nullptr) B2_CUDA_TRY(cudaFree(ctx->arena));
-    ctx->arena = nullptr;
-    ctx->arena_bytes = 0;
+    cudaStreamCaptureStatus capture = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(stream, &capture) != cudaSuccess) {
+        cudaGetLastError();
+        capture = cudaStreamCaptureStatusNone;
+    }
+    if (capture != cudaStreamCaptureStatusNone) {
+        return fail(B2_STATUS_INVALID_ARGUMENT,
+                    "the library's scratch arena would have to grow to %zu bytes inside a stream capture: make one "
+                    "call of this size outside the capture first, or pass a workspace", bytes);
+    }
     const size_t rounded = (bytes + (size_t{1} << 20) - 1) & ~((size_t{1} << 20) - 1);
-    B2_CUDA_TRY(cudaMalloc(&ctx->arena, rounded));
+    void* fresh = nullptr;
+    B2_CUDA_TRY(cudaMalloc(&fresh, rounded));
+    if (ctx->arena != nullptr) g_retired_arenas.push_back(ctx->arena);
+    ctx->arena = fresh;
     ctx->arena_bytes = rounded;
+    return B2_STATUS_OK;
+}
+
+int32_t take_decode_counters(DeviceContext* ctx, uint32_t count, uint32_t** out) {
+    std::lock_guard<std::mutex> lock(g_arena_mutex);
+    if (count > ctx->decode_counter_capacity) {
+        return fail(B2_STATUS_INVALID_ARGUMENT, "too many weight-row tiles for one decode launch");
+    }
+    if (ctx->decode_counter_next + count > ctx->decode_counter_capacity) ctx->decode_counter_next = 0;
+    *out = ctx->decode_counters + ctx->decode_counter_next;
+    ctx->decode_counter_next += count;
     return B2_STATUS_OK;
 }
 
@@ -219,6 +255,82 @@ bool aliases_weight(const b2_nf4_weight* weight, const void* p) {
            (weight->scales_secondary != nullptr && p == weight->scales_secondary);
 }
 
+
+// Which kernel serves a forward call of `rows` rows. B2_DECODE_IMPL selects for measurements:
+//   unset  rows 17..32 on the persistent decode kernel, rows <= 16 on the mma.sync decode kernel
+//   tmem   every batch of up to 32 rows on the persistent decode kernel
+//   old    the kernels in use before it (mma.sync up to 16 rows, the prefill kernel above)
+bool decode_tmem_wanted(uint64_t rows) {
+    static const char* impl = getenv("B2_DECODE_IMPL");
+    static const char* gemm_off = getenv("B2_DISABLE_TENSOR_GEMM");
+    if (gemm_off != nullptr || rows > 32) return false;
+    if (impl != nullptr && strcmp(impl, "old") == 0) return false;
+    if (impl != nullptr && strcmp(impl, "tmem") == 0) return true;
+    return rows > 16;
+}
+
+size_t pad256(size_t v) { return (v + 255) & ~size_t{255}; }
+
+// Scratch of the persistent decode kernel when the caller passes FP32 activations: their 16-bit
+// copy, then the partial tiles.
+size_t decode_tmem_workspace_bytes(const DeviceContext& ctx, const WeightView& w, uint64_t rows) {
+    return pad256(static_cast<size_t>(rows) * w.in_features * 2) + nf4_decode_tmem_workspace_bytes(ctx);
+}
+
+// `count` weights of one input width on the persistent decode kernel. Either `x` (FP32, converted
+// here: fp16 up to 16 rows, bf16 above) or `x_bf16` is given. With a caller workspace all scratch
+// comes from it; without one the 16-bit copy lives in the arena and the partial tiles in the
+// per-device buffer.
+int32_t decode_tmem_forward(DeviceContext* ctx, const WeightView* views, float* const* ys, uint32_t count,
+                            const float* x, const void* x_bf16, uint64_t rows, void* workspace,
+                            size_t workspace_bytes, cudaStream_t stream) {
+    const bool half = x_bf16 == nullptr && rows <= 16;
+    const size_t x16_bytes = x_bf16 != nullptr ? 0 : pad256(static_cast<size_t>(rows) * views[0].in_features * 2);
+    const size_t partial_bytes = nf4_decode_tmem_workspace_bytes(*ctx);
+    void* x16 = const_cast<void*>(x_bf16);
+    void* partial = ctx->decode_partial;
+    if (workspace != nullptr) {
+        if ((reinterpret_cast<uintptr_t>(workspace) & 15u) != 0) {
+            return fail(B2_STATUS_INVALID_ARGUMENT, "NF4 GEMM workspace must be 16-byte aligned");
+        }
+        if (workspace_bytes < x16_bytes + partial_bytes) {
+            return fail(B2_STATUS_INVALID_ARGUMENT, "NF4 GEMM workspace too small: need %zu bytes",
+                        x16_bytes + partial_bytes);
+        }
+        if (x_bf16 == nullptr) x16 = workspace;
+        partial = static_cast<uint8_t*>(workspace) + x16_bytes;
+    } else if (x_bf16 == nullptr) {
+        B2_TRY(reserve_arena(ctx, x16_bytes, stream));
+        x16 = ctx->arena;
+    }
+    if (x_bf16 == nullptr) {
+        const uint64_t n = rows * views[0].in_features;
+        if (half) {
+            B2_TRY(launch_f32_to_f16(*ctx, x, x16, n, stream));
+        } else {
+            B2_TRY(launch_f32_to_bf16(*ctx, x, x16, n, stream));
+        }
+    }
+    uint64_t tiles = 0;
+    for (uint32_t i = 0; i < count; ++i) tiles += (views[i].out_features + 127) / 128;
+    uint32_t* counters = nullptr;
+    B2_TRY(take_decode_counters(ctx, static_cast<uint32_t>(tiles), &counters));
+    return launch_nf4_decode_tmem(*ctx, views, ys, count, x16, half, rows, partial, counters, stream);
+}
+
+bool decode_tmem_takes(const WeightView* views, uint32_t count, const void* x, uint64_t rows) {
+    if (!decode_tmem_wanted(rows)) return false;
+    for (uint32_t i = 0; i < count; ++i) {
+        if (!nf4_decode_tmem_supported(views[i], x, rows)) return false;
+        if (views[i].encoding != views[0].encoding || views[i].block_size != views[0].block_size ||
+            views[i].scale_block_shift != views[0].scale_block_shift ||
+            views[i].in_features != views[0].in_features) {
+            return false;
+        }
+    }
+    return true;
+}
+
 int32_t linear_forward_impl(const b2_nf4_weight* weight, const float* x, float* y, uint64_t rows,
                             void* workspace, size_t workspace_bytes, cudaStream_t stream) {
     int32_t status = B2_STATUS_OK;
@@ -234,6 +346,10 @@ int32_t linear_forward_impl(const b2_nf4_weight* weight, const float* x, float* 
     if (aliases_weight(weight, y)) {
         return fail(B2_STATUS_INVALID_ARGUMENT, "quantized linear weight and output storage must not alias");
     }
+    if (decode_tmem_takes(&w, 1, x, rows)) {
+        float* ys[1] = {y};
+        return decode_tmem_forward(ctx, &w, ys, 1, x, nullptr, rows, workspace, workspace_bytes, stream);
+    }
     static const char* gemm_off = getenv("B2_DISABLE_TENSOR_GEMM");
     // More than 16 batch rows: the tcgen05 kernel that keeps the expanded weight tile in tensor
     // memory (decode batches of 17+ rows, speculative / chunked prefill, full prefill).
@@ -246,7 +362,7 @@ int32_t linear_forward_impl(const b2_nf4_weight* weight, const float* x, float* 
     if (gemm_off == nullptr && !tmem_off && (rows > 16 || tmem_all) && nf4_gemm_tmem_supported(w, x, rows)) {
         const size_t need = nf4_gemm_tmem_workspace_bytes(w, rows);
         if (workspace == nullptr) {
-            B2_TRY(reserve_arena(ctx, need));
+            B2_TRY(reserve_arena(ctx, need, stream));
             workspace = ctx->arena;
             workspace_bytes = ctx->arena_bytes;
         }
@@ -301,7 +417,7 @@ int32_t linear_forward_impl(const b2_nf4_weight* weight, const float* x, float* 
     if (gemm_off == nullptr && nf4_gemm_supported(w, x, rows, false)) {
         const size_t need = nf4_gemm_workspace_bytes(w, rows, false);
         if (workspace == nullptr) {
-            B2_TRY(reserve_arena(ctx, need));
+            B2_TRY(reserve_arena(ctx, need, stream));
             workspace = ctx->arena;
             workspace_bytes = ctx->arena_bytes;
         }
@@ -337,7 +453,7 @@ int32_t linear_backward_impl(const b2_nf4_weight* weight, const float* dy, float
     if (gemm_off == nullptr && !dense_off && nf4_backward_dense_supported(w, dy, rows)) {
         const size_t need = nf4_backward_dense_workspace_bytes(w, rows);
         if (workspace == nullptr) {
-            B2_TRY(reserve_arena(ctx, need));
+            B2_TRY(reserve_arena(ctx, need, stream));
             workspace = ctx->arena;
             workspace_bytes = ctx->arena_bytes;
         }
@@ -346,7 +462,7 @@ int32_t linear_backward_impl(const b2_nf4_weight* weight, const float* dy, float
     if (gemm_off == nullptr && nf4_gemm_supported(w, dy, rows, true)) {
         const size_t need = nf4_gemm_workspace_bytes(w, rows, true);
         if (workspace == nullptr) {
-            B2_TRY(reserve_arena(ctx, need));
+            B2_TRY(reserve_arena(ctx, need, stream));
             workspace = ctx->arena;
             workspace_bytes = ctx->arena_bytes;
         }
@@ -354,6 +470,8 @@ int32_t linear_backward_impl(const b2_nf4_weight* weight, const float* dy, float
     }
     return launch_nf4_linear_input_backward_generic(*ctx, w, dy, dx, rows, stream);
 }
+
+}  // namespace
 
 // checked_paged_decode_query_size and the table checks of
 // dispatch_paged_decode_attention_forward, attention/dispatch.cpp:179-219,440-509
@@ -389,7 +507,6 @@ int32_t check_paged_dims(uint32_t n_seq, uint32_t q_heads, uint32_t kv_heads, ui
     return B2_STATUS_OK;
 }
 
-}  // namespace
 }  // namespace b2
 
 using namespace b2;
@@ -457,7 +574,7 @@ int32_t b2_nf4_linear_forward_multi(const b2_nf4_weight* weights, uint32_t count
     static const char* gemm_off = getenv("B2_DISABLE_TENSOR_GEMM");
     static const char* gemm_impl = getenv("B2_GEMM_IMPL");
     const bool tmem_off = gemm_off != nullptr || (gemm_impl != nullptr && strcmp(gemm_impl, "smem") == 0);
-    bool fused = !tmem_off && rows > 16 && count <= 4 && count > 1 && x != nullptr;
+    bool fused = !tmem_off && (rows > 16 || decode_tmem_wanted(rows)) && count <= 4 && count > 1 && x != nullptr;
     WeightView views[4];
     for (uint32_t i = 0; fused && i < count; ++i) {
         if (ys[i] == nullptr || x == ys[i] || aliases_weight(&weights[i], ys[i]) ||
@@ -474,9 +591,18 @@ int32_t b2_nf4_linear_forward_multi(const b2_nf4_weight* weights, uint32_t count
         }
         return B2_STATUS_OK;
     }
+    if (decode_tmem_takes(views, count, x, rows)) {
+        return decode_tmem_forward(ctx, views, ys, count, x, nullptr, rows, workspace, workspace_bytes, stream);
+    }
+    if (rows <= 16) {   // the prefill kernel is not used for so few rows: one call per weight
+        for (uint32_t i = 0; i < count; ++i) {
+            B2_TRY(linear_forward_impl(&weights[i], x, ys[i], rows, workspace, workspace_bytes, stream));
+        }
+        return B2_STATUS_OK;
+    }
     const size_t need = nf4_gemm_tmem_workspace_bytes(views[0], rows);
     if (workspace == nullptr) {
-        B2_TRY(reserve_arena(ctx, need));
+        B2_TRY(reserve_arena(ctx, need, stream));
         workspace = ctx->arena;
         workspace_bytes = ctx->arena_bytes;
     }
@@ -502,6 +628,12 @@ size_t b2_nf4_linear_workspace_bytes(const b2_nf4_weight* weight, uint64_t rows,
     WeightView w;
     if (make_weight_view(weight, &w) != B2_STATUS_OK) return 0;
     clear_error();
+    if (backward == 0 && decode_tmem_takes(&w, 1, reinterpret_cast<const float*>(16), rows)) {
+        int32_t status = B2_STATUS_OK;
+        DeviceContext* ctx = device_context(&status);
+        clear_error();
+        if (ctx != nullptr) return decode_tmem_workspace_bytes(*ctx, w, rows);
+    }
     if (backward == 0 && rows > 16 && nf4_gemm_tmem_supported(w, reinterpret_cast<const float*>(16), rows)) {
         return nf4_gemm_tmem_workspace_bytes(w, rows);
     }
@@ -543,7 +675,7 @@ int32_t b2_paged_decode_attention(const float* q, const float* k_pages, const fl
     const size_t need =
         paged_decode_workspace_bytes(n_seq, q_heads, head_width, block_size, max_seq_len);
     if (workspace == nullptr && need > 0) {
-        B2_TRY(reserve_arena(ctx, need));
+        B2_TRY(reserve_arena(ctx, need, static_cast<cudaStream_t>(stream)));
         workspace = ctx->arena;
         workspace_bytes = ctx->arena_bytes;
     }
@@ -609,6 +741,10 @@ int32_t b2_nf4_linear_forward_multi_bf16(const b2_nf4_weight* weights, uint32_t 
                     "weights of one input width, 16-byte aligned rows); ask b2_nf4_linear_bf16_supported first");
     }
     clear_error();
+    if (decode_tmem_takes(views, count, x_bf16, rows)) {
+        return decode_tmem_forward(ctx, views, ys, count, nullptr, x_bf16, rows, nullptr, 0,
+                                   static_cast<cudaStream_t>(stream_ptr));
+    }
     return launch_nf4_gemm_tmem_multi(*ctx, views, ys, count, x_bf16, rows, static_cast<cudaStream_t>(stream_ptr));
 }
 
@@ -753,6 +889,26 @@ int32_t b2_peer_all_gather_columns_bf16(const float* local, uint64_t rows, uint6
 
 // ---- host-buffer seam ---------------------------------------------------------
 
+int32_t b2_attention_status_result(uint32_t bits) {
+    clear_error();
+    if (bits & B2_ATTN_STATUS_BAD_BLOCK) {
+        return fail(B2_STATUS_OUT_OF_RANGE, "paged decode attention block table contains an invalid block");
+    }
+    if (bits & B2_ATTN_STATUS_NAN_OR_POS_INF) {
+        return fail(B2_STATUS_DOMAIN_ERROR, "softmax rejects NaN and positive infinity");
+    }
+    if (bits & B2_ATTN_STATUS_ALL_NEG_INF) {
+        return fail(B2_STATUS_DOMAIN_ERROR, "softmax requires one finite value per slice");
+    }
+    if (bits != 0) {
+        // B2_ATTN_STATUS_TIMEOUT, or a bit this version does not know: either way the context is not valid
+        return fail(B2_STATUS_RUNTIME_ERROR,
+                    "paged decode attention did not complete (status 0x%x: a bounded wait for a page copy gave up); "
+                    "its output is invalid", bits);
+    }
+    return B2_STATUS_OK;
+}
+
 int32_t b2_check_device_errors(void) {
     int32_t status = B2_STATUS_OK;
     DeviceContext* ctx = device_context(&status);
@@ -777,6 +933,8 @@ static int32_t host_linear(const b2_nf4_weight* weight, const float* src_host, f
     WeightView w;
     B2_TRY(make_weight_view(weight, &w));
     B2_TRY(check_linear_dims(w, rows));
+    // one staging buffer per device: held from the first copy to the final synchronise
+    std::lock_guard<std::mutex> host_lock(g_host_mutex[ctx->device]);
     if (src_host == nullptr || dst_host == nullptr) {
         return fail(B2_STATUS_INVALID_ARGUMENT, "quantized linear host buffers must not be null");
     }
@@ -855,6 +1013,7 @@ int32_t b2_host_paged_decode_attention(const float* q_host, const float* k_pages
             }
         }
     }
+    std::lock_guard<std::mutex> host_lock(g_host_mutex[ctx->device]);
     const size_t q_bytes = static_cast<size_t>(n_seq) * q_heads * head_width * sizeof(float);
     const size_t table_bytes = static_cast<size_t>(n_seq) * max_blocks * sizeof(uint32_t);
     const size_t len_bytes = static_cast<size_t>(n_seq) * sizeof(uint32_t);
@@ -883,16 +1042,7 @@ int32_t b2_host_paged_decode_attention(const float* q_host, const float* k_pages
     B2_CUDA_TRY(cudaMemcpyAsync(ctx_host, d_ctx, q_bytes, cudaMemcpyDeviceToHost, stream));
     B2_CUDA_TRY(cudaMemcpyAsync(&host_status, d_status, sizeof(uint32_t), cudaMemcpyDeviceToHost, stream));
     B2_CUDA_TRY(cudaStreamSynchronize(stream));
-    if (host_status & B2_ATTN_STATUS_BAD_BLOCK) {
-        return fail(B2_STATUS_OUT_OF_RANGE, "paged decode attention block table contains an invalid block");
-    }
-    if (host_status & B2_ATTN_STATUS_NAN_OR_POS_INF) {
-        return fail(B2_STATUS_DOMAIN_ERROR, "softmax rejects NaN and positive infinity");
-    }
-    if (host_status & B2_ATTN_STATUS_ALL_NEG_INF) {
-        return fail(B2_STATUS_DOMAIN_ERROR, "softmax requires one finite value per slice");
-    }
-    return B2_STATUS_OK;
+    return b2_attention_status_result(host_status);
 }
 
 }  // extern "C"

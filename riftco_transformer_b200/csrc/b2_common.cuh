@@ -10,6 +10,7 @@
 #include <cstdarg>
 #include <cstdint>
 #include <cstdio>
+#include <mutex>
 
 namespace b2 {
 
@@ -53,6 +54,12 @@ struct DeviceContext {
     // Library-owned scratch arena used when a caller passes no workspace.
     void* arena = nullptr;
     size_t arena_bytes = 0;
+    // Scratch of the decode-batch linear: partial tiles of CTAs whose range ends inside a tile
+    // (fixed size, 2 per SM) and a ring of per-tile arrival counters (zero between launches).
+    void* decode_partial = nullptr;
+    uint32_t* decode_counters = nullptr;
+    uint32_t decode_counter_capacity = 0;
+    uint32_t decode_counter_next = 0;
     // Staging buffers of the host-buffer seam.
     void* stage = nullptr;
     size_t stage_bytes = 0;
@@ -64,11 +71,32 @@ struct DeviceContext {
 // recording an error (no device, wrong architecture, allocation failure).
 DeviceContext* device_context(int32_t* status);
 
-// Grows (never shrinks) the arena / staging buffers. Growing synchronises the
-// device, so the first call with a given size must not happen inside a stream
-// capture.
-int32_t reserve_arena(DeviceContext* ctx, size_t bytes);
+// Grows (never shrinks) the arena / staging buffers. Growing allocates, so it is
+// refused while `stream` is being captured; an arena that has been handed out is
+// never freed (graphs that captured its address stay valid), a larger one simply
+// replaces it for later calls.
+int32_t reserve_arena(DeviceContext* ctx, size_t bytes, cudaStream_t stream);
+// `count` zeroed arrival counters for one launch of the decode-batch linear.
+int32_t take_decode_counters(DeviceContext* ctx, uint32_t count, uint32_t** out);
 int32_t reserve_stage(DeviceContext* ctx, size_t device_bytes, size_t pinned_bytes);
+
+// Attributes set with cudaFuncSetAttribute (and occupancy answers) belong to ONE device, and a
+// process may drive several. `once_per_device` runs `configure` (returning a status) the first time
+// a device is seen, under a once_flag, and reports its outcome on every later call.
+constexpr int kMaxDevices = 64;
+struct PerDeviceOnce {
+    std::once_flag flag[kMaxDevices];
+    int32_t status[kMaxDevices] = {};
+};
+template <class Configure>
+inline int32_t once_per_device(PerDeviceOnce& state, int device, Configure&& configure) {
+    if (device < 0 || device >= kMaxDevices) return fail(B2_STATUS_RUNTIME_ERROR, "internal: device index out of range");
+    std::call_once(state.flag[device], [&] { state.status[device] = configure(); });
+    if (state.status[device] != B2_STATUS_OK) {
+        return fail(state.status[device], "a kernel could not be configured on device %d", device);
+    }
+    return B2_STATUS_OK;
+}
 
 // ---- weight view ----------------------------------------------------------------
 

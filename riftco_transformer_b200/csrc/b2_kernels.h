@@ -45,6 +45,14 @@ int32_t launch_nf4_gemm_tmem(const DeviceContext& ctx, const WeightView& w, cons
                              uint64_t rows, cudaStream_t stream);
 int32_t launch_nf4_gemm_tmem_multi(const DeviceContext& ctx, const WeightView* ws, float* const* ys, uint32_t count,
                                    const void* x_bf16, uint64_t rows, cudaStream_t stream);
+// nf4_decode_tmem.cu - persistent stream-K tcgen05 kernel for decode batches (1..32 rows); `x16` is the
+// bf16 (half == false) or fp16 (half == true) copy of the activations.
+bool nf4_decode_tmem_supported(const WeightView& w, const void* x, uint64_t rows);
+size_t nf4_decode_tmem_workspace_bytes(const DeviceContext& ctx);
+int32_t launch_f32_to_f16(const DeviceContext& ctx, const float* src, void* dst, uint64_t count, cudaStream_t stream);
+int32_t launch_nf4_decode_tmem(const DeviceContext& ctx, const WeightView* ws, float* const* ys, uint32_t count,
+                               const void* x16, bool half, uint64_t rows, void* partial, uint32_t* counters,
+                               cudaStream_t stream);
 // nf4_backward_dense.cu - input-backward for many rows: transposed bf16 expansion + plain tcgen05 GEMM.
 bool nf4_backward_dense_supported(const WeightView& w, const float* dy, uint64_t rows);
 size_t nf4_backward_dense_workspace_bytes(const WeightView& w, uint64_t rows);
@@ -67,6 +75,11 @@ struct PagedDecodeArgs {
     uint64_t physical_blocks;
     uint32_t* status;  // may be null
 };
+// Dimension rules of dispatch_paged_decode_attention_forward that need no view of device data
+// (src/core/backend/attention/dispatch.cpp:179-219,440-509); defined in api.cu.
+int32_t check_paged_dims(uint32_t n_seq, uint32_t q_heads, uint32_t kv_heads, uint32_t head_width,
+                         uint32_t block_size, uint64_t physical_blocks, uint32_t max_blocks,
+                         uint32_t max_seq_len);
 size_t paged_decode_workspace_bytes(uint32_t n_seq, uint32_t q_heads, uint32_t head_width,
                                     uint32_t block_size, uint32_t max_seq_len);
 int32_t launch_paged_decode(const DeviceContext& ctx, const PagedDecodeArgs& args, void* workspace,

@@ -124,8 +124,11 @@ rope_append_kernel(float* __restrict__ q, const float* __restrict__ k, const flo
     const uint32_t seq = blockIdx.x;
     const uint32_t pos = positions[seq];
     const uint32_t half = d / 2;
-    uint64_t phys = block_tables[static_cast<uint64_t>(seq) * max_blocks + pos / block_size];
-    bool bad = false;
+    // A position past the sequence's table row is treated like a bad block id: nothing is read from
+    // the neighbouring row and no page is written.
+    const uint32_t logical = pos / block_size;
+    bool bad = logical >= max_blocks;
+    uint64_t phys = bad ? 0 : block_tables[static_cast<uint64_t>(seq) * max_blocks + logical];
     if (phys >= physical_blocks) {
         bad = true;
         phys = 0;

@@ -274,11 +274,11 @@ int32_t launch_nf4_backward_dense(const DeviceContext& ctx, const WeightView& w,
     CUtensorMap map_a, map_b;
     B2_TRY(operand_map(&map_a, dy16, rows, w.out_features));            // dY  [M, K = out]
     B2_TRY(operand_map(&map_b, wt16, w.in_features, w.out_features));   // Wt  [N = in, K = out]
-    static bool configured = false;
-    if (!configured) {
+    static PerDeviceOnce configured;
+    B2_TRY(once_per_device(configured, ctx.device, []() -> int32_t {
         B2_CUDA_TRY(cudaFuncSetAttribute(bf16_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
-        configured = true;
-    }
+        return B2_STATUS_OK;
+    }));
     Params p;
     p.out = dx;
     p.m = static_cast<uint32_t>(rows);

@@ -1,0 +1,846 @@
+// Decode-batch packed-NF4 linear (1..32 activation rows) on the 5th-generation tensor cores:
+//   Y[m, out] = X[m, in] * W[out, in]^T      (reference loop:
+//   src/core/backend/nn/quantized_linear/reference/operations.cpp:49-81)
+//
+// The kernel is bound by how fast the packed weights stream through the SMs, so it is built as
+// a persistent weight-streaming pipeline, one CTA per SM:
+//
+//  * Work items are (128-row weight tile, 256-wide contraction round). The items of a launch -
+//    all tiles of up to four weights that share the activations - are numbered tile-major and cut
+//    into one contiguous range per CTA (stream-K), so every SM streams the same number of bytes
+//    whatever the shape or the shard size. A CTA whose range ends inside a tile leaves a partial
+//    tile; the partial tiles of one output tile are summed in a fixed order by whichever CTA
+//    finishes last (a counter per tile), so results do not depend on timing.
+//  * One thread streams the packed codes ([128 rows x 128 bytes], 128-byte swizzle), the tile's
+//    raw block scales and the second-level values they refer to into a shared-memory ring with
+//    cp.async.bulk.tensor; weights are immutable, so this starts before the dependency wait of a
+//    programmatic dependent launch, i.e. under the previous kernel's tail.
+//  * Sixteen expansion warps turn a round into its 16-bit operand form: thread (row, k-block)
+//    reads its 32 packed bytes from the ring, looks every byte up in a per-lane replicated
+//    byte -> pair table (one PRMT forms the address), multiplies by the block scale and writes its
+//    64 values with one tcgen05.st into the round's stage of TENSOR memory, where the weight tile
+//    is the A operand (lane = weight row). Three 256-wide stages keep expansion and MMAs apart.
+//  * One thread issues the sixteen tcgen05.mma (M128, N = 16 or 32 tokens, K16) of a round behind
+//    ONE barrier wait and commits once per round; the activations (16-bit, by TMA) are the B
+//    operand in shared memory.
+//
+// Two operand types share the code: bf16 (activations handed over as bf16, rel-L2 ~3e-3, used
+// above 16 rows) and fp16 with an FP32 row normaliser (rel-L2 ~5e-4, used up to 16 rows, where
+// the tolerance is 2e-3). Every mbarrier wait is bounded; a timeout sets an error word and the
+// kernel drains.
+#include "b2_common.cuh"
+#include "b2_kernels.h"
+#include "sm100_ptx.cuh"
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include <cstdlib>
+#include <mutex>
+
+namespace b2 {
+namespace {
+
+using namespace sm100;
+
+constexpr int kTileW = 128;                       // weight rows per tile (MMA M, TMEM lanes)
+constexpr int kRoundK = 256;                      // contraction values per round
+constexpr int kMaxTokens = 32;                    // activation rows per launch at most (MMA N)
+constexpr int kCodeBytes = kTileW * (kRoundK / 2);            // 16384: packed codes of one item
+constexpr int kScaleBoxBytes = kTileW * 16;                   // 2048: 16 bytes of raw scales per row
+constexpr int kSecondBox = 128;                               // second-level floats per item
+constexpr int kScaleOff = kCodeBytes;
+constexpr int kSecondOff = kCodeBytes + kScaleBoxBytes;
+constexpr int kWStageBytes = 19 * 1024;                       // codes + scales + second level, 1 KB granular
+constexpr int kMaxWStages = 6;
+constexpr int kXStages = 4;                                   // activation stages
+constexpr int kAStages = 3;                                   // tensor-memory stages of the expanded weights
+constexpr int kLutBytes = 65536;                              // 256 rows of 256 bytes (lane l at byte 4*l)
+constexpr int kLowHeader = 2048;                              // barriers + scale-code factor table
+constexpr int kExpandWarps = 16;
+constexpr int kFirstExpandWarp = 3;
+constexpr int kThreads = (kFirstExpandWarp + kExpandWarps) * 32;   // 608
+constexpr int kExpandThreads = kExpandWarps * 32;
+constexpr int kSmemBytes = 232448;                            // all of it: the ring takes what the rest leaves
+constexpr uint32_t kTmemColumns = 512;
+constexpr uint32_t kAccColumns = 128;                         // accumulator region (kMaxTokens used)
+constexpr uint32_t kStageColumns = kRoundK / 2;               // 128 columns: one round of 16-bit pairs
+constexpr int kMaxWeights = 4;
+constexpr int kPartialFloats = kMaxTokens * kTileW;           // one partial tile
+
+struct DecodeMaps {
+    CUtensorMap codes[kMaxWeights];     // u8 [out, in/2], box {128, 128}, 128-byte swizzle
+    CUtensorMap scales[kMaxWeights];    // u8 [out, blocks/row] box {16, 128}  or  f32 box {4, 128}
+    CUtensorMap second[kMaxWeights];    // f32 [n_second], box {128}
+};
+
+struct DecodeParams {
+    WeightView w[kMaxWeights];
+    float* out[kMaxWeights];
+    uint32_t n[kMaxWeights];
+    uint32_t tile_end[kMaxWeights];   // running count of 128-row tiles
+    uint32_t count;
+    uint32_t m, k;
+    uint32_t n_pad;            // 16 or 32: MMA N
+    uint32_t rounds;           // k / 256
+    uint32_t total_items;      // tiles * rounds
+    uint32_t blocks_per_row;   // k >> block_shift
+    uint32_t kshift;           // block_shift - 6: 64-wide k-blocks per scale block, as a shift
+    float* partial;            // [2 * gridDim.x][kPartialFloats]
+    uint32_t* counters;        // [tiles], zero before the launch; the kernel leaves them zero
+    uint32_t* error;
+    const uint32_t* lut;       // compact [256][32] words of 16-bit pairs
+};
+
+struct Barriers {
+    uint64_t w_full[kMaxWStages];
+    uint64_t w_empty[kMaxWStages];
+    uint64_t x_full[kXStages];
+    uint64_t x_empty[kXStages];     // tcgen05.commit: the round's MMAs have read the activation stage
+    uint64_t a_full[kAStages];
+    uint64_t done[kAStages];        // tcgen05.commit: the round's MMAs have read the tensor-memory stage
+    uint64_t acc_full;
+    uint32_t tmem_base;
+    uint32_t abort;
+    uint32_t last_flag;
+};
+static_assert(sizeof(Barriers) <= 256, "barrier block");
+
+template <bool kHalf>
+__device__ __forceinline__ uint32_t pair_mul(uint32_t a, uint32_t b) {
+    if (kHalf) {
+        __half2 r = __hmul2(*reinterpret_cast<__half2*>(&a), *reinterpret_cast<__half2*>(&b));
+        return *reinterpret_cast<uint32_t*>(&r);
+    }
+    __nv_bfloat162 r = __hmul2(*reinterpret_cast<__nv_bfloat162*>(&a), *reinterpret_cast<__nv_bfloat162*>(&b));
+    return *reinterpret_cast<uint32_t*>(&r);
+}
+template <bool kHalf>
+__device__ __forceinline__ uint32_t pair_of(float s) {
+    if (kHalf) {
+        __half2 p = __float2half2_rn(s);
+        return *reinterpret_cast<uint32_t*>(&p);
+    }
+    __nv_bfloat162 p = __float2bfloat162_rn(s);
+    return *reinterpret_cast<uint32_t*>(&p);
+}
+
+__device__ __forceinline__ uint32_t lds_u32(uint32_t a) {
+    uint32_t v;
+    asm("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint4 lds_u4(uint32_t a) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ float lds_f32(uint32_t a) {
+    float v;
+    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds_u8(uint32_t a) {
+    uint32_t v;
+    asm volatile("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ void cp_async_16(uint32_t dst32, const void* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(dst32), "l"(src));
+}
+__device__ __forceinline__ void tma_2d_at(uint32_t dst32, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst32), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
+        : "memory");
+}
+__device__ __forceinline__ void tma_1d_at(uint32_t dst32, const CUtensorMap* map, int x, uint64_t* bar) {
+    asm volatile("cp.async.bulk.tensor.1d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2}], [%3];"
+                 ::"r"(dst32), "l"(map), "r"(x), "r"(smem_u32(bar))
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+        "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]),
+          "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]),
+          "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() {
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+// 32 lanes x 16 consecutive columns: thread i of the warp gets lane (base + i).
+__device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void umma_a_tmem(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc,
+                                            uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// Instruction descriptor, kind::f16: 16-bit x 16-bit -> f32, both operands K-major.
+__device__ __forceinline__ uint32_t idesc_16bit(bool half, uint32_t m, uint32_t n) {
+    const uint32_t fmt = half ? 0u : 1u;   // 0 = f16, 1 = bf16
+    return (1u << 4) | (fmt << 7) | (fmt << 10) | ((n >> 3) << 17) | ((m >> 4) << 24);
+}
+// True in exactly one lane of a converged warp. Loops that issue TMA or tcgen05 instructions run
+// on the whole warp with the instruction itself under this predicate: the loop state stays
+// warp-uniform, so descriptors and addresses can live in uniform registers.
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile("{ .reg .pred p; elect.sync _|p, 0xFFFFFFFF; selp.u32 %0, 1, 0, p; }" : "=r"(pred));
+    return pred != 0;
+}
+__device__ __forceinline__ void expand_barrier() {
+    asm volatile("bar.sync 1, %0;" ::"n"(kExpandThreads) : "memory");
+}
+
+// Where the pieces of shared memory lie for this CTA: a pure function of the dynamic allocation's
+// address and of the token tile, so every role computes the same answer.
+struct SmemPlan {
+    uint32_t low32;       // barriers, factor table
+    uint32_t x32;         // activation stages
+    uint32_t lut32;       // 64 KB aligned table
+    uint32_t high32;      // ring stages behind the table
+    uint32_t low_w32;     // ring stages that fit below the table
+    uint32_t n_high, n_stages;
+    uint32_t x_stage_bytes;
+};
+__device__ __forceinline__ SmemPlan plan_smem(uint32_t raw32, uint32_t n_pad) {
+    SmemPlan s;
+    s.low32 = (raw32 + 1023u) & ~1023u;
+    s.x32 = s.low32 + kLowHeader;
+    s.x_stage_bytes = n_pad * (kRoundK * 2u);
+    const uint32_t low_end = s.x32 + kXStages * s.x_stage_bytes;
+    s.lut32 = (low_end + 65535u) & ~65535u;
+    s.high32 = s.lut32 + kLutBytes;
+    const uint32_t end32 = raw32 + kSmemBytes;
+    s.n_high = end32 > s.high32 ? (end32 - s.high32) / kWStageBytes : 0u;
+    s.low_w32 = (low_end + 1023u) & ~1023u;
+    const uint32_t n_low = s.lut32 > s.low_w32 ? (s.lut32 - s.low_w32) / kWStageBytes : 0u;
+    s.n_stages = min(s.n_high + n_low, static_cast<uint32_t>(kMaxWStages));
+    if (s.n_high > s.n_stages) s.n_high = s.n_stages;
+    return s;
+}
+__device__ __forceinline__ uint32_t w_stage_addr(const SmemPlan& s, uint32_t stage) {
+    return stage < s.n_high ? s.high32 + stage * kWStageBytes : s.low_w32 + (stage - s.n_high) * kWStageBytes;
+}
+
+// The weight (index, first row of the tile, output width) that owns tile `tile`.
+struct TileRef {
+    uint32_t wi, n0, n_out;
+};
+__device__ __forceinline__ TileRef locate_tile(const DecodeParams& p, uint32_t tile) {
+    uint32_t wi = 0, base = 0;
+#pragma unroll
+    for (int i = 1; i < kMaxWeights; ++i) {
+        if (static_cast<uint32_t>(i) < p.count && tile >= p.tile_end[i - 1]) {
+            wi = static_cast<uint32_t>(i);
+            base = p.tile_end[i - 1];
+        }
+    }
+    TileRef t;
+    t.wi = wi;
+    t.n0 = (tile - base) * kTileW;
+    t.n_out = p.n[0];
+#pragma unroll
+    for (int i = 1; i < kMaxWeights; ++i) {
+        if (wi == static_cast<uint32_t>(i)) t.n_out = p.n[i];
+    }
+    return t;
+}
+
+__device__ __forceinline__ uint32_t range_begin(uint32_t cta, uint32_t ctas, uint32_t items) {
+    return static_cast<uint32_t>(static_cast<uint64_t>(cta) * items / ctas);
+}
+// The CTA whose range holds `item`.
+__device__ __forceinline__ uint32_t cta_of_item(uint32_t item, uint32_t ctas, uint32_t items) {
+    return static_cast<uint32_t>(((static_cast<uint64_t>(item) + 1u) * ctas - 1u) / items);
+}
+
+template <bool kHalf>
+__global__ void __launch_bounds__(kThreads, 1)
+nf4_decode_tmem_kernel(const __grid_constant__ DecodeMaps maps, const __grid_constant__ CUtensorMap map_x,
+                       const DecodeParams p) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    const uint32_t raw32 = smem_u32(smem_raw);
+    const SmemPlan plan = plan_smem(raw32, p.n_pad);
+    uint8_t* low = smem_raw + (plan.low32 - raw32);
+    Barriers& bars = *reinterpret_cast<Barriers*>(low);
+    float* s_factor = reinterpret_cast<float*>(low + 256);   // scale code -> (code - 128) / 127
+    uint32_t* s_slots = reinterpret_cast<uint32_t*>(low + 1280);   // partial-tile slots of one output tile (<= 160)
+    volatile uint32_t* abort = &bars.abort;
+
+    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+    const uint32_t ctas = gridDim.x, cta = blockIdx.x;
+    const uint32_t R = p.rounds;
+    const uint32_t item_begin = range_begin(cta, ctas, p.total_items);
+    const uint32_t item_end = range_begin(cta + 1u, ctas, p.total_items);
+    const uint32_t n_stages = plan.n_stages;
+    const bool fp32_scales = p.w[0].encoding == B2_SCALES_FLOAT32;
+
+    if (n_stages < 3u) {   // the ring does not fit (never with the sizes this file is built for)
+        if (tid == 0 && p.error != nullptr) atomicOr(p.error, 2u);
+        return;
+    }
+
+    // ---- set-up that touches no caller tensor except the immutable weights ----
+    if (warp == 0) {
+        if (lane == 0) {
+            for (uint32_t s = 0; s < n_stages; ++s) {
+                mbar_init(&bars.w_full[s], 1);
+                mbar_init(&bars.w_empty[s], kExpandWarps);
+            }
+            for (int s = 0; s < kXStages; ++s) {
+                mbar_init(&bars.x_full[s], 1);
+                mbar_init(&bars.x_empty[s], 1);
+            }
+            for (int s = 0; s < kAStages; ++s) {
+                mbar_init(&bars.a_full[s], kExpandWarps);
+                mbar_init(&bars.done[s], 1);
+            }
+            mbar_init(&bars.acc_full, 1);
+            bars.abort = 0;
+            bars.last_flag = 0;
+            mbar_fence_init();
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        tmem_alloc(&bars.tmem_base, kTmemColumns);
+    }
+    // byte -> pair table, replicated per lane: entry v for lane l at v * 256 + 4 * l
+    for (uint32_t i = tid; i < 256u * 8u; i += kThreads) {
+        cp_async_16(plan.lut32 + (i >> 3) * 256u + (i & 7u) * 16u, p.lut + i * 4u);
+    }
+    asm volatile("cp.async.commit_group;" ::);
+    if (tid < 256) s_factor[tid] = dq_factor(tid);
+
+    const uint32_t w_tx = kCodeBytes + kScaleBoxBytes + (fp32_scales ? 0u : kSecondBox * 4u);
+    // Streams item `it` (ring slot `s`): packed codes, raw scales, second-level values.
+    auto issue_weights = [&](uint32_t it, uint32_t s) {
+        const uint32_t tile = it / R, rho = it - tile * R;
+        const TileRef t = locate_tile(p, tile);
+        const uint32_t dst = w_stage_addr(plan, s);
+        mbar_expect_tx(&bars.w_full[s], w_tx);
+        tma_2d_at(dst, &maps.codes[t.wi], static_cast<int>(rho * (kRoundK / 2)), static_cast<int>(t.n0),
+                  &bars.w_full[s]);
+        const uint32_t blk0 = (4u * rho) >> p.kshift;
+        if (fp32_scales) {
+            tma_2d_at(dst + kScaleOff, &maps.scales[t.wi], static_cast<int>(blk0 & ~3u), static_cast<int>(t.n0),
+                      &bars.w_full[s]);
+        } else {
+            tma_2d_at(dst + kScaleOff, &maps.scales[t.wi], static_cast<int>(blk0 & ~15u), static_cast<int>(t.n0),
+                      &bars.w_full[s]);
+            const WeightView& w = p.w[t.wi];
+            const uint32_t first = static_cast<uint32_t>(
+                (w.flat_block_base + static_cast<uint64_t>(t.n0) * p.blocks_per_row + blk0) >> w.scale_block_shift);
+            tma_1d_at(dst + kSecondOff, &maps.second[t.wi], static_cast<int>(first & ~3u), &bars.w_full[s]);
+        }
+    };
+    // The first ring fill goes out before the rest of the CTA has even synchronised.
+    uint32_t w_issued = 0;
+    if (warp == 0) {
+        for (; w_issued < n_stages && item_begin + w_issued < item_end; ++w_issued) {
+            if (elect_one()) issue_weights(item_begin + w_issued, w_issued);
+            __syncwarp();
+        }
+    }
+    asm volatile("cp.async.wait_group 0;" ::);
+    tcgen05_fence_before_sync();
+    __syncthreads();
+    tcgen05_fence_after_sync();
+    const uint32_t tmem_base = bars.tmem_base;
+    const uint32_t tmem_a = tmem_base + kAccColumns;
+    pdl_launch_dependents();
+
+    if (warp == 0) {
+        // ---- weight producer ----
+        uint32_t s = w_issued == n_stages ? 0u : w_issued, round_trip = w_issued == n_stages ? 1u : 0u;
+        for (uint32_t it = item_begin + w_issued; it < item_end; ++it) {
+            mbar_wait(&bars.w_empty[s], (round_trip - 1u) & 1u, abort);
+            if (elect_one()) issue_weights(it, s);
+            __syncwarp();
+            if (++s == n_stages) {
+                s = 0;
+                ++round_trip;
+            }
+        }
+    } else if (warp == 2) {
+        // ---- activation producer: [n_pad tokens x 256] per item as four 64-wide swizzled boxes ----
+        pdl_wait();
+        uint32_t s = 0, trip = 0, rho = item_begin % R;
+        for (uint32_t it = item_begin; it < item_end; ++it) {
+            if (trip > 0) mbar_wait(&bars.x_empty[s], (trip - 1u) & 1u, abort);
+            if (elect_one()) {
+                mbar_expect_tx(&bars.x_full[s], plan.x_stage_bytes);
+                const uint32_t dst = plan.x32 + s * plan.x_stage_bytes;
+#pragma unroll
+                for (uint32_t b = 0; b < 4u; ++b) {
+                    tma_2d_at(dst + b * (p.n_pad * 128u), &map_x, static_cast<int>(rho * kRoundK + b * 64u), 0,
+                              &bars.x_full[s]);
+                }
+            }
+            __syncwarp();
+            if (++rho == R) rho = 0;
+            if (++s == kXStages) {
+                s = 0;
+                ++trip;
+            }
+        }
+    } else if (warp == 1) {
+        // ---- MMA issuer: sixteen K16 steps per round behind one wait, one commit per round ----
+        const uint32_t idesc = idesc_16bit(kHalf, kTileW, p.n_pad);
+        const uint64_t dx0 = umma_desc_k_major_sw128(plan.x32);
+        const uint32_t x_stage16 = plan.x_stage_bytes >> 4, kb16 = (p.n_pad * 128u) >> 4;
+        uint32_t s = 0, trip = 0, xs = 0, x_trip = 0, rho = item_begin % R;
+        for (uint32_t it = item_begin; it < item_end; ++it) {
+            const bool first = it == item_begin || rho == 0u;
+            const bool last = it + 1u == item_end || rho + 1u == R;
+            mbar_wait(&bars.a_full[s], trip & 1u, abort);
+            mbar_wait(&bars.x_full[xs], x_trip & 1u, abort);
+            tcgen05_fence_after_sync();
+            if (elect_one()) {
+                const uint64_t dx_s = dx0 + xs * x_stage16;
+                const uint32_t a_s = tmem_a + s * kStageColumns;
+#pragma unroll
+                for (uint32_t kb = 0; kb < 4u; ++kb) {
+#pragma unroll
+                    for (uint32_t kk = 0; kk < 4u; ++kk) {
+                        umma_a_tmem(tmem_base, a_s + kb * 32u + kk * 8u, dx_s + kb * kb16 + kk * 2u, idesc,
+                                    (first && kb == 0u && kk == 0u) ? 0u : 1u);
+                    }
+                }
+                umma_commit(&bars.done[s]);
+                umma_commit(&bars.x_empty[xs]);
+                if (last) umma_commit(&bars.acc_full);
+            }
+            __syncwarp();
+            if (++rho == R) rho = 0;
+            if (++s == kAStages) {
+                s = 0;
+                ++trip;
+            }
+            if (++xs == kXStages) {
+                xs = 0;
+                ++x_trip;
+            }
+        }
+    } else {
+        // ---- expansion warps: thread = (weight row, k-block of the round) ----
+        pdl_wait();   // their epilogue writes caller memory
+        const uint32_t e = warp - kFirstExpandWarp;
+        const uint32_t g = e >> 2;                    // k-block of every round this warp expands
+        const uint32_t quarter = warp & 3u;           // the TMEM lanes this warp may touch
+        const uint32_t row = quarter * 32u + lane;    // weight row of the tile = TMEM lane
+        const uint32_t lut_lane = plan.lut32 | (lane * 4u);
+        const uint32_t lane_addr = (quarter * 32u) << 16;
+        // byte offsets of this thread's two 16-byte chunks inside a swizzled [128 x 128 B] box
+        const uint32_t code_off0 = row * 128u + (((2u * g) ^ (row & 7u)) << 4);
+        const uint32_t code_off1 = row * 128u + (((2u * g + 1u) ^ (row & 7u)) << 4);
+        const uint32_t sshift = p.w[0].scale_block_shift;
+        uint32_t ws = 0, as = 0, a_trip = 0, w_trip = 0, seg = 0;
+        TileRef tref = {0u, 0u, 0u};
+        float dq_offset = 0.0f;
+        uint32_t fbase_tile = 0;   // flat index of the first scale block of the tile's first row
+        uint32_t fbase_row = 0;    // ... of this thread's row
+        float norm = 1.0f, inv_norm = 1.0f;   // fp16 operands: the row's values are expanded as w / norm
+        bool live = false;
+        uint32_t v[32];
+
+        // Expands this thread's 64 weights of item (tile, rho) into v: waits for the ring slot, reads
+        // its 32 packed bytes and its scale, looks the bytes up, releases the slot.
+        auto expand = [&](uint32_t tile, uint32_t rho, bool new_tile, bool seg_begins) {
+            if (new_tile) {
+                tref = locate_tile(p, tile);
+                const WeightView& w = p.w[tref.wi];
+                dq_offset = w.offset;
+                fbase_tile = static_cast<uint32_t>(w.flat_block_base) + tref.n0 * p.blocks_per_row;
+                fbase_row = fbase_tile + row * p.blocks_per_row;
+                live = tref.n0 + row < tref.n_out;
+            }
+            const uint32_t stage32 = w_stage_addr(plan, ws);
+            mbar_wait(&bars.w_full[ws], w_trip & 1u, abort);
+            const uint4 c0 = lds_u4(stage32 + code_off0);
+            const uint4 c1 = lds_u4(stage32 + code_off1);
+            // Decoded scale of block `blk` of this row, from the raw values in the ring slot.
+            const uint32_t blk0 = (4u * rho) >> p.kshift;
+            auto block_scale = [&](uint32_t blk) -> float {
+                if (fp32_scales) return lds_f32(stage32 + kScaleOff + row * 16u + (blk - (blk0 & ~3u)) * 4u);
+                const uint32_t code = lds_u8(stage32 + kScaleOff + row * 16u + (blk - (blk0 & ~15u)));
+                const uint32_t first = (fbase_tile + blk0) >> sshift;
+                const uint32_t idx = ((fbase_row + blk) >> sshift) - (first & ~3u);
+                return dq_finish(s_factor[code], lds_f32(stage32 + kSecondOff + idx * 4u), dq_offset);
+            };
+            float scale = live ? block_scale((4u * rho + g) >> p.kshift) : 0.0f;
+            if (kHalf) {
+                // Keep the fp16 operand in range whatever the magnitude of the weights: every value of
+                // a row is divided by a power of two taken from the first scale of the row's segment
+                // (exact; the same for the four threads that share the row), and the row's sum is
+                // multiplied back in the epilogue.
+                if (seg_begins) {
+                    const uint32_t bits = live ? (__float_as_uint(block_scale(blk0)) & 0x7F800000u) : 0u;
+                    norm = (bits == 0u || bits == 0x7F800000u) ? 1.0f : __uint_as_float(bits);
+                    inv_norm = 1.0f / norm;
+                }
+                scale *= inv_norm;
+            }
+            const uint32_t s2 = pair_of<kHalf>(scale);
+            const uint32_t words[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+                const uint32_t word = words[q];
+                v[4 * q + 0] = pair_mul<kHalf>(lds_u32(__byte_perm(word, lut_lane, 0x7604u)), s2);
+                v[4 * q + 1] = pair_mul<kHalf>(lds_u32(__byte_perm(word, lut_lane, 0x7614u)), s2);
+                v[4 * q + 2] = pair_mul<kHalf>(lds_u32(__byte_perm(word, lut_lane, 0x7624u)), s2);
+                v[4 * q + 3] = pair_mul<kHalf>(lds_u32(__byte_perm(word, lut_lane, 0x7634u)), s2);
+            }
+            // the ring slot is free once every warp has its bytes in registers
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars.w_empty[ws]);
+            if (++ws == n_stages) {
+                ws = 0;
+                ++w_trip;
+            }
+        };
+
+        // The loop is software-pipelined: the store of item i into tensor memory is issued, then
+        // item i+1 is expanded into registers while that store completes, and only then does the
+        // warp wait for the store and publish item i to the MMA issuer.
+        uint32_t tile = item_begin / R, rho = item_begin - tile * R;
+        uint32_t seg_first_rho = rho;
+        expand(tile, rho, true, true);
+        for (uint32_t it = item_begin; it < item_end; ++it) {
+            if (a_trip > 0) mbar_wait(&bars.done[as], (a_trip - 1u) & 1u, abort);
+            tcgen05_fence_after_sync();
+            tmem_st_32x32(tmem_a + as * kStageColumns + g * 32u + lane_addr, v);
+            // what the epilogue of item `it` needs, before the next item replaces it
+            const uint32_t cur_tile = tile, cur_rho = rho, cur_first_rho = seg_first_rho;
+            const TileRef cur_ref = tref;
+            const bool cur_live = live;
+            const float cur_norm = norm;
+            const bool seg_ends = it + 1u == item_end || rho + 1u == R;
+            if (it + 1u < item_end) {
+                const bool new_tile = rho + 1u == R;
+                if (new_tile) {
+                    rho = 0;
+                    ++tile;
+                } else {
+                    ++rho;
+                }
+                if (seg_ends) seg_first_rho = rho;
+                expand(tile, rho, new_tile, seg_ends);
+            }
+            tmem_st_wait();
+            tcgen05_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars.a_full[as]);
+            if (++as == kAStages) {
+                as = 0;
+                ++a_trip;
+            }
+            if (!seg_ends) continue;
+
+            // ---- epilogue of the segment [cur_first_rho, cur_rho] of tile cur_tile ----
+            mbar_wait(&bars.acc_full, seg & 1u, abort);
+            ++seg;
+            tcgen05_fence_after_sync();
+            const bool whole = cur_first_rho == 0u && cur_rho + 1u == R;
+            float* out = p.out[0];
+#pragma unroll
+            for (int i = 1; i < kMaxWeights; ++i) {
+                if (cur_ref.wi == static_cast<uint32_t>(i)) out = p.out[i];
+            }
+            const uint32_t n = cur_ref.n0 + row;
+            const uint32_t slot = 2u * cta + (item_begin < cur_tile * R ? 1u : 0u);
+            float* partial = p.partial + static_cast<uint64_t>(slot) * kPartialFloats;
+            if (g * 16u < p.n_pad) {
+                uint32_t r[16];
+                tmem_ld_32x16(tmem_base + lane_addr + g * 16u, r);
+                tmem_ld_wait();
+#pragma unroll
+                for (uint32_t i = 0; i < 16u; ++i) {
+                    const uint32_t t = g * 16u + i;
+                    float val = __uint_as_float(r[i]);
+                    if (kHalf) val *= cur_norm;
+                    if (t < p.m) {
+                        if (whole) {
+                            if (cur_live) out[static_cast<uint64_t>(t) * cur_ref.n_out + n] = val;
+                        } else {
+                            partial[t * kTileW + row] = val;
+                        }
+                    }
+                }
+            }
+            tcgen05_fence_before_sync();
+            if (!whole) {
+                // Publish the partial tile; the CTA that arrives last sums all of them in CTA order.
+                const uint32_t c_first = cta_of_item(cur_tile * R, ctas, p.total_items);
+                const uint32_t c_last = cta_of_item(cur_tile * R + R - 1u, ctas, p.total_items);
+                __threadfence();
+                expand_barrier();
+                if (e == 0 && lane == 0) {
+                    const uint32_t old = atomicAdd(&p.counters[cur_tile], 1u);
+                    bars.last_flag = old == c_last - c_first ? 1u : 0u;
+                }
+                expand_barrier();
+                if (bars.last_flag != 0u) {
+                    __threadfence();
+                    const uint32_t et = tid - kFirstExpandWarp * 32u;
+                    const uint32_t parts = c_last - c_first + 1u;
+                    // where each part of this tile lies (a 64-bit division per part, done once)
+                    for (uint32_t c = et; c < parts; c += kExpandThreads) {
+                        const uint32_t cc = c_first + c;
+                        s_slots[c] = 2u * cc + (range_begin(cc, ctas, p.total_items) < cur_tile * R ? 1u : 0u);
+                    }
+                    expand_barrier();
+                    // Four floats per thread and step; the loads of up to four parts are in flight
+                    // together (their sum order is still part 0, 1, 2, ...).
+                    const uint32_t total4 = p.m * (kTileW / 4);
+                    for (uint32_t i4 = et; i4 < total4; i4 += kExpandThreads) {
+                        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+                        for (uint32_t c0 = 0; c0 < parts; c0 += 4u) {
+                            float4 pv[4];
+#pragma unroll
+                            for (uint32_t u = 0; u < 4u; ++u) {
+                                pv[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                                if (c0 + u < parts) {
+                                    pv[u] = __ldcg(reinterpret_cast<const float4*>(
+                                                p.partial + static_cast<uint64_t>(s_slots[c0 + u]) * kPartialFloats) + i4);
+                                }
+                            }
+#pragma unroll
+                            for (uint32_t u = 0; u < 4u; ++u) {
+                                if (c0 + u < parts) {
+                                    acc.x += pv[u].x;
+                                    acc.y += pv[u].y;
+                                    acc.z += pv[u].z;
+                                    acc.w += pv[u].w;
+                                }
+                            }
+                        }
+                        const uint32_t t = i4 / (kTileW / 4), rr = (i4 % (kTileW / 4)) * 4u;
+                        float* dst = out + static_cast<uint64_t>(t) * cur_ref.n_out + cur_ref.n0 + rr;
+                        if (cur_ref.n0 + rr + 3u < cur_ref.n_out && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
+                            *reinterpret_cast<float4*>(dst) = acc;
+                        } else {
+                            const float a4[4] = {acc.x, acc.y, acc.z, acc.w};
+                            for (uint32_t u = 0; u < 4u; ++u) {
+                                if (cur_ref.n0 + rr + u < cur_ref.n_out) dst[u] = a4[u];
+                            }
+                        }
+                    }
+                    if (e == 0 && lane == 0) p.counters[cur_tile] = 0u;   // every part has arrived: ready for the next launch
+                }
+                expand_barrier();   // last_flag and s_slots are rewritten by the next partial segment
+            }
+        }
+    }
+    tcgen05_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        tcgen05_fence_after_sync();
+        tmem_dealloc(tmem_base, kTmemColumns);
+        if (lane == 0 && bars.abort != 0 && p.error != nullptr) atomicOr(p.error, 1u);
+    }
+}
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult result;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &result) == cudaSuccess &&
+            result == cudaDriverEntryPointSuccess) {
+            fn = reinterpret_cast<EncodeTiledFn>(ptr);
+        }
+    });
+    return fn;
+}
+
+int32_t encode(const char* what, CUtensorMap* map, CUtensorMapDataType type, uint32_t rank, const void* base,
+               const cuuint64_t* dims, const cuuint64_t* strides, const cuuint32_t* box, CUtensorMapSwizzle swizzle) {
+    const cuuint32_t elem[2] = {1, 1};
+    const CUresult r = encode_tiled()(map, type, rank, const_cast<void*>(base), dims, strides, box, elem,
+                                      CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        return fail(B2_STATUS_RUNTIME_ERROR, "cuTensorMapEncodeTiled failed (%d) for the %s map", static_cast<int>(r), what);
+    }
+    return B2_STATUS_OK;
+}
+
+// fp32 -> fp16 row-major copy of the activations (pre-pass of the fp16 form).
+__global__ void __launch_bounds__(256)
+f32_to_f16_kernel(const float* __restrict__ src, __half* __restrict__ dst, uint64_t n4) {
+    pdl_launch_dependents();   // the linear that follows may start streaming its weights now
+    const uint64_t stride = static_cast<uint64_t>(gridDim.x) * blockDim.x;
+    for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n4; i += stride) {
+        const float4 v = __ldg(reinterpret_cast<const float4*>(src) + i);
+        __half2 lo = __floats2half2_rn(v.x, v.y), hi = __floats2half2_rn(v.z, v.w);
+        uint2 packed;
+        packed.x = *reinterpret_cast<uint32_t*>(&lo);
+        packed.y = *reinterpret_cast<uint32_t*>(&hi);
+        reinterpret_cast<uint2*>(dst)[i] = packed;
+    }
+}
+
+
+}  // namespace
+
+int32_t launch_f32_to_f16(const DeviceContext& ctx, const float* src, void* dst, uint64_t count, cudaStream_t stream) {
+    const uint64_t n4 = count / 4;
+    uint64_t blocks = (n4 + 255) / 256;
+    if (blocks > static_cast<uint64_t>(ctx.sm_count) * 16) blocks = static_cast<uint64_t>(ctx.sm_count) * 16;
+    if (blocks == 0) blocks = 1;
+    f32_to_f16_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(src, static_cast<__half*>(dst), n4);
+    B2_CUDA_TRY(cudaGetLastError());
+    return B2_STATUS_OK;
+}
+
+size_t nf4_decode_tmem_workspace_bytes(const DeviceContext& ctx) {
+    return static_cast<size_t>(2) * static_cast<size_t>(ctx.sm_count) * kPartialFloats * sizeof(float);
+}
+
+// Shapes this kernel takes: up to 32 rows, whole 256-wide rounds, scale blocks of at least 64
+// weights that divide a row, and arrays aligned the way a TMA descriptor needs them.
+bool nf4_decode_tmem_supported(const WeightView& w, const void* x, uint64_t rows) {
+    if (rows < 1 || rows > static_cast<uint64_t>(kMaxTokens)) return false;
+    if (w.in_features % kRoundK != 0 || w.block_size < 64 || w.in_features % w.block_size != 0) return false;
+    if (encode_tiled() == nullptr) return false;
+    if ((reinterpret_cast<uintptr_t>(w.codes) & 15u) != 0 || (reinterpret_cast<uintptr_t>(x) & 15u) != 0) return false;
+    const uint64_t bpr = w.in_features / w.block_size;
+    if (w.encoding == B2_SCALES_FLOAT32) {
+        if ((reinterpret_cast<uintptr_t>(w.fp32_scales) & 15u) != 0 || bpr % 4 != 0) return false;
+    } else {
+        if ((reinterpret_cast<uintptr_t>(w.scale_codes) & 15u) != 0 || bpr % 16 != 0) return false;
+        if ((reinterpret_cast<uintptr_t>(w.second_level) & 15u) != 0) return false;
+        // second-level values one item can refer to must fit the 128-float box
+        if ((((kTileW - 1) * bpr + 4) >> w.scale_block_shift) + 5 > static_cast<uint64_t>(kSecondBox)) return false;
+    }
+    const uint64_t tiles = (w.out_features + kTileW - 1) / kTileW;
+    if (tiles * (w.in_features / kRoundK) > 0x3FFFFFFFull) return false;
+    if ((w.out_features + kTileW) * bpr + w.flat_block_base > 0xFFFFFFFFull) return false;
+    return w.out_features <= 0x7FFFFFFFull && w.in_features <= 0x7FFFFFFFull;
+}
+
+// `x16` holds the activations as bf16 (half == false) or fp16 (half == true), [rows, in] row-major.
+// `partial` is scratch of nf4_decode_tmem_workspace_bytes(); `counters` are `tiles` zeroed words.
+int32_t launch_nf4_decode_tmem(const DeviceContext& ctx, const WeightView* ws, float* const* ys, uint32_t count,
+                               const void* x16, bool half, uint64_t rows, void* partial, uint32_t* counters,
+                               cudaStream_t stream) {
+    if (count == 0 || count > static_cast<uint32_t>(kMaxWeights)) {
+        return fail(B2_STATUS_INVALID_ARGUMENT, "between one and four weights per launch");
+    }
+    DecodeParams p;
+    DecodeMaps maps;
+    uint64_t tiles = 0;
+    for (uint32_t i = 0; i < static_cast<uint32_t>(kMaxWeights); ++i) {
+        const uint32_t src = i < count ? i : 0;
+        const WeightView& w = ws[src];
+        p.w[i] = w;
+        p.out[i] = ys[src];
+        p.n[i] = static_cast<uint32_t>(w.out_features);
+        if (i < count) tiles += (w.out_features + kTileW - 1) / kTileW;
+        p.tile_end[i] = static_cast<uint32_t>(tiles);
+        if (w.encoding != ws[0].encoding || w.block_size != ws[0].block_size ||
+            w.scale_block_shift != ws[0].scale_block_shift || w.in_features != ws[0].in_features) {
+            return fail(B2_STATUS_INVALID_ARGUMENT, "weights of one launch must share encoding, block sizes and width");
+        }
+        const uint64_t bpr = w.in_features / w.block_size;
+        {
+            const cuuint64_t dims[2] = {w.in_features / 2, w.out_features};
+            const cuuint64_t strides[1] = {w.in_features / 2};
+            const cuuint32_t box[2] = {kRoundK / 2, kTileW};
+            B2_TRY(encode("codes", &maps.codes[i], CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, w.codes, dims, strides, box,
+                          CU_TENSOR_MAP_SWIZZLE_128B));
+        }
+        if (w.encoding == B2_SCALES_FLOAT32) {
+            const cuuint64_t dims[2] = {bpr, w.out_features};
+            const cuuint64_t strides[1] = {bpr * 4};
+            const cuuint32_t box[2] = {4, kTileW};
+            B2_TRY(encode("fp32 scales", &maps.scales[i], CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, w.fp32_scales, dims,
+                          strides, box, CU_TENSOR_MAP_SWIZZLE_NONE));
+            maps.second[i] = maps.scales[i];   // unused for this encoding
+        } else {
+            const cuuint64_t dims[2] = {bpr, w.out_features};
+            const cuuint64_t strides[1] = {bpr};
+            const cuuint32_t box[2] = {16, kTileW};
+            B2_TRY(encode("scale codes", &maps.scales[i], CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, w.scale_codes, dims,
+                          strides, box, CU_TENSOR_MAP_SWIZZLE_NONE));
+            const uint64_t last = (w.flat_block_base + w.out_features * bpr - 1) >> w.scale_block_shift;
+            const cuuint64_t dims2[1] = {last + 1};
+            const cuuint64_t strides2[1] = {0};
+            const cuuint32_t box2[1] = {kSecondBox};
+            B2_TRY(encode("second-level", &maps.second[i], CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 1, w.second_level, dims2,
+                          strides2, box2, CU_TENSOR_MAP_SWIZZLE_NONE));
+        }
+    }
+    p.count = count;
+    p.m = static_cast<uint32_t>(rows);
+    p.k = static_cast<uint32_t>(ws[0].in_features);
+    p.n_pad = rows <= 16 ? 16u : 32u;
+    p.rounds = p.k / kRoundK;
+    p.total_items = static_cast<uint32_t>(tiles) * p.rounds;
+    p.blocks_per_row = static_cast<uint32_t>(ws[0].in_features / ws[0].block_size);
+    p.kshift = ws[0].block_shift - 6u;
+    p.partial = static_cast<float*>(partial);
+    p.counters = counters;
+    p.error = ctx.gemm_error;
+    p.lut = half ? ctx.gemv_lut : ctx.gemm_lut;
+
+    CUtensorMap map_x;
+    {
+        const cuuint64_t dims[2] = {ws[0].in_features, rows};
+        const cuuint64_t strides[1] = {ws[0].in_features * 2};
+        const cuuint32_t box[2] = {64, p.n_pad};
+        B2_TRY(encode("activations", &map_x, half ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16,
+                      2, x16, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B));
+    }
+    static PerDeviceOnce configured;
+    B2_TRY(once_per_device(configured, ctx.device, []() -> int32_t {
+        B2_CUDA_TRY(cudaFuncSetAttribute(nf4_decode_tmem_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         kSmemBytes));
+        B2_CUDA_TRY(cudaFuncSetAttribute(nf4_decode_tmem_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         kSmemBytes));
+        return B2_STATUS_OK;
+    }));
+    cudaLaunchConfig_t config = {};
+    const uint32_t ctas = p.total_items < static_cast<uint32_t>(ctx.sm_count) ? p.total_items
+                                                                               : static_cast<uint32_t>(ctx.sm_count);
+    config.gridDim = dim3(ctas);
+    config.blockDim = dim3(kThreads);
+    config.dynamicSmemBytes = kSmemBytes;
+    config.stream = stream;
+    cudaLaunchAttribute attr[1];
+    static const bool pdl = getenv("B2_DISABLE_PDL") == nullptr;
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attr;
+    config.numAttrs = pdl ? 1 : 0;
+    if (half) {
+        B2_CUDA_TRY(cudaLaunchKernelEx(&config, nf4_decode_tmem_kernel<true>, maps, map_x, p));
+    } else {
+        B2_CUDA_TRY(cudaLaunchKernelEx(&config, nf4_decode_tmem_kernel<false>, maps, map_x, p));
+    }
+    return B2_STATUS_OK;
+}
+
+}  // namespace b2

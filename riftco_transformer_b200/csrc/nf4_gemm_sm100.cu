@@ -521,14 +521,14 @@ int32_t launch_nf4_gemm(const DeviceContext& ctx, const WeightView& w, const flo
 
     CUtensorMap map;
     B2_TRY(make_operand_map(&map, workspace, rows, k));
-    static bool configured = false;
-    if (!configured) {
+    static PerDeviceOnce configured;
+    B2_TRY(once_per_device(configured, ctx.device, []() -> int32_t {
         B2_CUDA_TRY(cudaFuncSetAttribute(nf4_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          kSmemBytes));
         B2_CUDA_TRY(cudaFuncSetAttribute(nf4_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          kSmemBytes));
-        configured = true;
-    }
+        return B2_STATUS_OK;
+    }));
     GemmParams p;
     p.w = w;
     p.out = y;

@@ -459,11 +459,11 @@ int32_t launch_nf4_gemm_tmem_multi(const DeviceContext& ctx, const WeightView* w
                                       strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                                       CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(B2_STATUS_RUNTIME_ERROR, "cuTensorMapEncodeTiled failed (%d)", static_cast<int>(r));
-    static bool configured = false;
-    if (!configured) {
+    static PerDeviceOnce configured;
+    B2_TRY(once_per_device(configured, ctx.device, []() -> int32_t {
         B2_CUDA_TRY(cudaFuncSetAttribute(nf4_gemm_tmem_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
-        configured = true;
-    }
+        return B2_STATUS_OK;
+    }));
     cudaLaunchConfig_t config = {};
     // weight-row tiles vary fastest: CTAs that run together share the activation tile in L2
     config.gridDim = dim3(static_cast<unsigned>(weight_tiles), static_cast<unsigned>((rows + p.tile_t - 1) / p.tile_t),

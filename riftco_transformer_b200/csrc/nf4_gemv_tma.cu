@@ -475,12 +475,15 @@ EncodeTiledFn encode_tiled() {
 template <int MT>
 int32_t max_active_clusters(const DeviceContext& ctx, uint32_t ksplit, uint32_t* out) {
     auto kernel = nf4_gemv_tma_kernel<MT>;
-    static bool configured = false;
-    static int cached[9] = {0};
-    if (!configured) {
+    static PerDeviceOnce configured;                 // per template instance
+    static int cached_all[kMaxDevices][9] = {};      // clusters per cluster size, per device
+    static std::mutex cache_mutex;
+    B2_TRY(once_per_device(configured, ctx.device, [kernel]() -> int32_t {
         B2_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Layout<MT>::kSmemBytes));
-        configured = true;
-    }
+        return B2_STATUS_OK;
+    }));
+    std::lock_guard<std::mutex> lock(cache_mutex);
+    int* cached = cached_all[ctx.device];
     if (cached[ksplit] == 0) {
         cudaLaunchConfig_t config = {};
         config.blockDim = dim3(kThreads);

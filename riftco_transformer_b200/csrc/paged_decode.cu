@@ -590,7 +590,7 @@ size_t paged_decode_workspace_bytes(uint32_t n_seq, uint32_t q_heads, uint32_t h
     return heads * max_seq_len * sizeof(float);
 }
 
-int32_t launch_paged_decode(const DeviceContext&, const PagedDecodeArgs& a, void* workspace,
+int32_t launch_paged_decode(const DeviceContext& ctx, const PagedDecodeArgs& a, void* workspace,
                             size_t workspace_bytes, cudaStream_t stream) {
     const size_t need = paged_decode_workspace_bytes(a.n_seq, a.q_heads, a.head_width, a.block_size,
                                                      a.max_seq_len);
@@ -607,14 +607,14 @@ int32_t launch_paged_decode(const DeviceContext&, const PagedDecodeArgs& a, void
         static const char* impl = getenv("B2_ATTN_IMPL");   // "ldg" selects the register-load kernel
         const bool bulk = impl == nullptr || strcmp(impl, "ldg") != 0;
         if (bulk) {
-            static bool configured = false;
-            if (!configured) {
+            static PerDeviceOnce configured;
+            B2_TRY(once_per_device(configured, ctx.device, []() -> int32_t {
                 B2_CUDA_TRY(cudaFuncSetAttribute(paged_decode_bulk_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBulkSmemBytes));
                 B2_CUDA_TRY(cudaFuncSetAttribute(paged_decode_bulk_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBulkSmemBytes));
                 B2_CUDA_TRY(cudaFuncSetAttribute(paged_decode_bulk_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBulkSmemBytes));
                 B2_CUDA_TRY(cudaFuncSetAttribute(paged_decode_bulk_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBulkSmemBytes));
-                configured = true;
-            }
+                return B2_STATUS_OK;
+            }));
             switch (a.q_heads / a.kv_heads) {
             case 1: paged_decode_bulk_kernel<1><<<grid, kFastWarps * 32, kBulkSmemBytes, stream>>>(a, partials, splits); break;
             case 2: paged_decode_bulk_kernel<2><<<grid, kFastWarps * 32, kBulkSmemBytes, stream>>>(a, partials, splits); break;
@@ -669,7 +669,7 @@ bool g_scratch_ready[kMaxScratchDevices];
 // In host code `g_static_scratch` names a host-side shadow, not device memory;
 // the device address has to be asked for once per device, with that device
 // current. Nothing here allocates.
-int32_t static_scratch_pointer(void** out) {
+int32_t static_scratch_pointer(void** out, int* device_out) {
     int device = -1;
     cudaError_t err = cudaGetDevice(&device);
     if (err != cudaSuccess || device < 0 || device >= kMaxScratchDevices) {
@@ -696,6 +696,7 @@ int32_t static_scratch_pointer(void** out) {
         g_scratch_ready[device] = true;
     }
     *out = g_scratch_address[device];
+    *device_out = device;
     return B2_STATUS_OK;
 }
 
@@ -709,21 +710,9 @@ extern "C" int32_t b2_paged_decode_attention_noalloc(
     uint32_t max_seq_len, uint32_t* status, void* stream) {
     using namespace b2;
     clear_error();
-    if (n_seq == 0 || q_heads == 0 || kv_heads == 0 || head_width == 0 || block_size == 0 ||
-        physical_blocks == 0 || max_seq_len == 0 || max_blocks == 0) {
-        return fail(B2_STATUS_INVALID_ARGUMENT, "paged decode attention dimensions must be positive");
-    }
-    if (physical_blocks - 1 > 0xFFFFFFFFull) {
-        return fail(B2_STATUS_OVERFLOW, "paged decode attention physical block IDs exceed uint32_t");
-    }
-    if (q_heads % kv_heads != 0) {
-        return fail(B2_STATUS_INVALID_ARGUMENT,
-                    "paged decode attention query heads must be a multiple of KV heads");
-    }
-    if ((static_cast<uint64_t>(max_seq_len) - 1) / block_size + 1 > max_blocks) {
-        return fail(B2_STATUS_INVALID_ARGUMENT,
-                    "paged decode attention block table size does not match the sequence");
-    }
+    // the same dimension rules as b2_paged_decode_attention
+    B2_TRY(check_paged_dims(n_seq, q_heads, kv_heads, head_width, block_size, physical_blocks, max_blocks,
+                            max_seq_len));
     if (q == nullptr || k_pages == nullptr || v_pages == nullptr || block_tables == nullptr ||
         seq_lens == nullptr || ctx == nullptr) {
         return fail(B2_STATUS_INVALID_ARGUMENT, "paged decode attention pointers must not be null");
@@ -740,10 +729,10 @@ extern "C" int32_t b2_paged_decode_attention_noalloc(
                     need, kStaticScratchBytes);
     }
     void* scratch = nullptr;
-    B2_TRY(static_scratch_pointer(&scratch));
+    DeviceContext here;   // only the device index is read by the launcher
+    B2_TRY(static_scratch_pointer(&scratch, &here.device));
     PagedDecodeArgs args{q, k_pages, v_pages, block_tables, seq_lens, ctx,
                          n_seq, q_heads, kv_heads, head_width, block_size, max_blocks, max_seq_len,
                          physical_blocks, status};
-    DeviceContext unused;  // the launcher does not read it
-    return launch_paged_decode(unused, args, scratch, kStaticScratchBytes, static_cast<cudaStream_t>(stream));
+    return launch_paged_decode(here, args, scratch, kStaticScratchBytes, static_cast<cudaStream_t>(stream));
 }

@@ -74,3 +74,32 @@ def seeded_cases():
     V = rng.standard_normal((P, H, bs, d)).astype(np.float32)
     tab = rng.permutation(P)[: -(-n // bs)].astype(np.uint32)
     return dict(W1=W1, X1=X1, dY1=dY1, q=q, K=K, V=V, table=tab, seq_len=n)
+
+
+ROPE_POSITIONS = (0, 15, 16, 301, 2048)
+
+
+def decode_glue_inputs() -> dict:
+    """Seeded inputs of the decode-step primitives (RMSNorm, split-half RoPE, SiLU / SwiGLU hidden
+    state, greedy choice, token-by-token paged cache), including the special values the reference
+    treats explicitly: silu(-inf) = -0.0, large magnitudes on both sigmoid branches, ties and a
+    maximum in the last slot for the greedy choice."""
+    rng = np.random.default_rng(20250)
+    special = np.array([np.inf, -np.inf, 0.0, -0.0, 88.0, -88.0, 100.0, -100.0, -104.0, 1e-30, -1e-30], np.float32)
+    gate = np.concatenate([(rng.standard_normal(2037) * 6).astype(np.float32), special])
+    greedy = rng.standard_normal((6, 97)).astype(np.float32)
+    greedy[1, 40] = greedy[1, 70] = greedy[1].max() + 1.0     # tie: the first index wins
+    greedy[2, 96] = greedy[2].max() + 1.0                      # maximum in the last slot
+    greedy[3, 0] = greedy[3].max() + 1.0                       # maximum in the first slot
+    greedy[4, :] = 0.5                                         # all equal
+    return {
+        "rms_x": (rng.standard_normal((6, 1024)) * np.array([1, 10, 1e-3, 1e3, 1, 1])[:, None]).astype(np.float32),
+        "rms_scale": (1.0 + 0.1 * rng.standard_normal(1024)).astype(np.float32),
+        "rope_x": rng.standard_normal((2, 3, 1, 128)).astype(np.float32),
+        "silu_gate": gate,
+        "silu_up": rng.standard_normal(gate.size).astype(np.float32),
+        "greedy_logits": greedy,
+        "cache_q": rng.standard_normal((18, 2, 8)).astype(np.float32),
+        "cache_k": rng.standard_normal((18, 2, 8)).astype(np.float32),
+        "cache_v": rng.standard_normal((18, 2, 8)).astype(np.float32),
+    }

@@ -43,8 +43,8 @@ def payload_arrays(prefix: str, w: oracle.Nf4Weight) -> dict:
     return d
 
 
-from cases import (aligned_input, aligned_upstream, aligned_weight, edge_input,  # noqa: E402
-                   edge_upstream, edge_weight, paged_fixture, seeded_cases)
+from cases import (ROPE_POSITIONS, aligned_input, aligned_upstream, aligned_weight,  # noqa: E402
+                   decode_glue_inputs, edge_input, edge_upstream, edge_weight, paged_fixture, seeded_cases)
 
 
 def main() -> None:
@@ -126,6 +126,27 @@ def main() -> None:
     # One GQA-shaped sequence (32 query / 8 KV heads) through the unmodified operator.
     out["gqa_context"] = ref.paged_decode_gqa(c["q"], c["K"], c["V"], c["table"][None, :],
                                               np.array([c["seq_len"]], np.uint32))
+
+    # -- decode-step primitives around the hot path (reference entry points in oracle/ref_bridge.cpp)
+    g = decode_glue_inputs()
+    out["glue_rms"] = ref.rms_norm(g["rms_x"], g["rms_scale"], 1e-5)
+    for pos in ROPE_POSITIONS:
+        out[f"glue_rope_{pos}"] = ref.rope(g["rope_x"], pos, 1e4)
+    out["glue_silu"] = ref.silu_mul(g["silu_gate"])
+    out["glue_swiglu_hidden"] = ref.silu_mul(g["silu_gate"], g["silu_up"])
+    out["glue_greedy"] = np.array([ref.greedy(row) for row in g["greedy_logits"]], np.int64)
+    # one sequence fed token by token through the reference's paged KV cache (page 4, 5 pages): k is
+    # rotated by the reference first, so this pins RoPE + page append + paged attention end to end
+    steps = g["cache_q"].shape[0]
+    k_rot = np.stack([ref.rope(g["cache_k"][t][None, :, None, :], t, 1e4)[0, :, 0, :] for t in range(steps)])
+    q_rot = np.stack([ref.rope(g["cache_q"][t][None, :, None, :], t, 1e4)[0, :, 0, :] for t in range(steps)])
+    out["glue_cache_context"] = ref.paged_cache_decode(q_rot, k_rot, g["cache_v"], 4, 5)
+
+    # -- canonical packed model state written by the reference (RTNF4S1) ---------------------
+    for name, scale_block in (("rtnf4_dq", 32), ("rtnf4_f32", 0)):
+        stream, dump = ref.packed_model_fixture(32, 16, 64, 2, 2, 128, 64, scale_block, 7)
+        out[f"{name}_stream"] = stream
+        out[f"{name}_fields"] = dump
 
     np.savez_compressed(OUT / "reference_vectors.npz", **out)
     size = (OUT / "reference_vectors.npz").stat().st_size

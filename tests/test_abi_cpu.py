@@ -49,3 +49,25 @@ def test_no_cpu_fallback_without_a_device():
     status = lib.b2_paged_decode_attention(None, None, None, None, None, None, 1, 1, 1, 1, 1, 1, 1, 1,
                                            None, 0, None, None)
     assert status == _lib.STATUS_BACKEND_UNAVAILABLE
+
+
+def test_attention_status_word_mapping():
+    """b2_attention_status_result: what a synchronous caller reports for the device status word
+    (no GPU involved). A page copy whose bounded wait gave up must not pass as success."""
+    from riftco_transformer_b200 import _lib
+    from riftco_transformer_b200.backend import DomainError, _check
+    lib = _lib.lib
+    assert lib.b2_attention_status_result(0) == _lib.STATUS_OK
+    assert lib.b2_attention_status_result(_lib.ATTN_STATUS_BAD_BLOCK) == _lib.STATUS_OUT_OF_RANGE
+    assert b"invalid block" in lib.b2_last_error()
+    assert lib.b2_attention_status_result(_lib.ATTN_STATUS_NAN_OR_POS_INF) == _lib.STATUS_DOMAIN_ERROR
+    assert lib.b2_attention_status_result(_lib.ATTN_STATUS_ALL_NEG_INF) == _lib.STATUS_DOMAIN_ERROR
+    assert lib.b2_attention_status_result(_lib.ATTN_STATUS_TIMEOUT) == _lib.STATUS_RUNTIME_ERROR
+    assert b"did not complete" in lib.b2_last_error()
+    assert lib.b2_attention_status_result(0x40) == _lib.STATUS_RUNTIME_ERROR          # an unknown bit
+    # a bad block outranks the rest, as the host validation of the reference runs first
+    assert lib.b2_attention_status_result(_lib.ATTN_STATUS_BAD_BLOCK | _lib.ATTN_STATUS_TIMEOUT) == _lib.STATUS_OUT_OF_RANGE
+    with pytest.raises(RuntimeError):
+        _check(lib.b2_attention_status_result(_lib.ATTN_STATUS_TIMEOUT))
+    with pytest.raises(DomainError):
+        _check(lib.b2_attention_status_result(_lib.ATTN_STATUS_ALL_NEG_INF))

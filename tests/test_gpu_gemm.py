@@ -142,7 +142,9 @@ def test_input_backward_config3_sampled_rows(b2, port):
 @pytest.mark.parametrize("rows", [4, 32, 200])
 def test_multi_weight_forward_matches_single_calls(b2, port, rows):
     """b2_nf4_linear_forward_multi: q / k / v style projections of one input. Up to 16 rows it is a
-    loop of single calls; above, one conversion and one launch - bit-identical to the single calls."""
+    loop of single calls; above, one conversion and one launch. The products are those of the single
+    calls; only the order of the FP32 partial sums may differ (which CTA sums which slice of the
+    contraction depends on the tiles of the whole launch)."""
     import ctypes as C
 
     from riftco_transformer_b200 import _lib
@@ -164,7 +166,7 @@ def test_multi_weight_forward_matches_single_calls(b2, port, rows):
     for host, single, out in zip(hosts, singles, outs):
         got = out.cpu().numpy()
         assert rel_l2(got, port.linear_forward(host, x.cpu().numpy())) <= GEMM_TOL
-        assert (got.view(np.uint32) == single.view(np.uint32)).all()
+        assert rel_l2(got, single) <= 1e-5
     # an output used twice is a caller error, reported by the single-call path
     ptrs[1] = ptrs[0]
     with pytest.raises(ValueError):

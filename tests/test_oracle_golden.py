@@ -146,3 +146,57 @@ def test_port_matches_reference_library_on_random_shapes(port):
             assert (bits(port.dequantize(a)) == bits(ref.dequantize(b))).all()
             assert (bits(port.linear_forward(a, X)) == bits(ref.linear_forward(b, X))).all()
             assert (bits(port.linear_input_backward(a, dY)) == bits(ref.linear_input_backward(b, dY))).all()
+
+
+# ---- decode-step primitives: the restatements against vectors written by the reference ----------
+
+def test_rms_norm_matches_the_reference_bit_for_bit(port, golden):
+    g = cases.decode_glue_inputs()
+    got = port.rms_norm(g["rms_x"], g["rms_scale"], 1e-5)
+    assert (bits(got) == bits(golden["glue_rms"])).all()
+
+
+@pytest.mark.parametrize("position", cases.ROPE_POSITIONS)
+def test_split_half_rope_matches_the_reference_bit_for_bit(golden, position):
+    # the angle is evaluated in double and rounded once to FP32, like rotary_cos_sin
+    # (src/model/rotary_embedding.cpp:64-81); numpy's double pow / cos / sin agree with libm here
+    from oracle import decode_ref
+    g = cases.decode_glue_inputs()
+    got = decode_ref.rotate(g["rope_x"][:, :, 0, :], position, 1e4)
+    assert (bits(got) == bits(golden[f"glue_rope_{position}"][:, :, 0, :])).all()
+
+
+def test_silu_and_swiglu_hidden_match_the_reference_bit_for_bit(port, golden):
+    g = cases.decode_glue_inputs()
+    silu = port.silu_mul(g["silu_gate"])
+    assert (bits(silu) == bits(golden["glue_silu"])).all()
+    minus_inf = np.flatnonzero(np.isneginf(g["silu_gate"]))
+    assert minus_inf.size == 1 and bits(silu[minus_inf])[0] == 0x80000000      # silu(-inf) = -0.0
+    hidden = port.silu_mul(g["silu_gate"], g["silu_up"])
+    assert (bits(hidden) == bits(golden["glue_swiglu_hidden"])).all()
+
+
+def test_greedy_choice_takes_the_first_maximum(port, golden):
+    g = cases.decode_glue_inputs()
+    got = [port.greedy(row) for row in g["greedy_logits"]]
+    assert got == golden["glue_greedy"].tolist()
+    assert got[1] == 40 and got[2] == 96 and got[3] == 0 and got[4] == 0
+
+
+def test_rope_page_append_and_paged_attention_match_the_reference_cache(port, golden):
+    """One sequence token by token: rotate q and k at the token's position, write k / v into slot
+    position % page of page table[position / page], attend over everything appended so far. The
+    expected contexts come from the reference's PagedKvCachePool (append_and_attend)."""
+    from oracle import decode_ref
+    g = cases.decode_glue_inputs()
+    steps, heads, width = g["cache_q"].shape
+    page, pages = 4, 5
+    table = np.array([3, 0, 4, 1, 2], np.uint32)           # any permutation: results do not depend on it
+    K = np.full((pages, heads, page, width), 777.0, np.float32)
+    V = np.full((pages, heads, page, width), -777.0, np.float32)
+    for t in range(steps):
+        q = decode_ref.rotate(g["cache_q"][t], t, 1e4)
+        K[table[t // page], :, t % page] = decode_ref.rotate(g["cache_k"][t], t, 1e4)
+        V[table[t // page], :, t % page] = g["cache_v"][t]
+        ctx = port.paged_decode(q, K, V, table, t + 1)
+        assert (bits(ctx) == bits(golden["glue_cache_context"][t])).all(), t

@@ -2,8 +2,11 @@
 written with the layout of packed_model_state_bytes
 (src/c_api/model_state.cpp:27-113), and the malformed-stream cases of
 parse_packed_model_state (model_state.cpp:165-297) with the reference's
-messages. No golden stream of the reference is available for this format, so
-parity of the layout rests on restating the serializer field by field."""
+messages. Two streams written by the reference's own serializer for a small
+quantised DecoderOnlyTransformer (tests/golden/make_golden.py) pin the layout:
+the parser must locate every array of every weight exactly where the
+reference's packed_linear_weight_state() says it is, and this repository's
+writer must reproduce the reference's bytes."""
 import struct
 
 import numpy as np
@@ -111,3 +114,66 @@ def test_row_shards_are_slices_of_the_stream(payloads):
         assert part.flat_block_base == rows.start * blocks_per_row
     with pytest.raises(ValueError):
         rtnf4.load_weight(stream, entry, device="cpu", rank=0, world=5)     # 48 rows do not divide by 5
+
+
+def _fields(dump: np.ndarray):
+    """Weights of the field-by-field dump written beside each reference stream
+    (ref_packed_model_fixture, oracle/ref_bridge.cpp)."""
+    raw = dump.tobytes()
+    count = struct.unpack_from("<Q", raw, 0)[0]
+    at, out = 8, []
+    for _ in range(count):
+        o, i, block, n_codes, n_fp32, n_sc, n_second, sbs, offset_bits = struct.unpack_from("<9Q", raw, at)
+        at += 72
+        w = {"shape": (o, i), "block": block, "scale_block": sbs,
+             "offset": np.array([offset_bits & 0xFFFFFFFF], np.uint32).view(np.float32)[0]}
+        w["codes"] = np.frombuffer(raw, np.uint8, n_codes, at)
+        at += n_codes
+        w["fp32"] = np.frombuffer(raw, "<f4", n_fp32, at)
+        at += 4 * n_fp32
+        w["scale_codes"] = np.frombuffer(raw, np.uint8, n_sc, at)
+        at += n_sc
+        w["second"] = np.frombuffer(raw, "<f4", n_second, at)
+        at += 4 * n_second
+        out.append(w)
+    assert at == len(raw)
+    return out
+
+
+@pytest.mark.parametrize("name,double_quantized", [("rtnf4_dq", True), ("rtnf4_f32", False)])
+def test_streams_written_by_the_reference(golden, name, double_quantized):
+    import oracle
+    from riftco_transformer_b200 import rtnf4
+    stream = golden[f"{name}_stream"]
+    want = _fields(golden[f"{name}_fields"])
+    entries = rtnf4.index(stream)
+    # two blocks of six projections (q, k, v, o, expand, project) and the LM head
+    assert len(entries) == len(want) == 13
+    payloads = []
+    for e, w in zip(entries, want):
+        assert (e.out_features, e.in_features, e.block_size) == (*w["shape"], w["block"])
+        assert bool(e.double_quantized) == double_quantized
+        assert np.array_equal(stream[e.codes_offset:e.codes_offset + e.n_codes], w["codes"])
+        if double_quantized:
+            assert e.n_fp32_scales == 0 and e.scale_block_size == w["scale_block"]
+            assert np.float32(e.offset).view(np.uint32) == np.float32(w["offset"]).view(np.uint32)
+            assert np.array_equal(stream[e.scale_codes_offset:e.scale_codes_offset + e.n_scale_codes], w["scale_codes"])
+            second = stream[e.second_offset:e.second_offset + 4 * e.n_second].view("<f4")
+            assert np.array_equal(second.view(np.uint32), w["second"].view(np.uint32))
+            payloads.append(oracle.Nf4Weight(w["codes"], *w["shape"], w["block"], scale_codes=w["scale_codes"],
+                                             second_level=w["second"], scale_block_size=w["scale_block"],
+                                             offset=float(w["offset"])))
+        else:
+            assert e.n_scale_codes == 0 and e.n_second == 0 and e.offset == 0.0
+            scales = stream[e.fp32_scales_offset:e.fp32_scales_offset + 4 * e.n_fp32_scales].view("<f4")
+            assert np.array_equal(scales.view(np.uint32), w["fp32"].view(np.uint32))
+            payloads.append(oracle.Nf4Weight(w["codes"], *w["shape"], w["block"], fp32_scales=w["fp32"]))
+        # a weight loaded from the stream is the reference's payload (CPU device, whole and row-sharded)
+        whole = rtnf4.load_weight(stream, e, device="cpu")
+        assert np.array_equal(whole.codes.numpy(), w["codes"])
+        half = rtnf4.load_weight(stream, e, device="cpu", rank=1, world=2)
+        rows = e.out_features // 2
+        assert np.array_equal(half.codes.numpy(), w["codes"][rows * e.in_features // 2:])
+        assert half.flat_block_base == rows * e.in_features // e.block_size
+    # the writer of this repository reproduces the reference's stream byte for byte
+    assert rtnf4.dumps(payloads) == stream.tobytes()
