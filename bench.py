@@ -14,11 +14,20 @@ far more than L2, so no flush is needed between steps.
 
 At N = 1 the line also carries the per-kernel measurements the headline is made
 of (`kernels`): the NF4 GEMV decode sweep of the baseline (M in {1,4,16} on
-4096->4096, 4096->14336, 14336->4096) and paged GQA decode attention on 64
-sequences of length U[512, 8192], each as achieved HBM GB/s of its algorithmic
-bytes against the measured copy bandwidth.
+4096->4096, 4096->14336, 14336->4096, both scale encodings), the four batch-32
+linears of one decoder layer, paged GQA decode attention on 64 sequences of
+length U[512, 8192] - each as achieved HBM GB/s of its algorithmic bytes against
+the measured copy bandwidth - and the prefill GEMM / QLoRA input-backward of the
+baseline (M = 4096, both layers, both encodings) as TFLOP/s against the measured
+dense bf16 peak.
 
 Prints ONE JSON line (rank 0).
+
+    python bench.py --only linear --rows 32 --out 14336 --inp 4096 --launches 3
+    python bench.py --only attention --seqs 8 --context 4096 --launches 3
+
+run a few launches of one kernel on synthetic data and print their mean device
+time (for profilers and quick checks; not the JSON line).
 """
 from __future__ import annotations
 
@@ -131,8 +140,6 @@ LAYER_EQUIVALENTS = N_LAYERS + LM_HEAD[0] * LM_HEAD[1] / WEIGHTS_PER_LAYER
 def cpu_layer_sample():
     """Host payloads and inputs of ONE layer for ONE sequence at context 2049
     (synthetic, same distributions as the GPU arm)."""
-    import ctypes as C
-
     import numpy as np
     import oracle  # checker only; never on the product path
 
@@ -144,14 +151,7 @@ def cpu_layer_sample():
         blocks = n // BLOCK
         codes = rng.integers(0, 256, n // 2, dtype=np.uint8)
         scales = np.maximum(0.0479 + 0.0066 * rng.standard_normal(blocks), 0.02).astype(np.float32)
-        qs = np.zeros(blocks, np.uint8)
-        second = np.zeros(-(-blocks // SCALE_BLOCK), np.float32)
-        off = C.c_float(0)
-        port.lib.orc_double_quantize_scales(oracle._ptr(scales, oracle._f32p), blocks, SCALE_BLOCK,
-                                            oracle._ptr(qs, oracle._u8p), oracle._ptr(second, oracle._f32p),
-                                            C.byref(off))
-        weights.append(oracle.Nf4Weight(codes, o, i, BLOCK, scale_codes=qs, second_level=second,
-                                        scale_block_size=SCALE_BLOCK, offset=float(off.value)))
+        weights.append(port.double_quantize_payload(codes, scales, o, i, BLOCK, SCALE_BLOCK))
     seq = CONTEXT + 1
     pages = -(-seq // 16)
     k = rng.standard_normal((pages, 8, 16, 128)).astype(np.float32)
@@ -174,6 +174,46 @@ def cpu_layer_seconds(sample) -> tuple[float, str]:
         impl.linear_forward(w, x, threads=1)
     impl.paged_decode_gqa(q, k, v, table[None, :], np.array([seq], np.uint32), threads=1)
     return time.perf_counter() - t0, impl.kind
+
+
+def cpu_full_cases() -> dict:
+    """The reference's CPU loops on the baseline's kernel-level configurations that finish in
+    seconds, run IN FULL on one thread: config 1 (X[64,512] x W[1024,512], FP32 scales), the
+    M = 1 case of config 2 on all three layers (double-quantised scales) and one config-4
+    sequence (context 4352 = the mean of U[512, 8192], 32 query / 8 KV heads)."""
+    import numpy as np
+    import oracle
+
+    impl = oracle.ref() if oracle.ref_available() else oracle.port()
+    port = oracle.port()
+    rng = np.random.default_rng(4242)
+    out = {"kind": impl.kind, "threads": 1}
+    W = (rng.standard_normal((1024, 512)) * 0.02).astype(np.float32)
+    w1 = port.quantize_nf4(W, 64)
+    x1 = rng.standard_normal((64, 512)).astype(np.float32)
+    t0 = time.perf_counter()
+    impl.linear_forward(w1, x1, threads=1)
+    out["c1_64x512_to_1024_ms"] = round(1e3 * (time.perf_counter() - t0), 3)
+    for o, i in LAYERS:
+        n = o * i
+        blocks = n // BLOCK
+        codes = rng.integers(0, 256, n // 2, dtype=np.uint8)
+        scales = np.maximum(0.0479 + 0.0066 * rng.standard_normal(blocks), 0.02).astype(np.float32)
+        w = port.double_quantize_payload(codes, scales, o, i, BLOCK, SCALE_BLOCK)
+        x = rng.standard_normal((1, i)).astype(np.float32)
+        t0 = time.perf_counter()
+        impl.linear_forward(w, x, threads=1)
+        out[f"c2_M1_{i}to{o}_ms"] = round(1e3 * (time.perf_counter() - t0), 3)
+    seq = 4352
+    pages = -(-seq // 16)
+    k = rng.standard_normal((pages, 8, 16, 128)).astype(np.float32)
+    v = rng.standard_normal((pages, 8, 16, 128)).astype(np.float32)
+    table = rng.permutation(pages).astype(np.uint32)
+    q = rng.standard_normal((1, 32, 128)).astype(np.float32)
+    t0 = time.perf_counter()
+    impl.paged_decode_gqa(q, k, v, table[None, :], np.array([seq], np.uint32), threads=1)
+    out["c4_one_sequence_ctx4352_ms"] = round(1e3 * (time.perf_counter() - t0), 3)
+    return out
 
 
 def run_reference(args) -> None:
@@ -209,21 +249,24 @@ def run_reference(args) -> None:
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
         "warmup": warm, "ms_per_step": 1e3 * total / steps, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": workload_config(args.gpus),
-        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": kind,
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": kind, "extrapolated": True,
                          "sample": "per step: one layer (7 packed linears + paged attention) of one sequence at "
                                    "context 2049, on every host thread concurrently; scaled by 32 layers + LM head"},
+        "extrapolated": True,
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line))
 
 
-NCU_ATTENTION_READ_RATIO = 1.0007   # dram__bytes_read.sum / algorithmic bytes, profiles/paged_decode_bulk_8x4096.md
+# dram__bytes_read.sum / algorithmic K+V bytes in an ncu capture of the bulk attention kernel (8 sequences x 4096)
+NCU_ATTENTION_READ_RATIO = 1.0007
 
 
 def workload_config(world: int) -> dict:
     return {"workload": "7b_decode_step", "layers": N_LAYERS, "d_model": 4096, "q_heads": 32, "kv_heads": 8,
             "head_dim": 128, "ffn": 14336, "vocab": 32000, "batch": BATCH, "context": CONTEXT,
-            "weights": "nf4 block 64, double-quantised scales (u8 + f32 per 256)", "kv": "f32 pages of 16",
+            "weights": "N(0, 0.02^2) quantised to nf4 block 64, double-quantised scales (u8 + f32 per 256); every "
+                       "rank shards the same global payload by output rows", "kv": "f32 pages of 16",
             "sharding": f"output rows / kv heads over {world} gpu(s); activations joined at layer boundaries by the "
                         "library's peer-store all-gather kernel over NVLink (B2_PEER_GATHER=0: NCCL all-gather)",
             "l2": "each step reads ~21 GB of weights and KV, far larger than L2"}
@@ -254,40 +297,107 @@ def time_graph(torch, fn, reps: int, inner: int) -> float:
     return a.elapsed_time(b) * 1e3 / (reps * inner)
 
 
-def kernel_measurements(torch, b2, synth, peaks) -> dict:
-    """Per-kernel HBM rooflines on the baseline's kernel-level configurations."""
+def scale_payload_bytes(out_f: int, in_f: int, double_quantized: bool) -> int:
+    blocks = out_f * in_f // BLOCK
+    return blocks + 4 * (-(-blocks // SCALE_BLOCK)) + 4 if double_quantized else 4 * blocks
+
+
+def kernel_measurements(torch, b2, synth, peaks, device_index: int) -> dict:
+    """Per-kernel rooflines on the baseline's kernel-level configurations (N = 1 only)."""
+    import ctypes as C
+
     import numpy as np
+    from riftco_transformer_b200 import _lib
+    from riftco_transformer_b200._lib import lib
+    from riftco_transformer_b200.backend import _check, _stream_ptr
     out = {}
-    # NF4 GEMV decode sweep: enough resident instances per layer to exceed 2x L2.
     g = torch.Generator(device="cuda")
     g.manual_seed(5678)
+
+    # ---- config 2: NF4 GEMV decode sweep; enough resident instances per layer to exceed 2x L2 ----
     sweep = {}
-    for li, (o, i) in enumerate(LAYERS):
-        n_copies = max(3, -(-2 * L2_BYTES // packed_bytes(o, i)))
-        ws = [synth.packed_weight(o, i, seed=4321 + 97 * li + c) for c in range(n_copies)]
-        for m in BATCHES:
-            x = torch.randn((m, i), device="cuda", generator=g)
-            y = torch.empty((m, o), device="cuda")
+    for dq in (True, False):
+        for li, (o, i) in enumerate(LAYERS):
+            algorithmic = o * i // 2 + scale_payload_bytes(o, i, dq)
+            n_copies = max(3, -(-2 * L2_BYTES // algorithmic))
+            ws = [synth.packed_weight(o, i, seed=4321 + 97 * li + c, double_quantized=dq) for c in range(n_copies)]
+            for m in BATCHES:
+                x = torch.randn((m, i), device="cuda", generator=g)
+                y = torch.empty((m, o), device="cuda")
 
-            def launch(ws=ws, x=x, y=y, m=m, i=i, o=o):
-                for w in ws:
-                    b2.dispatch_quantized_linear_forward(x, w, y, (m, i, o, BLOCK))
+                def launch(ws=ws, x=x, y=y, m=m, i=i, o=o):
+                    for w in ws:
+                        b2.dispatch_quantized_linear_forward(x, w, y, (m, i, o, BLOCK))
 
-            us = time_graph(torch, launch, 20, n_copies)
-            gbps = packed_bytes(o, i) / us / 1e3
-            sweep[f"M{m}_{i}to{o}"] = {"us": round(us, 3), "gbps": round(gbps, 1),
-                                       "frac": round(gbps / peaks["hbm_gbs"], 4)}
-        del ws
+                us = time_graph(torch, launch, 20, n_copies)
+                gbps = algorithmic / us / 1e3
+                sweep[f"M{m}_{i}to{o}_{'dq' if dq else 'f32'}"] = {
+                    "us": round(us, 3), "gbps": round(gbps, 1), "frac": round(gbps / peaks["hbm_gbs"], 4)}
+            del ws
     out["nf4_gemv_sweep"] = {"kernel": "nf4_gemv_tma_kernel", "bound": "hbm", "unit": "GB/s",
-                             "bytes": "packed codes + scale payload per launch", "cases": sweep}
-    # Paged GQA decode attention: 64 sequences, context U[512, 8192].
+                             "bytes": "packed codes + scale payload per launch (dq: u8 scale codes + f32 per 256 "
+                                      "blocks; f32: one f32 scale per block)", "cases": sweep}
+
+    # ---- the four batch-32 linears of one decoder layer, as the decode step issues them ----
+    groups = {"q+k+v": [(4096, 4096), (1024, 4096), (1024, 4096)], "o": [(4096, 4096)],
+              "gate+up": [(14336, 4096), (14336, 4096)], "down": [(4096, 14336)]}
+    b32 = {}
+    for name, shapes in groups.items():
+        algorithmic = sum(o * i // 2 + scale_payload_bytes(o, i, True) for o, i in shapes)
+        n_sets = max(3, -(-2 * L2_BYTES // algorithmic))
+        sets = [[synth.packed_weight(o, i, seed=911 + 13 * s + j) for j, (o, i) in enumerate(shapes)]
+                for s in range(n_sets)]
+        x16 = torch.randn((BATCH, shapes[0][1]), device="cuda", generator=g).to(torch.bfloat16)
+        ys = [torch.empty((BATCH, o), device="cuda") for o, _ in shapes]
+        ptrs = (C.c_void_p * len(ys))(*[y.data_ptr() for y in ys])
+        structs = [(_lib.Nf4WeightStruct * len(ws))(*[w.struct() for w in ws]) for ws in sets]
+
+        def launch(structs=structs, n=len(ys), x16=x16, ptrs=ptrs):
+            for st in structs:
+                _check(lib.b2_nf4_linear_forward_multi_bf16(st, n, x16.data_ptr(), ptrs, BATCH, _stream_ptr(None)))
+
+        us = time_graph(torch, launch, 10, n_sets)
+        gbps = algorithmic / us / 1e3
+        b32[name] = {"us": round(us, 3), "bytes": algorithmic, "gbps": round(gbps, 1),
+                     "frac": round(gbps / peaks["hbm_gbs"], 4)}
+        del sets, structs
+    out["nf4_linear_b32"] = {"kernel": "nf4_decode_tmem_kernel", "bound": "hbm", "unit": "GB/s", "rows": BATCH,
+                             "input": "bf16 activations handed over by the producing kernel, one launch per group",
+                             "cases": b32}
+
+    # ---- config 3: prefill GEMM and QLoRA input-backward, M = 4096, both layers, both encodings ----
+    rows = 4096
+    c3 = {}
+    with ClockSampler(device_index) as sampler:
+        for o, i in [(14336, 4096), (4096, 14336)]:
+            x = torch.randn((rows, i), device="cuda", generator=g)
+            dy = torch.randn((rows, o), device="cuda", generator=g) * 0.01
+            y = torch.empty((rows, o), device="cuda")
+            dx = torch.empty((rows, i), device="cuda")
+            for dq in (True, False):
+                w = synth.packed_weight(o, i, seed=31337 + o, double_quantized=dq)
+                dims = (rows, i, o, BLOCK)
+                for kind, fn in (("forward", lambda: b2.dispatch_quantized_linear_forward(x, w, y, dims)),
+                                 ("input_backward", lambda: b2.dispatch_quantized_linear_input_backward(dy, w, dx, dims))):
+                    us = min(time_graph(torch, fn, 5, 1) for _ in range(3))   # activations + output exceed L2
+                    tflops = 2.0 * rows * o * i / us / 1e6
+                    c3[f"{kind}_{i}to{o}_{'dq' if dq else 'f32'}"] = {
+                        "us": round(us, 1), "tflops": round(tflops, 1),
+                        "frac": round(tflops / peaks["bf16_tflops"], 4)}
+            del x, dy, y, dx
+        torch.cuda.synchronize()
+    out["nf4_gemm_c3"] = {"kernel": "nf4_gemm_tmem_kernel (forward), nf4_dequant_transpose + bf16_gemm (input-backward)",
+                          "bound": "tensor", "unit": "TFLOP/s", "rows": rows, "peak": peaks["bf16_tflops"],
+                          "peak_kind": "dense bf16, burst", "flops": "2 * rows * out * in per call",
+                          "clocks": sampler.summary(), "cases": c3}
+
+    # ---- config 4: paged GQA decode attention, 64 sequences, context U[512, 8192] ----
     lens = np.random.default_rng(91011).integers(512, 8193, size=64)
     pool, tables, dlens = synth.paged_cache(lens, 8)
     q = torch.randn((64, 32, 128), device="cuda", generator=g)
     ctx = torch.empty_like(q)
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
     mx = int(lens.max())
-    from riftco_transformer_b200._lib import lib
     ws = torch.empty(max(lib.b2_paged_decode_workspace_bytes(64, 32, 128, 16, mx), 16), dtype=torch.uint8,
                      device="cuda")
     us = time_graph(torch, lambda: b2.paged_decode_attention(q, pool, tables, dlens, ctx, mx, status=status,
@@ -298,6 +408,68 @@ def kernel_measurements(torch, b2, synth, peaks) -> dict:
                               "frac": round(kv_bytes / us / 1e3 / peaks["hbm_gbs"], 4),
                               "status": int(status.item())}
     return out
+
+
+# ---- single-kernel runs for profilers --------------------------------------------------------------
+
+def probe_linear(args) -> None:
+    """`--launches` calls of the packed-NF4 linear, each on its own weight instance."""
+    import torch
+
+    import riftco_transformer_b200 as b2
+    from riftco_transformer_b200 import synth
+    rows, out_f, in_f = args.rows, args.out, args.inp
+    weights = [synth.packed_weight(out_f, in_f, seed=1000 + i, double_quantized=not args.fp32_scales)
+               for i in range(args.launches)]
+    shape = (rows, in_f, out_f, weights[0].block_size)
+    if args.backward:   # dX[rows, in] = dY[rows, out] * W
+        x = torch.randn((rows, out_f), device="cuda") * 0.01
+        y = torch.empty((rows, in_f), device="cuda")
+        call = b2.dispatch_quantized_linear_input_backward
+    else:               # Y[rows, out] = X[rows, in] * W^T
+        x = torch.randn((rows, in_f), device="cuda")
+        y = torch.empty((rows, out_f), device="cuda")
+        call = b2.dispatch_quantized_linear_forward
+    call(x, weights[0], y, shape)   # library set-up outside the timed launches
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for w in weights:
+        call(x, w, y, shape)
+    stop.record()
+    torch.cuda.synchronize()
+    b2.check_device_errors()
+    us = start.elapsed_time(stop) * 1e3 / args.launches
+    payload = weights[0].resident_payload_bytes()
+    print(f"linear {'input-backward' if args.backward else 'forward'} rows={rows} {in_f}->{out_f}: {us:.2f} us/launch "
+          f"(eager, launch gaps included), {payload} B of packed weight per launch = {payload / us / 1e3:.1f} GB/s, "
+          f"{2.0 * rows * out_f * in_f / us / 1e6:.1f} TFLOP/s")
+
+
+def probe_attention(args) -> None:
+    """`--launches` calls of paged decode attention for a batch on its own KV pool."""
+    import torch
+
+    import riftco_transformer_b200 as b2
+    from riftco_transformer_b200 import synth
+    pool, tables, lens = synth.paged_cache([args.context] * args.seqs, args.kv_heads, 128, 16, seed=7)
+    q = torch.randn((args.seqs, args.q_heads, 128), device="cuda")
+    ctx = torch.empty_like(q)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    b2.paged_decode_attention(q, pool, tables, lens, ctx, args.context, status=status)
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(args.launches):
+        b2.paged_decode_attention(q, pool, tables, lens, ctx, args.context, status=status)
+    stop.record()
+    torch.cuda.synchronize()
+    b2.check_device_errors()
+    us = start.elapsed_time(stop) * 1e3 / args.launches
+    kv_bytes = int(lens.sum().item()) * args.kv_heads * 128 * 4 * 2
+    print(f"attention seqs={args.seqs} context={args.context} heads={args.q_heads}/{args.kv_heads}: "
+          f"{us:.2f} us/launch, {kv_bytes} B of K/V per launch = {kv_bytes / us / 1e3:.1f} GB/s, "
+          f"status {int(status.item())}")
 
 
 def run_b200(args) -> None:
@@ -410,9 +582,9 @@ def run_b200(args) -> None:
     attn_us = max_over_ranks(time_graph(torch, attention_all_layers, 5, cfg.layers))
     kv_bytes_launch = inputs["kv_bytes_per_step"] / cfg.layers
     achieved = kv_bytes_launch / attn_us / 1e3
-    # DRAM traffic per launch: the ncu capture of a smaller case of this kernel
-    # (profiles/paged_decode_bulk_8x4096.md) read 1.0007 x its algorithmic K/V bytes and wrote its
-    # split partials and context; both scale with the tokens read, so they are scaled to this launch.
+    # DRAM traffic per launch: an ncu capture of a smaller case of this kernel (8 sequences x 4096
+    # tokens) read 1.0007 x its algorithmic K/V bytes and wrote its split partials and context; both
+    # scale with the tokens read, so they are scaled to this launch.
     splits = -(-(CONTEXT + 1) // 256)
     hq_local = cfg.q_heads // world
     traffic = int(kv_bytes_launch * NCU_ATTENTION_READ_RATIO) + BATCH * hq_local * (splits * 130 + 128) * 4
@@ -429,25 +601,53 @@ def run_b200(args) -> None:
     if int(step.status.item()) != 0:
         raise SystemExit(f"decode step reported status bits {int(step.status.item())} (bad block table or token id)")
 
+    # Correctness witness. The synthetic model is a function of the seed alone (every rank shards the
+    # same global payload), so the step's next tokens and logits can be compared across world sizes:
+    # the line carries a CRC of the next tokens, and with more than one rank, rank 0 rebuilds the whole
+    # model on its own GPU, runs the step unsharded and compares (token ids must agree; logits differ
+    # only by the order of FP32 partial sums, which depends on how many tiles a shard has).
+    import zlib
+    step.step(tokens, positions, seq_lens)
+    torch.cuda.synchronize()
+    check = {"next_tokens_crc32": zlib.crc32(step.next_tokens.cpu().numpy().tobytes())}
+    if world > 1:
+        logits_n = (step.logits if step.logits is not None else step.logits_local).clone()
+        tokens_n = step.next_tokens.clone()
+        barrier()
+        if rank == 0:
+            single, single_in = synthetic_step(cfg, BATCH, CONTEXT, 0, 1, device, None)
+            tok1, logits1 = single.step(single_in["tokens"], single_in["positions"], single_in["seq_lens"])
+            torch.cuda.synchronize()
+            diff = (logits_n.double() - logits1.double()).norm() / logits1.double().norm()
+            check.update({"single_gpu_next_tokens_crc32": zlib.crc32(tok1.cpu().numpy().tobytes()),
+                          "tokens_equal_single_gpu": bool((tok1 == tokens_n).all().item()),
+                          "logits_rel_l2_vs_single_gpu": float(diff.item())})
+            del single, single_in, tok1, logits1
+            torch.cuda.empty_cache()
+        barrier()
+
     kernels = None
     cpu_baseline = None
     if rank == 0 and world == 1:
         del graph
         if not args.no_kernels:
-            kernels = kernel_measurements(torch, b2, synth, peaks)
+            kernels = kernel_measurements(torch, b2, synth, peaks, local_rank)
         if not args.no_cpu_baseline:
             sec, kind = cpu_layer_seconds(cpu_layer_sample())
             cpu_baseline = {"value": 1.0 / (sec * LAYER_EQUIVALENTS), "unit": UNIT, "cores": 1, "kind": kind,
+                            "extrapolated": True,
                             "sample": "one layer (7 packed linears + paged attention) of one sequence at context "
-                                      "2049 on one thread, scaled by 32 layers + LM head"}
+                                      "2049 on one thread, scaled by 32 layers + LM head",
+                            "full_cases": cpu_full_cases()}
 
     if rank == 0:
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
-            "scaling": "strong", "vs_baseline": None, "dtype": "f32 (batch-32 linears: bf16 tcgen05 operands, f32 accumulate; the GEMV sweep: f16 mma.sync operands, f32 accumulate)",
+            "scaling": "strong", "vs_baseline": None, "dtype": "f32 (batch-32 linears: bf16 tcgen05 operands, f32 accumulate; the GEMV sweep: f16 operands, f32 accumulate)",
             "data": "synthetic", "config": workload_config(world), "roofline": roofline,
-            "step_roofline": step_roofline, "kernels": kernels, "cpu_baseline": cpu_baseline, "e2e": e2e,
+            "step_roofline": step_roofline, "check": check, "kernels": kernels, "cpu_baseline": cpu_baseline,
+            "e2e": e2e,
             "clocks": clocks, "gpu_launches": launches_per_step * args.steps,
         }
         print(json.dumps(line))
@@ -468,8 +668,25 @@ def main() -> None:
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-kernels", action="store_true", help="skip the per-kernel sweep measurements")
+    ap.add_argument("--only", default="all", choices=["all", "linear", "attention"],
+                    help="linear / attention: a few launches of one kernel (for profilers), no JSON line")
+    ap.add_argument("--rows", type=int, default=1)
+    ap.add_argument("--out", type=int, default=14336)
+    ap.add_argument("--inp", type=int, default=4096)
+    ap.add_argument("--launches", type=int, default=3)
+    ap.add_argument("--fp32-scales", action="store_true")
+    ap.add_argument("--backward", action="store_true", help="--only linear: the input-backward dX = dY * W")
+    ap.add_argument("--seqs", type=int, default=8)
+    ap.add_argument("--context", type=int, default=4096)
+    ap.add_argument("--q-heads", type=int, default=32)
+    ap.add_argument("--kv-heads", type=int, default=8)
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.only != "all":
+        import riftco_transformer_b200 as b2
+        if not b2.is_available():
+            raise SystemExit("riftco_b200: " + b2.unavailability_reason())
+        (probe_linear if args.only == "linear" else probe_attention)(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_b200(args)

@@ -159,6 +159,22 @@ class Port:
         return Nf4Weight(w.codes, w.out_features, w.in_features, block_size, scale_codes=qs,
                          second_level=second, scale_block_size=scale_block_size, offset=float(off.value))
 
+    def double_quantize_payload(self, codes, scales, out_features: int, in_features: int, block_size: int = 64,
+                                scale_block_size: int = 256) -> Nf4Weight:
+        """A double-quantised payload from packed codes and FP32 block scales already in hand (synthetic
+        payloads drawn in the packed domain): only the scales go through double_quantize_scales."""
+        s = _f32(scales)
+        qs = np.zeros(len(s), np.uint8)
+        second = np.zeros(-(-len(s) // scale_block_size), np.float32)
+        off = C.c_float(0)
+        rc = self.lib.orc_double_quantize_scales(
+            _ptr(s, _f32p), len(s), scale_block_size, _ptr(qs, _u8p), _ptr(second, _f32p), C.byref(off))
+        if rc:
+            raise OverflowError("NF4 scale mean exceeds the FP32 double-quantization range")
+        return Nf4Weight(np.ascontiguousarray(codes, np.uint8), out_features, in_features, block_size,
+                         scale_codes=qs, second_level=second, scale_block_size=scale_block_size,
+                         offset=float(off.value))
+
     def _cw(self, w: Nf4Weight) -> _OrcWeight:
         return _OrcWeight(
             _ptr(w.codes, _u8p), _ptr(w.fp32_scales, _f32p), _ptr(w.scale_codes, _u8p),

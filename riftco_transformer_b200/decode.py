@@ -380,27 +380,39 @@ WHOLE_ON_EVERY_RANK = ("wo", "w_down")   # see DecodeStep: replicated rather tha
 
 
 def synthetic_step(cfg: DecoderConfig, batch: int, context: int, rank: int = 0, world: int = 1, device="cuda",
-                   group=None, seed: int = 1234) -> tuple[DecodeStep, dict]:
-    """A DecodeStep over seeded synthetic shards for benchmarking: packed weights
-    drawn in the packed domain at the shard's own shape, KV pools ~ N(0,1) holding
-    `context` tokens per sequence, permuted block tables shared by all layers."""
+                   group=None, seed: int = 1234, whole=None, quantized: bool = True) -> tuple[DecodeStep, dict]:
+    """A DecodeStep over a seeded synthetic model for benchmarking and cross-checks.
+
+    Every rank builds the SAME global model from the seed - weights ~ N(0, 0.02^2) quantised to NF4
+    (block 64, double-quantised scales) by synth.quantized_weight - and takes its row shards as
+    views of the global payload (PackedNf4Weight.row_shard: no re-quantisation, the parent's
+    second-level scale groups, flat_block_base != 0). KV pools ~ N(0,1) hold `context` tokens per
+    sequence and are seeded per (layer, global KV head), so the heads a rank owns carry the same
+    values whatever the world size; block tables are one permutation shared by all layers. The
+    step's logits are therefore the same function of the seed at every world size, up to the order
+    of FP32 partial sums inside the linears.
+
+    `whole`: names of the layer weights every rank keeps whole (default: WHOLE_ON_EVERY_RANK when
+    world > 1). `quantized=False` draws the payloads directly in the packed domain (cheaper)."""
     from . import synth
     cfg.shard_check(world)
+    if whole is None:
+        whole = WHOLE_ON_EVERY_RANK if world > 1 else ()
     ops = CudaOps(device, group)
     shapes = weight_shapes(cfg)
+    make = synth.quantized_weight if quantized else synth.packed_weight
+
+    def shard(name, w):
+        return w if (world == 1 or name in whole) else w.row_shard(rank, world)
+
     weights: dict = {}
     for layer in range(cfg.layers):
         weights[layer] = {}
         for i, name in enumerate(LAYER_WEIGHTS):
             out_f, in_f = shapes[name]
-            if name in WHOLE_ON_EVERY_RANK:   # the same weight on every rank
-                weights[layer][name] = synth.packed_weight(out_f, in_f, device=device,
-                                                           seed=seed + 1000 * layer + 10 * i)
-            else:
-                weights[layer][name] = synth.packed_weight(out_f // world, in_f, device=device,
-                                                           seed=seed + 1000 * layer + 10 * i + rank)
+            weights[layer][name] = shard(name, make(out_f, in_f, device=device, seed=seed + 1000 * layer + 10 * i))
     out_f, in_f = shapes["lm_head"]
-    weights["lm_head"] = synth.packed_weight(out_f // world, in_f, device=device, seed=seed + 999983 + rank)
+    weights["lm_head"] = shard("lm_head", make(out_f, in_f, device=device, seed=seed + 999983))
     g = torch.Generator(device=device)
     g.manual_seed(seed + 7)
     norms = {layer: {"attn": 1.0 + 0.1 * torch.randn(cfg.d_model, device=device, generator=g),
@@ -414,15 +426,22 @@ def synthetic_step(cfg: DecoderConfig, batch: int, context: int, rank: int = 0, 
     total = blocks * batch
     perm = torch.randperm(total, device=device, generator=g).to(torch.int32)
     tables = perm.view(batch, blocks).contiguous()
+    tokens = torch.randint(0, cfg.vocab, (batch,), device=device, generator=g, dtype=torch.int32)
     pools = []
     hkv = cfg.kv_heads // world
     for layer in range(cfg.layers):
-        shape = (total, hkv, cfg.block_size, cfg.head_dim)
-        pools.append(PagedKvPool(torch.randn(shape, device=device, generator=g),
-                                 torch.randn(shape, device=device, generator=g)))
+        pages = []
+        for which in range(2):   # K, V
+            pool = torch.empty((total, hkv, cfg.block_size, cfg.head_dim), device=device)
+            for j in range(hkv):
+                head = rank * hkv + j
+                g.manual_seed(seed + 104729 * (layer + 1) + 31 * head + which)
+                pool[:, j] = torch.randn((total, cfg.block_size, cfg.head_dim), device=device, generator=g)
+            pages.append(pool)
+        pools.append(PagedKvPool(pages[0], pages[1]))
     step = DecodeStep(cfg, ops, weights, norms, embedding, pools, tables, batch, context + 1, rank, world)
     inputs = {
-        "tokens": torch.randint(0, cfg.vocab, (batch,), device=device, generator=g, dtype=torch.int32),
+        "tokens": tokens,
         "positions": torch.full((batch,), context, dtype=torch.int32, device=device),
         "seq_lens": torch.full((batch,), context + 1, dtype=torch.int32, device=device),
         "kv_bytes_per_step": cfg.layers * batch * (context + 1) * hkv * cfg.head_dim * 4 * 2,

@@ -171,3 +171,51 @@ def test_multi_weight_forward_matches_single_calls(b2, port, rows):
     ptrs[1] = ptrs[0]
     with pytest.raises(ValueError):
         _check(lib.b2_nf4_linear_forward_multi(structs, len(weights), x.data_ptr(), ptrs, rows, None, 0, None))
+
+
+def _device_quantized(b2, out_f, in_f, dq, seed):
+    """W ~ N(0, 0.02^2) quantised on the device by the torch restatement of the reference encoder
+    (held to the oracle bit for bit in test_gpu_parity.py), plus its host payload for the oracle."""
+    from riftco_transformer_b200 import synth
+    w = synth.quantized_weight(out_f, in_f, seed=seed, double_quantized=dq)
+    return w, synth.host_payload(w)
+
+
+@pytest.mark.parametrize("out_f,in_f,dq", [
+    (14336, 4096, False),   # 4096 -> 14336, FP32 scales
+    (4096, 14336, True),    # 14336 -> 4096, double-quantised
+    (4096, 14336, False),   # 14336 -> 4096, FP32 scales
+])
+def test_gemm_config3_remaining_forward_cases(b2, port, out_f, in_f, dq):
+    """Baseline configuration 3, forward, the cases test_gemm_config3_sampled_rows does not run:
+    M = 4096 tokens, checked on 24 sampled rows against the FP32 oracle."""
+    w, host = _device_quantized(b2, out_f, in_f, dq, seed=out_f + 7 * dq)
+    g = torch.Generator(device="cuda")
+    g.manual_seed(99)
+    x = torch.randn((4096, in_f), device="cuda", generator=g)
+    y = forward(b2, w, x)
+    idx = np.r_[0:8, 2000:2008, 4088:4096]
+    want = port.linear_forward(host, x[idx].cpu().numpy())
+    assert np.isfinite(y).all()
+    assert rel_l2(y[idx], want) <= GEMM_TOL
+    for j, r in enumerate(idx):
+        assert rel_l2(y[r], want[j]) <= 2 * GEMM_TOL
+
+
+@pytest.mark.parametrize("out_f,in_f,dq", [
+    (14336, 4096, False),   # dY [4096, 14336] -> dX [4096, 4096], FP32 scales
+    (4096, 14336, True),    # dY [4096, 4096] -> dX [4096, 14336], double-quantised
+    (4096, 14336, False),   # the same with FP32 scales
+])
+def test_input_backward_config3_remaining_cases(b2, port, out_f, in_f, dq):
+    """Baseline configuration 3, input-backward, the cases the sampled-row test above does not run:
+    dY ~ N(0, 1e-4), checked on 12 sampled rows."""
+    w, host = _device_quantized(b2, out_f, in_f, dq, seed=3 * out_f + dq)
+    g = torch.Generator(device="cuda")
+    g.manual_seed(98)
+    dy = torch.randn((4096, out_f), device="cuda", generator=g) * 0.01
+    dx = backward(b2, w, dy)
+    idx = np.r_[0:4, 2047:2051, 4092:4096]
+    want = port.linear_input_backward(host, dy[idx].cpu().numpy())
+    assert np.isfinite(dx).all()
+    assert rel_l2(dx[idx], want) <= GEMM_TOL

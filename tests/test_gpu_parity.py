@@ -330,6 +330,80 @@ def test_paged_decode_config4_sample(b2, port):
     assert rel_l2(got, port.paged_decode_gqa(q, K, V, tables, lens)) <= ATTN_TOL
 
 
+def test_paged_decode_config4_all_64_sequences(b2, port):
+    """The baseline's paged-decode configuration in full: 64 sequences with context U[512, 8192],
+    32 query / 8 KV heads, permuted pages (2.2 GB of K/V), every sequence against the oracle."""
+    rng = np.random.default_rng(91011)
+    hq, hkv, d, bs = 32, 8, 128, 16
+    lens = rng.integers(512, 8193, size=64).astype(np.uint32)
+    blocks = -(-lens.astype(np.int64) // bs)
+    P = int(blocks.sum())
+    perm = rng.permutation(P)
+    tables = np.zeros((64, int(blocks.max())), np.uint32)
+    at = 0
+    for s, nb in enumerate(blocks):
+        tables[s, :nb] = perm[at:at + nb]
+        at += nb
+    K = rng.standard_normal((P, hkv, bs, d), dtype=np.float32)
+    V = rng.standard_normal((P, hkv, bs, d), dtype=np.float32)
+    q = rng.standard_normal((64, hq, d), dtype=np.float32)
+    got, status = run_gqa(b2, q, K, V, tables, lens)
+    assert status == 0
+    want = port.paged_decode_gqa(q, K, V, tables, lens, threads=0)
+    assert rel_l2(got, want) <= ATTN_TOL
+    for s in range(64):
+        assert rel_l2(got[s], want[s]) <= ATTN_TOL, f"sequence {s} (len {lens[s]})"
+
+
+def test_device_encoder_matches_the_oracle_bit_for_bit(b2, port):
+    """synth.quantize - the reference's NF4 encoder restated in torch, which produces the benchmark's
+    weights on the device - against the C restatement of pack_nf4 / double_quantize_scales: same
+    codes (ties to the lower index, zero blocks -> scale 0 / code 7), same scales, same offset."""
+    from riftco_transformer_b200 import synth
+    rng = np.random.default_rng(31)
+    W = (rng.standard_normal((384, 1024)) * 0.02).astype(np.float32)
+    W[5, 64:128] = 0.0                      # a zero block
+    W[7, :64] = np.float32(0.02) * port.codebook()[np.arange(64) % 16] * np.float32(1.0)   # exact codebook points
+    W[9, 0:2] = (0.5, -0.5)                 # a value halfway between two levels after scaling
+    for dq in (True, False):
+        dev_w = synth.quantize(torch.from_numpy(W).cuda(), double_quantized=dq)
+        host = port.quantize_nf4_double_quantized(W, 64, 256) if dq else port.quantize_nf4(W, 64)
+        assert np.array_equal(dev_w.codes.cpu().numpy(), host.codes)
+        if dq:
+            assert np.array_equal(dev_w.primary.cpu().numpy(), host.scale_codes)
+            assert (bits(dev_w.secondary.cpu().numpy()) == bits(host.second_level)).all()
+            assert np.float32(dev_w.offset) == np.float32(host.offset)
+        else:
+            assert (bits(dev_w.primary.cpu().numpy()) == bits(host.fp32_scales)).all()
+        assert (bits(b2.dequantize(dev_w).cpu().numpy()) == bits(port.dequantize(host))).all()
+
+
+def test_rope_append_refuses_a_position_past_the_table(b2):
+    """A position whose page index lies past the sequence's table row is treated like a bad block:
+    the status bit is set and no page is written (the neighbouring row is never read)."""
+    from riftco_transformer_b200._lib import lib
+    from riftco_transformer_b200.backend import _check
+    heads, d, bs = 2, 128, 16
+    q = torch.randn((2, heads, d), device="cuda")
+    k = torch.randn((2, heads, d), device="cuda")
+    v = torch.randn((2, heads, d), device="cuda")
+    K = torch.full((4, heads, bs, d), 7.0, device="cuda")
+    V = torch.full((4, heads, bs, d), -7.0, device="cuda")
+    tables = torch.tensor([[0, 1], [2, 3]], dtype=torch.int32, device="cuda")
+    positions = torch.tensor([32, 5], dtype=torch.int32, device="cuda")    # 32 / 16 = 2: past a row of 2 entries
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    _check(lib.b2_rope_append_kv(q.data_ptr(), k.data_ptr(), v.data_ptr(), positions.data_ptr(), tables.data_ptr(),
+                                 K.data_ptr(), V.data_ptr(), 2, heads, heads, d, bs, 4, 2, 1e4, status.data_ptr(), None))
+    torch.cuda.synchronize()
+    assert int(status.item()) & 4
+    # sequence 1 appended normally (page 2, slot 5); nothing else changed, in particular not page 2's
+    # slot 0, which is where sequence 0 would have landed through its neighbour's table row
+    assert torch.equal(V[2, :, 5], v[1])
+    untouched = torch.ones((4, bs), dtype=torch.bool, device="cuda")
+    untouched[2, 5] = False
+    assert (V.permute(0, 2, 1, 3)[untouched] == -7.0).all() and (K.permute(0, 2, 1, 3)[untouched] == 7.0).all()
+
+
 def test_paged_decode_flags_bad_block_without_touching_it(b2):
     q = torch.randn((1, 8, 128), device="cuda")
     pool = b2.PagedKvPool(torch.randn((2, 8, 16, 128), device="cuda"), torch.randn((2, 8, 16, 128), device="cuda"))
@@ -343,6 +417,37 @@ def test_paged_decode_flags_bad_block_without_touching_it(b2):
 
 
 # ---- host-buffer seam -----------------------------------------------------------------
+
+def test_host_seam_from_two_threads_at_once(b2, port, c2_weights):
+    """The host-buffer forms share one staging buffer per device; concurrent callers must not see
+    each other's data (each call holds the device's lock from its first copy to its last)."""
+    import threading
+    host = c2_weights[(4096, 4096)]
+    w = b2.PackedNf4Weight.from_host(host)
+    rng = np.random.default_rng(12)
+    xs = [rng.standard_normal((4, 4096)).astype(np.float32) for _ in range(2)]
+    wants = [forward(b2, w, dev(x)) for x in xs]
+    errors = []
+
+    def worker(i):
+        try:
+            torch.cuda.set_device(0)
+            y = np.empty((4, 4096), np.float32)
+            for _ in range(40):
+                b2.host_quantized_linear_forward(xs[i], w, y, 4)
+                if not (bits(y) == bits(wants[i])).all():
+                    errors.append(f"thread {i}: output of another call")
+                    return
+        except Exception as e:   # noqa: BLE001
+            errors.append(repr(e))
+
+    threads = [threading.Thread(target=worker, args=(i,)) for i in range(2)]
+    for th in threads:
+        th.start()
+    for th in threads:
+        th.join()
+    assert not errors, errors
+
 
 def test_host_seam_matches_device_path(b2, port, c2_weights):
     host = c2_weights[(4096, 4096)]
