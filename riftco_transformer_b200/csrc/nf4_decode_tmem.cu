@@ -56,17 +56,22 @@ constexpr int kMaxWStages = 6;
 constexpr int kXStages = 4;                                   // activation stages
 constexpr int kAStages = 3;                                   // tensor-memory stages of the expanded weights
 constexpr int kLutBytes = 65536;                              // 256 rows of 256 bytes (lane l at byte 4*l)
-constexpr int kLowHeader = 2048;                              // barriers + scale-code factor table
+constexpr int kLowHeader = 3072;                              // barriers, scale-code factor table, slot lists
 constexpr int kExpandWarps = 16;
 constexpr int kFirstExpandWarp = 3;
 constexpr int kThreads = (kFirstExpandWarp + kExpandWarps) * 32;   // 608
 constexpr int kExpandThreads = kExpandWarps * 32;
+constexpr int kSetWarps = kExpandWarps / 2;                   // the expansion warps form two sets that alternate items
+constexpr int kSetThreads = kSetWarps * 32;
 constexpr int kSmemBytes = 232448;                            // all of it: the ring takes what the rest leaves
 constexpr uint32_t kTmemColumns = 512;
 constexpr uint32_t kAccColumns = 128;                         // accumulator region (kMaxTokens used)
 constexpr uint32_t kStageColumns = kRoundK / 2;               // 128 columns: one round of 16-bit pairs
 constexpr int kMaxWeights = 4;
 constexpr int kPartialFloats = kMaxTokens * kTileW;           // one partial tile
+// Polls before a wait gives up (a fraction of a second; every wait starts after the dependency wait
+// of a programmatic launch, so a healthy one lasts microseconds).
+constexpr uint32_t kPollBudget = 400000u;
 
 struct DecodeMaps {
     CUtensorMap codes[kMaxWeights];     // u8 [out, in/2], box {128, 128}, 128-byte swizzle
@@ -100,9 +105,10 @@ struct Barriers {
     uint64_t a_full[kAStages];
     uint64_t done[kAStages];        // tcgen05.commit: the round's MMAs have read the tensor-memory stage
     uint64_t acc_full;
+    uint64_t acc_empty;             // the epilogue has read the accumulator of the segment before
     uint32_t tmem_base;
     uint32_t abort;
-    uint32_t last_flag;
+    uint32_t last_flag[2];          // per expansion set
 };
 static_assert(sizeof(Barriers) <= 256, "barrier block");
 
@@ -204,8 +210,12 @@ __device__ __forceinline__ bool elect_one() {
     asm volatile("{ .reg .pred p; elect.sync _|p, 0xFFFFFFFF; selp.u32 %0, 1, 0, p; }" : "=r"(pred));
     return pred != 0;
 }
+// Named barriers: 1 for all expansion warps, 2 + set for the warps of one set.
 __device__ __forceinline__ void expand_barrier() {
     asm volatile("bar.sync 1, %0;" ::"n"(kExpandThreads) : "memory");
+}
+__device__ __forceinline__ void set_barrier(uint32_t set) {
+    asm volatile("bar.sync %0, %1;" ::"r"(2u + set), "n"(kSetThreads) : "memory");
 }
 
 // Where the pieces of shared memory lie for this CTA: a pure function of the dynamic allocation's
@@ -281,7 +291,7 @@ nf4_decode_tmem_kernel(const __grid_constant__ DecodeMaps maps, const __grid_con
     uint8_t* low = smem_raw + (plan.low32 - raw32);
     Barriers& bars = *reinterpret_cast<Barriers*>(low);
     float* s_factor = reinterpret_cast<float*>(low + 256);   // scale code -> (code - 128) / 127
-    uint32_t* s_slots = reinterpret_cast<uint32_t*>(low + 1280);   // partial-tile slots of one output tile (<= 160)
+    uint32_t* s_slots = reinterpret_cast<uint32_t*>(low + 1280);   // partial-tile slots of one output tile (<= 160), per set
     volatile uint32_t* abort = &bars.abort;
 
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
@@ -302,19 +312,20 @@ nf4_decode_tmem_kernel(const __grid_constant__ DecodeMaps maps, const __grid_con
         if (lane == 0) {
             for (uint32_t s = 0; s < n_stages; ++s) {
                 mbar_init(&bars.w_full[s], 1);
-                mbar_init(&bars.w_empty[s], kExpandWarps);
+                mbar_init(&bars.w_empty[s], kSetWarps);
             }
             for (int s = 0; s < kXStages; ++s) {
                 mbar_init(&bars.x_full[s], 1);
                 mbar_init(&bars.x_empty[s], 1);
             }
             for (int s = 0; s < kAStages; ++s) {
-                mbar_init(&bars.a_full[s], kExpandWarps);
+                mbar_init(&bars.a_full[s], kSetWarps);
                 mbar_init(&bars.done[s], 1);
             }
             mbar_init(&bars.acc_full, 1);
+            mbar_init(&bars.acc_empty, kSetWarps);
             bars.abort = 0;
-            bars.last_flag = 0;
+            bars.last_flag[0] = bars.last_flag[1] = 0;
             mbar_fence_init();
         }
         __syncwarp();
@@ -368,9 +379,12 @@ nf4_decode_tmem_kernel(const __grid_constant__ DecodeMaps maps, const __grid_con
 
     if (warp == 0) {
         // ---- weight producer ----
+        // (its first ring fill is out; every later wait depends on warps that start after the
+        // dependency wait, so it joins that wait and its own barrier waits stay short)
+        pdl_wait();
         uint32_t s = w_issued == n_stages ? 0u : w_issued, round_trip = w_issued == n_stages ? 1u : 0u;
         for (uint32_t it = item_begin + w_issued; it < item_end; ++it) {
-            mbar_wait(&bars.w_empty[s], (round_trip - 1u) & 1u, abort);
+            mbar_wait(&bars.w_empty[s], (round_trip - 1u) & 1u, abort, kPollBudget);
             if (elect_one()) issue_weights(it, s);
             __syncwarp();
             if (++s == n_stages) {
@@ -383,7 +397,7 @@ nf4_decode_tmem_kernel(const __grid_constant__ DecodeMaps maps, const __grid_con
         pdl_wait();
         uint32_t s = 0, trip = 0, rho = item_begin % R;
         for (uint32_t it = item_begin; it < item_end; ++it) {
-            if (trip > 0) mbar_wait(&bars.x_empty[s], (trip - 1u) & 1u, abort);
+            if (trip > 0) mbar_wait(&bars.x_empty[s], (trip - 1u) & 1u, abort, kPollBudget);
             if (elect_one()) {
                 mbar_expect_tx(&bars.x_full[s], plan.x_stage_bytes);
                 const uint32_t dst = plan.x32 + s * plan.x_stage_bytes;
@@ -402,15 +416,19 @@ nf4_decode_tmem_kernel(const __grid_constant__ DecodeMaps maps, const __grid_con
         }
     } else if (warp == 1) {
         // ---- MMA issuer: sixteen K16 steps per round behind one wait, one commit per round ----
+        pdl_wait();   // nothing it waits for can happen earlier
         const uint32_t idesc = idesc_16bit(kHalf, kTileW, p.n_pad);
         const uint64_t dx0 = umma_desc_k_major_sw128(plan.x32);
         const uint32_t x_stage16 = plan.x_stage_bytes >> 4, kb16 = (p.n_pad * 128u) >> 4;
-        uint32_t s = 0, trip = 0, xs = 0, x_trip = 0, rho = item_begin % R;
+        uint32_t s = 0, trip = 0, xs = 0, x_trip = 0, rho = item_begin % R, seg = 0;
         for (uint32_t it = item_begin; it < item_end; ++it) {
             const bool first = it == item_begin || rho == 0u;
             const bool last = it + 1u == item_end || rho + 1u == R;
-            mbar_wait(&bars.a_full[s], trip & 1u, abort);
-            mbar_wait(&bars.x_full[xs], x_trip & 1u, abort);
+            // a new segment overwrites the accumulator: the epilogue of the one before must have read it
+            if (first && seg > 0) mbar_wait(&bars.acc_empty, (seg - 1u) & 1u, abort, kPollBudget);
+            if (last) ++seg;
+            mbar_wait(&bars.a_full[s], trip & 1u, abort, kPollBudget);
+            mbar_wait(&bars.x_full[xs], x_trip & 1u, abort, kPollBudget);
             tcgen05_fence_after_sync();
             if (elect_one()) {
                 const uint64_t dx_s = dx0 + xs * x_stage16;
@@ -439,64 +457,51 @@ nf4_decode_tmem_kernel(const __grid_constant__ DecodeMaps maps, const __grid_con
             }
         }
     } else {
-        // ---- expansion warps: thread = (weight row, k-block of the round) ----
-        pdl_wait();   // their epilogue writes caller memory
+        // ---- expansion warps ----
+        // Two sets of eight warps alternate items (set 0 takes the CTA's items 0, 2, 4, ..., set 1
+        // the others), so while one set waits for its tensor-memory stores the other is looking
+        // bytes up. Inside a set, thread (row, half h) expands k-blocks 2h and 2h+1 of the item:
+        // 64 packed bytes, in two passes of 32 through the same registers.
+        // Expansion reads only the immutable weights, so it starts before the dependency wait of a
+        // programmatic launch and runs up to three items ahead; the wait comes before the first
+        // epilogue, which is the first thing here to touch memory an earlier kernel may write.
+        bool dependency_waited = false;
         const uint32_t e = warp - kFirstExpandWarp;
-        const uint32_t g = e >> 2;                    // k-block of every round this warp expands
+        const uint32_t set = e >> 3;
+        const uint32_t h = (e >> 2) & 1u;
         const uint32_t quarter = warp & 3u;           // the TMEM lanes this warp may touch
         const uint32_t row = quarter * 32u + lane;    // weight row of the tile = TMEM lane
         const uint32_t lut_lane = plan.lut32 | (lane * 4u);
         const uint32_t lane_addr = (quarter * 32u) << 16;
-        // byte offsets of this thread's two 16-byte chunks inside a swizzled [128 x 128 B] box
-        const uint32_t code_off0 = row * 128u + (((2u * g) ^ (row & 7u)) << 4);
-        const uint32_t code_off1 = row * 128u + (((2u * g + 1u) ^ (row & 7u)) << 4);
+        const uint32_t factor32 = plan.low32 + 256u;  // scale code -> factor table (shared address)
         const uint32_t sshift = p.w[0].scale_block_shift;
-        uint32_t ws = 0, as = 0, a_trip = 0, w_trip = 0, seg = 0;
+        // byte offsets of this thread's four 16-byte chunks inside a swizzled [128 x 128 B] box
+        uint32_t code_off[4];
+#pragma unroll
+        for (uint32_t c = 0; c < 4u; ++c) code_off[c] = row * 128u + (((4u * h + c) ^ (row & 7u)) << 4);
+
+        const uint32_t n_items = item_end - item_begin;
+        uint32_t ws = set, w_trip = 0;                 // ring slot / trip of this set's current item
+        uint32_t as = set, a_trip = 0;                 // tensor-memory stage / trip
         TileRef tref = {0u, 0u, 0u};
         float dq_offset = 0.0f;
-        uint32_t fbase_tile = 0;   // flat index of the first scale block of the tile's first row
-        uint32_t fbase_row = 0;    // ... of this thread's row
-        float norm = 1.0f, inv_norm = 1.0f;   // fp16 operands: the row's values are expanded as w / norm
+        uint32_t fbase_tile = 0, fbase_row = 0;        // flat index of the first scale block of the tile / of this row
         bool live = false;
+        float inv_norm = 1.0f, norm = 1.0f;
+        uint32_t stage32 = 0;
+        uint32_t acc_seen = 0;     // phases of acc_full this set has seen complete
         uint32_t v[32];
 
-        // Expands this thread's 64 weights of item (tile, rho) into v: waits for the ring slot, reads
-        // its 32 packed bytes and its scale, looks the bytes up, releases the slot.
-        auto expand = [&](uint32_t tile, uint32_t rho, bool new_tile, bool seg_begins) {
-            if (new_tile) {
-                tref = locate_tile(p, tile);
-                const WeightView& w = p.w[tref.wi];
-                dq_offset = w.offset;
-                fbase_tile = static_cast<uint32_t>(w.flat_block_base) + tref.n0 * p.blocks_per_row;
-                fbase_row = fbase_tile + row * p.blocks_per_row;
-                live = tref.n0 + row < tref.n_out;
-            }
-            const uint32_t stage32 = w_stage_addr(plan, ws);
-            mbar_wait(&bars.w_full[ws], w_trip & 1u, abort);
-            const uint4 c0 = lds_u4(stage32 + code_off0);
-            const uint4 c1 = lds_u4(stage32 + code_off1);
-            // Decoded scale of block `blk` of this row, from the raw values in the ring slot.
-            const uint32_t blk0 = (4u * rho) >> p.kshift;
-            auto block_scale = [&](uint32_t blk) -> float {
-                if (fp32_scales) return lds_f32(stage32 + kScaleOff + row * 16u + (blk - (blk0 & ~3u)) * 4u);
-                const uint32_t code = lds_u8(stage32 + kScaleOff + row * 16u + (blk - (blk0 & ~15u)));
-                const uint32_t first = (fbase_tile + blk0) >> sshift;
-                const uint32_t idx = ((fbase_row + blk) >> sshift) - (first & ~3u);
-                return dq_finish(s_factor[code], lds_f32(stage32 + kSecondOff + idx * 4u), dq_offset);
-            };
-            float scale = live ? block_scale((4u * rho + g) >> p.kshift) : 0.0f;
-            if (kHalf) {
-                // Keep the fp16 operand in range whatever the magnitude of the weights: every value of
-                // a row is divided by a power of two taken from the first scale of the row's segment
-                // (exact; the same for the four threads that share the row), and the row's sum is
-                // multiplied back in the epilogue.
-                if (seg_begins) {
-                    const uint32_t bits = live ? (__float_as_uint(block_scale(blk0)) & 0x7F800000u) : 0u;
-                    norm = (bits == 0u || bits == 0x7F800000u) ? 1.0f : __uint_as_float(bits);
-                    inv_norm = 1.0f / norm;
-                }
-                scale *= inv_norm;
-            }
+        // Decoded scale of block `blk` of this row from the raw values in the current ring slot.
+        auto block_scale = [&](uint32_t blk, uint32_t blk0) -> float {
+            if (fp32_scales) return lds_f32(stage32 + kScaleOff + row * 16u + (blk - (blk0 & ~3u)) * 4u);
+            const uint32_t code = lds_u8(stage32 + kScaleOff + row * 16u + (blk - (blk0 & ~15u)));
+            const uint32_t first = (fbase_tile + blk0) >> sshift;
+            const uint32_t idx = ((fbase_row + blk) >> sshift) - (first & ~3u);
+            return dq_finish(lds_f32(factor32 + code * 4u), lds_f32(stage32 + kSecondOff + idx * 4u), dq_offset);
+        };
+        // Looks one k-block's 32 bytes up into v, scaled.
+        auto lookup = [&](const uint4& c0, const uint4& c1, float scale) {
             const uint32_t s2 = pair_of<kHalf>(scale);
             const uint32_t words[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
 #pragma unroll
@@ -507,55 +512,128 @@ nf4_decode_tmem_kernel(const __grid_constant__ DecodeMaps maps, const __grid_con
                 v[4 * q + 2] = pair_mul<kHalf>(lds_u32(__byte_perm(word, lut_lane, 0x7624u)), s2);
                 v[4 * q + 3] = pair_mul<kHalf>(lds_u32(__byte_perm(word, lut_lane, 0x7634u)), s2);
             }
-            // the ring slot is free once every warp has its bytes in registers
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&bars.w_empty[ws]);
-            if (++ws == n_stages) {
-                ws = 0;
-                ++w_trip;
+        };
+        uint4 second_c0, second_c1;      // packed bytes of the item's second pass
+        float second_scale = 0.0f;
+        // First pass of item (tile, rho): waits for the ring slot, reads the thread's 64 packed bytes
+        // and its two scales, expands k-block 2h into v and keeps the rest for the second pass.
+        auto begin_item = [&](uint32_t tile, uint32_t rho, bool new_tile) {
+            if (new_tile) {
+                tref = locate_tile(p, tile);
+                const WeightView& w = p.w[tref.wi];
+                dq_offset = w.offset;
+                fbase_tile = static_cast<uint32_t>(w.flat_block_base) + tref.n0 * p.blocks_per_row;
+                fbase_row = fbase_tile + row * p.blocks_per_row;
+                live = tref.n0 + row < tref.n_out;
             }
+            stage32 = w_stage_addr(plan, ws);
+            mbar_wait(&bars.w_full[ws], w_trip & 1u, abort, kPollBudget);
+            const uint4 c0 = lds_u4(stage32 + code_off[0]);
+            const uint4 c1 = lds_u4(stage32 + code_off[1]);
+            second_c0 = lds_u4(stage32 + code_off[2]);
+            second_c1 = lds_u4(stage32 + code_off[3]);
+            const uint32_t blk0 = (4u * rho) >> p.kshift;
+            float scale = 0.0f;
+            second_scale = 0.0f;
+            if (live) {
+                scale = block_scale((4u * rho + 2u * h) >> p.kshift, blk0);
+                second_scale = block_scale((4u * rho + 2u * h + 1u) >> p.kshift, blk0);
+                if (kHalf) {
+                    scale *= inv_norm;
+                    second_scale *= inv_norm;
+                }
+            }
+            lookup(c0, c1, scale);
         };
 
-        // The loop is software-pipelined: the store of item i into tensor memory is issued, then
-        // item i+1 is expanded into registers while that store completes, and only then does the
-        // warp wait for the store and publish item i to the MMA issuer.
-        uint32_t tile = item_begin / R, rho = item_begin - tile * R;
-        uint32_t seg_first_rho = rho;
-        expand(tile, rho, true, true);
-        for (uint32_t it = item_begin; it < item_end; ++it) {
-            if (a_trip > 0) mbar_wait(&bars.done[as], (a_trip - 1u) & 1u, abort);
+        // Segments (runs of items inside one tile) are numbered from the CTA's first item: an item of
+        // tile T lies in segment T - tile_begin, which starts at rho_begin in the first tile and at 0
+        // in every later one.
+        const uint32_t tile_begin = item_begin / R, rho_begin = item_begin - tile_begin * R;
+        uint32_t tile = (item_begin + set) / R, rho = (item_begin + set) - tile * R;
+        if (kHalf) {
+            // Keep the fp16 operand in range whatever the magnitude of the weights: every expanded
+            // value of this CTA is divided by one power of two, taken from the first scale of the
+            // CTA's first item (row 0 of its tile), and the sums are multiplied back in the epilogue.
+            const TileRef t0 = locate_tile(p, tile_begin);
+            mbar_wait(&bars.w_full[0], 0u, abort, kPollBudget);
+            const uint32_t s0 = w_stage_addr(plan, 0u);
+            const uint32_t blk0 = (4u * rho_begin) >> p.kshift;
+            float first_scale;
+            if (fp32_scales) {
+                first_scale = lds_f32(s0 + kScaleOff + (blk0 - (blk0 & ~3u)) * 4u);
+            } else {
+                const uint32_t code = lds_u8(s0 + kScaleOff + (blk0 - (blk0 & ~15u)));
+                const uint32_t fb = static_cast<uint32_t>(p.w[t0.wi].flat_block_base) + t0.n0 * p.blocks_per_row;
+                const uint32_t idx = ((fb + blk0) >> sshift) - (((fb + blk0) >> sshift) & ~3u);
+                first_scale = dq_finish(lds_f32(factor32 + code * 4u), lds_f32(s0 + kSecondOff + idx * 4u), p.w[t0.wi].offset);
+            }
+            const uint32_t bits = __float_as_uint(first_scale) & 0x7F800000u;
+            norm = (bits == 0u || bits == 0x7F800000u) ? 1.0f : __uint_as_float(bits);
+            inv_norm = 1.0f / norm;
+            expand_barrier();   // every warp has read slot 0 before set 0 may release it
+        }
+        if (set < n_items) begin_item(tile, rho, true);
+        for (uint32_t j = set; j < n_items; j += 2u) {
+            const uint32_t it = item_begin + j;
+            // A parity wait only tells phase k from phase k - 1, and the epilogue of a segment that ends
+            // with the other set's item runs on the other set. So before this set publishes into
+            // segment s it observes the completion of every segment before s; with at least two rounds
+            // per tile it is then never more than one phase behind, and phase s cannot complete
+            // before this item is published.
+            for (; acc_seen < tile - tile_begin; ++acc_seen) mbar_wait(&bars.acc_full, acc_seen & 1u, abort, kPollBudget);
+            // ---- publish item j: both passes into tensor-memory stage `as` ----
+            if (a_trip > 0) mbar_wait(&bars.done[as], (a_trip - 1u) & 1u, abort, kPollBudget);
             tcgen05_fence_after_sync();
-            tmem_st_32x32(tmem_a + as * kStageColumns + g * 32u + lane_addr, v);
-            // what the epilogue of item `it` needs, before the next item replaces it
-            const uint32_t cur_tile = tile, cur_rho = rho, cur_first_rho = seg_first_rho;
+            const uint32_t taddr = tmem_a + as * kStageColumns + h * 64u + lane_addr;
+            tmem_st_32x32(taddr, v);
+            lookup(second_c0, second_c1, second_scale);
+            // the ring slot is free once every warp of the set has its bytes in registers
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars.w_empty[ws]);
+            tmem_st_32x32(taddr + 32u, v);
+            // what the epilogue of item j needs, before the next item replaces it
+            const uint32_t cur_tile = tile, cur_rho = rho, cur_seg = tile - tile_begin;
+            const uint32_t cur_first_rho = tile == tile_begin ? rho_begin : 0u;
             const TileRef cur_ref = tref;
             const bool cur_live = live;
-            const float cur_norm = norm;
             const bool seg_ends = it + 1u == item_end || rho + 1u == R;
-            if (it + 1u < item_end) {
-                const bool new_tile = rho + 1u == R;
-                if (new_tile) {
-                    rho = 0;
-                    ++tile;
-                } else {
-                    ++rho;
+            // ---- start this set's next item (j + 2) while the stores complete ----
+            ws += 2u;
+            if (ws >= n_stages) {
+                ws -= n_stages;
+                ++w_trip;
+            }
+            if (j + 2u < n_items) {
+                bool new_tile = false;
+                for (uint32_t step = 0; step < 2u; ++step) {   // walk two items ahead
+                    if (rho + 1u == R) {
+                        rho = 0;
+                        ++tile;
+                        new_tile = true;
+                    } else {
+                        ++rho;
+                    }
                 }
-                if (seg_ends) seg_first_rho = rho;
-                expand(tile, rho, new_tile, seg_ends);
+                begin_item(tile, rho, new_tile);
             }
             tmem_st_wait();
             tcgen05_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(&bars.a_full[as]);
-            if (++as == kAStages) {
-                as = 0;
+            as += 2u;
+            if (as >= kAStages) {
+                as -= kAStages;
                 ++a_trip;
             }
             if (!seg_ends) continue;
 
-            // ---- epilogue of the segment [cur_first_rho, cur_rho] of tile cur_tile ----
-            mbar_wait(&bars.acc_full, seg & 1u, abort);
-            ++seg;
+            // ---- epilogue of the segment [cur_first_rho, cur_rho] of tile cur_tile (this set's warps) ----
+            if (!dependency_waited) {
+                pdl_wait();
+                dependency_waited = true;
+            }
+            for (; acc_seen <= cur_seg; ++acc_seen) mbar_wait(&bars.acc_full, acc_seen & 1u, abort, kPollBudget);
             tcgen05_fence_after_sync();
             const bool whole = cur_first_rho == 0u && cur_rho + 1u == R;
             float* out = p.out[0];
@@ -566,15 +644,15 @@ nf4_decode_tmem_kernel(const __grid_constant__ DecodeMaps maps, const __grid_con
             const uint32_t n = cur_ref.n0 + row;
             const uint32_t slot = 2u * cta + (item_begin < cur_tile * R ? 1u : 0u);
             float* partial = p.partial + static_cast<uint64_t>(slot) * kPartialFloats;
-            if (g * 16u < p.n_pad) {
+            if (h * 16u < p.n_pad) {
                 uint32_t r[16];
-                tmem_ld_32x16(tmem_base + lane_addr + g * 16u, r);
+                tmem_ld_32x16(tmem_base + lane_addr + h * 16u, r);
                 tmem_ld_wait();
 #pragma unroll
                 for (uint32_t i = 0; i < 16u; ++i) {
-                    const uint32_t t = g * 16u + i;
+                    const uint32_t t = h * 16u + i;
                     float val = __uint_as_float(r[i]);
-                    if (kHalf) val *= cur_norm;
+                    if (kHalf) val *= norm;
                     if (t < p.m) {
                         if (whole) {
                             if (cur_live) out[static_cast<uint64_t>(t) * cur_ref.n_out + n] = val;
@@ -584,67 +662,83 @@ nf4_decode_tmem_kernel(const __grid_constant__ DecodeMaps maps, const __grid_con
                     }
                 }
             }
+            // the accumulator may be overwritten by the next segment's first MMA
             tcgen05_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars.acc_empty);
             if (!whole) {
                 // Publish the partial tile; the CTA that arrives last sums all of them in CTA order.
                 const uint32_t c_first = cta_of_item(cur_tile * R, ctas, p.total_items);
                 const uint32_t c_last = cta_of_item(cur_tile * R + R - 1u, ctas, p.total_items);
                 __threadfence();
-                expand_barrier();
-                if (e == 0 && lane == 0) {
+                set_barrier(set);
+                if ((e & 7u) == 0u && lane == 0) {
                     const uint32_t old = atomicAdd(&p.counters[cur_tile], 1u);
-                    bars.last_flag = old == c_last - c_first ? 1u : 0u;
+                    bars.last_flag[set] = old == c_last - c_first ? 1u : 0u;
                 }
-                expand_barrier();
-                if (bars.last_flag != 0u) {
+                set_barrier(set);
+                if (bars.last_flag[set] != 0u) {
                     __threadfence();
-                    const uint32_t et = tid - kFirstExpandWarp * 32u;
+                    const uint32_t st = (e & 7u) * 32u + lane;       // thread index inside the set
+                    uint32_t* slots = s_slots + set * 160u;
                     const uint32_t parts = c_last - c_first + 1u;
                     // where each part of this tile lies (a 64-bit division per part, done once)
-                    for (uint32_t c = et; c < parts; c += kExpandThreads) {
+                    for (uint32_t c = st; c < parts; c += kSetThreads) {
                         const uint32_t cc = c_first + c;
-                        s_slots[c] = 2u * cc + (range_begin(cc, ctas, p.total_items) < cur_tile * R ? 1u : 0u);
+                        slots[c] = 2u * cc + (range_begin(cc, ctas, p.total_items) < cur_tile * R ? 1u : 0u);
                     }
-                    expand_barrier();
-                    // Four floats per thread and step; the loads of up to four parts are in flight
-                    // together (their sum order is still part 0, 1, 2, ...).
+                    set_barrier(set);
+                    // Four floats per thread and position, two positions and up to eight parts in flight
+                    // together: the sum is bound by round trips to L2, not by bytes. Parts are still
+                    // added in CTA order (part 0, 1, 2, ...), so the result does not depend on timing.
                     const uint32_t total4 = p.m * (kTileW / 4);
-                    for (uint32_t i4 = et; i4 < total4; i4 += kExpandThreads) {
-                        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-                        for (uint32_t c0 = 0; c0 < parts; c0 += 4u) {
-                            float4 pv[4];
+                    for (uint32_t i4 = st; i4 < total4; i4 += 2u * kSetThreads) {
+                        const uint32_t pos[2] = {i4, i4 + kSetThreads};
+                        float4 acc[2] = {make_float4(0.f, 0.f, 0.f, 0.f), make_float4(0.f, 0.f, 0.f, 0.f)};
+                        for (uint32_t c0 = 0; c0 < parts; c0 += 8u) {
+                            float4 pv[2][8];
 #pragma unroll
-                            for (uint32_t u = 0; u < 4u; ++u) {
-                                pv[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-                                if (c0 + u < parts) {
-                                    pv[u] = __ldcg(reinterpret_cast<const float4*>(
-                                                p.partial + static_cast<uint64_t>(s_slots[c0 + u]) * kPartialFloats) + i4);
+                            for (uint32_t w2 = 0; w2 < 2u; ++w2) {
+#pragma unroll
+                                for (uint32_t u = 0; u < 8u; ++u) {
+                                    pv[w2][u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                                    if (c0 + u < parts && pos[w2] < total4) {
+                                        pv[w2][u] = __ldcg(reinterpret_cast<const float4*>(
+                                                        p.partial + static_cast<uint64_t>(slots[c0 + u]) * kPartialFloats) + pos[w2]);
+                                    }
                                 }
                             }
 #pragma unroll
-                            for (uint32_t u = 0; u < 4u; ++u) {
-                                if (c0 + u < parts) {
-                                    acc.x += pv[u].x;
-                                    acc.y += pv[u].y;
-                                    acc.z += pv[u].z;
-                                    acc.w += pv[u].w;
+                            for (uint32_t w2 = 0; w2 < 2u; ++w2) {
+#pragma unroll
+                                for (uint32_t u = 0; u < 8u; ++u) {
+                                    if (c0 + u < parts) {
+                                        acc[w2].x += pv[w2][u].x;
+                                        acc[w2].y += pv[w2][u].y;
+                                        acc[w2].z += pv[w2][u].z;
+                                        acc[w2].w += pv[w2][u].w;
+                                    }
                                 }
                             }
                         }
-                        const uint32_t t = i4 / (kTileW / 4), rr = (i4 % (kTileW / 4)) * 4u;
-                        float* dst = out + static_cast<uint64_t>(t) * cur_ref.n_out + cur_ref.n0 + rr;
-                        if (cur_ref.n0 + rr + 3u < cur_ref.n_out && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
-                            *reinterpret_cast<float4*>(dst) = acc;
-                        } else {
-                            const float a4[4] = {acc.x, acc.y, acc.z, acc.w};
-                            for (uint32_t u = 0; u < 4u; ++u) {
-                                if (cur_ref.n0 + rr + u < cur_ref.n_out) dst[u] = a4[u];
+#pragma unroll
+                        for (uint32_t w2 = 0; w2 < 2u; ++w2) {
+                            if (pos[w2] >= total4) continue;
+                            const uint32_t t = pos[w2] / (kTileW / 4), rr = (pos[w2] % (kTileW / 4)) * 4u;
+                            float* dst = out + static_cast<uint64_t>(t) * cur_ref.n_out + cur_ref.n0 + rr;
+                            if (cur_ref.n0 + rr + 3u < cur_ref.n_out && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
+                                *reinterpret_cast<float4*>(dst) = acc[w2];
+                            } else {
+                                const float a4[4] = {acc[w2].x, acc[w2].y, acc[w2].z, acc[w2].w};
+                                for (uint32_t u = 0; u < 4u; ++u) {
+                                    if (cur_ref.n0 + rr + u < cur_ref.n_out) dst[u] = a4[u];
+                                }
                             }
                         }
                     }
-                    if (e == 0 && lane == 0) p.counters[cur_tile] = 0u;   // every part has arrived: ready for the next launch
+                    if ((e & 7u) == 0u && lane == 0) p.counters[cur_tile] = 0u;   // every part has arrived: ready for the next launch
                 }
-                expand_barrier();   // last_flag and s_slots are rewritten by the next partial segment
+                set_barrier(set);   // last_flag and the slot list are rewritten by the set's next partial segment
             }
         }
     }
@@ -719,11 +813,12 @@ size_t nf4_decode_tmem_workspace_bytes(const DeviceContext& ctx) {
     return static_cast<size_t>(2) * static_cast<size_t>(ctx.sm_count) * kPartialFloats * sizeof(float);
 }
 
-// Shapes this kernel takes: up to 32 rows, whole 256-wide rounds, scale blocks of at least 64
+// Shapes this kernel takes: up to 32 rows, at least two whole 256-wide rounds, scale blocks of at least 64
 // weights that divide a row, and arrays aligned the way a TMA descriptor needs them.
 bool nf4_decode_tmem_supported(const WeightView& w, const void* x, uint64_t rows) {
     if (rows < 1 || rows > static_cast<uint64_t>(kMaxTokens)) return false;
-    if (w.in_features % kRoundK != 0 || w.block_size < 64 || w.in_features % w.block_size != 0) return false;
+    if (w.in_features % kRoundK != 0 || w.in_features < 2 * kRoundK) return false;   // whole rounds, two or more per tile
+    if (w.block_size < 64 || w.in_features % w.block_size != 0) return false;
     if (encode_tiled() == nullptr) return false;
     if ((reinterpret_cast<uintptr_t>(w.codes) & 15u) != 0 || (reinterpret_cast<uintptr_t>(x) & 15u) != 0) return false;
     const uint64_t bpr = w.in_features / w.block_size;
