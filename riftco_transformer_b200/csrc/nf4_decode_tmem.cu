@@ -465,7 +465,15 @@ nf4_decode_tmem_kernel(const __grid_constant__ DecodeMaps maps, const __grid_con
         // Expansion reads only the immutable weights, so it starts before the dependency wait of a
         // programmatic launch and runs up to three items ahead; the wait comes before the first
         // epilogue, which is the first thing here to touch memory an earlier kernel may write.
+        // Waits that depend on the MMAs (and through them on the activations) come after it too, so
+        // that no bounded wait has to outlast the previous kernel.
         bool dependency_waited = false;
+        auto depend = [&] {
+            if (!dependency_waited) {
+                pdl_wait();
+                dependency_waited = true;
+            }
+        };
         const uint32_t e = warp - kFirstExpandWarp;
         const uint32_t set = e >> 3;
         const uint32_t h = (e >> 2) & 1u;
@@ -581,6 +589,7 @@ nf4_decode_tmem_kernel(const __grid_constant__ DecodeMaps maps, const __grid_con
             // segment s it observes the completion of every segment before s; with at least two rounds
             // per tile it is then never more than one phase behind, and phase s cannot complete
             // before this item is published.
+            if (acc_seen < tile - tile_begin || a_trip > 0) depend();
             for (; acc_seen < tile - tile_begin; ++acc_seen) mbar_wait(&bars.acc_full, acc_seen & 1u, abort, kPollBudget);
             // ---- publish item j: both passes into tensor-memory stage `as` ----
             if (a_trip > 0) mbar_wait(&bars.done[as], (a_trip - 1u) & 1u, abort, kPollBudget);
@@ -629,10 +638,7 @@ nf4_decode_tmem_kernel(const __grid_constant__ DecodeMaps maps, const __grid_con
             if (!seg_ends) continue;
 
             // ---- epilogue of the segment [cur_first_rho, cur_rho] of tile cur_tile (this set's warps) ----
-            if (!dependency_waited) {
-                pdl_wait();
-                dependency_waited = true;
-            }
+            depend();
             for (; acc_seen <= cur_seg; ++acc_seen) mbar_wait(&bars.acc_full, acc_seen & 1u, abort, kPollBudget);
             tcgen05_fence_after_sync();
             const bool whole = cur_first_rho == 0u && cur_rho + 1u == R;
@@ -688,51 +694,39 @@ nf4_decode_tmem_kernel(const __grid_constant__ DecodeMaps maps, const __grid_con
                         slots[c] = 2u * cc + (range_begin(cc, ctas, p.total_items) < cur_tile * R ? 1u : 0u);
                     }
                     set_barrier(set);
-                    // Four floats per thread and position, two positions and up to eight parts in flight
-                    // together: the sum is bound by round trips to L2, not by bytes. Parts are still
-                    // added in CTA order (part 0, 1, 2, ...), so the result does not depend on timing.
+                    // Four floats per thread and step; the loads of up to eight parts are in flight
+                    // together (their sum order is still part 0, 1, 2, ...).
                     const uint32_t total4 = p.m * (kTileW / 4);
-                    for (uint32_t i4 = st; i4 < total4; i4 += 2u * kSetThreads) {
-                        const uint32_t pos[2] = {i4, i4 + kSetThreads};
-                        float4 acc[2] = {make_float4(0.f, 0.f, 0.f, 0.f), make_float4(0.f, 0.f, 0.f, 0.f)};
+                    for (uint32_t i4 = st; i4 < total4; i4 += kSetThreads) {
+                        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
                         for (uint32_t c0 = 0; c0 < parts; c0 += 8u) {
-                            float4 pv[2][8];
+                            float4 pv[8];
 #pragma unroll
-                            for (uint32_t w2 = 0; w2 < 2u; ++w2) {
-#pragma unroll
-                                for (uint32_t u = 0; u < 8u; ++u) {
-                                    pv[w2][u] = make_float4(0.f, 0.f, 0.f, 0.f);
-                                    if (c0 + u < parts && pos[w2] < total4) {
-                                        pv[w2][u] = __ldcg(reinterpret_cast<const float4*>(
-                                                        p.partial + static_cast<uint64_t>(slots[c0 + u]) * kPartialFloats) + pos[w2]);
-                                    }
+                            for (uint32_t u = 0; u < 8u; ++u) {
+                                pv[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                                if (c0 + u < parts) {
+                                    pv[u] = __ldcg(reinterpret_cast<const float4*>(
+                                                p.partial + static_cast<uint64_t>(slots[c0 + u]) * kPartialFloats) + i4);
                                 }
                             }
 #pragma unroll
-                            for (uint32_t w2 = 0; w2 < 2u; ++w2) {
-#pragma unroll
-                                for (uint32_t u = 0; u < 8u; ++u) {
-                                    if (c0 + u < parts) {
-                                        acc[w2].x += pv[w2][u].x;
-                                        acc[w2].y += pv[w2][u].y;
-                                        acc[w2].z += pv[w2][u].z;
-                                        acc[w2].w += pv[w2][u].w;
-                                    }
+                            for (uint32_t u = 0; u < 8u; ++u) {
+                                if (c0 + u < parts) {
+                                    acc.x += pv[u].x;
+                                    acc.y += pv[u].y;
+                                    acc.z += pv[u].z;
+                                    acc.w += pv[u].w;
                                 }
                             }
                         }
-#pragma unroll
-                        for (uint32_t w2 = 0; w2 < 2u; ++w2) {
-                            if (pos[w2] >= total4) continue;
-                            const uint32_t t = pos[w2] / (kTileW / 4), rr = (pos[w2] % (kTileW / 4)) * 4u;
-                            float* dst = out + static_cast<uint64_t>(t) * cur_ref.n_out + cur_ref.n0 + rr;
-                            if (cur_ref.n0 + rr + 3u < cur_ref.n_out && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
-                                *reinterpret_cast<float4*>(dst) = acc[w2];
-                            } else {
-                                const float a4[4] = {acc[w2].x, acc[w2].y, acc[w2].z, acc[w2].w};
-                                for (uint32_t u = 0; u < 4u; ++u) {
-                                    if (cur_ref.n0 + rr + u < cur_ref.n_out) dst[u] = a4[u];
-                                }
+                        const uint32_t t = i4 / (kTileW / 4), rr = (i4 % (kTileW / 4)) * 4u;
+                        float* dst = out + static_cast<uint64_t>(t) * cur_ref.n_out + cur_ref.n0 + rr;
+                        if (cur_ref.n0 + rr + 3u < cur_ref.n_out && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
+                            *reinterpret_cast<float4*>(dst) = acc;
+                        } else {
+                            const float a4[4] = {acc.x, acc.y, acc.z, acc.w};
+                            for (uint32_t u = 0; u < 4u; ++u) {
+                                if (cur_ref.n0 + rr + u < cur_ref.n_out) dst[u] = a4[u];
                             }
                         }
                     }
