@@ -114,6 +114,31 @@ B2_API const char* b2_unavailability_reason(void);
  * scale decode per storage.hpp:48-65). out: float[out*in]. */
 B2_API int32_t b2_nf4_dequantize(const b2_nf4_weight* weight, float* out, void* stream);
 
+/* The reference's NF4 encoder on a device tensor: values float[out,in] -> packed codes and block
+ * scales, bit for bit what QuantizedWeight::quantize_nf4 (scale_block_size == 0: scales_primary
+ * receives float[blocks]) and quantize_nf4_double_quantized (scales_primary receives uint8[blocks],
+ * scales_secondary float[ceil(blocks / scale_block_size)], *scale_offset the shared mean) produce:
+ * pack_nf4 / double_quantize_scales, src/core/quantization/quantized_weight.cpp:176-254, nearest
+ * level with ties to the lower code (src/core/quantization/nf4.cpp:55-68), a zero block keeps scale 0
+ * and code 7. codes: uint8[ceil(out*in/2)]. scale_offset is a HOST pointer; the call returns after
+ * the stream is idle. Non-finite values are INVALID_ARGUMENT ("NF4 source values must be finite"),
+ * a non-finite mean OVERFLOW. workspace: b2_nf4_quantize_workspace_bytes, 256-byte aligned. */
+B2_API size_t b2_nf4_quantize_workspace_bytes(uint64_t out_features, uint64_t in_features,
+                                              uint32_t block_size, uint64_t scale_block_size);
+B2_API int32_t b2_nf4_quantize(const float* values, uint64_t out_features, uint64_t in_features,
+                               uint32_t block_size, uint64_t scale_block_size, uint8_t* codes,
+                               void* scales_primary, float* scales_secondary, float* scale_offset,
+                               void* workspace, size_t workspace_bytes, void* stream);
+
+/* require_canonical_payload (quantized_weight.cpp:102-174) for a payload in device memory: the
+ * three array lengths against shape and block sizes, the unused high nibble of an odd element
+ * count, finite non-negative second-level and decoded block scales, and code 7 throughout every
+ * zero-scale block of the FP32-scale form; INVALID_ARGUMENT with the reference's message
+ * otherwise. b2_nf4_weight carries no lengths, so the compute entry points cannot apply these
+ * rules themselves: a loader calls this once per weight. Synchronous. */
+B2_API int32_t b2_nf4_validate_payload(const b2_nf4_weight* weight, uint64_t codes_bytes,
+                                       uint64_t primary_count, uint64_t secondary_count, void* stream);
+
 /* y[r,o] = sum_i x[r,i] * W[o,i]. x: float[rows,in], y: float[rows,out].
  * Replaces QuantizedLinearCapability::quantized_linear_forward
  * (src/core/backend/nn/quantized_linear/capability.hpp:35-41; CUDA launcher

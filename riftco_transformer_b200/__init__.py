@@ -21,7 +21,9 @@ _EXPORTS = (
     "host_quantized_linear_input_backward",
     "is_available",
     "paged_decode_attention",
+    "quantize_nf4",
     "unavailability_reason",
+    "validate_payload",
 )
 __all__ = list(_EXPORTS)
 

@@ -58,6 +58,9 @@ SIGNATURES = {
     "b2_is_available": (_i32, []),
     "b2_unavailability_reason": (C.c_char_p, []),
     "b2_nf4_dequantize": (_i32, [_W, _vp, _vp]),
+    "b2_nf4_quantize_workspace_bytes": (_sz, [_u64, _u64, _u32, _u64]),
+    "b2_nf4_quantize": (_i32, [_vp, _u64, _u64, _u32, _u64, _vp, _vp, _vp, C.POINTER(C.c_float), _vp, _sz, _vp]),
+    "b2_nf4_validate_payload": (_i32, [_W, _u64, _u64, _u64, _vp]),
     "b2_nf4_linear_forward": (_i32, [_W, _vp, _vp, _u64, _vp, _sz, _vp]),
     "b2_nf4_linear_forward_multi": (_i32, [_vp, _u32, _vp, _vp, _u64, _vp, _sz, _vp]),
     "b2_nf4_linear_bf16_supported": (_i32, [_vp, _u32, _u64]),

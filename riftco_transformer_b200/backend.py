@@ -175,6 +175,39 @@ class PackedNf4Weight:
             self.flat_block_base + b0)
 
 
+def quantize_nf4(values: torch.Tensor, block_size: int = 64, scale_block_size: int = 0, stream=None) -> PackedNf4Weight:
+    """QuantizedWeight::quantize_nf4 (scale_block_size == 0) / quantize_nf4_double_quantized on a
+    device tensor [out, in]: the reference's encoder, bit for bit, by the library's own kernels."""
+    _require_f32_cuda(values, "NF4 source")
+    if values.dim() != 2:
+        raise ValueError("NF4 quantization requires a matrix")
+    out_f, in_f = values.shape
+    n = out_f * in_f
+    blocks = -(-n // block_size)
+    dev = values.device
+    codes = torch.empty((n + 1) // 2, dtype=torch.uint8, device=dev)
+    dq = scale_block_size != 0
+    primary = torch.empty(blocks, dtype=torch.uint8 if dq else torch.float32, device=dev)
+    secondary = torch.empty(-(-blocks // scale_block_size), dtype=torch.float32, device=dev) if dq else None
+    need = lib.b2_nf4_quantize_workspace_bytes(out_f, in_f, block_size, scale_block_size)
+    workspace = torch.empty(max(need, 256), dtype=torch.uint8, device=dev)
+    offset = C.c_float(0.0)
+    _check(lib.b2_nf4_quantize(values.data_ptr(), out_f, in_f, block_size, scale_block_size, codes.data_ptr(),
+                               primary.data_ptr(), None if secondary is None else secondary.data_ptr(),
+                               C.byref(offset), workspace.data_ptr(), workspace.numel(), _stream_ptr(stream)))
+    return PackedNf4Weight(codes, primary, secondary,
+                           _lib.SCALES_DOUBLE_QUANTIZED_UINT8 if dq else _lib.SCALES_FLOAT32, block_size,
+                           scale_block_size, float(offset.value), out_f, in_f)
+
+
+def validate_payload(weight: PackedNf4Weight, stream=None) -> None:
+    """require_canonical_payload of the reference for a device-resident payload; raises ValueError."""
+    ws = weight.struct()
+    _check(lib.b2_nf4_validate_payload(C.byref(ws), weight.codes.numel(), weight.primary.numel(),
+                                       0 if weight.secondary is None else weight.secondary.numel(),
+                                       _stream_ptr(stream)))
+
+
 def dequantize(weight: PackedNf4Weight, stream=None) -> torch.Tensor:
     """QuantizedWeight::dequantize on the device, bit-exact."""
     out = torch.empty((weight.out_features, weight.in_features), dtype=torch.float32, device=weight.device)

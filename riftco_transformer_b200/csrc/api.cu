@@ -545,6 +545,82 @@ int32_t b2_nf4_dequantize(const b2_nf4_weight* weight, float* out, void* stream)
     return launch_nf4_dequantize(*ctx, w, out, static_cast<cudaStream_t>(stream));
 }
 
+size_t b2_nf4_quantize_workspace_bytes(uint64_t out_features, uint64_t in_features, uint32_t block_size,
+                                       uint64_t scale_block_size) {
+    int32_t status = B2_STATUS_OK;
+    DeviceContext* ctx = device_context(&status);
+    clear_error();
+    uint64_t n = 0;
+    if (ctx == nullptr || block_size == 0 || mul_overflows(out_features, in_features, &n)) return 0;
+    return nf4_quantize_workspace_bytes(*ctx, (n + block_size - 1) / block_size, scale_block_size != 0);
+}
+
+int32_t b2_nf4_quantize(const float* values, uint64_t out_features, uint64_t in_features, uint32_t block_size,
+                        uint64_t scale_block_size, uint8_t* codes, void* scales_primary, float* scales_secondary,
+                        float* scale_offset, void* workspace, size_t workspace_bytes, void* stream) {
+    clear_error();
+    int32_t status = B2_STATUS_OK;
+    DeviceContext* ctx = device_context(&status);
+    if (ctx == nullptr) return status;
+    if (out_features == 0 || in_features == 0) {
+        return fail(B2_STATUS_INVALID_ARGUMENT, "NF4 quantization requires a non-empty weight");
+    }
+    uint64_t n = 0;
+    if (mul_overflows(out_features, in_features, &n)) return fail(B2_STATUS_OVERFLOW, "NF4 weight element count overflows");
+    if (!block_size_supported(block_size)) {
+        return fail(B2_STATUS_INVALID_ARGUMENT, "NF4 block size must be a power of two between 32 and 4096");
+    }
+    if (scale_block_size != 0 && !block_size_supported(scale_block_size)) {
+        return fail(B2_STATUS_INVALID_ARGUMENT, "NF4 block size must be a power of two between 32 and 4096");
+    }
+    if (values == nullptr || codes == nullptr || scales_primary == nullptr ||
+        (scale_block_size != 0 && scales_secondary == nullptr)) {
+        return fail(B2_STATUS_INVALID_ARGUMENT, "NF4 quantization pointers must not be null");
+    }
+    const size_t need = nf4_quantize_workspace_bytes(*ctx, (n + block_size - 1) / block_size, scale_block_size != 0);
+    if (workspace == nullptr || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) {
+        return fail(B2_STATUS_INVALID_ARGUMENT, "NF4 quantization needs %zu bytes of 256-byte aligned workspace", need);
+    }
+    return run_nf4_quantize(*ctx, values, out_features, in_features, block_size, scale_block_size, codes,
+                            scales_primary, scales_secondary, scale_offset, workspace, static_cast<cudaStream_t>(stream));
+}
+
+int32_t b2_nf4_validate_payload(const b2_nf4_weight* weight, uint64_t codes_bytes, uint64_t primary_count,
+                                uint64_t secondary_count, void* stream) {
+    clear_error();
+    int32_t status = B2_STATUS_OK;
+    DeviceContext* ctx = device_context(&status);
+    if (ctx == nullptr) return status;
+    WeightView w;
+    B2_TRY(make_weight_view(weight, &w));
+    const uint64_t n = w.out_features * w.in_features;
+    const uint64_t blocks = (n + w.block_size - 1) / w.block_size;
+    if (codes_bytes != (n + 1) / 2) {
+        return fail(B2_STATUS_INVALID_ARGUMENT, "NF4 packed byte count does not match the weight shape");
+    }
+    uint64_t second_needed = 0;
+    if (w.encoding == B2_SCALES_FLOAT32) {
+        if (primary_count != blocks) {
+            return fail(B2_STATUS_INVALID_ARGUMENT, "NF4 scale count does not match the weight shape and block size");
+        }
+    } else {
+        if (primary_count != blocks) {
+            return fail(B2_STATUS_INVALID_ARGUMENT, "double-quantized NF4 scale-code count does not match the weight");
+        }
+        // a whole weight has exactly ceil(blocks / group) second-level scales; a row shard shares its
+        // parent's array and needs it to reach the shard's last block
+        second_needed = ((w.flat_block_base + blocks - 1) >> w.scale_block_shift) + 1;
+        if (w.flat_block_base == 0 ? secondary_count != second_needed : secondary_count < second_needed) {
+            return fail(B2_STATUS_INVALID_ARGUMENT, "double-quantized NF4 second-level scale count is invalid");
+        }
+    }
+    uint32_t* flags = nullptr;
+    B2_CUDA_TRY(cudaMalloc(&flags, 256));
+    const int32_t result = run_nf4_validate(*ctx, w, second_needed, flags, static_cast<cudaStream_t>(stream));
+    cudaFree(flags);
+    return result;
+}
+
 int32_t b2_nf4_linear_forward(const b2_nf4_weight* weight, const float* x, float* y, uint64_t rows,
                               void* workspace, size_t workspace_bytes, void* stream) {
     clear_error();

@@ -10,6 +10,14 @@ namespace b2 {
 int32_t launch_nf4_dequantize(const DeviceContext& ctx, const WeightView& w, float* out,
                               cudaStream_t stream);
 
+// nf4_quantize.cu - the reference's NF4 encoder and payload validation on the device (both synchronous).
+size_t nf4_quantize_workspace_bytes(const DeviceContext& ctx, uint64_t blocks, bool double_quantized);
+int32_t run_nf4_quantize(const DeviceContext& ctx, const float* values, uint64_t out_features, uint64_t in_features,
+                         uint32_t block_size, uint64_t scale_block_size, uint8_t* codes, void* primary,
+                         float* secondary, float* offset_out, void* workspace, cudaStream_t stream);
+int32_t run_nf4_validate(const DeviceContext& ctx, const WeightView& w, uint64_t second_count, uint32_t* flags_word,
+                         cudaStream_t stream);
+
 // nf4_linear_generic.cu - any shape, any block size, FP32 SIMT.
 int32_t launch_nf4_linear_forward_generic(const DeviceContext& ctx, const WeightView& w,
                                           const float* x, float* y, uint64_t rows,

@@ -176,9 +176,16 @@ def test_multi_weight_forward_matches_single_calls(b2, port, rows):
 def _device_quantized(b2, out_f, in_f, dq, seed):
     """W ~ N(0, 0.02^2) quantised on the device by the torch restatement of the reference encoder
     (held to the oracle bit for bit in test_gpu_parity.py), plus its host payload for the oracle."""
+    import oracle
     from riftco_transformer_b200 import synth
     w = synth.quantized_weight(out_f, in_f, seed=seed, double_quantized=dq)
-    return w, synth.host_payload(w)
+    if dq:
+        host = oracle.Nf4Weight(w.codes.cpu().numpy(), out_f, in_f, w.block_size,
+                                scale_codes=w.primary.cpu().numpy(), second_level=w.secondary.cpu().numpy(),
+                                scale_block_size=w.scale_block_size, offset=w.offset)
+    else:
+        host = oracle.Nf4Weight(w.codes.cpu().numpy(), out_f, in_f, w.block_size, fp32_scales=w.primary.cpu().numpy())
+    return w, host
 
 
 @pytest.mark.parametrize("out_f,in_f,dq", [

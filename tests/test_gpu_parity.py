@@ -471,3 +471,86 @@ def test_host_seam_matches_device_path(b2, port, c2_weights):
     bad[0] = 99
     with pytest.raises(IndexError):
         b2.host_paged_decode_attention_forward(c["q"], pool, bad[None, :], np.array([c["seq_len"]], np.uint32), ctx)
+
+
+# ---- encoder and payload validation on the device ---------------------------------------------
+
+@pytest.mark.parametrize("shape,block,sblock", [((384, 1024), 64, 256), ((33, 33), 32, 32), ((7, 96), 32, 0),
+                                                  ((256, 512), 128, 0), ((1024, 4096), 64, 256)])
+def test_device_quantize_matches_the_reference_encoder_bit_for_bit(b2, port, shape, block, sblock):
+    """b2_nf4_quantize against the C restatement of pack_nf4 / double_quantize_scales (itself held to
+    the reference's vectors): codes incl. ties and an odd tail, zero blocks, scales, offset."""
+    rng = np.random.default_rng(shape[0] * 7 + block)
+    W = (rng.standard_normal(shape) * 0.02).astype(np.float32)
+    flat = W.reshape(-1)
+    flat[block:2 * block] = 0.0                                             # a zero block
+    flat[:16] = np.float32(0.03) * port.codebook()                          # exact levels once scaled
+    flat[16:18] = np.float32(0.03) * np.float32(0.5) * (port.codebook()[3] + port.codebook()[4])   # a midpoint
+    flat[18] = 0.03
+    dev_w = b2.quantize_nf4(torch.from_numpy(W).cuda(), block, sblock)
+    host = port.quantize_nf4_double_quantized(W, block, sblock) if sblock else port.quantize_nf4(W, block)
+    assert np.array_equal(dev_w.codes.cpu().numpy(), host.codes)
+    if sblock:
+        assert np.array_equal(dev_w.primary.cpu().numpy(), host.scale_codes)
+        assert (bits(dev_w.secondary.cpu().numpy()) == bits(host.second_level)).all()
+        assert np.float32(dev_w.offset).view(np.uint32) == np.float32(host.offset).view(np.uint32)
+    else:
+        assert (bits(dev_w.primary.cpu().numpy()) == bits(host.fp32_scales)).all()
+    b2.validate_payload(dev_w)          # what the encoder writes is canonical
+    assert (bits(b2.dequantize(dev_w).cpu().numpy()) == bits(port.dequantize(host))).all()
+
+
+def test_device_quantize_rejects_non_finite_values(b2):
+    W = torch.zeros((4, 64), device="cuda")
+    W[2, 5] = float("inf")
+    with pytest.raises(ValueError, match="NF4 source values must be finite"):
+        b2.quantize_nf4(W, 64, 0)
+    W[2, 5] = float("nan")
+    with pytest.raises(ValueError, match="NF4 source values must be finite"):
+        b2.quantize_nf4(W, 32, 32)
+
+
+def test_validate_payload_applies_the_canonical_rules(b2, port):
+    """require_canonical_payload, src/core/quantization/quantized_weight.cpp:102-174, message by message."""
+    import dataclasses
+    rng = np.random.default_rng(3)
+    W = (rng.standard_normal((8, 96)) * 0.02).astype(np.float32)
+    W[1, :32] = 0.0
+    plain = b2.PackedNf4Weight.from_host(port.quantize_nf4(W, 32))
+    nested = b2.PackedNf4Weight.from_host(port.quantize_nf4_double_quantized(W, 32, 32))
+    b2.validate_payload(plain)
+    b2.validate_payload(nested)
+
+    def broken(w, **changes):
+        return dataclasses.replace(w, **changes)
+
+    with pytest.raises(ValueError, match="packed byte count"):
+        b2.validate_payload(broken(plain, codes=plain.codes[:-1].clone()))
+    with pytest.raises(ValueError, match="scale count does not match"):
+        b2.validate_payload(broken(plain, primary=plain.primary[:-1].clone()))
+    with pytest.raises(ValueError, match="scale-code count"):
+        b2.validate_payload(broken(nested, primary=nested.primary[:-1].clone()))
+    with pytest.raises(ValueError, match="second-level scale count"):
+        b2.validate_payload(broken(nested, secondary=torch.cat([nested.secondary, nested.secondary[:1]])))
+    bad = plain.primary.clone()
+    bad[3] = -1.0
+    with pytest.raises(ValueError, match="block scales must be finite and nonnegative"):
+        b2.validate_payload(broken(plain, primary=bad))
+    bad = plain.primary.clone()
+    bad[5] = float("nan")
+    with pytest.raises(ValueError, match="block scales must be finite and nonnegative"):
+        b2.validate_payload(broken(plain, primary=bad))
+    bad = nested.secondary.clone()
+    bad[0] = float("inf")
+    with pytest.raises(ValueError, match="second-level scales must be finite and nonnegative"):
+        b2.validate_payload(broken(nested, secondary=bad))
+    codes = plain.codes.clone()            # the zero block (row 1, first 32 weights) must hold code 7 only
+    codes[(96 + 4) // 2] = 0x73
+    with pytest.raises(ValueError, match="canonical zero code 7"):
+        b2.validate_payload(broken(plain, codes=codes))
+    odd = b2.PackedNf4Weight.from_host(port.quantize_nf4((rng.standard_normal((3, 11)) * 0.1).astype(np.float32), 32))
+    b2.validate_payload(odd)
+    codes = odd.codes.clone()
+    codes[-1] |= 0x50                      # 33 elements: the last byte's high nibble is unused
+    with pytest.raises(ValueError, match="unused high nibble"):
+        b2.validate_payload(broken(odd, codes=codes))
