@@ -239,6 +239,7 @@ class DecodeStep:
         self.cfg, self.ops, self.rank, self.world = cfg, ops, rank, world
         self.w, self.norms, self.embedding, self.pools, self.tables = weights, norms, embedding, pools, tables
         self.batch, self.max_seq_len = batch, max_seq_len
+        self.active_layers = cfg.layers   # a step may be cut short after this many layers (cross-checks)
         d, hd = cfg.d_model, cfg.head_dim
         self.hq, self.hkv = cfg.q_heads // world, cfg.kv_heads // world
         e = ops.empty
@@ -330,7 +331,7 @@ class DecodeStep:
         cfg, ops = self.cfg, self.ops
         ops.gather_rows(self.embedding, tokens, self.x, self.status)
         pending = None  # residual delta not yet added to x
-        for layer in range(cfg.layers):
+        for layer in range(self.active_layers):
             w, nm = self.w[layer], self.norms[layer]
             self._norm(pending, nm["attn"])
             self._linears_of_n([w["wq"], w["wk"], w["wv"]],

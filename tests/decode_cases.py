@@ -77,3 +77,27 @@ def run(step, model):
         tokens, positions, seq_lens = tokens.to(dev), positions.to(dev), seq_lens.to(dev)
     nxt, logits = step.step(tokens, positions, seq_lens)
     return nxt.cpu().numpy().copy(), logits.cpu().numpy().copy()
+
+
+def oracle_payload(w):
+    """The host payload (oracle.Nf4Weight) of a device-resident PackedNf4Weight."""
+    codes = w.codes.cpu().numpy()
+    if w.secondary is None:
+        return oracle.Nf4Weight(codes, w.out_features, w.in_features, w.block_size, fp32_scales=w.primary.cpu().numpy())
+    return oracle.Nf4Weight(codes, w.out_features, w.in_features, w.block_size, scale_codes=w.primary.cpu().numpy(),
+                            second_level=w.secondary.cpu().numpy(), scale_block_size=w.scale_block_size,
+                            offset=w.offset)
+
+
+def checker_step_of(step):
+    """The CPU checker's DecodeStep over the very tensors of an UNSHARDED CUDA DecodeStep (weights as
+    host payloads, norms, embedding, KV pools, tables): what the oracle says the step must compute."""
+    from riftco_transformer_b200.decode import DecodeStep
+    assert step.world == 1
+    cfg = step.cfg
+    weights = {layer: {n: oracle_payload(step.w[layer][n]) for n in LAYER_WEIGHTS} for layer in range(cfg.layers)}
+    weights["lm_head"] = oracle_payload(step.w["lm_head"])
+    norms = {k: ({a: b.cpu() for a, b in v.items()} if isinstance(v, dict) else v.cpu()) for k, v in step.norms.items()}
+    pools = [decode_ref.HostPool(p.key_pages.cpu().clone(), p.value_pages.cpu().clone()) for p in step.pools]
+    return DecodeStep(cfg, decode_ref.CheckerOps(None), weights, norms, step.embedding.cpu(), pools,
+                      step.tables.cpu(), step.batch, step.max_seq_len, 0, 1)
