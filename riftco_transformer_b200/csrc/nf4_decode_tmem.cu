@@ -104,8 +104,8 @@ struct Barriers {
     uint64_t x_empty[kXStages];     // tcgen05.commit: the round's MMAs have read the activation stage
     uint64_t a_full[kAStages];
     uint64_t done[kAStages];        // tcgen05.commit: the round's MMAs have read the tensor-memory stage
-    uint64_t acc_full;
-    uint64_t acc_empty;             // the epilogue has read the accumulator of the segment before
+    uint64_t acc_full[2];           // per accumulator (segment parity): the segment's MMAs have completed
+    uint64_t acc_empty[2];          // ... and its epilogue has read the accumulator
     uint32_t tmem_base;
     uint32_t abort;
     uint32_t last_flag[2];          // per expansion set
@@ -322,8 +322,10 @@ nf4_decode_tmem_kernel(const __grid_constant__ DecodeMaps maps, const __grid_con
                 mbar_init(&bars.a_full[s], kSetWarps);
                 mbar_init(&bars.done[s], 1);
             }
-            mbar_init(&bars.acc_full, 1);
-            mbar_init(&bars.acc_empty, kSetWarps);
+            for (int a = 0; a < 2; ++a) {
+                mbar_init(&bars.acc_full[a], 1);
+                mbar_init(&bars.acc_empty[a], kSetWarps);
+            }
             bars.abort = 0;
             bars.last_flag[0] = bars.last_flag[1] = 0;
             mbar_fence_init();
@@ -424,9 +426,10 @@ nf4_decode_tmem_kernel(const __grid_constant__ DecodeMaps maps, const __grid_con
         for (uint32_t it = item_begin; it < item_end; ++it) {
             const bool first = it == item_begin || rho == 0u;
             const bool last = it + 1u == item_end || rho + 1u == R;
-            // a new segment overwrites the accumulator: the epilogue of the one before must have read it
-            if (first && seg > 0) mbar_wait(&bars.acc_empty, (seg - 1u) & 1u, abort, kPollBudget);
-            if (last) ++seg;
+            // Segment s accumulates in accumulator s & 1; before it overwrites that accumulator the
+            // epilogue of segment s - 2 must have read it.
+            const uint32_t acc_index = seg & 1u;
+            if (first && seg > 1u) mbar_wait(&bars.acc_empty[acc_index], ((seg >> 1) - 1u) & 1u, abort, kPollBudget);
             mbar_wait(&bars.a_full[s], trip & 1u, abort, kPollBudget);
             mbar_wait(&bars.x_full[xs], x_trip & 1u, abort, kPollBudget);
             tcgen05_fence_after_sync();
@@ -437,15 +440,18 @@ nf4_decode_tmem_kernel(const __grid_constant__ DecodeMaps maps, const __grid_con
                 for (uint32_t kb = 0; kb < 4u; ++kb) {
 #pragma unroll
                     for (uint32_t kk = 0; kk < 4u; ++kk) {
-                        umma_a_tmem(tmem_base, a_s + kb * 32u + kk * 8u, dx_s + kb * kb16 + kk * 2u, idesc,
-                                    (first && kb == 0u && kk == 0u) ? 0u : 1u);
+                        umma_a_tmem(tmem_base + acc_index * kMaxTokens, a_s + kb * 32u + kk * 8u,
+                                    dx_s + kb * kb16 + kk * 2u, idesc, (first && kb == 0u && kk == 0u) ? 0u : 1u);
                     }
                 }
+                // the accumulator's barrier first: whoever has seen the stage barrier of a segment's last
+                // item complete can rely on the accumulator barrier having completed too
+                if (last) umma_commit(&bars.acc_full[acc_index]);
                 umma_commit(&bars.done[s]);
                 umma_commit(&bars.x_empty[xs]);
-                if (last) umma_commit(&bars.acc_full);
             }
             __syncwarp();
+            if (last) ++seg;
             if (++rho == R) rho = 0;
             if (++s == kAStages) {
                 s = 0;
@@ -497,7 +503,6 @@ nf4_decode_tmem_kernel(const __grid_constant__ DecodeMaps maps, const __grid_con
         bool live = false;
         float inv_norm = 1.0f, norm = 1.0f;
         uint32_t stage32 = 0;
-        uint32_t acc_seen = 0;     // phases of acc_full this set has seen complete
         uint32_t v[32];
 
         // Decoded scale of block `blk` of this row from the raw values in the current ring slot.
@@ -584,13 +589,7 @@ nf4_decode_tmem_kernel(const __grid_constant__ DecodeMaps maps, const __grid_con
         if (set < n_items) begin_item(tile, rho, true);
         for (uint32_t j = set; j < n_items; j += 2u) {
             const uint32_t it = item_begin + j;
-            // A parity wait only tells phase k from phase k - 1, and the epilogue of a segment that ends
-            // with the other set's item runs on the other set. So before this set publishes into
-            // segment s it observes the completion of every segment before s; with at least two rounds
-            // per tile it is then never more than one phase behind, and phase s cannot complete
-            // before this item is published.
-            if (acc_seen < tile - tile_begin || a_trip > 0) depend();
-            for (; acc_seen < tile - tile_begin; ++acc_seen) mbar_wait(&bars.acc_full, acc_seen & 1u, abort, kPollBudget);
+            if (a_trip > 0) depend();
             // ---- publish item j: both passes into tensor-memory stage `as` ----
             if (a_trip > 0) mbar_wait(&bars.done[as], (a_trip - 1u) & 1u, abort, kPollBudget);
             tcgen05_fence_after_sync();
@@ -638,8 +637,14 @@ nf4_decode_tmem_kernel(const __grid_constant__ DecodeMaps maps, const __grid_con
             if (!seg_ends) continue;
 
             // ---- epilogue of the segment [cur_first_rho, cur_rho] of tile cur_tile (this set's warps) ----
+            // Segment s uses accumulator s & 1 and is phase s >> 1 of that accumulator's barrier. A parity
+            // wait can only tell a phase from the one before it, so the phase before (segment s - 2) must
+            // be complete when this wait starts: it is, because this set has published the segment's
+            // last item, which lies at least three items after the end of segment s - 2 (tiles have two
+            // or more rounds) and so reused a tensor-memory stage that segment s - 2's last MMAs released
+            // - and those committed to the accumulator barrier first.
             depend();
-            for (; acc_seen <= cur_seg; ++acc_seen) mbar_wait(&bars.acc_full, acc_seen & 1u, abort, kPollBudget);
+            mbar_wait(&bars.acc_full[cur_seg & 1u], (cur_seg >> 1) & 1u, abort, kPollBudget);
             tcgen05_fence_after_sync();
             const bool whole = cur_first_rho == 0u && cur_rho + 1u == R;
             float* out = p.out[0];
@@ -652,7 +657,7 @@ nf4_decode_tmem_kernel(const __grid_constant__ DecodeMaps maps, const __grid_con
             float* partial = p.partial + static_cast<uint64_t>(slot) * kPartialFloats;
             if (h * 16u < p.n_pad) {
                 uint32_t r[16];
-                tmem_ld_32x16(tmem_base + lane_addr + h * 16u, r);
+                tmem_ld_32x16(tmem_base + (cur_seg & 1u) * kMaxTokens + lane_addr + h * 16u, r);
                 tmem_ld_wait();
 #pragma unroll
                 for (uint32_t i = 0; i < 16u; ++i) {
@@ -668,10 +673,10 @@ nf4_decode_tmem_kernel(const __grid_constant__ DecodeMaps maps, const __grid_con
                     }
                 }
             }
-            // the accumulator may be overwritten by the next segment's first MMA
+            // the accumulator may now be overwritten by the first MMA of the segment after next
             tcgen05_fence_before_sync();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&bars.acc_empty);
+            if (lane == 0) mbar_arrive(&bars.acc_empty[cur_seg & 1u]);
             if (!whole) {
                 // Publish the partial tile; the CTA that arrives last sums all of them in CTA order.
                 const uint32_t c_first = cta_of_item(cur_tile * R, ctas, p.total_items);
@@ -695,7 +700,8 @@ nf4_decode_tmem_kernel(const __grid_constant__ DecodeMaps maps, const __grid_con
                     }
                     set_barrier(set);
                     // Four floats per thread and step; the loads of up to eight parts are in flight
-                    // together (their sum order is still part 0, 1, 2, ...).
+                    // together (their sum order is still part 0, 1, 2, ...). Deliberately narrow: more
+                    // loads in flight would need registers the expansion loop cannot spare.
                     const uint32_t total4 = p.m * (kTileW / 4);
                     for (uint32_t i4 = st; i4 < total4; i4 += kSetThreads) {
                         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
