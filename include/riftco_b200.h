@@ -152,6 +152,17 @@ B2_API int32_t b2_nf4_linear_forward(const b2_nf4_weight* weight, const float* x
                               uint64_t rows, void* workspace, size_t workspace_bytes,
                               void* stream);
 
+/* A packed-NF4 linear with a low-rank adapter: y = x * W^T + scale * ((x * A^T) * B^T), A [rank, in],
+ * B [out, rank] FP32 device arrays, scale = alpha / rank. Replaces Linear::forward with an attached
+ * adapter (src/nn/linear.cpp:165-172: base_output + lora_->forward(input)) and LowRankAdapter::forward
+ * (src/nn/low_rank_adapter.cpp:132-158) on top of the packed base weight. The base projection runs
+ * on the same kernels as b2_nf4_linear_forward; the branch is FP32. rank <= 64. workspace:
+ * b2_nf4_linear_lora_workspace_bytes (NULL: the library's arena). */
+B2_API size_t b2_nf4_linear_lora_workspace_bytes(const b2_nf4_weight* weight, uint64_t rows, uint32_t rank);
+B2_API int32_t b2_nf4_linear_forward_lora(const b2_nf4_weight* weight, const float* x, const float* lora_a,
+                                          const float* lora_b, uint32_t rank, float scale, float* y,
+                                          uint64_t rows, void* workspace, size_t workspace_bytes, void* stream);
+
 /* Several packed linears of the SAME input in one call: ys[i][r,o] = sum_k x[r,k] * W_i[o,k]
  * for `count` weights with equal in_features (the q / k / v projections of an attention block,
  * the gate / up projections of a SwiGLU block: src/model/grouped_query_attention.cpp:61-94,
@@ -303,6 +314,20 @@ B2_API int32_t b2_rope_append_kv(float* q, const float* k, const float* v, const
                                  uint32_t n_seq, uint32_t q_heads, uint32_t kv_heads,
                                  uint32_t head_width, uint32_t block_size, uint64_t physical_blocks,
                                  uint32_t max_blocks, float theta, uint32_t* status, void* stream);
+
+/* b2_rope_append_kv for a CHUNK of tokens (batched prefill): q / k / v hold n_tokens rows, token t
+ * belongs to sequence token_seq[t] (its block-table row) and sits at positions[t]. Several tokens
+ * of one sequence may be given in one call, in any order; each lands in slot positions[t] %
+ * block_size of page block_tables[token_seq[t]][positions[t] / block_size]. The reference prefills
+ * token by token through decode_token (src/stages/serving/generation.cpp:260-398) and
+ * copy_token_to_page (src/stages/serving/cache/page_table_cache.cpp:44-77); this call writes what
+ * that loop writes, for the whole chunk at once. */
+B2_API int32_t b2_rope_append_kv_tokens(float* q, const float* k, const float* v, const uint32_t* positions,
+                                        const uint32_t* token_seq, const uint32_t* block_tables,
+                                        float* k_pages, float* v_pages, uint32_t n_tokens, uint32_t q_heads,
+                                        uint32_t kv_heads, uint32_t head_width, uint32_t block_size,
+                                        uint64_t physical_blocks, uint32_t max_blocks, float theta,
+                                        uint32_t* status, void* stream);
 
 /* out = silu(gate) * up, silu as silu_forward (src/nn/activations.cpp:38-58);
  * the product is SwiGLU's hidden state (src/model/swiglu.cpp:27-29). */

@@ -126,6 +126,7 @@ class Port:
         L.orc_silu_mul.argtypes = [_f32p, _f32p, C.c_size_t, _f32p]
         L.orc_greedy.restype = C.c_size_t
         L.orc_greedy.argtypes = [_f32p, C.c_size_t]
+        L.orc_lora_forward.argtypes = [_f32p, _f32p, _f32p] + [C.c_size_t] * 4 + [C.c_float, _f32p, _f32p]
 
     # -- format ---------------------------------------------------------
     def codebook(self) -> np.ndarray:
@@ -259,6 +260,17 @@ class Port:
         v = _f32(logits).ravel()
         return int(self.lib.orc_greedy(_ptr(v, _f32p), v.size))
 
+    def lora_forward(self, x, a, b, scale: float) -> np.ndarray:
+        """((x A^T) B^T) * scale: x [rows, in], a [rank, in], b [out, rank]."""
+        x, a, b = _f32(x), _f32(a), _f32(b)
+        rows, in_f = x.shape
+        rank, out_f = a.shape[0], b.shape[0]
+        reduced = np.empty((rows, rank), np.float32)
+        out = np.empty((rows, out_f), np.float32)
+        self.lib.orc_lora_forward(_ptr(x, _f32p), _ptr(a, _f32p), _ptr(b, _f32p), rows, in_f, out_f, rank, scale,
+                                  _ptr(reduced, _f32p), _ptr(out, _f32p))
+        return out
+
 
 class ReferenceError_(RuntimeError):
     def __init__(self, status: int, message: str) -> None:
@@ -299,6 +311,8 @@ class Reference:
             L.ref_paged_cache_decode.argtypes = [_f32p, _f32p, _f32p, u64, u64, u64, u64, u64, _f32p]
             L.ref_packed_model_fixture.argtypes = [u64, u64, u64, u64, u64, u64, u64, u64, C.c_uint32,
                                                    _u8p, u64, C.POINTER(u64), _u8p, u64, C.POINTER(u64)]
+        if hasattr(L, "ref_lora_forward"):
+            L.ref_lora_forward.argtypes = [_f32p, _f32p, _f32p, u64, u64, u64, u64, C.c_float, _f32p]
         self.last_seconds = 0.0
 
     def _check(self, rc: int) -> None:
@@ -447,6 +461,13 @@ class Reference:
         self._check(self.lib.ref_paged_cache_decode(_ptr(q, _f32p), _ptr(k, _f32p), _ptr(v, _f32p), steps, heads,
                                                     width, block_size, block_count, _ptr(ctx, _f32p)))
         return ctx
+
+    def lora_forward(self, x, a, b, scale: float) -> np.ndarray:
+        x, a, b = _f32(x), _f32(a), _f32(b)
+        out = np.empty((x.shape[0], b.shape[0]), np.float32)
+        self._check(self.lib.ref_lora_forward(_ptr(x, _f32p), _ptr(a, _f32p), _ptr(b, _f32p), x.shape[0], x.shape[1],
+                                              b.shape[0], a.shape[0], scale, _ptr(out, _f32p)))
+        return out
 
     def packed_model_fixture(self, vocabulary, context, width, heads, blocks, feed_forward, block_size,
                              scale_block_size, seed):

@@ -490,4 +490,23 @@ int ref_packed_model_fixture(std::uint64_t vocabulary, std::uint64_t context, st
     });
 }
 
+// The LoRA branch with the reference's own operators, in the order of LowRankAdapter::forward
+// (src/nn/low_rank_adapter.cpp:132-158): matmul(matmul(x, A^T), B^T) * scale. x [rows, in],
+// a [rank, in], b [out, rank] -> out [rows, out].
+int ref_lora_forward(const float* x, const float* a, const float* b, std::uint64_t rows,
+                     std::uint64_t in_features, std::uint64_t out_features, std::uint64_t rank, float scale,
+                     float* out) {
+    return guarded([&] {
+        CpuScope cpu;
+        using riftco_transformer::matmul;
+        using riftco_transformer::transpose_2d;
+        const Variable input(Tensor({rows, in_features}, std::vector<float>(x, x + rows * in_features), g_backend), false);
+        const Variable lora_a(Tensor({rank, in_features}, std::vector<float>(a, a + rank * in_features), g_backend), false);
+        const Variable lora_b(Tensor({out_features, rank}, std::vector<float>(b, b + out_features * rank), g_backend), false);
+        const Variable reduced = matmul(input, transpose_2d(lora_a));
+        const Variable expanded = matmul(reduced, transpose_2d(lora_b));
+        copy_out((expanded * scale).value(), out);
+    });
+}
+
 }  // extern "C"

@@ -341,3 +341,33 @@ size_t orc_greedy(const float* logits, size_t n) {
     }
     return selected;
 }
+
+/* LowRankAdapter::forward, src/nn/low_rank_adapter.cpp:132-158: ((x * A^T) * B^T) * scale with
+ * A [rank, in], B [out, rank]; both products are the reference matmul (one FP32 accumulator per
+ * output, contraction index ascending: src/core/backend/adapters/cpu/adapter.cpp:170-200). A
+ * Linear with an adapter returns base + this (src/nn/linear.cpp:165-172). `reduced` is scratch
+ * of rows * rank floats. */
+void orc_lora_forward(const float* x, const float* a, const float* b, size_t rows,
+                      size_t in_features, size_t out_features, size_t rank, float scale,
+                      float* reduced, float* out) {
+    for (size_t r = 0; r < rows; ++r) {
+        for (size_t j = 0; j < rank; ++j) {
+            float total = 0.0f;
+            for (size_t i = 0; i < in_features; ++i) {
+                const float product = x[r * in_features + i] * a[j * in_features + i];
+                total += product;
+            }
+            reduced[r * rank + j] = total;
+        }
+    }
+    for (size_t r = 0; r < rows; ++r) {
+        for (size_t o = 0; o < out_features; ++o) {
+            float total = 0.0f;
+            for (size_t j = 0; j < rank; ++j) {
+                const float product = reduced[r * rank + j] * b[o * rank + j];
+                total += product;
+            }
+            out[r * out_features + o] = total * scale;
+        }
+    }
+}

@@ -115,6 +115,11 @@ void orc_rms_norm(const float* x, const float* scale, size_t rows, size_t width,
 void orc_silu_mul(const float* gate, const float* up, size_t n, float* out);
 size_t orc_greedy(const float* logits, size_t n);
 
+/* ((x * A^T) * B^T) * scale, the LoRA branch of a Linear; `reduced` is scratch [rows, rank]. */
+void orc_lora_forward(const float* x, const float* a, const float* b, size_t rows,
+                      size_t in_features, size_t out_features, size_t rank, float scale,
+                      float* reduced, float* out);
+
 #ifdef __cplusplus
 }
 #endif

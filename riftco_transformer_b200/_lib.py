@@ -62,6 +62,8 @@ SIGNATURES = {
     "b2_nf4_quantize": (_i32, [_vp, _u64, _u64, _u32, _u64, _vp, _vp, _vp, C.POINTER(C.c_float), _vp, _sz, _vp]),
     "b2_nf4_validate_payload": (_i32, [_W, _u64, _u64, _u64, _vp]),
     "b2_nf4_linear_forward": (_i32, [_W, _vp, _vp, _u64, _vp, _sz, _vp]),
+    "b2_nf4_linear_lora_workspace_bytes": (_sz, [_W, _u64, _u32]),
+    "b2_nf4_linear_forward_lora": (_i32, [_W, _vp, _vp, _vp, _u32, C.c_float, _vp, _u64, _vp, _sz, _vp]),
     "b2_nf4_linear_forward_multi": (_i32, [_vp, _u32, _vp, _vp, _u64, _vp, _sz, _vp]),
     "b2_nf4_linear_bf16_supported": (_i32, [_vp, _u32, _u64]),
     "b2_nf4_linear_forward_multi_bf16": (_i32, [_vp, _u32, _vp, _vp, _u64, _vp]),
@@ -78,6 +80,8 @@ SIGNATURES = {
     "b2_silu_mul_bf16": (_i32, [_vp, _vp, _vp, _vp, _u64, _vp]),
     "b2_rope_append_kv": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u32, _u64, _u32,
                                  C.c_float, _vp, _vp]),
+    "b2_rope_append_kv_tokens": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u32, _u64,
+                                        _u32, C.c_float, _vp, _vp]),
     "b2_silu_mul": (_i32, [_vp, _vp, _vp, _u64, _vp]),
     "b2_add": (_i32, [_vp, _vp, _vp, _u64, _vp]),
     "b2_gather_rows": (_i32, [_vp, _vp, _vp, _u32, _u32, _u32, _vp, _vp]),

@@ -628,6 +628,54 @@ int32_t b2_nf4_linear_forward(const b2_nf4_weight* weight, const float* x, float
                                static_cast<cudaStream_t>(stream));
 }
 
+size_t b2_nf4_linear_lora_workspace_bytes(const b2_nf4_weight* weight, uint64_t rows, uint32_t rank) {
+    return pad256(b2_nf4_linear_workspace_bytes(weight, rows, 0)) + lora_workspace_bytes(rows, rank);
+}
+
+int32_t b2_nf4_linear_forward_lora(const b2_nf4_weight* weight, const float* x, const float* lora_a,
+                                   const float* lora_b, uint32_t rank, float scale, float* y, uint64_t rows,
+                                   void* workspace, size_t workspace_bytes, void* stream_ptr) {
+    clear_error();
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+    int32_t status = B2_STATUS_OK;
+    DeviceContext* ctx = device_context(&status);
+    if (ctx == nullptr) return status;
+    if (lora_a == nullptr || lora_b == nullptr) {
+        return fail(B2_STATUS_INVALID_ARGUMENT, "LoRA factors must not be null");
+    }
+    if (weight == nullptr) return fail(B2_STATUS_INVALID_ARGUMENT, "NF4 weight must not be null");
+    // checked_rank / checked_alpha, src/nn/low_rank_adapter.cpp:20-62
+    if (rank == 0 || rank > weight->in_features || rank > weight->out_features) {
+        return fail(B2_STATUS_INVALID_ARGUMENT, "LoRA rank must be positive and no larger than either width");
+    }
+    if (!lora_rank_supported(rank)) {
+        return fail(B2_STATUS_INVALID_ARGUMENT, "LoRA rank above 64 is not supported by this backend");
+    }
+    if (!std::isfinite(scale)) return fail(B2_STATUS_INVALID_ARGUMENT, "LoRA scale must be finite");
+    if (y == lora_a || y == lora_b) {
+        return fail(B2_STATUS_INVALID_ARGUMENT, "quantized linear weight and output storage must not alias");
+    }
+    // scratch: the base kernel's part first, then the [rows, rank] reduction
+    const size_t base_need = pad256(b2_nf4_linear_workspace_bytes(weight, rows, 0));
+    const size_t lora_need = lora_workspace_bytes(rows, rank);
+    clear_error();
+    uint8_t* scratch = static_cast<uint8_t*>(workspace);
+    if (workspace == nullptr) {
+        B2_TRY(reserve_arena(ctx, base_need + lora_need, stream));
+        scratch = static_cast<uint8_t*>(ctx->arena);
+        workspace_bytes = ctx->arena_bytes;
+    }
+    if (workspace_bytes < base_need + lora_need) {
+        return fail(B2_STATUS_INVALID_ARGUMENT, "NF4 LoRA workspace too small: need %zu bytes", base_need + lora_need);
+    }
+    if ((reinterpret_cast<uintptr_t>(scratch) & 15u) != 0) {
+        return fail(B2_STATUS_INVALID_ARGUMENT, "NF4 GEMM workspace must be 16-byte aligned");
+    }
+    B2_TRY(linear_forward_impl(weight, x, y, rows, base_need != 0 ? scratch : nullptr, base_need, stream));
+    return launch_lora_branch(*ctx, x, lora_a, lora_b, y, rows, weight->in_features, weight->out_features, rank, scale,
+                              reinterpret_cast<float*>(scratch + base_need), stream);
+}
+
 int32_t b2_nf4_linear_forward_multi(const b2_nf4_weight* weights, uint32_t count, const float* x, float* const* ys,
                                     uint64_t rows, void* workspace, size_t workspace_bytes, void* stream_ptr) {
     clear_error();
@@ -852,11 +900,13 @@ int32_t b2_rmsnorm_bf16(const float* x, const float* delta, float* x_out, const 
                           static_cast<cudaStream_t>(stream));
 }
 
-int32_t b2_rope_append_kv(float* q, const float* k, const float* v, const uint32_t* positions,
-                          const uint32_t* block_tables, float* k_pages, float* v_pages, uint32_t n_seq,
-                          uint32_t q_heads, uint32_t kv_heads, uint32_t head_width, uint32_t block_size,
-                          uint64_t physical_blocks, uint32_t max_blocks, float theta, uint32_t* status_word,
-                          void* stream) {
+namespace {
+
+int32_t rope_append_impl(float* q, const float* k, const float* v, const uint32_t* positions,
+                         const uint32_t* token_seq, const uint32_t* block_tables, float* k_pages, float* v_pages,
+                         uint32_t n_tokens, uint32_t q_heads, uint32_t kv_heads, uint32_t head_width,
+                         uint32_t block_size, uint64_t physical_blocks, uint32_t max_blocks, float theta,
+                         uint32_t* status_word, void* stream) {
     clear_error();
     int32_t status = B2_STATUS_OK;
     if (device_context(&status) == nullptr) return status;
@@ -864,7 +914,7 @@ int32_t b2_rope_append_kv(float* q, const float* k, const float* v, const uint32
         k_pages == nullptr || v_pages == nullptr) {
         return fail(B2_STATUS_INVALID_ARGUMENT, "rotary/append pointers must not be null");
     }
-    if (n_seq == 0 || q_heads == 0 || kv_heads == 0 || head_width == 0 || block_size == 0 ||
+    if (n_tokens == 0 || q_heads == 0 || kv_heads == 0 || head_width == 0 || block_size == 0 ||
         physical_blocks == 0 || max_blocks == 0) {
         return fail(B2_STATUS_INVALID_ARGUMENT, "rotary/append dimensions must be positive");
     }
@@ -874,9 +924,33 @@ int32_t b2_rope_append_kv(float* q, const float* k, const float* v, const uint32
     if (!std::isfinite(theta) || theta <= 0.0f) {
         return fail(B2_STATUS_INVALID_ARGUMENT, "rotary theta must be finite and positive");
     }
-    return launch_rope_append(q, k, v, positions, block_tables, k_pages, v_pages, n_seq, q_heads, kv_heads,
-                              head_width, block_size, physical_blocks, max_blocks, theta, status_word,
+    return launch_rope_append(q, k, v, positions, token_seq, block_tables, k_pages, v_pages, n_tokens, q_heads,
+                              kv_heads, head_width, block_size, physical_blocks, max_blocks, theta, status_word,
                               static_cast<cudaStream_t>(stream));
+}
+
+}  // namespace
+
+int32_t b2_rope_append_kv(float* q, const float* k, const float* v, const uint32_t* positions,
+                          const uint32_t* block_tables, float* k_pages, float* v_pages, uint32_t n_seq,
+                          uint32_t q_heads, uint32_t kv_heads, uint32_t head_width, uint32_t block_size,
+                          uint64_t physical_blocks, uint32_t max_blocks, float theta, uint32_t* status_word,
+                          void* stream) {
+    return rope_append_impl(q, k, v, positions, nullptr, block_tables, k_pages, v_pages, n_seq, q_heads, kv_heads,
+                            head_width, block_size, physical_blocks, max_blocks, theta, status_word, stream);
+}
+
+int32_t b2_rope_append_kv_tokens(float* q, const float* k, const float* v, const uint32_t* positions,
+                                 const uint32_t* token_seq, const uint32_t* block_tables, float* k_pages,
+                                 float* v_pages, uint32_t n_tokens, uint32_t q_heads, uint32_t kv_heads,
+                                 uint32_t head_width, uint32_t block_size, uint64_t physical_blocks,
+                                 uint32_t max_blocks, float theta, uint32_t* status_word, void* stream) {
+    if (token_seq == nullptr) {
+        clear_error();
+        return fail(B2_STATUS_INVALID_ARGUMENT, "rotary/append pointers must not be null");
+    }
+    return rope_append_impl(q, k, v, positions, token_seq, block_tables, k_pages, v_pages, n_tokens, q_heads,
+                            kv_heads, head_width, block_size, physical_blocks, max_blocks, theta, status_word, stream);
 }
 
 int32_t b2_silu_mul(const float* gate, const float* up, float* out, uint64_t n, void* stream) {

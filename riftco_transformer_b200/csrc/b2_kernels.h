@@ -18,6 +18,13 @@ int32_t run_nf4_quantize(const DeviceContext& ctx, const float* values, uint64_t
 int32_t run_nf4_validate(const DeviceContext& ctx, const WeightView& w, uint64_t second_count, uint32_t* flags_word,
                          cudaStream_t stream);
 
+// nf4_lora.cu - the low-rank adapter branch added to a base projection already in y.
+bool lora_rank_supported(uint64_t rank);
+size_t lora_workspace_bytes(uint64_t rows, uint64_t rank);
+int32_t launch_lora_branch(const DeviceContext& ctx, const float* x, const float* a, const float* b, float* y,
+                           uint64_t rows, uint64_t in_features, uint64_t out_features, uint32_t rank, float scale,
+                           float* reduced, cudaStream_t stream);
+
 // nf4_linear_generic.cu - any shape, any block size, FP32 SIMT.
 int32_t launch_nf4_linear_forward_generic(const DeviceContext& ctx, const WeightView& w,
                                           const float* x, float* y, uint64_t rows,
@@ -98,8 +105,10 @@ int32_t launch_paged_decode(const DeviceContext& ctx, const PagedDecodeArgs& arg
 // y_bf16 / out_bf16 (nullable): a bf16 copy of the result, the form the tensor-core linears read.
 int32_t launch_rmsnorm(const float* x, const float* delta, float* x_out, const float* scale, float* y,
                        void* y_bf16, uint64_t rows, uint32_t width, float eps, cudaStream_t stream);
+// token_seq == nullptr: one token per sequence (token index = block-table row); else the row of each token.
 int32_t launch_rope_append(float* q, const float* k, const float* v, const uint32_t* positions,
-                           const uint32_t* block_tables, float* k_pages, float* v_pages, uint32_t n_seq,
+                           const uint32_t* token_seq, const uint32_t* block_tables, float* k_pages,
+                           float* v_pages, uint32_t n_seq,
                            uint32_t q_heads, uint32_t kv_heads, uint32_t d, uint32_t block_size,
                            uint64_t physical_blocks, uint32_t max_blocks, float theta, uint32_t* status,
                            cudaStream_t stream);

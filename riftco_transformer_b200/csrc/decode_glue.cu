@@ -116,19 +116,24 @@ rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ delta, flo
 // items and of its v row, so a decode batch of a few dozen sequences still covers the SMs.
 __global__ void __launch_bounds__(256)
 rope_append_kernel(float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
-                   const uint32_t* __restrict__ positions, const uint32_t* __restrict__ block_tables,
+                   const uint32_t* __restrict__ positions, const uint32_t* __restrict__ token_seq,
+                   const uint32_t* __restrict__ block_tables,
                    float* __restrict__ k_pages, float* __restrict__ v_pages, uint32_t q_heads,
                    uint32_t kv_heads, uint32_t d, uint32_t block_size, uint64_t physical_blocks,
                    uint32_t max_blocks, float theta, uint32_t* status) {
     sm100::pdl_launch_dependents();   // a following decode GEMV may start its set-up now
+    // blockIdx.x is the token: row of q / k / v and entry of `positions`. With token_seq == nullptr
+    // every sequence contributes one token (a decode step) and the token index is the sequence;
+    // otherwise token_seq names the sequence - the block-table row - of each token (a prefill chunk).
     const uint32_t seq = blockIdx.x;
+    const uint32_t table_row = token_seq != nullptr ? token_seq[seq] : seq;
     const uint32_t pos = positions[seq];
     const uint32_t half = d / 2;
     // A position past the sequence's table row is treated like a bad block id: nothing is read from
     // the neighbouring row and no page is written.
     const uint32_t logical = pos / block_size;
     bool bad = logical >= max_blocks;
-    uint64_t phys = bad ? 0 : block_tables[static_cast<uint64_t>(seq) * max_blocks + logical];
+    uint64_t phys = bad ? 0 : block_tables[static_cast<uint64_t>(table_row) * max_blocks + logical];
     if (phys >= physical_blocks) {
         bad = true;
         phys = 0;
@@ -307,7 +312,8 @@ int32_t launch_rmsnorm(const float* x, const float* delta, float* x_out, const f
 }
 
 int32_t launch_rope_append(float* q, const float* k, const float* v, const uint32_t* positions,
-                           const uint32_t* block_tables, float* k_pages, float* v_pages, uint32_t n_seq,
+                           const uint32_t* token_seq, const uint32_t* block_tables, float* k_pages,
+                           float* v_pages, uint32_t n_seq,
                            uint32_t q_heads, uint32_t kv_heads, uint32_t d, uint32_t block_size,
                            uint64_t physical_blocks, uint32_t max_blocks, float theta, uint32_t* status,
                            cudaStream_t stream) {
@@ -315,7 +321,7 @@ int32_t launch_rope_append(float* q, const float* k, const float* v, const uint3
     const uint32_t pairs = (q_heads + kv_heads) * (d / 2);
     uint32_t slices = (pairs + 511u) / 512u;
     slices = slices == 0 ? 1u : (slices > 16u ? 16u : slices);
-    rope_append_kernel<<<dim3(n_seq, slices), 256, 0, stream>>>(q, k, v, positions, block_tables, k_pages, v_pages, q_heads,
+    rope_append_kernel<<<dim3(n_seq, slices), 256, 0, stream>>>(q, k, v, positions, token_seq, block_tables, k_pages, v_pages, q_heads,
                                                   kv_heads, d, block_size, physical_blocks, max_blocks, theta,
                                                   status);
     B2_CUDA_TRY(cudaGetLastError());

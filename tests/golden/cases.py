@@ -103,3 +103,13 @@ def decode_glue_inputs() -> dict:
         "cache_k": rng.standard_normal((18, 2, 8)).astype(np.float32),
         "cache_v": rng.standard_normal((18, 2, 8)).astype(np.float32),
     }
+
+
+def lora_inputs() -> dict:
+    """A small Linear with a low-rank adapter: x [5, 96], A [4, 96], B [40, 4], scale = alpha / rank."""
+    rng = np.random.default_rng(4040)
+    return {"x": rng.standard_normal((5, 96)).astype(np.float32),
+            "a": (rng.standard_normal((4, 96)) * 0.1).astype(np.float32),
+            "b": (rng.standard_normal((40, 4)) * 0.1).astype(np.float32),
+            "w": (rng.standard_normal((40, 96)) * 0.02).astype(np.float32),
+            "scale": np.float32(8.0 / 4.0)}

@@ -44,7 +44,8 @@ def payload_arrays(prefix: str, w: oracle.Nf4Weight) -> dict:
 
 
 from cases import (ROPE_POSITIONS, aligned_input, aligned_upstream, aligned_weight,  # noqa: E402
-                   decode_glue_inputs, edge_input, edge_upstream, edge_weight, paged_fixture, seeded_cases)
+                   decode_glue_inputs, edge_input, edge_upstream, edge_weight, lora_inputs, paged_fixture,
+                   seeded_cases)
 
 
 def main() -> None:
@@ -141,6 +142,12 @@ def main() -> None:
     k_rot = np.stack([ref.rope(g["cache_k"][t][None, :, None, :], t, 1e4)[0, :, 0, :] for t in range(steps)])
     q_rot = np.stack([ref.rope(g["cache_q"][t][None, :, None, :], t, 1e4)[0, :, 0, :] for t in range(steps)])
     out["glue_cache_context"] = ref.paged_cache_decode(q_rot, k_rot, g["cache_v"], 4, 5)
+
+    # -- LoRA branch of a Linear and the adapted NF4 linear (base + branch) ---------------------
+    lo = lora_inputs()
+    out["lora_branch"] = ref.lora_forward(lo["x"], lo["a"], lo["b"], float(lo["scale"]))
+    wl = ref.quantize_nf4(lo["w"], 32)
+    out["lora_adapted_linear"] = ref.linear_forward(wl, lo["x"]) + out["lora_branch"]
 
     # -- canonical packed model state written by the reference (RTNF4S1) ---------------------
     for name, scale_block in (("rtnf4_dq", 32), ("rtnf4_f32", 0)):

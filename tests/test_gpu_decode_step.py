@@ -221,3 +221,58 @@ def test_decode_step_with_and_without_the_bf16_handoff(monkeypatch):
         results.append((nxt.clone(), logits.clone(), step.ops.launches))
     assert torch.equal(results[0][1], results[1][1]) and torch.equal(results[0][0], results[1][0])
     assert results[0][2] == results[1][2] - (3 * cfg.layers + 1)   # one pass less per q/k/v, gate/up, down, LM head
+
+
+def test_rope_append_of_a_prefill_chunk():
+    """b2_rope_append_kv_tokens: a chunk of tokens of several sequences in one call writes exactly what
+    token-by-token calls write (same q, same K / V pages), and what the CPU restatement - pinned to the
+    reference's paged cache - says."""
+    from riftco_transformer_b200._lib import lib
+    from riftco_transformer_b200.backend import _check
+    dev = torch.device("cuda", 0)
+    rng = np.random.default_rng(21)
+    hq, hkv, d, bs, P, max_blocks = 8, 2, 128, 16, 24, 6
+    # tokens of three sequences, interleaved and out of order: (sequence, position)
+    toks = [(0, 0), (1, 17), (0, 1), (2, 95), (0, 2), (1, 18), (0, 15), (0, 16), (2, 64), (1, 16)]
+    tables = np.stack([rng.permutation(P)[:max_blocks] for _ in range(3)]).astype(np.int32)
+    # make the three rows disjoint so that no two tokens share a slot
+    tables = (np.arange(3 * max_blocks).reshape(3, max_blocks)).astype(np.int32) % P
+    q = rng.standard_normal((len(toks), hq, d)).astype(np.float32)
+    k = rng.standard_normal((len(toks), hkv, d)).astype(np.float32)
+    v = rng.standard_normal((len(toks), hkv, d)).astype(np.float32)
+    token_seq = np.array([s for s, _ in toks], np.int32)
+    positions = np.array([p for _, p in toks], np.int32)
+
+    def fresh():
+        return (torch.full((P, hkv, bs, d), 7.0, device=dev), torch.full((P, hkv, bs, d), -7.0, device=dev))
+
+    K1, V1 = fresh()
+    q1 = torch.from_numpy(q).to(dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    tt, tk, tv = torch.from_numpy(tables).to(dev), torch.from_numpy(k).to(dev), torch.from_numpy(v).to(dev)
+    _check(lib.b2_rope_append_kv_tokens(q1.data_ptr(), tk.data_ptr(), tv.data_ptr(), torch.from_numpy(positions).to(dev).data_ptr(),
+                                        torch.from_numpy(token_seq).to(dev).data_ptr(), tt.data_ptr(), K1.data_ptr(),
+                                        V1.data_ptr(), len(toks), hq, hkv, d, bs, P, max_blocks, 1e4, status.data_ptr(), None))
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    # token by token through the single-token entry point (one "sequence" per call)
+    K2, V2 = fresh()
+    q2 = torch.from_numpy(q).to(dev)
+    for t, (s, pos) in enumerate(toks):
+        row = torch.from_numpy(tables[s:s + 1]).to(dev)
+        _check(lib.b2_rope_append_kv(q2[t:t + 1].data_ptr(), tk[t:t + 1].data_ptr(), tv[t:t + 1].data_ptr(),
+                                     torch.tensor([pos], dtype=torch.int32, device=dev).data_ptr(), row.data_ptr(),
+                                     K2.data_ptr(), V2.data_ptr(), 1, hq, hkv, d, bs, P, max_blocks, 1e4, status.data_ptr(), None))
+    torch.cuda.synchronize()
+    assert torch.equal(q1, q2) and torch.equal(K1, K2) and torch.equal(V1, V2)
+    # against the CPU restatement
+    for t, (s, pos) in enumerate(toks):
+        page, slot = tables[s, pos // bs], pos % bs
+        assert rel_l2(q1[t].cpu().numpy(), decode_ref.rotate(q[t], pos, 1e4)) <= 1e-6
+        assert rel_l2(K1[page, :, slot].cpu().numpy(), decode_ref.rotate(k[t], pos, 1e4)) <= 1e-6
+        assert np.array_equal(V1[page, :, slot].cpu().numpy(), v[t])
+    written = sorted((int(tables[s, p // bs]), p % bs) for s, p in toks)
+    mask = torch.ones((P, bs), dtype=torch.bool, device=dev)
+    for page, slot in written:
+        mask[page, slot] = False
+    assert (V1.permute(0, 2, 1, 3)[mask] == -7.0).all() and (K1.permute(0, 2, 1, 3)[mask] == 7.0).all()

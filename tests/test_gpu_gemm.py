@@ -226,3 +226,62 @@ def test_input_backward_config3_remaining_cases(b2, port, out_f, in_f, dq):
     want = port.linear_input_backward(host, dy[idx].cpu().numpy())
     assert np.isfinite(dx).all()
     assert rel_l2(dx[idx], want) <= GEMM_TOL
+
+
+# ---- low-rank adapter branch --------------------------------------------------------------------
+
+def _lora_forward(b2, w, x, a, b, scale):
+    import ctypes as C
+
+    from riftco_transformer_b200._lib import lib
+    from riftco_transformer_b200.backend import _check
+    rows = x.shape[0]
+    y = torch.full((rows, w.out_features), float("nan"), device="cuda")
+    ws = w.struct()
+    need = lib.b2_nf4_linear_lora_workspace_bytes(C.byref(ws), rows, a.shape[0])
+    scratch = torch.empty(max(need, 16), dtype=torch.uint8, device="cuda")
+    _check(lib.b2_nf4_linear_forward_lora(C.byref(ws), x.data_ptr(), a.data_ptr(), b.data_ptr(), a.shape[0], scale,
+                                          y.data_ptr(), rows, scratch.data_ptr(), scratch.numel(), None))
+    b2.check_device_errors()
+    return y.cpu().numpy()
+
+
+def test_lora_reference_vector(b2, golden):
+    """The adapted linear of the golden file (written by the reference: base + ((x A^T) B^T) * scale)."""
+    import cases
+    from conftest import weight_from_golden  # noqa: F401
+    import oracle
+    lo = cases.lora_inputs()
+    host = oracle.port().quantize_nf4(lo["w"], 32)
+    w = b2.PackedNf4Weight.from_host(host)
+    got = _lora_forward(b2, w, torch.from_numpy(lo["x"]).cuda(), torch.from_numpy(lo["a"]).cuda(),
+                        torch.from_numpy(lo["b"]).cuda(), float(lo["scale"]))
+    assert rel_l2(got, golden["lora_adapted_linear"]) <= 2e-3
+
+
+@pytest.mark.parametrize("rows,out_f,in_f,rank,dq", [
+    (4, 4096, 4096, 16, True),       # decode rows: FP32-accumulate base kernel, tolerance 2e-3
+    (32, 1024, 4096, 8, True),       # decode batch on the tensor cores
+    (300, 1000, 1024, 64, False),    # prefill rows, ragged tiles, the largest rank
+    (17, 256, 512, 3, True),         # a rank that fills no vector
+])
+def test_lora_against_oracle(b2, port, rows, out_f, in_f, rank, dq):
+    rng = np.random.default_rng(rows + rank)
+    W = (rng.standard_normal((out_f, in_f)) * 0.02).astype(np.float32)
+    host = port.quantize_nf4_double_quantized(W, 64, 256) if dq else port.quantize_nf4(W, 64)
+    x = rng.standard_normal((rows, in_f)).astype(np.float32)
+    a = (rng.standard_normal((rank, in_f)) * 0.05).astype(np.float32)
+    b = (rng.standard_normal((out_f, rank)) * 0.05).astype(np.float32)
+    scale = 16.0 / rank
+    w = b2.PackedNf4Weight.from_host(host)
+    got = _lora_forward(b2, w, *(torch.from_numpy(t).cuda() for t in (x, a, b)), scale)
+    base = port.linear_forward(host, x)
+    branch = port.lora_forward(x, a, b, scale)
+    assert np.isfinite(got).all()
+    tol = 2e-3 if rows <= 16 else GEMM_TOL
+    assert rel_l2(got, base + branch) <= tol
+    # the branch on its own is FP32: subtracting the library's own base projection leaves it
+    assert rel_l2(got - forward(b2, w, torch.from_numpy(x).cuda()), branch) <= 1e-4
+    with pytest.raises(ValueError):
+        _lora_forward(b2, w, torch.from_numpy(x).cuda(), torch.from_numpy(np.zeros((65, in_f), np.float32)).cuda(),
+                      torch.from_numpy(np.zeros((out_f, 65), np.float32)).cuda(), 1.0)

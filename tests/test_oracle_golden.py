@@ -200,3 +200,11 @@ def test_rope_page_append_and_paged_attention_match_the_reference_cache(port, go
         V[table[t // page], :, t % page] = g["cache_v"][t]
         ctx = port.paged_decode(q, K, V, table, t + 1)
         assert (bits(ctx) == bits(golden["glue_cache_context"][t])).all(), t
+
+
+def test_lora_branch_matches_the_reference_bit_for_bit(port, golden):
+    lo = cases.lora_inputs()
+    got = port.lora_forward(lo["x"], lo["a"], lo["b"], float(lo["scale"]))
+    assert (bits(got) == bits(golden["lora_branch"])).all()
+    base = port.linear_forward(port.quantize_nf4(lo["w"], 32), lo["x"])
+    assert (bits(base + got) == bits(golden["lora_adapted_linear"])).all()
