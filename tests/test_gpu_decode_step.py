@@ -250,19 +250,23 @@ def test_rope_append_of_a_prefill_chunk():
     q1 = torch.from_numpy(q).to(dev)
     status = torch.zeros(1, dtype=torch.int32, device=dev)
     tt, tk, tv = torch.from_numpy(tables).to(dev), torch.from_numpy(k).to(dev), torch.from_numpy(v).to(dev)
-    _check(lib.b2_rope_append_kv_tokens(q1.data_ptr(), tk.data_ptr(), tv.data_ptr(), torch.from_numpy(positions).to(dev).data_ptr(),
-                                        torch.from_numpy(token_seq).to(dev).data_ptr(), tt.data_ptr(), K1.data_ptr(),
+    d_pos, d_seq = torch.from_numpy(positions).to(dev), torch.from_numpy(token_seq).to(dev)
+    _check(lib.b2_rope_append_kv_tokens(q1.data_ptr(), tk.data_ptr(), tv.data_ptr(), d_pos.data_ptr(),
+                                        d_seq.data_ptr(), tt.data_ptr(), K1.data_ptr(),
                                         V1.data_ptr(), len(toks), hq, hkv, d, bs, P, max_blocks, 1e4, status.data_ptr(), None))
     torch.cuda.synchronize()
     assert int(status.item()) == 0
     # token by token through the single-token entry point (one "sequence" per call)
     K2, V2 = fresh()
     q2 = torch.from_numpy(q).to(dev)
+    keep = []   # the calls only enqueue: their arguments must outlive the loop
     for t, (s, pos) in enumerate(toks):
         row = torch.from_numpy(tables[s:s + 1]).to(dev)
+        one = torch.tensor([pos], dtype=torch.int32, device=dev)
+        keep += [row, one]
         _check(lib.b2_rope_append_kv(q2[t:t + 1].data_ptr(), tk[t:t + 1].data_ptr(), tv[t:t + 1].data_ptr(),
-                                     torch.tensor([pos], dtype=torch.int32, device=dev).data_ptr(), row.data_ptr(),
-                                     K2.data_ptr(), V2.data_ptr(), 1, hq, hkv, d, bs, P, max_blocks, 1e4, status.data_ptr(), None))
+                                     one.data_ptr(), row.data_ptr(), K2.data_ptr(), V2.data_ptr(), 1, hq, hkv, d, bs, P,
+                                     max_blocks, 1e4, status.data_ptr(), None))
     torch.cuda.synchronize()
     assert torch.equal(q1, q2) and torch.equal(K1, K2) and torch.equal(V1, V2)
     # against the CPU restatement
