@@ -166,11 +166,14 @@ B2_API int32_t b2_nf4_linear_forward_lora(const b2_nf4_weight* weight, const flo
 /* Several packed linears of the SAME input in one call: ys[i][r,o] = sum_k x[r,k] * W_i[o,k]
  * for `count` weights with equal in_features (the q / k / v projections of an attention block,
  * the gate / up projections of a SwiGLU block: src/model/grouped_query_attention.cpp:61-94,
- * src/model/swiglu.cpp:27-29 apply them one after the other to the same tensor). Results are
- * those of `count` calls of b2_nf4_linear_forward with the same arguments; with more than 16
- * rows and up to four weights the activations are converted once and one kernel launch covers
- * every weight's tiles. Validation, workspace and stream rules as for b2_nf4_linear_forward
- * (the workspace need is that of any single one of the calls). */
+ * src/model/swiglu.cpp:27-29 apply them one after the other to the same tensor). With more
+ * than 16 rows and up to four weights the activations are converted once and one kernel launch
+ * covers every weight's tiles. Results agree with `count` calls of b2_nf4_linear_forward on the
+ * same arguments to FP32 summation order (the persistent decode kernel cuts the contraction of
+ * a tile where its work list says, and the list depends on how many tiles one launch holds):
+ * relative L2 difference <= 1e-5, and bit-for-bit from one call of this function to the next.
+ * Validation, workspace and stream rules as for b2_nf4_linear_forward (the workspace need is
+ * that of any single one of the calls). */
 B2_API int32_t b2_nf4_linear_forward_multi(const b2_nf4_weight* weights, uint32_t count, const float* x,
                                     float* const* ys, uint64_t rows, void* workspace,
                                     size_t workspace_bytes, void* stream);
@@ -388,6 +391,25 @@ B2_API int32_t b2_argmax(const float* logits, uint32_t* out, uint32_t rows, uint
  * reads a device status word the same way after its kernels
  * (src/core/backend/attention/cuda/common.cuh:124-133). */
 B2_API int32_t b2_check_device_errors(void);
+
+/* Which kernel family served the calling thread's last linear or attention call. The library
+ * picks the kernel from the request's shape and alignment alone; every family computes the
+ * result the reference's dispatch_quantized_linear_forward / _input_backward
+ * (src/core/backend/nn/quantized_linear/dispatch.cpp:317-370) and
+ * dispatch_paged_decode_attention_forward define. This entry lets a test assert that a shape
+ * reached the path it is meant to cover. Needs no GPU. */
+#define B2_ROUTE_NONE 0
+#define B2_ROUTE_DECODE_TMEM 1      /* persistent tcgen05 decode kernel, up to 32 rows */
+#define B2_ROUTE_GEMV_TMA 2         /* TMA-fed mma.sync decode kernel, up to 16 rows per pass */
+#define B2_ROUTE_GEMV_TILE 3        /* tiled mma.sync decode kernel: any out_features, in % 64 == 0 */
+#define B2_ROUTE_GEMM_TMEM 4        /* tcgen05 GEMM, expanded weight tile in tensor memory */
+#define B2_ROUTE_GEMM_SMEM 5        /* tcgen05 GEMM that transposes the nibbles inside the SM: input
+                                     * backward of 33..511 rows */
+#define B2_ROUTE_BACKWARD_DENSE 6   /* input backward: transposed bf16 expansion + tcgen05 GEMM */
+#define B2_ROUTE_GENERIC 7          /* FP32 SIMT kernels, any shape */
+#define B2_ROUTE_ATTENTION_BULK 8   /* head_width 128, block_size 16, rep in {1,2,4,8} */
+#define B2_ROUTE_ATTENTION_GENERIC 9
+B2_API int32_t b2_last_route(void);
 
 /* ---- host-buffer seam --------------------------------------------------- */
 /*

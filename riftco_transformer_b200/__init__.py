@@ -20,6 +20,7 @@ _EXPORTS = (
     "host_quantized_linear_forward",
     "host_quantized_linear_input_backward",
     "is_available",
+    "last_route",
     "paged_decode_attention",
     "quantize_nf4",
     "unavailability_reason",

@@ -78,6 +78,16 @@ def check_device_errors() -> None:
     _check(lib.b2_check_device_errors())
 
 
+ROUTES = ("none", "decode_tmem", "gemv_tma", "gemv_tile", "gemm_tmem", "gemm_smem", "backward_dense",
+          "generic", "attention_bulk", "attention_generic")
+
+
+def last_route() -> str:
+    """The kernel family that served this thread's last linear or attention call
+    (B2_ROUTE_* of the header, by name)."""
+    return ROUTES[lib.b2_last_route()]
+
+
 def _stream_ptr(stream) -> int:
     if stream is None:
         stream = torch.cuda.current_stream()

@@ -50,6 +50,11 @@ bool mul_overflows(uint64_t a, uint64_t b, uint64_t* out) {
 
 }  // namespace
 
+// The kernel family the calling thread's last linear or attention call was served by, so that a
+// test can tell which path a shape took.
+thread_local int32_t g_last_route = B2_ROUTE_NONE;
+void note_route(int32_t route) { g_last_route = route; }
+
 int32_t fail(int32_t status, const char* format, ...) {
     char buffer[512];
     va_list args;
@@ -256,19 +261,19 @@ bool aliases_weight(const b2_nf4_weight* weight, const void* p) {
 }
 
 
-// Which kernel serves a forward call of `rows` rows. B2_DECODE_IMPL selects for measurements:
-//   unset  rows 17..32 on the persistent decode kernel, rows <= 16 on the mma.sync decode kernel
-//   tmem   every batch of up to 32 rows on the persistent decode kernel
-//   old    the kernels in use before it (mma.sync up to 16 rows, the prefill kernel above)
+// Which decode kernel serves a forward call of up to 32 rows: 17..32 rows go to the persistent
+// tcgen05 decode kernel, fewer to the mma.sync decode kernel. B2_DECODE_IMPL=tmem sends every
+// batch of up to 32 rows to the persistent kernel (its fp16 form for up to 16 rows is tested
+// that way).
 bool decode_tmem_wanted(uint64_t rows) {
     static const char* impl = getenv("B2_DECODE_IMPL");
-    static const char* gemm_off = getenv("B2_DISABLE_TENSOR_GEMM");
-    if (gemm_off != nullptr || rows > 32) return false;
-    if (impl != nullptr && strcmp(impl, "old") == 0) return false;
+    if (rows > 32) return false;
     if (impl != nullptr && strcmp(impl, "tmem") == 0) return true;
     return rows > 16;
 }
 
+// The kernel family the calling thread's last linear or attention call was served by
+// (B2_ROUTE_* of the header), so that a test can tell which path a shape took.
 size_t pad256(size_t v) { return (v + 255) & ~size_t{255}; }
 
 // Scratch of the persistent decode kernel when the caller passes FP32 activations: their 16-bit
@@ -348,18 +353,13 @@ int32_t linear_forward_impl(const b2_nf4_weight* weight, const float* x, float* 
     }
     if (decode_tmem_takes(&w, 1, x, rows)) {
         float* ys[1] = {y};
+        note_route(B2_ROUTE_DECODE_TMEM);
         return decode_tmem_forward(ctx, &w, ys, 1, x, nullptr, rows, workspace, workspace_bytes, stream);
     }
-    static const char* gemm_off = getenv("B2_DISABLE_TENSOR_GEMM");
     // More than 16 batch rows: the tcgen05 kernel that keeps the expanded weight tile in tensor
-    // memory (decode batches of 17+ rows, speculative / chunked prefill, full prefill).
-    // B2_GEMM_IMPL=smem sends 17..32 rows to the decode GEMV and the rest to the shared-memory
-    // tcgen05 kernel instead; B2_LINEAR_IMPL=tmem sends every batch size here (A/B measurements).
-    static const char* gemm_impl = getenv("B2_GEMM_IMPL");
-    static const char* linear_impl = getenv("B2_LINEAR_IMPL");
-    const bool tmem_all = linear_impl != nullptr && strcmp(linear_impl, "tmem") == 0;
-    const bool tmem_off = gemm_impl != nullptr && strcmp(gemm_impl, "smem") == 0;
-    if (gemm_off == nullptr && !tmem_off && (rows > 16 || tmem_all) && nf4_gemm_tmem_supported(w, x, rows)) {
+    // memory (speculative / chunked prefill, full prefill, and decode batches whose shape the
+    // persistent decode kernel does not take).
+    if (rows > 16 && nf4_gemm_tmem_supported(w, x, rows)) {
         const size_t need = nf4_gemm_tmem_workspace_bytes(w, rows);
         if (workspace == nullptr) {
             B2_TRY(reserve_arena(ctx, need, stream));
@@ -372,57 +372,32 @@ int32_t linear_forward_impl(const b2_nf4_weight* weight, const float* x, float* 
         if ((reinterpret_cast<uintptr_t>(workspace) & 15u) != 0) {
             return fail(B2_STATUS_INVALID_ARGUMENT, "NF4 GEMM workspace must be 16-byte aligned");
         }
+        note_route(B2_ROUTE_GEMM_TMEM);
         B2_TRY(launch_f32_to_bf16(*ctx, x, workspace, rows * w.in_features, stream));
         return launch_nf4_gemm_tmem(*ctx, w, workspace, y, rows, stream);
     }
     if (nf4_gemv_supported(w, x, y, rows)) {
-        // B2_GEMV_IMPL=tile forces the non-persistent kernel (for A/B measurements).
-        static const char* impl = getenv("B2_GEMV_IMPL");
-        uint32_t spw = 0, ksplit = 0;
-        // Default: the TMA-fed kernel (rows <= 16; 17..32 as two passes). B2_GEMV_IMPL=stream / tile
-        // select the register-pipelined and the tiled kernels for A/B measurements.
-        if (impl == nullptr || strcmp(impl, "tma") == 0) {
-            uint32_t per = 0;
-            if (nf4_gemv_tma_plan(*ctx, w, x, rows, &ksplit, &per)) {
-                return launch_nf4_gemv_tma(*ctx, w, x, y, rows, ksplit, per, stream);
-            }
-            if (rows > 16 && nf4_gemv_tma_plan(*ctx, w, x, 16, &ksplit, &per)) {
+        // Up to 32 rows: the TMA-fed mma.sync decode kernel (17..32 rows as two passes; the second
+        // finds the packed weight in L2), else the tiled decode kernel, which takes any row count
+        // of the weight.
+        uint32_t ksplit = 0, per = 0;
+        if (nf4_gemv_tma_plan(*ctx, w, x, rows, &ksplit, &per)) {
+            note_route(B2_ROUTE_GEMV_TMA);
+            return launch_nf4_gemv_tma(*ctx, w, x, y, rows, ksplit, per, stream);
+        }
+        if (rows > 16 && nf4_gemv_tma_plan(*ctx, w, x, 16, &ksplit, &per)) {
+            uint32_t ks2 = 0, per2 = 0;
+            if (nf4_gemv_tma_plan(*ctx, w, x + 16 * w.in_features, rows - 16, &ks2, &per2)) {
+                note_route(B2_ROUTE_GEMV_TMA);
                 B2_TRY(launch_nf4_gemv_tma(*ctx, w, x, y, 16, ksplit, per, stream));
-                uint32_t ks2 = 0, per2 = 0;
-                if (nf4_gemv_tma_plan(*ctx, w, x + 16 * w.in_features, rows - 16, &ks2, &per2)) {
-                    return launch_nf4_gemv_tma(*ctx, w, x + 16 * w.in_features, y + 16 * w.out_features,
-                                               rows - 16, ks2, per2, stream);
-                }
-                return fail(B2_STATUS_RUNTIME_ERROR, "internal: TMA decode plan failed for the second pass");
+                return launch_nf4_gemv_tma(*ctx, w, x + 16 * w.in_features, y + 16 * w.out_features,
+                                           rows - 16, ks2, per2, stream);
             }
         }
-        if ((impl == nullptr || strcmp(impl, "tile") != 0) &&
-            nf4_gemv_stream_plan(*ctx, w, rows, &spw, &ksplit)) {
-            return launch_nf4_gemv_stream(*ctx, w, x, y, rows, spw, ksplit, stream);
-        }
-        // 17..32 rows: two passes of the streaming kernel over 16 rows each. The second pass finds
-        // the packed weight in L2 (a 7B-class layer is at most ~30 MB), so HBM is still read once.
-        if ((impl == nullptr || strcmp(impl, "tile") != 0) && rows > 16 &&
-            nf4_gemv_stream_plan(*ctx, w, 16, &spw, &ksplit)) {
-            B2_TRY(launch_nf4_gemv_stream(*ctx, w, x, y, 16, spw, ksplit, stream));
-            const uint64_t rest = rows - 16;
-            uint32_t spw2 = 0, ks2 = 0;
-            if (nf4_gemv_stream_plan(*ctx, w, rest, &spw2, &ks2)) {
-                return launch_nf4_gemv_stream(*ctx, w, x + 16 * w.in_features, y + 16 * w.out_features, rest,
-                                              spw2, ks2, stream);
-            }
-        }
+        note_route(B2_ROUTE_GEMV_TILE);
         return launch_nf4_gemv(*ctx, w, x, y, rows, stream);
     }
-    if (gemm_off == nullptr && nf4_gemm_supported(w, x, rows, false)) {
-        const size_t need = nf4_gemm_workspace_bytes(w, rows, false);
-        if (workspace == nullptr) {
-            B2_TRY(reserve_arena(ctx, need, stream));
-            workspace = ctx->arena;
-            workspace_bytes = ctx->arena_bytes;
-        }
-        return launch_nf4_gemm(*ctx, w, x, y, rows, false, workspace, workspace_bytes, stream);
-    }
+    note_route(B2_ROUTE_GENERIC);
     return launch_nf4_linear_forward_generic(*ctx, w, x, y, rows, stream);
 }
 
@@ -445,29 +420,29 @@ int32_t linear_backward_impl(const b2_nf4_weight* weight, const float* dy, float
     if (aliases_weight(weight, dx)) {
         return fail(B2_STATUS_INVALID_ARGUMENT, "quantized linear weight and output storage must not alias");
     }
-    static const char* gemm_off = getenv("B2_DISABLE_TENSOR_GEMM");
-    // From 512 rows: expand W once, transposed, into scratch and run a plain bf16 tcgen05 GEMM
-    // (B2_BACKWARD_IMPL=fused keeps the kernel that transposes nibbles inside the SM).
-    static const char* backward_impl = getenv("B2_BACKWARD_IMPL");
-    const bool dense_off = backward_impl != nullptr && strcmp(backward_impl, "fused") == 0;
-    if (gemm_off == nullptr && !dense_off && nf4_backward_dense_supported(w, dy, rows)) {
+    // From 512 rows: expand W once, transposed, into scratch and run a plain bf16 tcgen05 GEMM;
+    // below that the kernel that transposes nibbles inside the SM.
+    if (nf4_backward_dense_supported(w, dy, rows)) {
         const size_t need = nf4_backward_dense_workspace_bytes(w, rows);
         if (workspace == nullptr) {
             B2_TRY(reserve_arena(ctx, need, stream));
             workspace = ctx->arena;
             workspace_bytes = ctx->arena_bytes;
         }
+        note_route(B2_ROUTE_BACKWARD_DENSE);
         return launch_nf4_backward_dense(*ctx, w, dy, dx, rows, workspace, workspace_bytes, stream);
     }
-    if (gemm_off == nullptr && nf4_gemm_supported(w, dy, rows, true)) {
+    if (nf4_gemm_supported(w, dy, rows, true)) {
         const size_t need = nf4_gemm_workspace_bytes(w, rows, true);
         if (workspace == nullptr) {
             B2_TRY(reserve_arena(ctx, need, stream));
             workspace = ctx->arena;
             workspace_bytes = ctx->arena_bytes;
         }
+        note_route(B2_ROUTE_GEMM_SMEM);
         return launch_nf4_gemm(*ctx, w, dy, dx, rows, true, workspace, workspace_bytes, stream);
     }
+    note_route(B2_ROUTE_GENERIC);
     return launch_nf4_linear_input_backward_generic(*ctx, w, dy, dx, rows, stream);
 }
 
@@ -695,10 +670,7 @@ int32_t b2_nf4_linear_forward_multi(const b2_nf4_weight* weights, uint32_t count
     if (ctx == nullptr) return status;
     // One launch when every weight can take the tensor-memory kernel on the same activations;
     // otherwise the calls are simply made one after the other.
-    static const char* gemm_off = getenv("B2_DISABLE_TENSOR_GEMM");
-    static const char* gemm_impl = getenv("B2_GEMM_IMPL");
-    const bool tmem_off = gemm_off != nullptr || (gemm_impl != nullptr && strcmp(gemm_impl, "smem") == 0);
-    bool fused = !tmem_off && (rows > 16 || decode_tmem_wanted(rows)) && count <= 4 && count > 1 && x != nullptr;
+    bool fused = (rows > 16 || decode_tmem_wanted(rows)) && count <= 4 && count > 1 && x != nullptr;
     WeightView views[4];
     for (uint32_t i = 0; fused && i < count; ++i) {
         if (ys[i] == nullptr || x == ys[i] || aliases_weight(&weights[i], ys[i]) ||
@@ -716,6 +688,7 @@ int32_t b2_nf4_linear_forward_multi(const b2_nf4_weight* weights, uint32_t count
         return B2_STATUS_OK;
     }
     if (decode_tmem_takes(views, count, x, rows)) {
+        note_route(B2_ROUTE_DECODE_TMEM);
         return decode_tmem_forward(ctx, views, ys, count, x, nullptr, rows, workspace, workspace_bytes, stream);
     }
     if (rows <= 16) {   // the prefill kernel is not used for so few rows: one call per weight
@@ -736,6 +709,7 @@ int32_t b2_nf4_linear_forward_multi(const b2_nf4_weight* weights, uint32_t count
     if ((reinterpret_cast<uintptr_t>(workspace) & 15u) != 0) {
         return fail(B2_STATUS_INVALID_ARGUMENT, "NF4 GEMM workspace must be 16-byte aligned");
     }
+    note_route(B2_ROUTE_GEMM_TMEM);
     B2_TRY(launch_f32_to_bf16(*ctx, x, workspace, rows * views[0].in_features, stream));
     return launch_nf4_gemm_tmem_multi(*ctx, views, ys, count, workspace, rows, stream);
 }
@@ -764,9 +738,11 @@ size_t b2_nf4_linear_workspace_bytes(const b2_nf4_weight* weight, uint64_t rows,
     if (backward != 0 && nf4_backward_dense_supported(w, reinterpret_cast<const float*>(16), rows)) {
         return nf4_backward_dense_workspace_bytes(w, rows);
     }
-    if (!nf4_gemm_supported(w, reinterpret_cast<const float*>(16), rows, backward != 0)) return 0;
-    return nf4_gemm_workspace_bytes(w, rows, backward != 0);
+    if (backward == 0 || !nf4_gemm_supported(w, reinterpret_cast<const float*>(16), rows, true)) return 0;
+    return nf4_gemm_workspace_bytes(w, rows, true);
 }
+
+int32_t b2_last_route(void) { return g_last_route; }
 
 size_t b2_paged_decode_workspace_bytes(uint32_t n_seq, uint32_t q_heads, uint32_t head_width,
                                        uint32_t block_size, uint32_t max_seq_len) {
@@ -812,9 +788,6 @@ namespace {
 // matrix of `rows` rows; false when any of them cannot.
 bool bf16_input_views(const b2_nf4_weight* weights, uint32_t count, const void* x_bf16, uint64_t rows,
                       WeightView* views) {
-    static const char* gemm_off = getenv("B2_DISABLE_TENSOR_GEMM");
-    static const char* gemm_impl = getenv("B2_GEMM_IMPL");
-    if (gemm_off != nullptr || (gemm_impl != nullptr && strcmp(gemm_impl, "smem") == 0)) return false;
     if (weights == nullptr || count == 0 || count > 4 || rows <= 16) return false;
     for (uint32_t i = 0; i < count; ++i) {
         if (make_weight_view(&weights[i], &views[i]) != B2_STATUS_OK ||
@@ -866,9 +839,11 @@ int32_t b2_nf4_linear_forward_multi_bf16(const b2_nf4_weight* weights, uint32_t 
     }
     clear_error();
     if (decode_tmem_takes(views, count, x_bf16, rows)) {
+        note_route(B2_ROUTE_DECODE_TMEM);
         return decode_tmem_forward(ctx, views, ys, count, nullptr, x_bf16, rows, nullptr, 0,
                                    static_cast<cudaStream_t>(stream_ptr));
     }
+    note_route(B2_ROUTE_GEMM_TMEM);
     return launch_nf4_gemm_tmem_multi(*ctx, views, ys, count, x_bf16, rows, static_cast<cudaStream_t>(stream_ptr));
 }
 

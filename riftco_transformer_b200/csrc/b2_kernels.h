@@ -33,17 +33,14 @@ int32_t launch_nf4_linear_input_backward_generic(const DeviceContext& ctx, const
                                                  const float* dy, float* dx, uint64_t rows,
                                                  cudaStream_t stream);
 
-// nf4_gemv.cu - decode path, rows <= 32.
+// Records the kernel family (B2_ROUTE_*) that serves the calling thread's current call.
+void note_route(int32_t route);
+
+// nf4_gemv.cu - tiled decode kernel, rows <= 32, any row count of the weight.
 bool nf4_gemv_supported(const WeightView& w, const float* x, const float* y, uint64_t rows);
 int32_t launch_nf4_gemv(const DeviceContext& ctx, const WeightView& w, const float* x, float* y,
                         uint64_t rows, cudaStream_t stream);
 int32_t init_gemv_lut(DeviceContext* ctx);
-
-// nf4_gemv_stream.cu - persistent, software-pipelined decode kernel, rows <= 16.
-bool nf4_gemv_stream_plan(const DeviceContext& ctx, const WeightView& w, uint64_t rows,
-                          uint32_t* spw_out, uint32_t* ksplit_out);
-int32_t launch_nf4_gemv_stream(const DeviceContext& ctx, const WeightView& w, const float* x, float* y,
-                               uint64_t rows, uint32_t spw, uint32_t ksplit, cudaStream_t stream);
 
 // nf4_gemv_tma.cu - TMA-fed decode kernel, rows <= 16.
 bool nf4_gemv_tma_plan(const DeviceContext& ctx, const WeightView& w, const float* x, uint64_t rows,

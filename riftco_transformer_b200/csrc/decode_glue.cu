@@ -44,7 +44,7 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
 // rows, so a row gets up to 1024 threads, 16-byte accesses, and its values stay
 // in registers between the two passes when they fit (two float4 per thread).
 __global__ void __launch_bounds__(1024)
-rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ delta, float* __restrict__ x_out,
+rmsnorm_kernel(const float* x, const float* __restrict__ delta, float* x_out,   // x_out may be x
                const float* __restrict__ scale, float* __restrict__ y, __nv_bfloat16* __restrict__ y16,
                uint32_t width, float eps, uint32_t vec4) {
     sm100::pdl_launch_dependents();   // a following linear kernel may start its set-up now
@@ -201,7 +201,7 @@ __device__ __forceinline__ float silu_ref(float value) {
 }
 
 __global__ void __launch_bounds__(256)
-silu_mul_kernel(const float* __restrict__ gate, const float* __restrict__ up, float* __restrict__ out,
+silu_mul_kernel(const float* gate, const float* up, float* out,   // out may be gate or up
                 __nv_bfloat16* __restrict__ out16, uint64_t n) {
     sm100::pdl_launch_dependents();   // a following decode GEMV may start its set-up now
     const uint64_t stride = static_cast<uint64_t>(gridDim.x) * blockDim.x;
@@ -213,7 +213,7 @@ silu_mul_kernel(const float* __restrict__ gate, const float* __restrict__ up, fl
 }
 
 __global__ void __launch_bounds__(256)
-add_kernel(const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ out, uint64_t n) {
+add_kernel(const float* a, const float* b, float* out, uint64_t n) {   // out may be a or b
     sm100::pdl_launch_dependents();   // a following decode GEMV may start its set-up now
     const uint64_t stride = static_cast<uint64_t>(gridDim.x) * blockDim.x;
     for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {

@@ -925,11 +925,10 @@ int32_t launch_nf4_decode_tmem(const DeviceContext& ctx, const WeightView* ws, f
     config.dynamicSmemBytes = kSmemBytes;
     config.stream = stream;
     cudaLaunchAttribute attr[1];
-    static const bool pdl = getenv("B2_DISABLE_PDL") == nullptr;
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     config.attrs = attr;
-    config.numAttrs = pdl ? 1 : 0;
+    config.numAttrs = 1;
     if (half) {
         B2_CUDA_TRY(cudaLaunchKernelEx(&config, nf4_decode_tmem_kernel<true>, maps, map_x, p));
     } else {

@@ -1,8 +1,9 @@
 // Packed-NF4 linear on the 5th-generation tensor cores with the expanded weight tile in SHARED
 // memory:
-//   backward  dX[M, in] = dY[M, out] * W[out, in]      (the kernel in use for rows > 32)
-//   forward   Y[M, out] = X[M, in] * W[out, in]^T      (B2_GEMM_IMPL=smem; the default forward
-//                                                      kernel is nf4_gemm_tmem.cu)
+//   backward  dX[M, in] = dY[M, out] * W[out, in]      (in use for 33..511 rows; from 512 rows
+//                                                      nf4_backward_dense.cu)
+//   (the template's forward form, Y = X * W^T, is not instantiated: the library's forward
+//   calls go to nf4_gemm_tmem.cu and nf4_decode_tmem.cu)
 // (reference loops: src/core/backend/nn/quantized_linear/reference/operations.cpp:49-115).
 //
 // One CTA owns a 256 x 256 output tile as two 128 x 256 FP32 accumulators in
@@ -503,9 +504,10 @@ size_t nf4_gemm_workspace_bytes(const WeightView& w, uint64_t rows, bool backwar
 
 int32_t launch_nf4_gemm(const DeviceContext& ctx, const WeightView& w, const float* x, float* y, uint64_t rows,
                         bool backward, void* workspace, size_t workspace_bytes, cudaStream_t stream) {
-    const uint64_t k = backward ? w.out_features : w.in_features;
-    const uint64_t n = backward ? w.in_features : w.out_features;
-    const size_t need = nf4_gemm_workspace_bytes(w, rows, backward);
+    if (!backward) return fail(B2_STATUS_RUNTIME_ERROR, "internal: this kernel serves the input backward only");
+    const uint64_t k = w.out_features;
+    const uint64_t n = w.in_features;
+    const size_t need = nf4_gemm_workspace_bytes(w, rows, true);
     if (workspace == nullptr || workspace_bytes < need) {
         return fail(B2_STATUS_INVALID_ARGUMENT, "NF4 GEMM workspace too small: need %zu bytes", need);
     }
@@ -523,8 +525,6 @@ int32_t launch_nf4_gemm(const DeviceContext& ctx, const WeightView& w, const flo
     B2_TRY(make_operand_map(&map, workspace, rows, k));
     static PerDeviceOnce configured;
     B2_TRY(once_per_device(configured, ctx.device, []() -> int32_t {
-        B2_CUDA_TRY(cudaFuncSetAttribute(nf4_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         kSmemBytes));
         B2_CUDA_TRY(cudaFuncSetAttribute(nf4_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          kSmemBytes));
         return B2_STATUS_OK;
@@ -538,11 +538,7 @@ int32_t launch_nf4_gemm(const DeviceContext& ctx, const WeightView& w, const flo
     p.error = ctx.gemm_error;
     p.lut = ctx.gemm_lut;
     const dim3 grid(static_cast<unsigned>((n + kBN - 1) / kBN), static_cast<unsigned>((rows + kBM - 1) / kBM));
-    if (backward) {
-        nf4_gemm_kernel<true><<<grid, kThreads, kSmemBytes, stream>>>(map, p);
-    } else {
-        nf4_gemm_kernel<false><<<grid, kThreads, kSmemBytes, stream>>>(map, p);
-    }
+    nf4_gemm_kernel<true><<<grid, kThreads, kSmemBytes, stream>>>(map, p);
     B2_CUDA_TRY(cudaGetLastError());
     return B2_STATUS_OK;
 }

@@ -477,12 +477,11 @@ int32_t launch_nf4_gemm_tmem_multi(const DeviceContext& ctx, const WeightView* w
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = ksplit;
     // The kernel calls griddepcontrol.wait before it touches a caller tensor, so it may be
-    // scheduled while the conversion pre-pass drains. B2_DISABLE_PDL=1 restores plain stream order.
-    static const bool pdl = getenv("B2_DISABLE_PDL") == nullptr;
+    // scheduled while the conversion pre-pass drains.
     attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     config.attrs = attr;
-    config.numAttrs = pdl ? 2 : 1;
+    config.numAttrs = 2;
     B2_CUDA_TRY(cudaLaunchKernelEx(&config, nf4_gemm_tmem_kernel, map, p));
     return B2_STATUS_OK;
 }

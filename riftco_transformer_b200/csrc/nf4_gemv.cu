@@ -315,14 +315,13 @@ __global__ void gemv_lut_init_kernel(uint32_t* lut) {
 
 template <int MT>
 int32_t launch_config(const DeviceContext& ctx, const GemvParams& p, uint32_t ksplit, cudaStream_t stream) {
-    (void)ctx;
     using S = Smem<MT>;
     auto kernel = nf4_gemv_kernel<MT>;
-    static bool configured = false;  // per template instance
-    if (!configured) {
+    static PerDeviceOnce configured;  // per template instance
+    B2_TRY(once_per_device(configured, ctx.device, [&]() -> int32_t {
         B2_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal));
-        configured = true;
-    }
+        return B2_STATUS_OK;
+    }));
     const uint32_t row_tiles = static_cast<uint32_t>((p.w.out_features + kRowsTile - 1) / kRowsTile);
     cudaLaunchConfig_t config = {};
     config.gridDim = dim3(row_tiles * ksplit);
@@ -358,7 +357,6 @@ bool nf4_gemv_supported(const WeightView& w, const float* x, const float* y, uin
            w.out_features <= 0x3FFFFFFFull;
 }
 
-// B2_GEMV_KSPLIT (1..8) overrides the cluster size along the contraction, for experiments.
 int32_t launch_nf4_gemv(const DeviceContext& ctx, const WeightView& w, const float* x, float* y,
                         uint64_t rows, cudaStream_t stream) {
     GemvParams p;
@@ -372,11 +370,6 @@ int32_t launch_nf4_gemv(const DeviceContext& ctx, const WeightView& w, const flo
     // One chunk per cluster rank where the portable cluster limit of 8 allows.
     uint32_t ksplit = (p.steps_total + chunk - 1) / chunk;
     if (ksplit > 8) ksplit = 8;
-    static const char* env_ks = getenv("B2_GEMV_KSPLIT");
-    if (env_ks != nullptr) {
-        const int v = atoi(env_ks);
-        if (v >= 1 && v <= 8) ksplit = static_cast<uint32_t>(v);
-    }
     p.steps_per_cta = (p.steps_total + ksplit - 1) / ksplit;
     if (rows <= 8) return launch_config<1>(ctx, p, ksplit, stream);
     if (rows <= 16) return launch_config<2>(ctx, p, ksplit, stream);

@@ -533,13 +533,11 @@ int32_t launch_tma(const DeviceContext& ctx, const CUtensorMap& map_w, const CUt
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
     // Programmatic stream serialisation: the kernel may start while its predecessor drains; it
-    // calls griddepcontrol.wait before it reads or writes any caller tensor. B2_DISABLE_PDL=1
-    // restores plain stream order.
-    static const bool pdl = getenv("B2_DISABLE_PDL") == nullptr;
+    // calls griddepcontrol.wait before it reads or writes any caller tensor.
     attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     config.attrs = attr;
-    config.numAttrs = pdl ? 2 : 1;
+    config.numAttrs = 2;
     config.gridDim = dim3(clusters * ksplit);
     B2_CUDA_TRY(cudaLaunchKernelEx(&config, kernel, map_w, map_s, map_2, p));
     return B2_STATUS_OK;

@@ -11,7 +11,7 @@
 // that read: 8 * head_width bytes per (token, kv head).
 //
 // Two paths:
-//  * paged_decode_fast_kernel  - head_width 128, block_size 16, rep in {1,2,4,8}.
+//  * paged_decode_bulk_kernel  - head_width 128, block_size 16, rep in {1,2,4,8}.
 //  * paged_decode_generic_*    - any shape (the reference's own test uses
 //    head_width 3 and block_size 2), scores spilled to workspace.
 // Non-finite scores are reported through a device status word, never by
@@ -35,202 +35,8 @@ constexpr int kFastWarps = 4;
 constexpr int kTokensPerCta = 256; // split size: 16 pages, 4 per warp
 constexpr int kPartialStride = kD + 2;  // m, l, acc[128]
 
-__device__ __forceinline__ float4 ldg_stream_f4(const float* p) {
-    float4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.f32 {%0,%1,%2,%3}, [%4];\n"
-                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
-                 : "l"(p));
-    return v;
-}
-
-template <int REP>
-__global__ void __launch_bounds__(kFastWarps * 32)
-paged_decode_fast_kernel(const PagedDecodeArgs a, float* __restrict__ partials, uint32_t max_splits) {
-    sm100::pdl_launch_dependents();   // a following decode GEMV may start its set-up now
-    const uint32_t split = blockIdx.x, kvh = blockIdx.y, seq = blockIdx.z;
-    const uint32_t len = __ldg(a.seq_lens + seq);
-    const uint32_t n_splits = (len + kTokensPerCta - 1) / kTokensPerCta;
-    if (split >= n_splits) return;
-
-    const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
-    const uint32_t grp = lane >> 3, sub = lane & 7u;
-    const float scale = 1.0f / sqrtf(static_cast<float>(kD));
-
-    __shared__ __align__(16) float s_p[kFastWarps][kPage][REP];
-    __shared__ float s_m[kFastWarps][REP], s_l[kFastWarps][REP];
-    __shared__ __align__(16) float s_acc[kFastWarps][REP][kD];
-
-    // Query slices used by the score phase: dims 4*sub + 32*j .. +3.
-    float4 q[REP][4];
-    const float* qbase = a.q + (static_cast<uint64_t>(seq) * a.q_heads + kvh * REP) * kD;
-#pragma unroll
-    for (int h = 0; h < REP; ++h)
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-            q[h][j] = __ldg(reinterpret_cast<const float4*>(qbase + h * kD + 4 * sub + 32 * j));
-
-    float m[REP], l[REP];
-    float4 acc[REP];
-#pragma unroll
-    for (int h = 0; h < REP; ++h) {
-        m[h] = -INFINITY;
-        l[h] = 0.0f;
-        acc[h] = make_float4(0.f, 0.f, 0.f, 0.f);
-    }
-    uint32_t flags = 0;
-
-    const uint32_t tok_begin = split * kTokensPerCta;
-    const uint32_t tok_end = min(tok_begin + kTokensPerCta, len);
-    const uint32_t page_begin = tok_begin / kPage;
-    const uint32_t page_end = (tok_end + kPage - 1) / kPage;
-    const uint32_t* table = a.block_tables + static_cast<uint64_t>(seq) * a.max_blocks;
-    const uint64_t page_stride = static_cast<uint64_t>(a.kv_heads) * kPage * kD;
-
-    for (uint32_t pg = page_begin + warp; pg < page_end; pg += kFastWarps) {
-        uint64_t phys = __ldg(table + pg);
-        if (phys >= a.physical_blocks) {
-            flags |= B2_ATTN_STATUS_BAD_BLOCK;
-            phys = 0;
-        }
-        const float* kp = a.k_pages + phys * page_stride + static_cast<uint64_t>(kvh) * kPage * kD;
-        const float* vp = a.v_pages + phys * page_stride + static_cast<uint64_t>(kvh) * kPage * kD;
-        const uint32_t valid = min(static_cast<uint32_t>(kPage), len - pg * kPage);
-
-        // ---- scores: 4 passes of 4 tokens, 8 lanes per token ----
-        float4 kreg[4][4];
-#pragma unroll
-        for (int ps = 0; ps < 4; ++ps)
-#pragma unroll
-            for (int j = 0; j < 4; ++j)
-                kreg[ps][j] = ldg_stream_f4(kp + (4 * ps + grp) * kD + 4 * sub + 32 * j);
-
-        float sc[4][REP];
-#pragma unroll
-        for (int ps = 0; ps < 4; ++ps) {
-#pragma unroll
-            for (int h = 0; h < REP; ++h) {
-                float d = 0.0f;
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    d = fmaf(q[h][j].x, kreg[ps][j].x, d);
-                    d = fmaf(q[h][j].y, kreg[ps][j].y, d);
-                    d = fmaf(q[h][j].z, kreg[ps][j].z, d);
-                    d = fmaf(q[h][j].w, kreg[ps][j].w, d);
-                }
-                d += __shfl_xor_sync(0xFFFFFFFFu, d, 1);
-                d += __shfl_xor_sync(0xFFFFFFFFu, d, 2);
-                d += __shfl_xor_sync(0xFFFFFFFFu, d, 4);
-                d *= scale;
-                const bool in_range = static_cast<uint32_t>(4 * ps + grp) < valid;
-                if (in_range && (isnan(d) || d == INFINITY)) flags |= B2_ATTN_STATUS_NAN_OR_POS_INF;
-                sc[ps][h] = in_range ? d : -INFINITY;
-            }
-        }
-
-        // ---- online softmax update (all lanes keep identical m, l) ----
-        float rescale[REP];
-#pragma unroll
-        for (int h = 0; h < REP; ++h) {
-            float pm = fmaxf(fmaxf(sc[0][h], sc[1][h]), fmaxf(sc[2][h], sc[3][h]));
-            pm = fmaxf(pm, __shfl_xor_sync(0xFFFFFFFFu, pm, 8));
-            pm = fmaxf(pm, __shfl_xor_sync(0xFFFFFFFFu, pm, 16));
-            const float m_new = fmaxf(m[h], pm);
-            const bool dead = (m_new == -INFINITY) || isnan(m_new);
-            rescale[h] = dead ? 1.0f : __expf(m[h] - m_new);
-            float ps_sum = 0.0f;
-#pragma unroll
-            for (int ps = 0; ps < 4; ++ps) {
-                const float e = dead ? 0.0f : __expf(sc[ps][h] - m_new);
-                sc[ps][h] = e;
-                ps_sum += e;
-            }
-            ps_sum += __shfl_xor_sync(0xFFFFFFFFu, ps_sum, 8);
-            ps_sum += __shfl_xor_sync(0xFFFFFFFFu, ps_sum, 16);
-            l[h] = l[h] * rescale[h] + ps_sum;
-            m[h] = dead ? m[h] : m_new;
-        }
-        // Lane `sub` of each token group publishes head `sub`'s probability.
-        __syncwarp();
-        if (sub < REP) {
-#pragma unroll
-            for (int ps = 0; ps < 4; ++ps) {
-                float v = sc[ps][0];
-#pragma unroll
-                for (int h = 1; h < REP; ++h) v = (sub == static_cast<uint32_t>(h)) ? sc[ps][h] : v;
-                s_p[warp][4 * ps + grp][sub] = v;
-            }
-        }
-        __syncwarp();
-
-        // ---- values: lane owns dims 4*lane .. 4*lane+3 for every head ----
-#pragma unroll
-        for (int h = 0; h < REP; ++h) {
-            acc[h].x *= rescale[h];
-            acc[h].y *= rescale[h];
-            acc[h].z *= rescale[h];
-            acc[h].w *= rescale[h];
-        }
-#pragma unroll 4
-        for (uint32_t tk = 0; tk < valid; ++tk) {
-            const float4 v = ldg_stream_f4(vp + tk * kD + 4 * lane);
-#pragma unroll
-            for (int h = 0; h < REP; ++h) {
-                const float pr = s_p[warp][tk][h];
-                acc[h].x = fmaf(pr, v.x, acc[h].x);
-                acc[h].y = fmaf(pr, v.y, acc[h].y);
-                acc[h].z = fmaf(pr, v.z, acc[h].z);
-                acc[h].w = fmaf(pr, v.w, acc[h].w);
-            }
-        }
-    }
-
-    // ---- combine the warps of the CTA ----
-#pragma unroll
-    for (int h = 0; h < REP; ++h) {
-        if (lane == 0) {
-            s_m[warp][h] = m[h];
-            s_l[warp][h] = l[h];
-        }
-        *reinterpret_cast<float4*>(&s_acc[warp][h][4 * lane]) = acc[h];
-    }
-    if (flags != 0 && a.status != nullptr) atomicOr(a.status, flags);
-    __syncthreads();
-
-    // Thread c (0..127) finishes dim c of every head.
-    const uint32_t c = threadIdx.x;
-#pragma unroll
-    for (int h = 0; h < REP; ++h) {
-        float mm = -INFINITY;
-#pragma unroll
-        for (int wv = 0; wv < kFastWarps; ++wv) mm = fmaxf(mm, s_m[wv][h]);
-        float ll = 0.0f, o = 0.0f;
-#pragma unroll
-        for (int wv = 0; wv < kFastWarps; ++wv) {
-            const float f = (s_m[wv][h] == -INFINITY) ? 0.0f : __expf(s_m[wv][h] - mm);
-            ll = fmaf(s_l[wv][h], f, ll);
-            o = fmaf(s_acc[wv][h][c], f, o);
-        }
-        const uint64_t head = static_cast<uint64_t>(seq) * a.q_heads + kvh * REP + h;
-        if (n_splits == 1) {
-            if (mm == -INFINITY) {
-                if (c == 0 && a.status != nullptr) atomicOr(a.status, B2_ATTN_STATUS_ALL_NEG_INF);
-                a.ctx[head * kD + c] = 0.0f;
-            } else {
-                a.ctx[head * kD + c] = o / ll;
-            }
-        } else {
-            float* dst = partials + (head * max_splits + split) * kPartialStride;
-            if (c == 0) {
-                dst[0] = mm;
-                dst[1] = ll;
-            }
-            dst[2 + c] = o;
-        }
-    }
-}
-
-// Same arithmetic as paged_decode_fast_kernel, but the K and V chunks of a page (8 KB each,
-// contiguous in the pool) are brought into shared memory by cp.async.bulk: every warp owns a ring
+// Fast path (head_width 128, block_size 16, rep in {1,2,4,8}). The K and V chunks of a page (8 KB
+// each, contiguous in the pool) are brought into shared memory by cp.async.bulk: every warp owns a ring
 // of three 8 KB slots and keeps the next K, V and K chunks in flight while it works on one, so
 // 24 KB per warp (up to 192 KB per SM) are outstanding without holding them in registers.
 // The mbarrier waits are bounded; a timeout sets bit 3 of the status word.
@@ -604,30 +410,20 @@ int32_t launch_paged_decode(const DeviceContext& ctx, const PagedDecodeArgs& a, 
         if (splits > 65535) return fail(B2_STATUS_OVERFLOW, "paged decode sequence too long");
         const dim3 grid(splits, a.kv_heads, a.n_seq);
         float* partials = static_cast<float*>(workspace);
-        static const char* impl = getenv("B2_ATTN_IMPL");   // "ldg" selects the register-load kernel
-        const bool bulk = impl == nullptr || strcmp(impl, "ldg") != 0;
-        if (bulk) {
-            static PerDeviceOnce configured;
-            B2_TRY(once_per_device(configured, ctx.device, []() -> int32_t {
-                B2_CUDA_TRY(cudaFuncSetAttribute(paged_decode_bulk_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBulkSmemBytes));
-                B2_CUDA_TRY(cudaFuncSetAttribute(paged_decode_bulk_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBulkSmemBytes));
-                B2_CUDA_TRY(cudaFuncSetAttribute(paged_decode_bulk_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBulkSmemBytes));
-                B2_CUDA_TRY(cudaFuncSetAttribute(paged_decode_bulk_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBulkSmemBytes));
-                return B2_STATUS_OK;
-            }));
-            switch (a.q_heads / a.kv_heads) {
-            case 1: paged_decode_bulk_kernel<1><<<grid, kFastWarps * 32, kBulkSmemBytes, stream>>>(a, partials, splits); break;
-            case 2: paged_decode_bulk_kernel<2><<<grid, kFastWarps * 32, kBulkSmemBytes, stream>>>(a, partials, splits); break;
-            case 4: paged_decode_bulk_kernel<4><<<grid, kFastWarps * 32, kBulkSmemBytes, stream>>>(a, partials, splits); break;
-            default: paged_decode_bulk_kernel<8><<<grid, kFastWarps * 32, kBulkSmemBytes, stream>>>(a, partials, splits); break;
-            }
-        } else {
-            switch (a.q_heads / a.kv_heads) {
-            case 1: paged_decode_fast_kernel<1><<<grid, kFastWarps * 32, 0, stream>>>(a, partials, splits); break;
-            case 2: paged_decode_fast_kernel<2><<<grid, kFastWarps * 32, 0, stream>>>(a, partials, splits); break;
-            case 4: paged_decode_fast_kernel<4><<<grid, kFastWarps * 32, 0, stream>>>(a, partials, splits); break;
-            default: paged_decode_fast_kernel<8><<<grid, kFastWarps * 32, 0, stream>>>(a, partials, splits); break;
-            }
+        note_route(B2_ROUTE_ATTENTION_BULK);
+        static PerDeviceOnce configured;
+        B2_TRY(once_per_device(configured, ctx.device, []() -> int32_t {
+            B2_CUDA_TRY(cudaFuncSetAttribute(paged_decode_bulk_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBulkSmemBytes));
+            B2_CUDA_TRY(cudaFuncSetAttribute(paged_decode_bulk_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBulkSmemBytes));
+            B2_CUDA_TRY(cudaFuncSetAttribute(paged_decode_bulk_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBulkSmemBytes));
+            B2_CUDA_TRY(cudaFuncSetAttribute(paged_decode_bulk_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBulkSmemBytes));
+            return B2_STATUS_OK;
+        }));
+        switch (a.q_heads / a.kv_heads) {
+        case 1: paged_decode_bulk_kernel<1><<<grid, kFastWarps * 32, kBulkSmemBytes, stream>>>(a, partials, splits); break;
+        case 2: paged_decode_bulk_kernel<2><<<grid, kFastWarps * 32, kBulkSmemBytes, stream>>>(a, partials, splits); break;
+        case 4: paged_decode_bulk_kernel<4><<<grid, kFastWarps * 32, kBulkSmemBytes, stream>>>(a, partials, splits); break;
+        default: paged_decode_bulk_kernel<8><<<grid, kFastWarps * 32, kBulkSmemBytes, stream>>>(a, partials, splits); break;
         }
         B2_CUDA_TRY(cudaGetLastError());
         if (splits > 1) {
@@ -639,6 +435,7 @@ int32_t launch_paged_decode(const DeviceContext& ctx, const PagedDecodeArgs& a, 
     const uint64_t tasks = static_cast<uint64_t>(a.n_seq) * a.q_heads;
     const uint64_t blocks = (tasks + 3) / 4;
     if (blocks > 0x7FFFFFFFull) return fail(B2_STATUS_OVERFLOW, "paged decode batch too large");
+    note_route(B2_ROUTE_ATTENTION_GENERIC);
     paged_decode_generic_kernel<<<static_cast<unsigned>(blocks), 128, 0, stream>>>(
         a, static_cast<float*>(workspace));
     B2_CUDA_TRY(cudaGetLastError());

@@ -14,7 +14,7 @@ CASES = [
     (17, [512], 4096, 64, True),             # 4 tiles, 64 items: fewer CTAs than SMs
     (32, [14336], 4096, 64, True),           # whole tiles and split tiles in one launch
     (32, [4096], 14336, 64, True),           # long contraction, second-level groups straddle rows
-    (23, [1000], 256, 64, True),             # one round per tile, ragged last tile
+    (23, [1000], 512, 64, True),             # two rounds per tile (the shortest width taken), ragged last tile
     (32, [640, 128, 136], 512, 64, True),    # three weights of one input (q / k / v style), ragged tiles
     (32, [4096, 1024, 1024], 4096, 64, True),
     (20, [768], 1024, 128, False),           # FP32 scales, block 128
@@ -59,6 +59,7 @@ def run_case(b2, port, case, tol, shard=None):
             _check(lib.b2_nf4_linear_forward(C.byref(structs[0]), xd.data_ptr(), ys[0].data_ptr(), rows, None, 0, None))
         else:
             _check(lib.b2_nf4_linear_forward_multi(structs, len(weights), xd.data_ptr(), ptrs, rows, None, 0, None))
+        assert lib.b2_last_route() == 1, (case, lib.b2_last_route())   # B2_ROUTE_DECODE_TMEM
         b2.check_device_errors()
         for host, y in zip(hosts, ys):
             got = y.cpu().numpy()

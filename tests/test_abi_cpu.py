@@ -71,3 +71,18 @@ def test_attention_status_word_mapping():
         _check(lib.b2_attention_status_result(_lib.ATTN_STATUS_TIMEOUT))
     with pytest.raises(DomainError):
         _check(lib.b2_attention_status_result(_lib.ATTN_STATUS_ALL_NEG_INF))
+
+
+def test_route_names_follow_the_header():
+    """backend.ROUTES is indexed by the header's B2_ROUTE_* values; a thread that made no call
+    reports none."""
+    import re
+    from pathlib import Path
+
+    from riftco_transformer_b200 import backend
+    header = (Path(__file__).resolve().parents[1] / "include" / "riftco_b200.h").read_text()
+    routes = dict((name.lower(), int(value)) for name, value in re.findall(r"#define B2_ROUTE_(\w+) (\d+)", header))
+    assert sorted(routes.values()) == list(range(len(backend.ROUTES)))
+    for name, value in routes.items():
+        assert backend.ROUTES[value] == name
+    assert backend.last_route() == "none"

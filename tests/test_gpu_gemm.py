@@ -162,6 +162,8 @@ def test_multi_weight_forward_matches_single_calls(b2, port, rows):
     structs = (_lib.Nf4WeightStruct * len(weights))(*[w.struct() for w in weights])
     ptrs = (C.c_void_p * len(weights))(*[o.data_ptr() for o in outs])
     _check(lib.b2_nf4_linear_forward_multi(structs, len(weights), x.data_ptr(), ptrs, rows, None, 0, None))
+    if rows > 16:   # mixed scale encodings: not one launch of the decode kernel, but one of the prefill kernel
+        assert b2.last_route() == "gemm_tmem"
     b2.check_device_errors()
     for host, single, out in zip(hosts, singles, outs):
         got = out.cpu().numpy()

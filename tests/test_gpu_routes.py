@@ -1,0 +1,96 @@
+"""Every kernel family the library can choose is reached by a shape, through the C ABI, and held
+to the CPU oracle there. The library picks the kernel from the request alone; ``last_route``
+says which one served the call, so a path cannot silently lose its coverage when the selection
+rules change. Needs a B200."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import rel_l2
+from test_gpu_parity import backward, dev, forward, run_gqa
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def b2():
+    import riftco_transformer_b200 as pkg
+    assert pkg.is_available(), pkg.unavailability_reason()
+    return pkg
+
+
+def _weight(port, out_f, in_f, block, dq, seed):
+    rng = np.random.default_rng(seed)
+    W = (rng.standard_normal((out_f, in_f)) * 0.02).astype(np.float32)
+    return port.quantize_nf4_double_quantized(W, block, 256) if dq else port.quantize_nf4(W, block)
+
+
+# (route, rows, out, in, block, double-quantised, tolerance)
+FORWARD = [
+    ("decode_tmem", 32, 512, 1024, 64, True, 1e-2),    # bf16 operands on tcgen05
+    ("decode_tmem", 17, 384, 512, 64, False, 1e-2),    # FP32 scales, ragged last 128-row tile
+    ("gemv_tma", 4, 4096, 4096, 64, True, 2e-3),       # fp16 operands on mma.sync
+    ("gemv_tma", 16, 1024, 2048, 128, False, 2e-3),
+    ("gemv_tile", 3, 1000, 192, 64, True, 2e-3),       # out_features no multiple of the TMA row tile
+    ("gemv_tile", 20, 130, 2048 + 64, 64, True, 2e-3), # 17..32 rows of a width the decode kernel refuses
+    ("gemm_tmem", 64, 512, 1024, 64, True, 1e-2),
+    ("gemm_tmem", 24, 640, 192, 64, False, 1e-2),      # 17..32 rows, width no multiple of 256
+    ("generic", 5, 33, 96, 32, False, 1e-5),           # block size under 64: FP32 SIMT
+    ("generic", 40, 7, 24, 8, True, 1e-5),
+]
+
+
+@pytest.mark.parametrize("route,rows,out_f,in_f,block,dq,tol", FORWARD)
+def test_forward_routes(b2, port, route, rows, out_f, in_f, block, dq, tol):
+    host = _weight(port, out_f, in_f, block, dq, out_f * 31 + in_f + rows)
+    x = np.random.default_rng(rows).standard_normal((rows, in_f)).astype(np.float32)
+    y = forward(b2, b2.PackedNf4Weight.from_host(host), dev(x))
+    assert b2.last_route() == route
+    want = port.linear_forward(host, x)
+    assert rel_l2(y, want) <= tol
+    for r in range(rows):
+        assert rel_l2(y[r], want[r]) <= 2 * tol
+
+
+BACKWARD = [
+    ("backward_dense", 512, 768, 320, 64, True, 1e-2),
+    ("gemm_smem", 64, 768, 320, 64, True, 1e-2),
+    ("gemm_smem", 33, 128, 64, 64, False, 1e-2),
+    ("generic", 19, 768, 320, 64, True, 1e-5),         # 32 rows or fewer
+    ("generic", 600, 96, 48, 16, False, 1e-5),         # block size under 64
+]
+
+
+@pytest.mark.parametrize("route,rows,out_f,in_f,block,dq,tol", BACKWARD)
+def test_input_backward_routes(b2, port, route, rows, out_f, in_f, block, dq, tol):
+    host = _weight(port, out_f, in_f, block, dq, out_f * 17 + in_f + rows)
+    dy = (np.random.default_rng(rows).standard_normal((rows, out_f)) * 0.01).astype(np.float32)
+    dx = backward(b2, b2.PackedNf4Weight.from_host(host), dev(dy))
+    assert b2.last_route() == route
+    assert rel_l2(dx, port.linear_input_backward(host, dy)) <= tol
+
+
+@pytest.mark.parametrize("route,hq,hkv,d,bs", [
+    ("attention_bulk", 8, 2, 128, 16),
+    ("attention_generic", 8, 2, 128, 8),      # page size other than 16
+    ("attention_generic", 6, 2, 64, 16),      # head width other than 128, three query heads per KV head
+    ("attention_generic", 2, 1, 3, 2),        # the reference test's own shape class
+])
+def test_attention_routes(b2, port, route, hq, hkv, d, bs):
+    rng = np.random.default_rng(hq * 100 + d + bs)
+    lens = np.array([1, bs, bs + 1, 5 * bs + 3], np.uint32)
+    blocks = -(-lens.astype(np.int64) // bs)
+    P = int(blocks.sum()) + 2
+    perm = rng.permutation(P)
+    tables = np.zeros((len(lens), int(blocks.max())), np.uint32)
+    at = 0
+    for s, nb in enumerate(blocks):
+        tables[s, :nb] = perm[at:at + nb]
+        at += nb
+    K = rng.standard_normal((P, hkv, bs, d)).astype(np.float32)
+    V = rng.standard_normal((P, hkv, bs, d)).astype(np.float32)
+    q = rng.standard_normal((len(lens), hq, d)).astype(np.float32)
+    got, status = run_gqa(b2, q, K, V, tables, lens)
+    assert b2.last_route() == route
+    assert status == 0
+    assert rel_l2(got, port.paged_decode_gqa(q, K, V, tables, lens)) <= 2e-3
