@@ -377,22 +377,13 @@ int32_t linear_forward_impl(const b2_nf4_weight* weight, const float* x, float* 
         return launch_nf4_gemm_tmem(*ctx, w, workspace, y, rows, stream);
     }
     if (nf4_gemv_supported(w, x, y, rows)) {
-        // Up to 32 rows: the TMA-fed mma.sync decode kernel (17..32 rows as two passes; the second
-        // finds the packed weight in L2), else the tiled decode kernel, which takes any row count
-        // of the weight.
+        // What the two tcgen05 kernels above did not take (up to 16 rows; 17..32 rows of a weight
+        // whose codes are only 8-byte aligned): the TMA-fed mma.sync decode kernel, else the tiled
+        // decode kernel, which takes any row count of the weight.
         uint32_t ksplit = 0, per = 0;
-        if (nf4_gemv_tma_plan(*ctx, w, x, rows, &ksplit, &per)) {
+        if (rows <= 16 && nf4_gemv_tma_plan(*ctx, w, x, rows, &ksplit, &per)) {
             note_route(B2_ROUTE_GEMV_TMA);
             return launch_nf4_gemv_tma(*ctx, w, x, y, rows, ksplit, per, stream);
-        }
-        if (rows > 16 && nf4_gemv_tma_plan(*ctx, w, x, 16, &ksplit, &per)) {
-            uint32_t ks2 = 0, per2 = 0;
-            if (nf4_gemv_tma_plan(*ctx, w, x + 16 * w.in_features, rows - 16, &ks2, &per2)) {
-                note_route(B2_ROUTE_GEMV_TMA);
-                B2_TRY(launch_nf4_gemv_tma(*ctx, w, x, y, 16, ksplit, per, stream));
-                return launch_nf4_gemv_tma(*ctx, w, x + 16 * w.in_features, y + 16 * w.out_features,
-                                           rows - 16, ks2, per2, stream);
-            }
         }
         note_route(B2_ROUTE_GEMV_TILE);
         return launch_nf4_gemv(*ctx, w, x, y, rows, stream);

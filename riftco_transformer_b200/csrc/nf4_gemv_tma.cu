@@ -1,7 +1,7 @@
-// Decode kernel for the packed-NF4 linear, batch rows <= 32, fed by TMA:
+// Decode kernel for the packed-NF4 linear, batch rows <= 16, fed by TMA:
 // y[r,o] = sum_i x[r,i] * W[o,i].
 //
-// Same arithmetic as nf4_gemv_stream.cu (W as the 16-row A operand of
+// Same arithmetic as nf4_gemv.cu (W as the 16-row A operand of
 // mma.sync m16n8k16, activations resident in registers as fp16 B fragments,
 // one PRMT + one conflict-free table load per packed byte, FP32 block scale
 // applied per 64-weight partial sum), but the packed codes no longer travel
@@ -508,8 +508,7 @@ int32_t max_active_clusters(const DeviceContext& ctx, uint32_t ksplit, uint32_t*
 
 int32_t active_clusters_for(const DeviceContext& ctx, uint64_t rows, uint32_t ksplit, uint32_t* out) {
     if (rows <= 8) return max_active_clusters<1>(ctx, ksplit, out);
-    if (rows <= 16) return max_active_clusters<2>(ctx, ksplit, out);
-    return max_active_clusters<4>(ctx, ksplit, out);
+    return max_active_clusters<2>(ctx, ksplit, out);
 }
 
 template <int MT>
@@ -562,7 +561,7 @@ int32_t encode(const char* what, CUtensorMap* map, CUtensorMapDataType type, uin
 // enough second-level values per tile to fit the 32-float box.
 bool nf4_gemv_tma_plan(const DeviceContext& ctx, const WeightView& w, const float* x, uint64_t rows,
                        uint32_t* ksplit_out, uint32_t* steps_per_cta_out) {
-    if (rows < 1 || rows > 32 || w.in_features % kStepK != 0 || w.block_size < kStepK) return false;
+    if (rows < 1 || rows > 16 || w.in_features % kStepK != 0 || w.block_size < kStepK) return false;
     if ((reinterpret_cast<uintptr_t>(w.codes) & 15u) != 0 || (reinterpret_cast<uintptr_t>(x) & 15u) != 0) return false;
     if (encode_tiled() == nullptr) return false;
     if (w.in_features % w.block_size != 0 || w.out_features % kTileRows != 0) return false;
@@ -578,7 +577,7 @@ bool nf4_gemv_tma_plan(const DeviceContext& ctx, const WeightView& w, const floa
     const uint64_t row_tiles = w.out_features / kTileRows;
     if (steps > 0xFFFFFFull || row_tiles > 0x7FFFFFFull || w.out_features > 0x7FFFFFFFull) return false;
     if ((w.out_features + 2048) * (blocks_per_row + 1) + w.flat_block_base > 0xFFFFFFFFull) return false;
-    const uint64_t cap = rows <= 16 ? 64 : 32;   // steps one CTA covers (16 warps x 4 or 2)
+    const uint64_t cap = 64;   // steps one CTA covers (16 warps x 4)
     uint64_t ks = (steps + cap - 1) / cap;
     if (ks > 8) return false;
     uint64_t per = (steps + ks - 1) / ks;
@@ -641,8 +640,7 @@ int32_t launch_nf4_gemv_tma(const DeviceContext& ctx, const WeightView& w, const
     p.lut = ctx.gemv_lut;
     p.error = ctx.gemm_error;
     if (rows <= 8) return launch_tma<1>(ctx, map_w, map_s, map_2, p, ksplit, stream);
-    if (rows <= 16) return launch_tma<2>(ctx, map_w, map_s, map_2, p, ksplit, stream);
-    return launch_tma<4>(ctx, map_w, map_s, map_2, p, ksplit, stream);
+    return launch_tma<2>(ctx, map_w, map_s, map_2, p, ksplit, stream);
 }
 
 }  // namespace b2

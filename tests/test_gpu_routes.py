@@ -32,7 +32,7 @@ FORWARD = [
     ("gemv_tma", 4, 4096, 4096, 64, True, 2e-3),       # fp16 operands on mma.sync
     ("gemv_tma", 16, 1024, 2048, 128, False, 2e-3),
     ("gemv_tile", 3, 1000, 192, 64, True, 2e-3),       # out_features no multiple of the TMA row tile
-    ("gemv_tile", 20, 130, 2048 + 64, 64, True, 2e-3), # 17..32 rows of a width the decode kernel refuses
+    ("gemv_tile", 9, 130, 2048 + 64, 64, False, 2e-3),
     ("gemm_tmem", 64, 512, 1024, 64, True, 1e-2),
     ("gemm_tmem", 24, 640, 192, 64, False, 1e-2),      # 17..32 rows, width no multiple of 256
     ("generic", 5, 33, 96, 32, False, 1e-5),           # block size under 64: FP32 SIMT
@@ -50,6 +50,22 @@ def test_forward_routes(b2, port, route, rows, out_f, in_f, block, dq, tol):
     assert rel_l2(y, want) <= tol
     for r in range(rows):
         assert rel_l2(y[r], want[r]) <= 2 * tol
+
+
+@pytest.mark.parametrize("rows,route,tol", [(4, "gemv_tile", 2e-3), (20, "gemv_tile", 2e-3), (40, "generic", 1e-5)])
+def test_codes_that_are_only_8_byte_aligned(b2, port, rows, route, tol):
+    """The TMA-fed and tcgen05 kernels want 16-byte aligned codes; a weight placed at an address
+    that is 8 modulo 16 is served by the kernels that read it with plain loads."""
+    host = _weight(port, 512, 1024, 64, True, 99)
+    w = b2.PackedNf4Weight.from_host(host)
+    shifted = torch.empty(w.codes.numel() + 16, dtype=torch.uint8, device="cuda")
+    shifted[8:8 + w.codes.numel()] = w.codes
+    w.codes = shifted[8:8 + w.codes.numel()]
+    assert w.codes.data_ptr() % 16 == 8
+    x = np.random.default_rng(rows).standard_normal((rows, 1024)).astype(np.float32)
+    y = forward(b2, w, dev(x))
+    assert b2.last_route() == route
+    assert rel_l2(y, port.linear_forward(host, x)) <= tol
 
 
 BACKWARD = [
