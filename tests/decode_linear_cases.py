@@ -14,20 +14,21 @@ CASES = [
     (17, [512], 4096, 64, True),             # 4 tiles, 64 items: fewer CTAs than SMs
     (32, [14336], 4096, 64, True),           # whole tiles and split tiles in one launch
     (32, [4096], 14336, 64, True),           # long contraction, second-level groups straddle rows
-    (23, [1000], 512, 64, True),             # two rounds per tile (the shortest width taken), ragged last tile
-    (32, [640, 128, 136], 512, 64, True),    # three weights of one input (q / k / v style), ragged tiles
+    (23, [1000], 1024, 64, True),            # four rounds per tile, ragged last tile
+    (32, [640, 128, 136], 1024, 64, True),   # three weights of one input (q / k / v style), ragged tiles
     (32, [4096, 1024, 1024], 4096, 64, True),
     (20, [768], 1024, 128, False),           # FP32 scales, block 128
-    (32, [256], 2048, 256, True),            # block 256: four k-blocks share a scale
+    (32, [256], 4096, 256, True),            # block 256: four k-blocks share a scale
     (32, [384], 768, 64, False),             # FP32 scales, block 64, three rounds
+    (19, [200], 512, 64, False),             # the shortest width taken: two rounds
 ]
 SMALL_ROW_CASES = [
     (1, [4096], 4096, 64, True),
     (4, [14336], 4096, 64, True),
     (16, [4096], 14336, 64, True),
-    (9, [1000], 512, 64, True),
+    (9, [1000], 1024, 64, True),
     (5, [640, 128], 512, 64, False),
-    (16, [300], 1024, 128, True),
+    (16, [300], 2048, 128, True),
 ]
 
 

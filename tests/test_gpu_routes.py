@@ -35,8 +35,9 @@ FORWARD = [
     ("gemv_tile", 9, 130, 2048 + 64, 64, False, 2e-3),
     ("gemm_tmem", 64, 512, 1024, 64, True, 1e-2),
     ("gemm_tmem", 24, 640, 192, 64, False, 1e-2),      # 17..32 rows, width no multiple of 256
+    ("gemm_tmem", 32, 256, 512, 64, True, 1e-2),       # 8 scale codes per row: under one 16-byte TMA box
     ("generic", 5, 33, 96, 32, False, 1e-5),           # block size under 64: FP32 SIMT
-    ("generic", 40, 7, 24, 8, True, 1e-5),
+    ("generic", 40, 7, 96, 32, True, 1e-5),
 ]
 
 
@@ -73,7 +74,7 @@ BACKWARD = [
     ("gemm_smem", 64, 768, 320, 64, True, 1e-2),
     ("gemm_smem", 33, 128, 64, 64, False, 1e-2),
     ("generic", 19, 768, 320, 64, True, 1e-5),         # 32 rows or fewer
-    ("generic", 600, 96, 48, 16, False, 1e-5),         # block size under 64
+    ("generic", 600, 96, 64, 32, False, 1e-5),         # block size under 64
 ]
 
 
