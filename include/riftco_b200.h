@@ -251,7 +251,24 @@ B2_API int32_t b2_paged_decode_attention(const float* q, const float* k_pages,
                                   size_t workspace_bytes, uint32_t* status,
                                   void* stream);
 
-/* Scratch bytes for the call above (split-K partial results). */
+/* b2_paged_decode_attention that also writes a bf16 copy of the context
+ * (ctx_bf16: [n_seq, q_heads, head_width], round to nearest even of the FP32
+ * value stored in ctx), for a following output projection that reads bf16
+ * activations (b2_nf4_linear_forward_multi_bf16): the projection then needs no
+ * conversion pass. In the reference the projection consumes the attention
+ * output directly (src/model/grouped_query_attention.cpp:254,
+ * output_.forward(merge_attention_heads(attention.context))). */
+B2_API int32_t b2_paged_decode_attention_bf16(const float* q, const float* k_pages,
+                                  const float* v_pages, const uint32_t* block_tables,
+                                  const uint32_t* seq_lens, float* ctx, void* ctx_bf16,
+                                  uint32_t n_seq, uint32_t q_heads, uint32_t kv_heads,
+                                  uint32_t head_width, uint32_t block_size,
+                                  uint64_t physical_blocks, uint32_t max_blocks,
+                                  uint32_t max_seq_len, void* workspace,
+                                  size_t workspace_bytes, uint32_t* status,
+                                  void* stream);
+
+/* Scratch bytes for the calls above (split-K partial results). */
 B2_API size_t b2_paged_decode_workspace_bytes(uint32_t n_seq, uint32_t q_heads,
                                        uint32_t head_width, uint32_t block_size,
                                        uint32_t max_seq_len);

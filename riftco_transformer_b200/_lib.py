@@ -71,6 +71,8 @@ SIGNATURES = {
     "b2_nf4_linear_workspace_bytes": (_sz, [_W, _u64, _i32]),
     "b2_paged_decode_attention": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u32,
                                          _u64, _u32, _u32, _vp, _sz, _vp, _vp]),
+    "b2_paged_decode_attention_bf16": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u32,
+                                              _u64, _u32, _u32, _vp, _sz, _vp, _vp]),
     "b2_paged_decode_workspace_bytes": (_sz, [_u32, _u32, _u32, _u32, _u32]),
     "b2_attention_status_result": (_i32, [_u32]),
     "b2_last_route": (_i32, []),

@@ -740,12 +740,14 @@ size_t b2_paged_decode_workspace_bytes(uint32_t n_seq, uint32_t q_heads, uint32_
     return paged_decode_workspace_bytes(n_seq, q_heads, head_width, block_size, max_seq_len);
 }
 
-int32_t b2_paged_decode_attention(const float* q, const float* k_pages, const float* v_pages,
-                                  const uint32_t* block_tables, const uint32_t* seq_lens, float* ctx_out,
-                                  uint32_t n_seq, uint32_t q_heads, uint32_t kv_heads,
-                                  uint32_t head_width, uint32_t block_size, uint64_t physical_blocks,
-                                  uint32_t max_blocks, uint32_t max_seq_len, void* workspace,
-                                  size_t workspace_bytes, uint32_t* status_word, void* stream) {
+namespace {
+
+int32_t paged_decode_impl(const float* q, const float* k_pages, const float* v_pages,
+                          const uint32_t* block_tables, const uint32_t* seq_lens, float* ctx_out,
+                          void* ctx_bf16, uint32_t n_seq, uint32_t q_heads, uint32_t kv_heads,
+                          uint32_t head_width, uint32_t block_size, uint64_t physical_blocks,
+                          uint32_t max_blocks, uint32_t max_seq_len, void* workspace,
+                          size_t workspace_bytes, uint32_t* status_word, void* stream) {
     clear_error();
     int32_t status = B2_STATUS_OK;
     DeviceContext* ctx = device_context(&status);
@@ -757,12 +759,16 @@ int32_t b2_paged_decode_attention(const float* q, const float* k_pages, const fl
         return fail(B2_STATUS_INVALID_ARGUMENT, "paged decode attention pointers must not be null");
     }
     // require_distinct, attention/dispatch.cpp:504-506.
-    if (ctx_out == q || ctx_out == k_pages || ctx_out == v_pages) {
+    if (ctx_out == q || ctx_out == k_pages || ctx_out == v_pages || ctx_bf16 == q || ctx_bf16 == k_pages ||
+        ctx_bf16 == v_pages || ctx_bf16 == ctx_out) {
         return fail(B2_STATUS_INVALID_ARGUMENT, "paged decode attention output must not alias an input");
+    }
+    if ((reinterpret_cast<uintptr_t>(ctx_bf16) & 1u) != 0) {
+        return fail(B2_STATUS_INVALID_ARGUMENT, "the bf16 copy must be 2-byte aligned");
     }
     PagedDecodeArgs args{q, k_pages, v_pages, block_tables, seq_lens, ctx_out,
                          n_seq, q_heads, kv_heads, head_width, block_size, max_blocks, max_seq_len,
-                         physical_blocks, status_word};
+                         physical_blocks, status_word, ctx_bf16};
     const size_t need =
         paged_decode_workspace_bytes(n_seq, q_heads, head_width, block_size, max_seq_len);
     if (workspace == nullptr && need > 0) {
@@ -771,6 +777,34 @@ int32_t b2_paged_decode_attention(const float* q, const float* k_pages, const fl
         workspace_bytes = ctx->arena_bytes;
     }
     return launch_paged_decode(*ctx, args, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
+}
+
+}  // namespace
+
+int32_t b2_paged_decode_attention(const float* q, const float* k_pages, const float* v_pages,
+                                  const uint32_t* block_tables, const uint32_t* seq_lens, float* ctx_out,
+                                  uint32_t n_seq, uint32_t q_heads, uint32_t kv_heads,
+                                  uint32_t head_width, uint32_t block_size, uint64_t physical_blocks,
+                                  uint32_t max_blocks, uint32_t max_seq_len, void* workspace,
+                                  size_t workspace_bytes, uint32_t* status_word, void* stream) {
+    return paged_decode_impl(q, k_pages, v_pages, block_tables, seq_lens, ctx_out, nullptr, n_seq, q_heads,
+                             kv_heads, head_width, block_size, physical_blocks, max_blocks, max_seq_len,
+                             workspace, workspace_bytes, status_word, stream);
+}
+
+int32_t b2_paged_decode_attention_bf16(const float* q, const float* k_pages, const float* v_pages,
+                                       const uint32_t* block_tables, const uint32_t* seq_lens, float* ctx_out,
+                                       void* ctx_bf16, uint32_t n_seq, uint32_t q_heads, uint32_t kv_heads,
+                                       uint32_t head_width, uint32_t block_size, uint64_t physical_blocks,
+                                       uint32_t max_blocks, uint32_t max_seq_len, void* workspace,
+                                       size_t workspace_bytes, uint32_t* status_word, void* stream) {
+    if (ctx_bf16 == nullptr) {
+        clear_error();
+        return fail(B2_STATUS_INVALID_ARGUMENT, "paged decode attention pointers must not be null");
+    }
+    return paged_decode_impl(q, k_pages, v_pages, block_tables, seq_lens, ctx_out, ctx_bf16, n_seq, q_heads,
+                             kv_heads, head_width, block_size, physical_blocks, max_blocks, max_seq_len,
+                             workspace, workspace_bytes, status_word, stream);
 }
 
 namespace {

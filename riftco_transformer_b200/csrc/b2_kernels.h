@@ -86,6 +86,7 @@ struct PagedDecodeArgs {
     uint32_t n_seq, q_heads, kv_heads, head_width, block_size, max_blocks, max_seq_len;
     uint64_t physical_blocks;
     uint32_t* status;  // may be null
+    void* ctx16 = nullptr;   // optional bf16 copy of ctx (round to nearest even), written with it
 };
 // Dimension rules of dispatch_paged_decode_attention_forward that need no view of device data
 // (src/core/backend/attention/dispatch.cpp:179-219,440-509); defined in api.cu.

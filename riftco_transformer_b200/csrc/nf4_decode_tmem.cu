@@ -56,7 +56,7 @@ constexpr int kMaxWStages = 6;
 constexpr int kXStages = 4;                                   // activation stages
 constexpr int kAStages = 3;                                   // tensor-memory stages of the expanded weights
 constexpr int kLutBytes = 65536;                              // 256 rows of 256 bytes (lane l at byte 4*l)
-constexpr int kLowHeader = 3072;                              // barriers, scale-code factor table, slot lists
+constexpr int kLowHeader = 3072;                              // barriers, slot lists
 constexpr int kExpandWarps = 16;
 constexpr int kFirstExpandWarp = 3;
 constexpr int kThreads = (kFirstExpandWarp + kExpandWarps) * 32;   // 608
@@ -146,6 +146,26 @@ __device__ __forceinline__ float lds_f32(uint32_t a) {
     asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(a));
     return v;
 }
+__device__ __forceinline__ float2 lds_f32x2(uint32_t a) {
+    float2 v;
+    asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds_u16(uint32_t a) {
+    uint32_t v;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=r"(v) : "r"(a));
+    return v;
+}
+// (code - 128) / 127 rounded like the IEEE division of dq_factor, without the division: the
+// product with the rounded reciprocal, corrected by one Newton step, is the correctly rounded
+// quotient for each of the 256 codes (checked exhaustively against the division).
+__device__ __forceinline__ float dq_factor_fma(uint32_t scale_code) {
+    const float x = static_cast<float>(static_cast<int>(scale_code) - 128);
+    const float r = 1.0f / 127.0f;
+    const float q0 = __fmul_rn(x, r);
+    const float e = __fmaf_rn(-q0, 127.0f, x);
+    return __fmaf_rn(e, r, q0);
+}
 __device__ __forceinline__ uint32_t lds_u8(uint32_t a) {
     uint32_t v;
     asm volatile("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(a));
@@ -221,7 +241,7 @@ __device__ __forceinline__ void set_barrier(uint32_t set) {
 // Where the pieces of shared memory lie for this CTA: a pure function of the dynamic allocation's
 // address and of the token tile, so every role computes the same answer.
 struct SmemPlan {
-    uint32_t low32;       // barriers, factor table
+    uint32_t low32;       // barriers, slot lists
     uint32_t x32;         // activation stages
     uint32_t lut32;       // 64 KB aligned table
     uint32_t high32;      // ring stages behind the table
@@ -290,7 +310,6 @@ nf4_decode_tmem_kernel(const __grid_constant__ DecodeMaps maps, const __grid_con
     const SmemPlan plan = plan_smem(raw32, p.n_pad);
     uint8_t* low = smem_raw + (plan.low32 - raw32);
     Barriers& bars = *reinterpret_cast<Barriers*>(low);
-    float* s_factor = reinterpret_cast<float*>(low + 256);   // scale code -> (code - 128) / 127
     uint32_t* s_slots = reinterpret_cast<uint32_t*>(low + 1280);   // partial-tile slots of one output tile (<= 160), per set
     volatile uint32_t* abort = &bars.abort;
 
@@ -339,7 +358,6 @@ nf4_decode_tmem_kernel(const __grid_constant__ DecodeMaps maps, const __grid_con
         cp_async_16(plan.lut32 + (i >> 3) * 256u + (i & 7u) * 16u, p.lut + i * 4u);
     }
     asm volatile("cp.async.commit_group;" ::);
-    if (tid < 256) s_factor[tid] = dq_factor(tid);
 
     const uint32_t w_tx = kCodeBytes + kScaleBoxBytes + (fp32_scales ? 0u : kSecondBox * 4u);
     // Streams item `it` (ring slot `s`): packed codes, raw scales, second-level values.
@@ -487,7 +505,6 @@ nf4_decode_tmem_kernel(const __grid_constant__ DecodeMaps maps, const __grid_con
         const uint32_t row = quarter * 32u + lane;    // weight row of the tile = TMEM lane
         const uint32_t lut_lane = plan.lut32 | (lane * 4u);
         const uint32_t lane_addr = (quarter * 32u) << 16;
-        const uint32_t factor32 = plan.low32 + 256u;  // scale code -> factor table (shared address)
         const uint32_t sshift = p.w[0].scale_block_shift;
         // byte offsets of this thread's four 16-byte chunks inside a swizzled [128 x 128 B] box
         uint32_t code_off[4];
@@ -505,13 +522,40 @@ nf4_decode_tmem_kernel(const __grid_constant__ DecodeMaps maps, const __grid_con
         uint32_t stage32 = 0;
         uint32_t v[32];
 
-        // Decoded scale of block `blk` of this row from the raw values in the current ring slot.
-        auto block_scale = [&](uint32_t blk, uint32_t blk0) -> float {
-            if (fp32_scales) return lds_f32(stage32 + kScaleOff + row * 16u + (blk - (blk0 & ~3u)) * 4u);
-            const uint32_t code = lds_u8(stage32 + kScaleOff + row * 16u + (blk - (blk0 & ~15u)));
-            const uint32_t first = (fbase_tile + blk0) >> sshift;
-            const uint32_t idx = ((fbase_row + blk) >> sshift) - (first & ~3u);
-            return dq_finish(lds_f32(factor32 + code * 4u), lds_f32(stage32 + kSecondOff + idx * 4u), dq_offset);
+        // Decoded scales of this thread's two k-blocks (blocks `b0` and `b1` of its row; b1 is b0 or
+        // b0 + 1) from the raw values in the current ring slot. A row's raw scales are 16 bytes apart,
+        // so every load here costs a warp four shared-memory wavefronts: both values come with one
+        // load where they are neighbours, and the code -> factor step is arithmetic
+        // ((code - 128) / 127, correctly rounded by one Newton step: exact for all 256 codes).
+        auto block_scales = [&](uint32_t b0, uint32_t b1, uint32_t blk0, float& s0, float& s1) {
+            if (fp32_scales) {
+                const uint32_t at = stage32 + kScaleOff + row * 16u + (b0 - (blk0 & ~3u)) * 4u;
+                if (b1 != b0 && (b0 & 1u) == 0u) {
+                    const float2 both = lds_f32x2(at);
+                    s0 = both.x;
+                    s1 = both.y;
+                } else {
+                    s0 = lds_f32(at);
+                    s1 = b1 != b0 ? lds_f32(at + 4u) : s0;
+                }
+                return;
+            }
+            const uint32_t at = stage32 + kScaleOff + row * 16u + (b0 - (blk0 & ~15u));
+            uint32_t code0, code1;
+            if (b1 != b0 && (b0 & 1u) == 0u) {
+                const uint32_t both = lds_u16(at);
+                code0 = both & 0xFFu;
+                code1 = both >> 8;
+            } else {
+                code0 = lds_u8(at);
+                code1 = b1 != b0 ? lds_u8(at + 1u) : code0;
+            }
+            const uint32_t first = ((fbase_tile + blk0) >> sshift) & ~3u;
+            const uint32_t idx0 = ((fbase_row + b0) >> sshift) - first;
+            const uint32_t idx1 = ((fbase_row + b1) >> sshift) - first;
+            // (the second-level values are the same for nearly every lane: broadcast loads)
+            s0 = dq_finish(dq_factor_fma(code0), lds_f32(stage32 + kSecondOff + idx0 * 4u), dq_offset);
+            s1 = dq_finish(dq_factor_fma(code1), lds_f32(stage32 + kSecondOff + idx1 * 4u), dq_offset);
         };
         // Looks one k-block's 32 bytes up into v, scaled.
         auto lookup = [&](const uint4& c0, const uint4& c1, float scale) {
@@ -549,8 +593,8 @@ nf4_decode_tmem_kernel(const __grid_constant__ DecodeMaps maps, const __grid_con
             float scale = 0.0f;
             second_scale = 0.0f;
             if (live) {
-                scale = block_scale((4u * rho + 2u * h) >> p.kshift, blk0);
-                second_scale = block_scale((4u * rho + 2u * h + 1u) >> p.kshift, blk0);
+                block_scales((4u * rho + 2u * h) >> p.kshift, (4u * rho + 2u * h + 1u) >> p.kshift, blk0, scale,
+                             second_scale);
                 if (kHalf) {
                     scale *= inv_norm;
                     second_scale *= inv_norm;
@@ -579,7 +623,7 @@ nf4_decode_tmem_kernel(const __grid_constant__ DecodeMaps maps, const __grid_con
                 const uint32_t code = lds_u8(s0 + kScaleOff + (blk0 - (blk0 & ~15u)));
                 const uint32_t fb = static_cast<uint32_t>(p.w[t0.wi].flat_block_base) + t0.n0 * p.blocks_per_row;
                 const uint32_t idx = ((fb + blk0) >> sshift) - (((fb + blk0) >> sshift) & ~3u);
-                first_scale = dq_finish(lds_f32(factor32 + code * 4u), lds_f32(s0 + kSecondOff + idx * 4u), p.w[t0.wi].offset);
+                first_scale = dq_finish(dq_factor_fma(code), lds_f32(s0 + kSecondOff + idx * 4u), p.w[t0.wi].offset);
             }
             const uint32_t bits = __float_as_uint(first_scale) & 0x7F800000u;
             norm = (bits == 0u || bits == 0x7F800000u) ? 1.0f : __uint_as_float(bits);

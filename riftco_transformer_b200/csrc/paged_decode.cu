@@ -21,6 +21,8 @@
 #include "b2_kernels.h"
 #include "sm100_ptx.cuh"
 
+#include <cuda_bf16.h>
+
 #include <cmath>
 #include <cstdlib>
 #include <cstring>
@@ -34,6 +36,12 @@ constexpr int kPage = 16;          // tokens per page of the fast path
 constexpr int kFastWarps = 4;
 constexpr int kTokensPerCta = 256; // split size: 16 pages, 4 per warp
 constexpr int kPartialStride = kD + 2;  // m, l, acc[128]
+
+// One context value, and its bf16 copy when the caller asked for one.
+__device__ __forceinline__ void put_ctx(const PagedDecodeArgs& a, uint64_t index, float value) {
+    a.ctx[index] = value;
+    if (a.ctx16 != nullptr) static_cast<__nv_bfloat16*>(a.ctx16)[index] = __float2bfloat16_rn(value);
+}
 
 // Fast path (head_width 128, block_size 16, rep in {1,2,4,8}). The K and V chunks of a page (8 KB
 // each, contiguous in the pool) are brought into shared memory by cp.async.bulk: every warp owns a ring
@@ -257,9 +265,9 @@ paged_decode_bulk_kernel(const PagedDecodeArgs a, float* __restrict__ partials, 
         if (n_splits == 1) {
             if (mm == -INFINITY) {
                 if (c == 0 && a.status != nullptr) atomicOr(a.status, B2_ATTN_STATUS_ALL_NEG_INF);
-                a.ctx[head * kD + c] = 0.0f;
+                put_ctx(a, head * kD + c, 0.0f);
             } else {
-                a.ctx[head * kD + c] = o / ll;
+                put_ctx(a, head * kD + c, o / ll);
             }
         } else {
             float* dst = partials + (head * max_splits + split) * kPartialStride;
@@ -294,9 +302,9 @@ paged_decode_merge_kernel(const PagedDecodeArgs a, const float* __restrict__ par
     }
     if (mm == -INFINITY) {
         if (c == 0 && a.status != nullptr) atomicOr(a.status, B2_ATTN_STATUS_ALL_NEG_INF);
-        a.ctx[head * kD + c] = 0.0f;
+        put_ctx(a, head * kD + c, 0.0f);
     } else {
-        a.ctx[head * kD + c] = o / ll;
+        put_ctx(a, head * kD + c, o / ll);
     }
 }
 
@@ -348,7 +356,7 @@ paged_decode_generic_kernel(const PagedDecodeArgs a, float* __restrict__ scores)
     }
     if (mx == -INFINITY && !(flags & B2_ATTN_STATUS_NAN_OR_POS_INF)) flags |= B2_ATTN_STATUS_ALL_NEG_INF;
     if (flags & (B2_ATTN_STATUS_NAN_OR_POS_INF | B2_ATTN_STATUS_ALL_NEG_INF)) {
-        for (uint32_t c = lane; c < d; c += 32) a.ctx[task * d + c] = 0.0f;
+        for (uint32_t c = lane; c < d; c += 32) put_ctx(a, task * d + c, 0.0f);
         if (lane == 0 && a.status != nullptr) atomicOr(a.status, flags);
         return;
     }
@@ -367,7 +375,7 @@ paged_decode_generic_kernel(const PagedDecodeArgs a, float* __restrict__ scores)
             const float pr = static_cast<float>(static_cast<double>(sc[pos]) / denom);
             total = __fadd_rn(total, __fmul_rn(pr, __ldg(a.v_pages + page_offset(pos, flags) + c)));
         }
-        a.ctx[task * d + c] = total;
+        put_ctx(a, task * d + c, total);
     }
     if (flags != 0 && lane == 0 && a.status != nullptr) atomicOr(a.status, flags);
 }

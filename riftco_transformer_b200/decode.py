@@ -180,15 +180,25 @@ class CudaOps:
                                      tables.shape[1], theta, status.data_ptr(), _stream_ptr(None)))
         self.launches += 1
 
-    def attention(self, q, pool: PagedKvPool, tables, seq_lens, ctx, max_seq_len: int, status, workspace) -> None:
+    attention_writes_bf16 = True   # `attention` takes `ctx16`: a bf16 copy of the context for the o-projection
+
+    def attention(self, q, pool: PagedKvPool, tables, seq_lens, ctx, max_seq_len: int, status, workspace,
+                  ctx16=None) -> None:
         n_seq, q_heads, d = q.shape
-        _check(lib.b2_paged_decode_attention(
-            q.data_ptr(), pool.key_pages.data_ptr(), pool.value_pages.data_ptr(), tables.data_ptr(),
-            seq_lens.data_ptr(), ctx.data_ptr(), n_seq, q_heads, pool.kv_heads, d, pool.block_size,
-            pool.physical_blocks, tables.shape[1], max_seq_len,
-            None if workspace is None else workspace.data_ptr(),
-            0 if workspace is None else workspace.numel() * workspace.element_size(), status.data_ptr(),
-            _stream_ptr(None)))
+        ws = None if workspace is None else workspace.data_ptr()
+        ws_bytes = 0 if workspace is None else workspace.numel() * workspace.element_size()
+        if ctx16 is None:
+            _check(lib.b2_paged_decode_attention(
+                q.data_ptr(), pool.key_pages.data_ptr(), pool.value_pages.data_ptr(), tables.data_ptr(),
+                seq_lens.data_ptr(), ctx.data_ptr(), n_seq, q_heads, pool.kv_heads, d, pool.block_size,
+                pool.physical_blocks, tables.shape[1], max_seq_len, ws, ws_bytes, status.data_ptr(),
+                _stream_ptr(None)))
+        else:
+            _check(lib.b2_paged_decode_attention_bf16(
+                q.data_ptr(), pool.key_pages.data_ptr(), pool.value_pages.data_ptr(), tables.data_ptr(),
+                seq_lens.data_ptr(), ctx.data_ptr(), ctx16.data_ptr(), n_seq, q_heads, pool.kv_heads, d,
+                pool.block_size, pool.physical_blocks, tables.shape[1], max_seq_len, ws, ws_bytes,
+                status.data_ptr(), _stream_ptr(None)))
         self.launches += 2 if max_seq_len > 256 else 1
 
     def attention_workspace(self, n_seq, q_heads, d, block_size, max_seq_len):
@@ -296,6 +306,11 @@ class DecodeStep:
             self.h16 = e((B, cfg.ffn), dtype=torch.bfloat16)
         if world > 1 and gather_bf16:
             self.ctx16, self.hfull16 = ops.bf16_of(self.ctx), ops.bf16_of(self.h)
+        # one rank: attention writes the bf16 copy of its context that the o-projection reads
+        self.attn16 = None
+        if world == 1 and getattr(ops, "attention_writes_bf16", False) and takes_bf16([w0["wo"]], B):
+            self.attn16 = e((B, self.hq * hd), dtype=torch.bfloat16)
+            self.ctx16 = self.attn16
 
     def _gather(self, local, full):
         if self.world == 1:
@@ -339,8 +354,12 @@ class DecodeStep:
                                 self.v.view(self.batch, -1)])
             ops.rope_append(self.q, self.k, self.v, positions, self.tables, self.pools[layer], cfg.theta,
                             self.status)
-            ops.attention(self.q, self.pools[layer], self.tables, seq_lens, self.ctx_local, self.max_seq_len,
-                          self.status, self.workspace)
+            if self.attn16 is not None:
+                ops.attention(self.q, self.pools[layer], self.tables, seq_lens, self.ctx_local, self.max_seq_len,
+                              self.status, self.workspace, ctx16=self.attn16)
+            else:
+                ops.attention(self.q, self.pools[layer], self.tables, seq_lens, self.ctx_local, self.max_seq_len,
+                              self.status, self.workspace)
             ctx = self._gather(self.ctx_local, self.ctx)
             if self.whole_o:
                 self._linear(ctx, self.ctx16, w["wo"], self.o)

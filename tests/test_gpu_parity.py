@@ -554,3 +554,42 @@ def test_validate_payload_applies_the_canonical_rules(b2, port):
     codes[-1] |= 0x50                      # 33 elements: the last byte's high nibble is unused
     with pytest.raises(ValueError, match="unused high nibble"):
         b2.validate_payload(broken(odd, codes=codes))
+
+
+@pytest.mark.parametrize("hq,hkv,d,bs", [(8, 2, 128, 16), (6, 2, 64, 16)])
+def test_paged_decode_writes_the_bf16_copy_of_its_context(b2, hq, hkv, d, bs):
+    """b2_paged_decode_attention_bf16: the FP32 context is the one b2_paged_decode_attention writes,
+    bit for bit, and the bf16 copy is its round-to-nearest-even (single-split, merged and generic
+    paths)."""
+    from riftco_transformer_b200._lib import lib
+    from riftco_transformer_b200.backend import _check
+    rng = np.random.default_rng(hq + d)
+    lens = np.array([3, 200, 256, 257, 1500], np.uint32)
+    blocks = -(-lens.astype(np.int64) // bs)
+    P = int(blocks.sum())
+    perm = rng.permutation(P)
+    tables = np.zeros((len(lens), int(blocks.max())), np.uint32)
+    at = 0
+    for s, nb in enumerate(blocks):
+        tables[s, :nb] = perm[at:at + nb]
+        at += nb
+    K = dev(rng.standard_normal((P, hkv, bs, d)).astype(np.float32))
+    V = dev(rng.standard_normal((P, hkv, bs, d)).astype(np.float32))
+    q = dev(rng.standard_normal((len(lens), hq, d)).astype(np.float32))
+    t, ln = dev(tables.view(np.int32)), dev(lens.view(np.int32))
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    plain = torch.empty_like(q)
+    both = torch.empty_like(q)
+    half = torch.empty(q.shape, dtype=torch.bfloat16, device="cuda")
+    args = (len(lens), hq, hkv, d, bs, P, tables.shape[1], int(lens.max()), None, 0, status.data_ptr(), None)
+    _check(lib.b2_paged_decode_attention(q.data_ptr(), K.data_ptr(), V.data_ptr(), t.data_ptr(), ln.data_ptr(),
+                                         plain.data_ptr(), *args))
+    _check(lib.b2_paged_decode_attention_bf16(q.data_ptr(), K.data_ptr(), V.data_ptr(), t.data_ptr(), ln.data_ptr(),
+                                              both.data_ptr(), half.data_ptr(), *args))
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    assert torch.equal(plain.view(torch.int32), both.view(torch.int32))
+    assert torch.equal(half.view(torch.int16), both.to(torch.bfloat16).view(torch.int16))
+    with pytest.raises(ValueError):
+        _check(lib.b2_paged_decode_attention_bf16(q.data_ptr(), K.data_ptr(), V.data_ptr(), t.data_ptr(),
+                                                  ln.data_ptr(), both.data_ptr(), None, *args))
