@@ -685,7 +685,14 @@ nf4_decode_tmem_kernel(const __grid_constant__ DecodeMaps maps, const __grid_con
             const TileRef cur_ref = tref;
             const bool cur_live = live;
             const bool seg_ends = it + 1u == item_end || rho + 1u == R;
-            // ---- start this set's next item (j + 2) while the stores complete ----
+            // Publish before the next item is touched: a tensor-memory stage comes back only after the
+            // MMAs that read it, so the time from "stage free" to "stage published" sets the pace of
+            // the whole pipeline and must not contain the next item's lookups.
+            tmem_st_wait();
+            tcgen05_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars.a_full[as]);
+            // ---- start this set's next item (j + 2) ----
             ws = ws2;
             w_trip = w_trip2;
             done_ready = more && a_trip2 > 0u ? mbar_test_u32(&bars.done[as2], (a_trip2 - 1u) & 1u) : 0u;
@@ -702,10 +709,6 @@ nf4_decode_tmem_kernel(const __grid_constant__ DecodeMaps maps, const __grid_con
                 }
                 begin_item(tile, rho, new_tile);
             }
-            tmem_st_wait();
-            tcgen05_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&bars.a_full[as]);
             as = as2;
             a_trip = a_trip2;
             if (!seg_ends) continue;
