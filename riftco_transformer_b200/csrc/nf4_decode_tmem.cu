@@ -32,11 +32,14 @@
 #include "b2_kernels.h"
 #include "sm100_ptx.cuh"
 
+#include <cooperative_groups.h>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
 #include <cstdlib>
 #include <mutex>
+
+namespace cg = cooperative_groups;
 
 namespace b2 {
 namespace {
@@ -91,6 +94,7 @@ struct DecodeParams {
     uint32_t total_items;      // tiles * rounds
     uint32_t blocks_per_row;   // k >> block_shift
     uint32_t kshift;           // block_shift - 6: 64-wide k-blocks per scale block, as a shift
+    uint32_t cluster_k;        // > 1: the CTAs of a cluster of this size split one tile's rounds
     float* partial;            // [2 * gridDim.x][kPartialFloats]
     uint32_t* counters;        // [tiles], zero before the launch; the kernel leaves them zero
     uint32_t* error;
@@ -316,8 +320,20 @@ nf4_decode_tmem_kernel(const __grid_constant__ DecodeMaps maps, const __grid_con
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
     const uint32_t ctas = gridDim.x, cta = blockIdx.x;
     const uint32_t R = p.rounds;
-    const uint32_t item_begin = range_begin(cta, ctas, p.total_items);
-    const uint32_t item_end = range_begin(cta + 1u, ctas, p.total_items);
+    // Work split. Few tiles (tiles * 2 <= SMs): a cluster of cluster_k CTAs owns one tile, CTA r of it
+    // the rounds [r * R / k, (r + 1) * R / k), and the partial tiles meet in the leader's registers
+    // through distributed shared memory. Otherwise stream-K: CTA c takes the c-th equal share of the
+    // (tile, round) list, and partial tiles meet in global memory.
+    const bool clustered = p.cluster_k > 1u;
+    uint32_t item_begin, item_end;
+    if (clustered) {
+        const uint32_t tile = cta / p.cluster_k, r = cta - tile * p.cluster_k;
+        item_begin = tile * R + r * R / p.cluster_k;
+        item_end = tile * R + (r + 1u) * R / p.cluster_k;
+    } else {
+        item_begin = range_begin(cta, ctas, p.total_items);
+        item_end = range_begin(cta + 1u, ctas, p.total_items);
+    }
     const uint32_t n_stages = plan.n_stages;
     const bool fp32_scales = p.w[0].encoding == B2_SCALES_FLOAT32;
 
@@ -731,7 +747,10 @@ nf4_decode_tmem_kernel(const __grid_constant__ DecodeMaps maps, const __grid_con
             }
             const uint32_t n = cur_ref.n0 + row;
             const uint32_t slot = 2u * cta + (item_begin < cur_tile * R ? 1u : 0u);
-            float* partial = p.partial + static_cast<uint64_t>(slot) * kPartialFloats;
+            // (in a cluster the partial tile stays in this CTA's shared memory: ring slot 0, which is
+            // free because the segment's last MMAs, and with them every item of this CTA, are complete)
+            float* partial = clustered ? reinterpret_cast<float*>(smem_raw + (w_stage_addr(plan, 0u) - raw32))
+                                       : p.partial + static_cast<uint64_t>(slot) * kPartialFloats;
             if (h * 16u < p.n_pad) {
                 uint32_t r[16];
                 tmem_ld_32x16(tmem_base + (cur_seg & 1u) * kMaxTokens + lane_addr + h * 16u, r);
@@ -754,7 +773,7 @@ nf4_decode_tmem_kernel(const __grid_constant__ DecodeMaps maps, const __grid_con
             tcgen05_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(&bars.acc_empty[cur_seg & 1u]);
-            if (!whole) {
+            if (!whole && !clustered) {
                 // Publish the partial tile; the CTA that arrives last sums all of them in CTA order.
                 const uint32_t c_first = cta_of_item(cur_tile * R, ctas, p.total_items);
                 const uint32_t c_last = cta_of_item(cur_tile * R + R - 1u, ctas, p.total_items);
@@ -818,6 +837,54 @@ nf4_decode_tmem_kernel(const __grid_constant__ DecodeMaps maps, const __grid_con
                 set_barrier(set);   // last_flag and the slot list are rewritten by the set's next partial segment
             }
         }
+    }
+    if (clustered) {
+        // Every CTA of the cluster holds its partial tile [token][row] in its own shared memory. The
+        // leader adds them in rank order (a fixed order: results repeat bit for bit) and writes the
+        // output tile; the second barrier keeps the peers' shared memory alive until it has read it.
+        cg::cluster_group cluster = cg::this_cluster();
+        cluster.sync();
+        if (cluster.block_rank() == 0u && warp >= static_cast<uint32_t>(kFirstExpandWarp)) {
+            const uint32_t tile = cta / p.cluster_k;
+            const TileRef ref = locate_tile(p, tile);
+            float* out = p.out[0];
+#pragma unroll
+            for (int i = 1; i < kMaxWeights; ++i) {
+                if (ref.wi == static_cast<uint32_t>(i)) out = p.out[i];
+            }
+            const float4* mine = reinterpret_cast<const float4*>(smem_raw + (w_stage_addr(plan, 0u) - raw32));
+            const uint32_t st = tid - kFirstExpandWarp * 32u;
+            const uint32_t total4 = p.m * (kTileW / 4);
+            for (uint32_t i4 = st; i4 < total4; i4 += kExpandThreads) {
+                float4 pv[8];
+#pragma unroll
+                for (uint32_t q = 0; q < 8u; ++q) {
+                    pv[q] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (q < p.cluster_k) pv[q] = cluster.map_shared_rank(mine, q)[i4];
+                }
+                float4 acc = pv[0];
+#pragma unroll
+                for (uint32_t q = 1; q < 8u; ++q) {
+                    if (q < p.cluster_k) {
+                        acc.x += pv[q].x;
+                        acc.y += pv[q].y;
+                        acc.z += pv[q].z;
+                        acc.w += pv[q].w;
+                    }
+                }
+                const uint32_t t = i4 / (kTileW / 4), rr = (i4 % (kTileW / 4)) * 4u;
+                float* dst = out + static_cast<uint64_t>(t) * ref.n_out + ref.n0 + rr;
+                if (ref.n0 + rr + 3u < ref.n_out && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
+                    *reinterpret_cast<float4*>(dst) = acc;
+                } else {
+                    const float a4[4] = {acc.x, acc.y, acc.z, acc.w};
+                    for (uint32_t u = 0; u < 4u; ++u) {
+                        if (ref.n0 + rr + u < ref.n_out) dst[u] = a4[u];
+                    }
+                }
+            }
+        }
+        cluster.sync();
     }
     tcgen05_fence_before_sync();
     __syncthreads();
@@ -913,6 +980,40 @@ bool nf4_decode_tmem_supported(const WeightView& w, const void* x, uint64_t rows
     return w.out_features <= 0x7FFFFFFFull && w.in_features <= 0x7FFFFFFFull;
 }
 
+namespace {
+
+// Clusters of `k` CTAs of this kernel that can be resident on the device at once (cached per device).
+int32_t resident_clusters(const DeviceContext& ctx, bool half, uint32_t k, uint32_t* out) {
+    static int cached[kMaxDevices][2][9] = {};
+    static std::mutex cache_mutex;
+    std::lock_guard<std::mutex> lock(cache_mutex);
+    int& slot = cached[ctx.device][half ? 1 : 0][k];
+    if (slot == 0) {
+        cudaLaunchConfig_t config = {};
+        config.blockDim = dim3(kThreads);
+        config.dynamicSmemBytes = kSmemBytes;
+        config.gridDim = dim3(static_cast<unsigned>(ctx.sm_count / k) * k);
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = k;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        config.attrs = attr;
+        config.numAttrs = 1;
+        int n = 0;
+        if (half) {
+            B2_CUDA_TRY(cudaOccupancyMaxActiveClusters(&n, nf4_decode_tmem_kernel<true>, &config));
+        } else {
+            B2_CUDA_TRY(cudaOccupancyMaxActiveClusters(&n, nf4_decode_tmem_kernel<false>, &config));
+        }
+        slot = n > 0 ? n : -1;
+    }
+    *out = slot > 0 ? static_cast<uint32_t>(slot) : 0u;
+    return B2_STATUS_OK;
+}
+
+}  // namespace
+
 // `x16` holds the activations as bf16 (half == false) or fp16 (half == true), [rows, in] row-major.
 // `partial` is scratch of nf4_decode_tmem_workspace_bytes(); `counters` are `tiles` zeroed words.
 int32_t launch_nf4_decode_tmem(const DeviceContext& ctx, const WeightView* ws, float* const* ys, uint32_t count,
@@ -995,17 +1096,42 @@ int32_t launch_nf4_decode_tmem(const DeviceContext& ctx, const WeightView* ws, f
         return B2_STATUS_OK;
     }));
     cudaLaunchConfig_t config = {};
-    const uint32_t ctas = p.total_items < static_cast<uint32_t>(ctx.sm_count) ? p.total_items
-                                                                               : static_cast<uint32_t>(ctx.sm_count);
-    config.gridDim = dim3(ctas);
     config.blockDim = dim3(kThreads);
     config.dynamicSmemBytes = kSmemBytes;
     config.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     config.attrs = attr;
     config.numAttrs = 1;
+    // Few tiles: one cluster per tile, as many CTAs per cluster as the SMs allow (at least two rounds
+    // each), provided every cluster can be resident at once.
+    const uint32_t sms = static_cast<uint32_t>(ctx.sm_count);
+    uint32_t cluster_k = 1;
+    if (tiles * 2 <= sms) {
+        uint32_t k = sms / static_cast<uint32_t>(tiles);
+        if (k > 8u) k = 8u;
+        if (k > p.rounds / 2u) k = p.rounds / 2u;
+        for (; k >= 2u; --k) {
+            uint32_t resident = 0;
+            B2_TRY(resident_clusters(ctx, half, k, &resident));
+            if (resident >= tiles) {
+                cluster_k = k;
+                break;
+            }
+        }
+    }
+    p.cluster_k = cluster_k;
+    if (cluster_k > 1u) {
+        config.gridDim = dim3(static_cast<uint32_t>(tiles) * cluster_k);
+        attr[1].id = cudaLaunchAttributeClusterDimension;
+        attr[1].val.clusterDim.x = cluster_k;
+        attr[1].val.clusterDim.y = 1;
+        attr[1].val.clusterDim.z = 1;
+        config.numAttrs = 2;
+    } else {
+        config.gridDim = dim3(p.total_items < sms ? p.total_items : sms);
+    }
     if (half) {
         B2_CUDA_TRY(cudaLaunchKernelEx(&config, nf4_decode_tmem_kernel<true>, maps, map_x, p));
     } else {
