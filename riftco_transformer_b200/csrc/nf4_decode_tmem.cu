@@ -457,10 +457,6 @@ nf4_decode_tmem_kernel(const __grid_constant__ DecodeMaps maps, const __grid_con
         const uint64_t dx0 = umma_desc_k_major_sw128(plan.x32);
         const uint32_t x_stage16 = plan.x_stage_bytes >> 4, kb16 = (p.n_pad * 128u) >> 4;
         uint32_t s = 0, trip = 0, xs = 0, x_trip = 0, rho = item_begin % R, seg = 0;
-        // Both operand barriers of the coming item were seen complete by the tests issued before the
-        // previous item's MMAs: a barrier is a round trip through the shared-memory pipe, which the
-        // expansion warps keep busy, so the question is asked early and the answer read late.
-        uint32_t ready = 0;
         for (uint32_t it = item_begin; it < item_end; ++it) {
             const bool first = it == item_begin || rho == 0u;
             const bool last = it + 1u == item_end || rho + 1u == R;
@@ -468,17 +464,9 @@ nf4_decode_tmem_kernel(const __grid_constant__ DecodeMaps maps, const __grid_con
             // epilogue of segment s - 2 must have read it.
             const uint32_t acc_index = seg & 1u;
             if (first && seg > 1u) mbar_wait(&bars.acc_empty[acc_index], ((seg >> 1) - 1u) & 1u, abort, kPollBudget);
-            if (ready == 0u) {
-                mbar_wait(&bars.a_full[s], trip & 1u, abort, kPollBudget);
-                mbar_wait(&bars.x_full[xs], x_trip & 1u, abort, kPollBudget);
-            }
+            mbar_wait(&bars.a_full[s], trip & 1u, abort, kPollBudget);
+            mbar_wait(&bars.x_full[xs], x_trip & 1u, abort, kPollBudget);
             tcgen05_fence_after_sync();
-            uint32_t next_a = 0, next_x = 0;
-            if (it + 1u < item_end) {
-                const uint32_t s2 = s + 1u == kAStages ? 0u : s + 1u, xs2 = xs + 1u == kXStages ? 0u : xs + 1u;
-                next_a = mbar_test_u32(&bars.a_full[s2], (s2 == 0u ? trip + 1u : trip) & 1u);
-                next_x = mbar_test_u32(&bars.x_full[xs2], (xs2 == 0u ? x_trip + 1u : x_trip) & 1u);
-            }
             if (elect_one()) {
                 const uint64_t dx_s = dx0 + xs * x_stage16;
                 const uint32_t a_s = tmem_a + s * kStageColumns;
@@ -497,7 +485,6 @@ nf4_decode_tmem_kernel(const __grid_constant__ DecodeMaps maps, const __grid_con
                 umma_commit(&bars.x_empty[xs]);
             }
             __syncwarp();
-            ready = next_a & next_x;
             if (last) ++seg;
             if (++rho == R) rho = 0;
             if (++s == kAStages) {
@@ -535,10 +522,11 @@ nf4_decode_tmem_kernel(const __grid_constant__ DecodeMaps maps, const __grid_con
         const uint32_t lut_lane = plan.lut32 | (lane * 4u);
         const uint32_t lane_addr = (quarter * 32u) << 16;
         const uint32_t sshift = p.w[0].scale_block_shift;
-        // byte offsets of this thread's four 16-byte chunks inside a swizzled [128 x 128 B] box
-        uint32_t code_off[4];
-#pragma unroll
-        for (uint32_t c = 0; c < 4u; ++c) code_off[c] = row * 128u + (((4u * h + c) ^ (row & 7u)) << 4);
+        // This thread's four 16-byte chunks inside a swizzled [128 x 128 B] box: chunk c of the row's
+        // half h lies at ((4h + c) ^ (row & 7)) * 16, which is code_base + ((c ^ (row & 3)) << 4).
+        const uint32_t code_base = row * 128u + (((4u * h) ^ (row & 4u)) << 4);
+        const uint32_t code_low = (row & 3u) << 4;
+        auto code_off = [&](uint32_t c) { return code_base + ((c << 4) ^ code_low); };
 
         const uint32_t n_items = item_end - item_begin;
         uint32_t ws = set, w_trip = 0;                 // ring slot / trip of this set's current item
@@ -599,14 +587,6 @@ nf4_decode_tmem_kernel(const __grid_constant__ DecodeMaps maps, const __grid_con
                 v[4 * q + 3] = pair_mul<kHalf>(lds_u32(__byte_perm(word, lut_lane, 0x7634u)), s2);
             }
         };
-        // Answers of barrier tests issued well before the wait they stand for (1: already complete).
-        // A barrier access is a round trip through the shared-memory pipe, which the table lookups keep
-        // busy; asked early, the answer arrives while the lookups run.
-        uint32_t w_ready = 0, done_ready = 0;
-        // An early test of the ring slot of this set's next item is sound only if the slot's previous
-        // phase is known to be complete, which holds when this set consumed it (an even ring: the slot's
-        // previous item is n_stages items back and belongs to the same set).
-        const bool w_early = (n_stages & 1u) == 0u;
         uint4 second_c0, second_c1;      // packed bytes of the item's second pass
         float second_scale = 0.0f;
         // First pass of item (tile, rho): waits for the ring slot, reads the thread's 64 packed bytes
@@ -621,11 +601,11 @@ nf4_decode_tmem_kernel(const __grid_constant__ DecodeMaps maps, const __grid_con
                 live = tref.n0 + row < tref.n_out;
             }
             stage32 = w_stage_addr(plan, ws);
-            if (w_ready == 0u) mbar_wait(&bars.w_full[ws], w_trip & 1u, abort, kPollBudget);
-            const uint4 c0 = lds_u4(stage32 + code_off[0]);
-            const uint4 c1 = lds_u4(stage32 + code_off[1]);
-            second_c0 = lds_u4(stage32 + code_off[2]);
-            second_c1 = lds_u4(stage32 + code_off[3]);
+            mbar_wait(&bars.w_full[ws], w_trip & 1u, abort, kPollBudget);
+            const uint4 c0 = lds_u4(stage32 + code_off(0u));
+            const uint4 c1 = lds_u4(stage32 + code_off(1u));
+            second_c0 = lds_u4(stage32 + code_off(2u));
+            second_c1 = lds_u4(stage32 + code_off(3u));
             const uint32_t blk0 = (4u * rho) >> p.kshift;
             float scale = 0.0f;
             second_scale = 0.0f;
@@ -672,22 +652,8 @@ nf4_decode_tmem_kernel(const __grid_constant__ DecodeMaps maps, const __grid_con
             const uint32_t it = item_begin + j;
             if (a_trip > 0) depend();
             // ---- publish item j: both passes into tensor-memory stage `as` ----
-            if (a_trip > 0 && done_ready == 0u) mbar_wait(&bars.done[as], (a_trip - 1u) & 1u, abort, kPollBudget);
+            if (a_trip > 0) mbar_wait(&bars.done[as], (a_trip - 1u) & 1u, abort, kPollBudget);
             tcgen05_fence_after_sync();
-            // slot and stage of this set's next item (j + 2); their barriers are tested now and
-            // read when the item is reached
-            uint32_t ws2 = ws + 2u, w_trip2 = w_trip;
-            if (ws2 >= n_stages) {
-                ws2 -= n_stages;
-                ++w_trip2;
-            }
-            uint32_t as2 = as + 2u, a_trip2 = a_trip;
-            if (as2 >= kAStages) {
-                as2 -= kAStages;
-                ++a_trip2;
-            }
-            const bool more = j + 2u < n_items;
-            w_ready = more && w_early ? mbar_test_u32(&bars.w_full[ws2], w_trip2 & 1u) : 0u;
             const uint32_t taddr = tmem_a + as * kStageColumns + h * 64u + lane_addr;
             tmem_st_32x32(taddr, v);
             lookup(second_c0, second_c1, second_scale);
@@ -709,10 +675,12 @@ nf4_decode_tmem_kernel(const __grid_constant__ DecodeMaps maps, const __grid_con
             __syncwarp();
             if (lane == 0) mbar_arrive(&bars.a_full[as]);
             // ---- start this set's next item (j + 2) ----
-            ws = ws2;
-            w_trip = w_trip2;
-            done_ready = more && a_trip2 > 0u ? mbar_test_u32(&bars.done[as2], (a_trip2 - 1u) & 1u) : 0u;
-            if (more) {
+            ws += 2u;
+            if (ws >= n_stages) {
+                ws -= n_stages;
+                ++w_trip;
+            }
+            if (j + 2u < n_items) {
                 bool new_tile = false;
                 for (uint32_t step = 0; step < 2u; ++step) {   // walk two items ahead
                     if (rho + 1u == R) {
@@ -725,8 +693,11 @@ nf4_decode_tmem_kernel(const __grid_constant__ DecodeMaps maps, const __grid_con
                 }
                 begin_item(tile, rho, new_tile);
             }
-            as = as2;
-            a_trip = a_trip2;
+            as += 2u;
+            if (as >= kAStages) {
+                as -= kAStages;
+                ++a_trip;
+            }
             if (!seg_ends) continue;
 
             // ---- epilogue of the segment [cur_first_rho, cur_rho] of tile cur_tile (this set's warps) ----

@@ -53,17 +53,6 @@ __device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
         : "memory");
     return done != 0;
 }
-// The test as a value (1: the phase has completed) for code that asks early and reads the answer
-// later: the round trip to the barrier then overlaps with whatever is issued in between.
-__device__ __forceinline__ uint32_t mbar_test_u32(uint64_t* bar, uint32_t parity) {
-    uint32_t done;
-    asm volatile(
-        "{ .reg .pred p; mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
-        : "=r"(done)
-        : "r"(smem_u32(bar)), "r"(parity)
-        : "memory");
-    return done;
-}
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort,
                                           uint32_t budget = 2000000u) {
     if (mbar_test_wait(bar, parity)) return true;   // the common case on a pipeline that runs ahead
