@@ -214,11 +214,38 @@ def build_reference_with_b200_adapter(force: bool = False) -> Path | None:
     return REF_B200_LIB
 
 
+REF_CONFORMANCE = REF_DIR / "quantized_linear_backend_tests"
+
+
+def build_reference_conformance_tests(force: bool = False) -> Path | None:
+    """The reference's own accelerator conformance executable for the packed-NF4 linear
+    (tests/core/backend/test_quantized_linear_backend.cpp, target quantized_linear_backend_tests of
+    tests/CMakeLists.txt:549-563), compiled where it lies with RIFTCO_TRANSFORMER_TEST_REQUIRE_CUDA=1
+    and linked against the reference core that carries this repo's adapter: run on a B200 it fails
+    unless the CUDA backend is available and matches the CPU oracle on the reference's fixtures.
+    None without a checkout or without the adapter build."""
+    root = reference_dir()
+    lib = build_reference_with_b200_adapter(force)
+    if root is None or lib is None:
+        return REF_CONFORMANCE if REF_CONFORMANCE.exists() else None
+    source = root / "tests/core/backend/test_quantized_linear_backend.cpp"
+    if not force and _newer(REF_CONFORMANCE, [source, lib]):
+        return REF_CONFORMANCE
+    includes = ["-I", str(root / "include"), "-I", str(root / "src")]
+    _run([
+        "g++", *CXXFLAGS, *includes, "-DRIFTCO_TRANSFORMER_TEST_REQUIRE_CUDA=1", str(source),
+        "-o", str(REF_CONFORMANCE), "-pthread", "-L", str(REF_DIR), "-lriftco_ref_b200",
+        "-Wl,-rpath,$ORIGIN", "-Wl,-rpath,$ORIGIN/../../riftco_transformer_b200/lib",
+    ])
+    return REF_CONFORMANCE
+
+
 def main() -> None:
     force = "--force" in sys.argv
     print("oracle:", build_oracle(force))
     print("reference:", build_reference(force))
     print("reference + B200 adapter:", build_reference_with_b200_adapter(force))
+    print("reference conformance executable:", build_reference_conformance_tests(force))
 
 
 if __name__ == "__main__":

@@ -78,3 +78,24 @@ def test_errors_keep_the_reference_types(cuda_ref, port):
     with pytest.raises(oracle.ReferenceError_) as e:
         cuda_ref.paged_decode(q, k, v, np.array([0, 1, 9], np.uint32), 5)   # block id outside the pool
     assert e.value.status in (1, 2)
+
+
+def test_reference_conformance_executable():
+    """The reference's own accelerator test for the packed-NF4 linear
+    (tests/core/backend/test_quantized_linear_backend.cpp, built with
+    RIFTCO_TRANSFORMER_TEST_REQUIRE_CUDA=1 against the reference core + this repo's adapter):
+    aligned and edge fixtures in both scale encodings, forward and input backward, at the
+    reference's accelerator tolerance, plus its storage-size rules. Its output is kept as a log."""
+    import subprocess
+    from pathlib import Path
+    root = Path(__file__).resolve().parents[1]
+    exe = root / "oracle" / "_ref" / "quantized_linear_backend_tests"
+    if not exe.exists():
+        pytest.skip("the conformance executable is prebuilt from a checkout of the reference (oracle/build.py)")
+    proc = subprocess.run([str(exe)], capture_output=True, text=True, timeout=600)
+    out_dir = root / "gpurun_out"
+    out_dir.mkdir(exist_ok=True)
+    (out_dir / "reference_quantized_linear_backend_tests.log").write_text(
+        f"$ oracle/_ref/quantized_linear_backend_tests\n{proc.stdout}{proc.stderr}exit code {proc.returncode}\n")
+    assert proc.returncode == 0, proc.stdout + proc.stderr
+    assert "quantized-linear backend tests passed" in proc.stdout
