@@ -220,7 +220,7 @@ def test_decode_step_with_and_without_the_bf16_handoff(monkeypatch):
         assert int(step.status.item()) == 0
         results.append((nxt.clone(), logits.clone(), step.ops.launches))
     assert torch.equal(results[0][1], results[1][1]) and torch.equal(results[0][0], results[1][0])
-    assert results[0][2] == results[1][2] - (3 * cfg.layers + 1)   # one pass less per q/k/v, gate/up, down, LM head
+    assert results[0][2] == results[1][2] - (4 * cfg.layers + 1)   # one pass less per q/k/v, o, gate/up, down, LM head
 
 
 def test_rope_append_of_a_prefill_chunk():
