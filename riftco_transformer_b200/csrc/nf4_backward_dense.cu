@@ -30,50 +30,54 @@ using namespace sm100;
 
 // ---- pre-pass: Wt[i, o] = bf16(W[o, i]) ----------------------------------------------------------
 
-constexpr int kTr = 64;   // 64 x 64 tile of W per CTA
+constexpr int kTrRows = 64;              // output rows of W per CTA (the GEMM's contraction)
+constexpr int kTrCols = 256;             // input columns of W per CTA: 128 contiguous packed bytes per row
+constexpr int kTrPitch = kTrRows + 8;    // bf16 per shared-memory row: 144 B, rows stay 16-byte aligned
 
+// A CTA expands a [64 x 256] tile of W and writes it transposed: 256 rows of Wt, 128 contiguous
+// bytes each. Thread (row = t % 64, q = t / 64) expands the 64 weights [64q, 64q + 64) of its row
+// (one scale block, as blocks hold at least 64 weights and start on multiples of 64): a warp is 32
+// consecutive rows of one q, so its 2-byte stores into the transposed tile fall into 64 contiguous
+// bytes. The store phase moves 16 bytes per thread, eight threads per 128-byte row of Wt.
 __global__ void __launch_bounds__(256)
 nf4_dequant_transpose_kernel(const WeightView w, __nv_bfloat16* __restrict__ wt) {
     pdl_launch_dependents();
-    __shared__ float tile[kTr][kTr + 1];
+    __shared__ __align__(16) __nv_bfloat16 tile[kTrCols][kTrPitch];
     __shared__ float codebook[16];   // a per-lane index into __constant__ memory would serialise the warp
     if (threadIdx.x < 16) codebook[threadIdx.x] = kNf4Codebook[threadIdx.x];
     __syncthreads();
     const uint64_t in = w.in_features, out = w.out_features;
-    const uint32_t i0 = blockIdx.x * kTr, o0 = blockIdx.y * kTr;
-    // load: thread (row = t / 4, quarter = t % 4) expands 16 weights (8 packed bytes)
+    const uint32_t i0 = blockIdx.x * kTrCols, o0 = blockIdx.y * kTrRows;
     const uint32_t t = threadIdx.x;
     {
-        const uint32_t row = t >> 2, q = t & 3u;
-        const uint64_t flat = (static_cast<uint64_t>(o0) + row) * in + i0 + 16u * q;
-        const uint2 packed = __ldg(reinterpret_cast<const uint2*>(w.codes + (flat >> 1)));
-        const float scale = decode_block_scale(w, flat >> w.block_shift);
-        const uint32_t words[2] = {packed.x, packed.y};
+        const uint32_t row = t & 63u, q = t >> 6;
+        if (i0 + 64u * q < in) {
+            const uint64_t flat = (static_cast<uint64_t>(o0) + row) * in + i0 + 64u * q;
+            const uint2* src = reinterpret_cast<const uint2*>(w.codes + (flat >> 1));
+            const uint2 p0 = __ldg(src), p1 = __ldg(src + 1), p2 = __ldg(src + 2), p3 = __ldg(src + 3);
+            const float scale = decode_block_scale(w, flat >> w.block_shift);
+            const uint32_t words[8] = {p0.x, p0.y, p1.x, p1.y, p2.x, p2.y, p3.x, p3.y};
 #pragma unroll
-        for (int k = 0; k < 16; ++k) {
-            const uint32_t code = (words[k >> 3] >> (4 * (k & 7))) & 0xFu;
-            tile[row][16 * q + k] = codebook[code] * scale;
+            for (int k = 0; k < 64; ++k) {
+                const uint32_t code = (words[k >> 3] >> (4 * (k & 7))) & 0xFu;
+                tile[64u * q + k][row] = __float2bfloat16_rn(codebook[code] * scale);
+            }
         }
     }
     __syncthreads();
-    // store: thread (column = t / 4, quarter = t % 4) writes 16 consecutive output-row values
-    {
-        const uint32_t col = t >> 2, q = t & 3u;
-        __nv_bfloat16* dst = wt + (static_cast<uint64_t>(i0) + col) * out + o0 + 16u * q;
-        uint32_t v[8];
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
-            __nv_bfloat162 pair = __floats2bfloat162_rn(tile[16 * q + 2 * k][col], tile[16 * q + 2 * k + 1][col]);
-            v[k] = *reinterpret_cast<uint32_t*>(&pair);
+    for (uint32_t it = 0; it < 8u; ++it) {
+        const uint32_t idx = t + 256u * it, col = idx >> 3, chunk = idx & 7u;
+        if (i0 + col < in) {
+            const uint4 v = *reinterpret_cast<const uint4*>(&tile[col][chunk * 8u]);
+            *reinterpret_cast<uint4*>(wt + (static_cast<uint64_t>(i0) + col) * out + o0 + chunk * 8u) = v;
         }
-        reinterpret_cast<uint4*>(dst)[0] = make_uint4(v[0], v[1], v[2], v[3]);
-        reinterpret_cast<uint4*>(dst)[1] = make_uint4(v[4], v[5], v[6], v[7]);
     }
 }
 
 // ---- GEMM: both operands bf16 K-major in global memory ----------------------------------------------
 
-constexpr int kBM = 256, kBN = 256, kBK = 64;
+constexpr int kBM = 256, kBK = 64;
 constexpr int kStages = 3;
 constexpr int kOperandBytes = 256 * kBK * 2;            // 32 KB per operand and stage
 constexpr int kStageBytes = 2 * kOperandBytes;
@@ -96,15 +100,20 @@ struct Barriers {
     uint32_t abort;
 };
 
+// BN: in-columns per tile (256, 224 or 192). The host picks the width that needs the fewest
+// tile-widths of time on the device's SMs: 14336 in-columns at 4096 rows are 896 tiles of 256
+// (6.05 waves of 148, paid as 7) but 1024 tiles of 224 (6.9 waves, paid as 7 x 224 / 256).
+template <int BN>
 __global__ void __launch_bounds__(kThreads, 1)
 bf16_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const Params p) {
+    constexpr uint32_t kBytesB = BN * kBK * 2;   // B operand of a stage (its slot stays 32 KB)
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     __shared__ __align__(8) Barriers bars;
     const uint32_t raw32 = smem_u32(smem_raw);
     const uint32_t base32 = (raw32 + 1023u) & ~1023u;
     uint8_t* smem = smem_raw + (base32 - raw32);
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
-    const uint32_t n0 = blockIdx.x * kBN, m0 = blockIdx.y * kBM;
+    const uint32_t n0 = blockIdx.x * BN, m0 = blockIdx.y * kBM;
     const uint32_t num_kb = p.k / kBK;
     volatile uint32_t* abort = &bars.abort;
 
@@ -135,7 +144,7 @@ bf16_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             uint32_t s = 0, ph = 0;
             for (uint32_t kb = 0; kb < num_kb; ++kb) {
                 if (kb >= kStages) mbar_wait(&bars.done[s], ph ^ 1u, abort);
-                mbar_expect_tx(&bars.full[s], kStageBytes);
+                mbar_expect_tx(&bars.full[s], kOperandBytes + kBytesB);
                 tma_load_2d(smem + s * kStageBytes, &map_a, static_cast<int>(kb * kBK), static_cast<int>(m0),
                             &bars.full[s]);
                 tma_load_2d(smem + s * kStageBytes + kOperandBytes, &map_b, static_cast<int>(kb * kBK),
@@ -148,7 +157,7 @@ bf16_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            constexpr uint32_t idesc = umma_idesc_bf16_f32(128, kBN);
+            constexpr uint32_t idesc = umma_idesc_bf16_f32(128, BN);
             const uint64_t d0 = umma_desc_k_major_sw128(base32);
             uint32_t s = 0, ph = 0;
             for (uint32_t kb = 0; kb < num_kb; ++kb) {
@@ -178,7 +187,8 @@ bf16_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         tcgen05_fence_after_sync();
         const uint32_t quarter = warp & 3u, half = ((warp - 2u) >> 2) & 1u, col_half = (warp - 2u) >> 3;
         const uint32_t row_out = m0 + half * 128u + quarter * 32u + lane;
-        for (uint32_t c = col_half * (kBN / 64); c < (col_half + 1u) * (kBN / 64); ++c) {
+        constexpr uint32_t kChunks = BN / 32, kFirstHalf = (kChunks + 1) / 2;   // 32-column chunks per accumulator
+        for (uint32_t c = col_half == 0u ? 0u : kFirstHalf; c < (col_half == 0u ? kFirstHalf : kChunks); ++c) {
             uint32_t v[32];
             tmem_ld_32x32(tmem_base + ((quarter * 32u) << 16) + half * 256u + c * 32u, v);
             tmem_ld_wait();
@@ -224,11 +234,11 @@ EncodeTiledFn encode_tiled() {
     return fn;
 }
 
-// bf16 [rows][cols] row-major, box = 64 columns x 256 rows, 128-byte swizzle, zero fill outside.
-int32_t operand_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols) {
+// bf16 [rows][cols] row-major, box = 64 columns x `box_rows` rows, 128-byte swizzle, zero fill outside.
+int32_t operand_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
     const cuuint64_t dims[2] = {cols, rows};
     const cuuint64_t strides[1] = {cols * 2};
-    const cuuint32_t box[2] = {kBK, 256};
+    const cuuint32_t box[2] = {kBK, box_rows};
     const cuuint32_t elem[2] = {1, 1};
     const CUresult r = encode_tiled()(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides,
                                       box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
@@ -267,16 +277,31 @@ int32_t launch_nf4_backward_dense(const DeviceContext& ctx, const WeightView& w,
     uint8_t* dy16 = static_cast<uint8_t*>(workspace);
     uint8_t* wt16 = dy16 + dy_bytes;
     B2_TRY(launch_f32_to_bf16(ctx, dy, dy16, rows * w.out_features, stream));
-    const dim3 tgrid(static_cast<unsigned>(w.in_features / kTr), static_cast<unsigned>(w.out_features / kTr));
+    const dim3 tgrid(static_cast<unsigned>((w.in_features + kTrCols - 1) / kTrCols),
+                     static_cast<unsigned>(w.out_features / kTrRows));
     nf4_dequant_transpose_kernel<<<tgrid, 256, 0, stream>>>(w, reinterpret_cast<__nv_bfloat16*>(wt16));
     B2_CUDA_TRY(cudaGetLastError());
 
+    // tile width: the fewest tile-widths of time over the device's SMs (ties go to the wider tile)
+    const uint64_t m_tiles = (rows + kBM - 1) / kBM;
+    uint32_t bn = 256;
+    uint64_t best = ~0ull;
+    for (uint32_t cand : {256u, 224u, 192u}) {
+        const uint64_t tiles = ((w.in_features + cand - 1) / cand) * m_tiles;
+        const uint64_t cost = ((tiles + ctx.sm_count - 1) / ctx.sm_count) * cand;
+        if (cost < best) {
+            best = cost;
+            bn = cand;
+        }
+    }
     CUtensorMap map_a, map_b;
-    B2_TRY(operand_map(&map_a, dy16, rows, w.out_features));            // dY  [M, K = out]
-    B2_TRY(operand_map(&map_b, wt16, w.in_features, w.out_features));   // Wt  [N = in, K = out]
+    B2_TRY(operand_map(&map_a, dy16, rows, w.out_features, 256));            // dY  [M, K = out]
+    B2_TRY(operand_map(&map_b, wt16, w.in_features, w.out_features, bn));    // Wt  [N = in, K = out]
     static PerDeviceOnce configured;
     B2_TRY(once_per_device(configured, ctx.device, []() -> int32_t {
-        B2_CUDA_TRY(cudaFuncSetAttribute(bf16_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+        B2_CUDA_TRY(cudaFuncSetAttribute(bf16_gemm_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+        B2_CUDA_TRY(cudaFuncSetAttribute(bf16_gemm_kernel<224>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+        B2_CUDA_TRY(cudaFuncSetAttribute(bf16_gemm_kernel<192>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
         return B2_STATUS_OK;
     }));
     Params p;
@@ -285,8 +310,14 @@ int32_t launch_nf4_backward_dense(const DeviceContext& ctx, const WeightView& w,
     p.n = static_cast<uint32_t>(w.in_features);
     p.k = static_cast<uint32_t>(w.out_features);
     p.error = ctx.gemm_error;
-    const dim3 grid(static_cast<unsigned>((w.in_features + kBN - 1) / kBN), static_cast<unsigned>((rows + kBM - 1) / kBM));
-    bf16_gemm_kernel<<<grid, kThreads, kSmemBytes, stream>>>(map_a, map_b, p);
+    const dim3 grid(static_cast<unsigned>((w.in_features + bn - 1) / bn), static_cast<unsigned>(m_tiles));
+    if (bn == 256) {
+        bf16_gemm_kernel<256><<<grid, kThreads, kSmemBytes, stream>>>(map_a, map_b, p);
+    } else if (bn == 224) {
+        bf16_gemm_kernel<224><<<grid, kThreads, kSmemBytes, stream>>>(map_a, map_b, p);
+    } else {
+        bf16_gemm_kernel<192><<<grid, kThreads, kSmemBytes, stream>>>(map_a, map_b, p);
+    }
     B2_CUDA_TRY(cudaGetLastError());
     return B2_STATUS_OK;
 }
