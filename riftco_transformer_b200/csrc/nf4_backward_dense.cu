@@ -186,24 +186,27 @@ bf16_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         mbar_wait(&bars.acc_full, 0u, abort, 20000000u);
         tcgen05_fence_after_sync();
         const uint32_t quarter = warp & 3u, half = ((warp - 2u) >> 2) & 1u, col_half = (warp - 2u) >> 3;
-        const uint32_t row_out = m0 + half * 128u + quarter * 32u + lane;
         constexpr uint32_t kChunks = BN / 32, kFirstHalf = (kChunks + 1) / 2;   // 32-column chunks per accumulator
         for (uint32_t c = col_half == 0u ? 0u : kFirstHalf; c < (col_half == 0u ? kFirstHalf : kChunks); ++c) {
             uint32_t v[32];
             tmem_ld_32x32(tmem_base + ((quarter * 32u) << 16) + half * 256u + c * 32u, v);
             tmem_ld_wait();
             const uint32_t col0 = n0 + c * 32u;
-            if (row_out < p.m && col0 < p.n) {
-                float* dst = p.out + static_cast<uint64_t>(row_out) * p.n + col0;
-                if (col0 + 32u <= p.n && (p.n & 3u) == 0u) {
+            // Transpose the warp's [32 rows x 32 columns] chunk through shared memory (the operand
+            // ring is free: every MMA has completed) so that each store instruction writes one
+            // row's 128 contiguous bytes instead of 16 bytes of 32 different rows.
+            float* scratch = reinterpret_cast<float*>(smem) + (warp - 2u) * (32u * 33u);
+            __syncwarp();
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        reinterpret_cast<float4*>(dst)[i] =
-                            make_float4(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]),
-                                        __uint_as_float(v[4 * i + 2]), __uint_as_float(v[4 * i + 3]));
+            for (int i = 0; i < 32; ++i) scratch[lane * 33u + i] = __uint_as_float(v[i]);
+            __syncwarp();
+            const uint32_t row_base = m0 + half * 128u + quarter * 32u;
+            if (col0 + lane < p.n) {
+#pragma unroll 8
+                for (uint32_t r = 0; r < 32u; ++r) {
+                    if (row_base + r < p.m) {
+                        p.out[static_cast<uint64_t>(row_base + r) * p.n + col0 + lane] = scratch[r * 33u + lane];
                     }
-                } else {
-                    for (uint32_t i = 0; i < 32u && col0 + i < p.n; ++i) dst[i] = __uint_as_float(v[i]);
                 }
             }
         }
