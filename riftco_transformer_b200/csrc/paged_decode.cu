@@ -291,14 +291,33 @@ paged_decode_merge_kernel(const PagedDecodeArgs a, const float* __restrict__ par
     if (n_splits <= 1) return;
     const uint64_t head = static_cast<uint64_t>(seq) * a.q_heads + h;
     const float* src = partials + head * max_splits * kPartialStride;
+    // Eight splits at a time with all their loads issued before the first use: a loop that uses
+    // each value as it arrives pays one L2 round trip per split.
     float mm = -INFINITY;
-    for (uint32_t s = 0; s < n_splits; ++s) mm = fmaxf(mm, __ldg(src + s * kPartialStride));
+    for (uint32_t s0 = 0; s0 < n_splits; s0 += 8u) {
+        float m8[8];
+#pragma unroll
+        for (uint32_t u = 0; u < 8u; ++u) m8[u] = s0 + u < n_splits ? __ldg(src + (s0 + u) * kPartialStride) : -INFINITY;
+#pragma unroll
+        for (uint32_t u = 0; u < 8u; ++u) mm = fmaxf(mm, m8[u]);
+    }
     float ll = 0.0f, o = 0.0f;
-    for (uint32_t s = 0; s < n_splits; ++s) {
-        const float ms = __ldg(src + s * kPartialStride);
-        const float f = (ms == -INFINITY) ? 0.0f : __expf(ms - mm);
-        ll = fmaf(__ldg(src + s * kPartialStride + 1), f, ll);
-        o = fmaf(__ldg(src + s * kPartialStride + 2 + c), f, o);
+    for (uint32_t s0 = 0; s0 < n_splits; s0 += 8u) {
+        float m8[8], l8[8], o8[8];
+#pragma unroll
+        for (uint32_t u = 0; u < 8u; ++u) {
+            const bool live = s0 + u < n_splits;
+            const float* part = src + (s0 + u) * kPartialStride;
+            m8[u] = live ? __ldg(part) : -INFINITY;
+            l8[u] = live ? __ldg(part + 1) : 0.0f;
+            o8[u] = live ? __ldg(part + 2 + c) : 0.0f;
+        }
+#pragma unroll
+        for (uint32_t u = 0; u < 8u; ++u) {   // split order, as before
+            const float f = (m8[u] == -INFINITY) ? 0.0f : __expf(m8[u] - mm);
+            ll = fmaf(l8[u], f, ll);
+            o = fmaf(o8[u], f, o);
+        }
     }
     if (mm == -INFINITY) {
         if (c == 0 && a.status != nullptr) atomicOr(a.status, B2_ATTN_STATUS_ALL_NEG_INF);
