@@ -244,11 +244,14 @@ nf4_gemv_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     }
     asm volatile("cp.async.commit_group;\n" ::);
     if (tid < 256) reinterpret_cast<float*>(low + L::kFactorOff)[tid] = dq_factor(tid);
-    pdl_launch_dependents();
-    pdl_wait();
+    // The first ring fill reads only the immutable weights and writes only this CTA's shared memory,
+    // so it too goes out before the dependency wait: the loads are in flight while the previous
+    // kernel drains. Activations and outputs are touched after the wait.
     if (tid == 0) {
         for (uint32_t slot = 0; slot < my_tiles && slot < NS; ++slot) issue_tile(slot);
     }
+    pdl_launch_dependents();
+    pdl_wait();
 
     {
         const uint32_t box = warp / kWarpsPerBox;
