@@ -11,18 +11,26 @@
 //    whatever the shape or the shard size. A CTA whose range ends inside a tile leaves a partial
 //    tile; the partial tiles of one output tile are summed in a fixed order by whichever CTA
 //    finishes last (a counter per tile), so results do not depend on timing.
+//  * A launch with few tiles (tiles * 2 <= SMs: the q/k/v, o and down projections of a 7B-shaped
+//    layer, and every sharded layer) is split differently: one thread-block cluster per tile, CTA r
+//    of k takes the rounds [r * R / k, (r + 1) * R / k), the partial tiles stay in shared memory and
+//    the cluster's leader adds them in rank order through distributed shared memory. That replaces
+//    the global round trip (store, fence, counter, reload) at the end of such a launch by two
+//    cluster barriers.
 //  * One thread streams the packed codes ([128 rows x 128 bytes], 128-byte swizzle), the tile's
 //    raw block scales and the second-level values they refer to into a shared-memory ring with
 //    cp.async.bulk.tensor; weights are immutable, so this starts before the dependency wait of a
 //    programmatic dependent launch, i.e. under the previous kernel's tail.
-//  * Sixteen expansion warps turn a round into its 16-bit operand form: thread (row, k-block)
-//    reads its 32 packed bytes from the ring, looks every byte up in a per-lane replicated
-//    byte -> pair table (one PRMT forms the address), multiplies by the block scale and writes its
-//    64 values with one tcgen05.st into the round's stage of TENSOR memory, where the weight tile
-//    is the A operand (lane = weight row). Three 256-wide stages keep expansion and MMAs apart.
-//  * One thread issues the sixteen tcgen05.mma (M128, N = 16 or 32 tokens, K16) of a round behind
-//    ONE barrier wait and commits once per round; the activations (16-bit, by TMA) are the B
-//    operand in shared memory.
+//  * Sixteen expansion warps, in two sets that alternate items, turn a round into its 16-bit
+//    operand form: thread (row, half) reads its 64 packed bytes from the ring, looks every byte up
+//    in a per-lane replicated byte -> pair table (one PRMT forms the address), multiplies by the
+//    block scale and writes the values with two tcgen05.st of 32 columns into the round's stage of
+//    TENSOR memory, where the weight tile is the A operand (lane = weight row). Three 256-wide
+//    stages keep expansion and MMAs apart.
+//  * One warp issues the sixteen tcgen05.mma (M128, N = 16 or 32 tokens, K16) of a round behind
+//    ONE barrier wait and commits once per round (warp-convergent loop, the instructions under
+//    elect.sync); the activations (16-bit, by TMA) are the B operand in shared memory. Two
+//    accumulators alternate between the segments of a CTA's range.
 //
 // Two operand types share the code: bf16 (activations handed over as bf16, rel-L2 ~3e-3, used
 // above 16 rows) and fp16 with an FP32 row normaliser (rel-L2 ~5e-4, used up to 16 rows, where
