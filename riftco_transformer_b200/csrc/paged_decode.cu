@@ -45,10 +45,13 @@ __device__ __forceinline__ void put_ctx(const PagedDecodeArgs& a, uint64_t index
 
 // Fast path (head_width 128, block_size 16, rep in {1,2,4,8}). The K and V chunks of a page (8 KB
 // each, contiguous in the pool) are brought into shared memory by cp.async.bulk: every warp owns a ring
-// of three 8 KB slots and keeps the next K, V and K chunks in flight while it works on one, so
-// 24 KB per warp (up to 192 KB per SM) are outstanding without holding them in registers.
+// of two 8 KB slots and has the next chunk in flight while it works on one. 64 KB per CTA lets three
+// CTAs share an SM (192 KB outstanding per SM, none of it in registers); three slots per warp and two
+// CTAs per SM hold the same bytes in flight but measured slower (96.9 vs 92.3 us per launch inside the
+// decode step, 350 vs 333 us on 64 sequences of 512-8192 tokens): with more CTAs per SM a CTA that
+// ends and its successor that starts stall a smaller share of the SM's loads.
 // The mbarrier waits are bounded; a timeout sets bit 3 of the status word.
-constexpr int kBulkSlots = 3;
+constexpr int kBulkSlots = 2;
 constexpr int kChunkBytes = kPage * kD * 4;   // 8 KB: one (page, kv head) of K or of V
 constexpr int kBulkSmemBytes = kFastWarps * kBulkSlots * kChunkBytes;
 
