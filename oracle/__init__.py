@@ -106,7 +106,8 @@ class Port:
     kind = "port"
 
     def __init__(self) -> None:
-        self.lib = C.CDLL(str(_build.build_oracle()))
+        # RIFTCO_ORACLE_SANITIZE=1: the ASan + UBSan build (the process must preload libasan)
+        self.lib = C.CDLL(str(_build.build_oracle(sanitize=os.environ.get("RIFTCO_ORACLE_SANITIZE") == "1")))
         L = self.lib
         L.orc_nf4_codebook.restype = _f32p
         L.orc_nearest_nf4_code.restype = C.c_uint8

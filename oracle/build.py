@@ -32,6 +32,7 @@ HERE = Path(__file__).resolve().parent
 BUILD_DIR = HERE / "_build"
 REF_DIR = HERE / "_ref"
 ORACLE_LIB = BUILD_DIR / "libriftco_oracle.so"
+ORACLE_SAN_LIB = BUILD_DIR / "libriftco_oracle_san.so"
 REF_LIB = REF_DIR / "libriftco_ref.so"
 REF_B200_LIB = REF_DIR / "libriftco_ref_b200.so"
 
@@ -128,17 +129,25 @@ def _newer(target: Path, sources: list[Path]) -> bool:
     return all(s.stat().st_mtime <= t for s in sources)
 
 
-def build_oracle(force: bool = False) -> Path:
-    """Compile the C restatement; returns the library path."""
+def build_oracle(force: bool = False, sanitize: bool = False) -> Path:
+    """Compile the C restatement; returns the library path. `sanitize` builds a second library
+    with AddressSanitizer and UndefinedBehaviorSanitizer (single-threaded, -O1), which
+    tests/test_oracle_sanitized_cpu.py runs the golden-vector tests against."""
     sources = [HERE / "riftco_oracle.c", HERE / "riftco_oracle.h"]
-    if not force and _newer(ORACLE_LIB, sources):
-        return ORACLE_LIB
+    target = ORACLE_SAN_LIB if sanitize else ORACLE_LIB
+    if not force and _newer(target, sources):
+        return target
     BUILD_DIR.mkdir(exist_ok=True)
+    if sanitize:
+        flags = ["-O1", "-g", "-fno-omit-frame-pointer", "-fsanitize=address,undefined",
+                 "-fno-sanitize-recover=undefined"]
+    else:
+        flags = ["-O2", "-fopenmp"]
     _run([
-        "gcc", "-std=c11", "-O2", "-ffp-contract=off", "-fopenmp", "-fPIC",
-        "-shared", "-o", str(ORACLE_LIB), str(HERE / "riftco_oracle.c"), "-lm",
+        "gcc", "-std=c11", *flags, "-ffp-contract=off", "-fPIC",
+        "-shared", "-o", str(target), str(HERE / "riftco_oracle.c"), "-lm",
     ])
-    return ORACLE_LIB
+    return target
 
 
 def reference_dir() -> Path | None:

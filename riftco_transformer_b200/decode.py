@@ -342,11 +342,17 @@ class DecodeStep:
 
     def step(self, tokens, positions, seq_lens):
         """tokens int32 [B]; positions uint32/int32 [B] = index of the new token;
-        seq_lens = positions + 1. Returns (next_tokens [B], logits [B, vocab])."""
+        seq_lens = positions + 1. Returns (next_tokens [B], logits [B, vocab]).
+        With B2_NVTX=1 every layer is an NVTX range (for timeline tools; off by default)."""
         cfg, ops = self.cfg, self.ops
+        nvtx = os.environ.get("B2_NVTX", "0") == "1"
         ops.gather_rows(self.embedding, tokens, self.x, self.status)
         pending = None  # residual delta not yet added to x
         for layer in range(self.active_layers):
+            if nvtx:
+                if layer > 0:
+                    torch.cuda.nvtx.range_pop()
+                torch.cuda.nvtx.range_push(f"decode layer {layer}")
             w, nm = self.w[layer], self.norms[layer]
             self._norm(pending, nm["attn"])
             self._linears_of_n([w["wq"], w["wk"], w["wv"]],
@@ -382,6 +388,8 @@ class DecodeStep:
             else:
                 self._linear(h, self.hfull16, w["w_down"], self.down_local)
                 pending = self._gather(self.down_local, self.down)
+        if nvtx and self.active_layers > 0:
+            torch.cuda.nvtx.range_pop()
         self._norm(pending, self.norms["final"])
         self._linears_of_n([self.w["lm_head"]], [self.logits_local])
         logits = self._gather(self.logits_local, self.logits)

@@ -46,3 +46,26 @@ def rel_l2(actual, expected):
     a = np.asarray(actual, np.float64)
     e = np.asarray(expected, np.float64)
     return float(np.linalg.norm(a - e) / max(np.linalg.norm(e), 1e-30))
+
+
+class Guarded:
+    """A float32 CUDA output tensor between two guard bands filled with a bit pattern no kernel
+    writes: `check()` fails if a kernel stored a single element outside the tensor it was given."""
+
+    GUARD = 4096          # elements on each side (16 KB)
+    PATTERN = 0x7FC0BEEF  # a NaN with a recognisable payload
+
+    def __init__(self, shape, device="cuda"):
+        import torch
+        n = int(np.prod(shape))
+        self.raw = torch.full((n + 2 * self.GUARD,), 0, dtype=torch.int32, device=device)
+        self.raw.fill_(self.PATTERN - (1 << 32) if self.PATTERN >= (1 << 31) else self.PATTERN)
+        self.tensor = self.raw[self.GUARD:self.GUARD + n].view(torch.float32).view(*shape)
+
+    def check(self):
+        import torch
+        torch.cuda.synchronize()
+        want = self.PATTERN - (1 << 32) if self.PATTERN >= (1 << 31) else self.PATTERN
+        lo, hi = self.raw[:self.GUARD], self.raw[-self.GUARD:]
+        assert bool((lo == want).all()), "a kernel wrote below its output tensor"
+        assert bool((hi == want).all()), "a kernel wrote past its output tensor"

@@ -52,7 +52,9 @@ def run_case(b2, port, case, tol, shard=None):
         weights.append(b2.PackedNf4Weight.from_host(hosts[-1]))
     x = rng.standard_normal((rows, in_f)).astype(np.float32)
     xd = torch.from_numpy(x).cuda()
-    ys = [torch.full((rows, w.out_features), float("nan"), device="cuda") for w in weights]
+    from conftest import Guarded
+    guards = [Guarded((rows, w.out_features)) for w in weights]   # NaN-filled, with guard bands around
+    ys = [g.tensor for g in guards]
     structs = (_lib.Nf4WeightStruct * len(weights))(*[w.struct() for w in weights])
     ptrs = (C.c_void_p * len(weights))(*[y.data_ptr() for y in ys])
     for _ in range(2):   # twice: the arrival counters must be back at zero after a launch
@@ -62,6 +64,8 @@ def run_case(b2, port, case, tol, shard=None):
             _check(lib.b2_nf4_linear_forward_multi(structs, len(weights), xd.data_ptr(), ptrs, rows, None, 0, None))
         assert lib.b2_last_route() == 1, (case, lib.b2_last_route())   # B2_ROUTE_DECODE_TMEM
         b2.check_device_errors()
+        for g in guards:
+            g.check()
         for host, y in zip(hosts, ys):
             got = y.cpu().numpy()
             want = port.linear_forward(host, x)

@@ -11,7 +11,7 @@ import pytest
 import torch
 
 import cases
-from conftest import bits, rel_l2, weight_from_golden
+from conftest import Guarded, bits, rel_l2, weight_from_golden
 
 pytestmark = pytest.mark.gpu
 
@@ -39,19 +39,21 @@ def close_with_floor(actual, expected, tol):
 
 
 def forward(b2, w, x):
+    """Through the C ABI into an output placed between guard bands: every caller of this helper
+    also checks that the kernel it reached wrote nothing outside its [rows, out] tensor."""
     rows = x.shape[0]
-    y = torch.empty((rows, w.out_features), dtype=torch.float32, device="cuda")
-    b2.dispatch_quantized_linear_forward(x, w, y, (rows, w.in_features, w.out_features, w.block_size))
-    torch.cuda.synchronize()
-    return y.cpu().numpy()
+    out = Guarded((rows, w.out_features))
+    b2.dispatch_quantized_linear_forward(x, w, out.tensor, (rows, w.in_features, w.out_features, w.block_size))
+    out.check()
+    return out.tensor.cpu().numpy()
 
 
 def backward(b2, w, dy):
     rows = dy.shape[0]
-    dx = torch.empty((rows, w.in_features), dtype=torch.float32, device="cuda")
-    b2.dispatch_quantized_linear_input_backward(dy, w, dx, (rows, w.in_features, w.out_features, w.block_size))
-    torch.cuda.synchronize()
-    return dx.cpu().numpy()
+    out = Guarded((rows, w.in_features))
+    b2.dispatch_quantized_linear_input_backward(dy, w, out.tensor, (rows, w.in_features, w.out_features, w.block_size))
+    out.check()
+    return out.tensor.cpu().numpy()
 
 
 # ---- dequantisation: bit-exact ---------------------------------------------------
@@ -263,13 +265,13 @@ def test_paged_decode_contract_and_special_values(b2):
 
 def run_gqa(b2, q, K, V, tables, lens):
     n_seq, hq, d = q.shape
-    ctx = torch.empty((n_seq, hq, d), dtype=torch.float32, device="cuda")
+    out = Guarded((n_seq, hq, d))
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
     pool = b2.PagedKvPool(dev(K), dev(V))
-    b2.paged_decode_attention(dev(q), pool, dev(tables.view(np.int32)), dev(lens.view(np.int32)), ctx,
+    b2.paged_decode_attention(dev(q), pool, dev(tables.view(np.int32)), dev(lens.view(np.int32)), out.tensor,
                               int(lens.max()), status=status)
-    torch.cuda.synchronize()
-    return ctx.cpu().numpy(), int(status.item())
+    out.check()
+    return out.tensor.cpu().numpy(), int(status.item())
 
 
 def test_paged_decode_gqa_golden_sequence(b2, golden):
