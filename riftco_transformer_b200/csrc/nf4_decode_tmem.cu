@@ -106,7 +106,6 @@ struct DecodeParams {
     float* partial;            // [2 * gridDim.x][kPartialFloats]
     uint32_t* counters;        // [tiles], zero before the launch; the kernel leaves them zero
     uint32_t* error;
-    const uint32_t* lut;       // compact [256][32] words of 16-bit pairs
 };
 
 struct Barriers {
@@ -378,10 +377,22 @@ nf4_decode_tmem_kernel(const __grid_constant__ DecodeMaps maps, const __grid_con
         tmem_alloc(&bars.tmem_base, kTmemColumns);
     }
     // byte -> pair table, replicated per lane: entry v for lane l at v * 256 + 4 * l
+    // (built here from the sixteen codebook values rather than copied from global memory: a CTA
+    // that becomes resident late has this on its critical path, and the copy is an L2 round trip)
     for (uint32_t i = tid; i < 256u * 8u; i += kThreads) {
-        cp_async_16(plan.lut32 + (i >> 3) * 256u + (i & 7u) * 16u, p.lut + i * 4u);
+        const uint32_t v = i >> 3;
+        const float lo = kNf4Codebook[v & 15u], hi = kNf4Codebook[v >> 4];
+        uint32_t word;
+        if (kHalf) {
+            const __half2 pair = __floats2half2_rn(lo, hi);
+            word = *reinterpret_cast<const uint32_t*>(&pair);
+        } else {
+            const __nv_bfloat162 pair = __floats2bfloat162_rn(lo, hi);
+            word = *reinterpret_cast<const uint32_t*>(&pair);
+        }
+        asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(plan.lut32 + v * 256u + (i & 7u) * 16u), "r"(word)
+                     : "memory");
     }
-    asm volatile("cp.async.commit_group;" ::);
 
     const uint32_t w_tx = kCodeBytes + kScaleBoxBytes + (fp32_scales ? 0u : kSecondBox * 4u);
     // Streams item `it` (ring slot `s`): packed codes, raw scales, second-level values.
@@ -413,7 +424,6 @@ nf4_decode_tmem_kernel(const __grid_constant__ DecodeMaps maps, const __grid_con
             __syncwarp();
         }
     }
-    asm volatile("cp.async.wait_group 0;" ::);
     tcgen05_fence_before_sync();
     __syncthreads();
     tcgen05_fence_after_sync();
@@ -863,7 +873,11 @@ nf4_decode_tmem_kernel(const __grid_constant__ DecodeMaps maps, const __grid_con
                 }
             }
         }
-        cluster.sync();
+        // The peers only have to outlive the leader's reads of their shared memory, which are
+        // complete when it gets here (their values have been stored): no memory ordering is needed,
+        // and a releasing arrive would wait for the output stores to be acknowledged.
+        asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
+        asm volatile("barrier.cluster.wait.aligned;" ::: "memory");
     }
     tcgen05_fence_before_sync();
     __syncthreads();
@@ -1056,7 +1070,6 @@ int32_t launch_nf4_decode_tmem(const DeviceContext& ctx, const WeightView* ws, f
     p.partial = static_cast<float*>(partial);
     p.counters = counters;
     p.error = ctx.gemm_error;
-    p.lut = half ? ctx.gemv_lut : ctx.gemm_lut;
 
     CUtensorMap map_x;
     {
