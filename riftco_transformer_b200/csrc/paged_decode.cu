@@ -51,9 +51,11 @@ __device__ __forceinline__ void put_ctx(const PagedDecodeArgs& a, uint64_t index
 // decode step, 350 vs 333 us on 64 sequences of 512-8192 tokens): with more CTAs per SM a CTA that
 // ends and its successor that starts stall a smaller share of the SM's loads.
 // The mbarrier waits are bounded; a timeout sets bit 3 of the status word.
-constexpr int kBulkSlots = 2;
+// Grids of at most two waves of the three-slot form (which fits two CTAs per SM) are a question of
+// wave count instead: 576 CTAs are 1.95 waves of 296 but 1.3 waves of 444, so such launches take
+// the three-slot form when it needs fewer CTA-widths of time (see launch_paged_decode).
 constexpr int kChunkBytes = kPage * kD * 4;   // 8 KB: one (page, kv head) of K or of V
-constexpr int kBulkSmemBytes = kFastWarps * kBulkSlots * kChunkBytes;
+constexpr int bulk_smem_bytes(int slots) { return kFastWarps * slots * kChunkBytes; }
 
 __device__ __forceinline__ void bulk_load(uint32_t dst32, const void* src, uint32_t bytes, uint64_t* bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
@@ -66,7 +68,7 @@ __device__ __forceinline__ float4 lds_f4(uint32_t a) {
     return v;
 }
 
-template <int REP>
+template <int REP, int kBulkSlots>
 __global__ void __launch_bounds__(kFastWarps * 32)
 paged_decode_bulk_kernel(const PagedDecodeArgs a, float* __restrict__ partials, uint32_t max_splits) {
     sm100::pdl_launch_dependents();   // a following decode GEMV may start its set-up now
@@ -443,17 +445,41 @@ int32_t launch_paged_decode(const DeviceContext& ctx, const PagedDecodeArgs& a, 
         note_route(B2_ROUTE_ATTENTION_BULK);
         static PerDeviceOnce configured;
         B2_TRY(once_per_device(configured, ctx.device, []() -> int32_t {
-            B2_CUDA_TRY(cudaFuncSetAttribute(paged_decode_bulk_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBulkSmemBytes));
-            B2_CUDA_TRY(cudaFuncSetAttribute(paged_decode_bulk_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBulkSmemBytes));
-            B2_CUDA_TRY(cudaFuncSetAttribute(paged_decode_bulk_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBulkSmemBytes));
-            B2_CUDA_TRY(cudaFuncSetAttribute(paged_decode_bulk_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBulkSmemBytes));
+            B2_CUDA_TRY(cudaFuncSetAttribute(paged_decode_bulk_kernel<1, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, bulk_smem_bytes(2)));
+            B2_CUDA_TRY(cudaFuncSetAttribute(paged_decode_bulk_kernel<2, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, bulk_smem_bytes(2)));
+            B2_CUDA_TRY(cudaFuncSetAttribute(paged_decode_bulk_kernel<4, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, bulk_smem_bytes(2)));
+            B2_CUDA_TRY(cudaFuncSetAttribute(paged_decode_bulk_kernel<8, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, bulk_smem_bytes(2)));
+            B2_CUDA_TRY(cudaFuncSetAttribute(paged_decode_bulk_kernel<1, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, bulk_smem_bytes(3)));
+            B2_CUDA_TRY(cudaFuncSetAttribute(paged_decode_bulk_kernel<2, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, bulk_smem_bytes(3)));
+            B2_CUDA_TRY(cudaFuncSetAttribute(paged_decode_bulk_kernel<4, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, bulk_smem_bytes(3)));
+            B2_CUDA_TRY(cudaFuncSetAttribute(paged_decode_bulk_kernel<8, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, bulk_smem_bytes(3)));
             return B2_STATUS_OK;
         }));
-        switch (a.q_heads / a.kv_heads) {
-        case 1: paged_decode_bulk_kernel<1><<<grid, kFastWarps * 32, kBulkSmemBytes, stream>>>(a, partials, splits); break;
-        case 2: paged_decode_bulk_kernel<2><<<grid, kFastWarps * 32, kBulkSmemBytes, stream>>>(a, partials, splits); break;
-        case 4: paged_decode_bulk_kernel<4><<<grid, kFastWarps * 32, kBulkSmemBytes, stream>>>(a, partials, splits); break;
-        default: paged_decode_bulk_kernel<8><<<grid, kFastWarps * 32, kBulkSmemBytes, stream>>>(a, partials, splits); break;
+        // Two slots per warp (three CTAs per SM) by default; three slots (two CTAs per SM) where the
+        // grid is between one and two waves of that form and it needs fewer CTA-widths of time
+        // (measured on 32 sequences of 2049 tokens: 2 kv heads 33.8 vs 36.7 us, 1 kv head 19.2 vs 18.4 us).
+        const uint64_t ctas = static_cast<uint64_t>(splits) * a.kv_heads * a.n_seq;
+        const uint64_t sms = ctx.sm_count > 0 ? static_cast<uint64_t>(ctx.sm_count) : 148u;
+        const bool three_slots = ctas > 2 * sms && ctas <= 4 * sms &&
+                                 ((ctas + 2 * sms - 1) / (2 * sms)) * 2 < ((ctas + 3 * sms - 1) / (3 * sms)) * 3;
+        const uint32_t rep = a.q_heads / a.kv_heads;
+        const unsigned threads = kFastWarps * 32;
+        if (three_slots) {
+            constexpr int kBytes = bulk_smem_bytes(3);
+            switch (rep) {
+            case 1: paged_decode_bulk_kernel<1, 3><<<grid, threads, kBytes, stream>>>(a, partials, splits); break;
+            case 2: paged_decode_bulk_kernel<2, 3><<<grid, threads, kBytes, stream>>>(a, partials, splits); break;
+            case 4: paged_decode_bulk_kernel<4, 3><<<grid, threads, kBytes, stream>>>(a, partials, splits); break;
+            default: paged_decode_bulk_kernel<8, 3><<<grid, threads, kBytes, stream>>>(a, partials, splits); break;
+            }
+        } else {
+            constexpr int kBytes = bulk_smem_bytes(2);
+            switch (rep) {
+            case 1: paged_decode_bulk_kernel<1, 2><<<grid, threads, kBytes, stream>>>(a, partials, splits); break;
+            case 2: paged_decode_bulk_kernel<2, 2><<<grid, threads, kBytes, stream>>>(a, partials, splits); break;
+            case 4: paged_decode_bulk_kernel<4, 2><<<grid, threads, kBytes, stream>>>(a, partials, splits); break;
+            default: paged_decode_bulk_kernel<8, 2><<<grid, threads, kBytes, stream>>>(a, partials, splits); break;
+            }
         }
         B2_CUDA_TRY(cudaGetLastError());
         if (splits > 1) {
