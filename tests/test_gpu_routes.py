@@ -111,3 +111,29 @@ def test_attention_routes(b2, port, route, hq, hkv, d, bs):
     assert b2.last_route() == route
     assert status == 0
     assert rel_l2(got, port.paged_decode_gqa(q, K, V, tables, lens)) <= 2e-3
+
+
+def test_attention_grid_between_one_and_two_waves(b2, port):
+    """16 sequences x 4 KV heads x 9 splits = 576 CTAs: the launcher takes the three-slot form of
+    the fast kernel there (two CTAs per SM, fewer waves); larger and smaller grids take two slots.
+    Same arithmetic either way, so the result is held to the oracle like any other."""
+    rng = np.random.default_rng(576)
+    hkv, rep, d, bs = 4, 2, 128, 16
+    lens = np.full(16, 2049, np.uint32)
+    lens[3], lens[11] = 1800, 2047          # fewer splits for two sequences: their spare CTAs exit at once
+    blocks = -(-lens.astype(np.int64) // bs)
+    P = int(blocks.sum())
+    perm = rng.permutation(P)
+    tables = np.zeros((len(lens), int(blocks.max())), np.uint32)
+    at = 0
+    for s, nb in enumerate(blocks):
+        tables[s, :nb] = perm[at:at + nb]
+        at += nb
+    K = rng.standard_normal((P, hkv, bs, d)).astype(np.float32)
+    V = rng.standard_normal((P, hkv, bs, d)).astype(np.float32)
+    q = rng.standard_normal((len(lens), hkv * rep, d)).astype(np.float32)
+    got, status = run_gqa(b2, q, K, V, tables, lens)
+    assert b2.last_route() == "attention_bulk" and status == 0
+    want = port.paged_decode_gqa(q, K, V, tables, lens)
+    for s in range(len(lens)):
+        assert rel_l2(got[s], want[s]) <= 2e-3, f"sequence {s}"
