@@ -202,10 +202,29 @@ __device__ __forceinline__ float silu_ref(float value) {
 
 __global__ void __launch_bounds__(256)
 silu_mul_kernel(const float* gate, const float* up, float* out,   // out may be gate or up
-                __nv_bfloat16* __restrict__ out16, uint64_t n) {
+                __nv_bfloat16* __restrict__ out16, uint64_t n, uint32_t vec4) {
     sm100::pdl_launch_dependents();   // a following decode GEMV may start its set-up now
     const uint64_t stride = static_cast<uint64_t>(gridDim.x) * blockDim.x;
-    for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
+    const uint64_t first = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (vec4 != 0u) {   // 16-byte accesses: four elements per thread and step
+        const uint64_t n4 = n / 4;
+        for (uint64_t i = first; i < n4; i += stride) {
+            const float4 g = reinterpret_cast<const float4*>(gate)[i];
+            const float4 u = reinterpret_cast<const float4*>(up)[i];
+            const float4 o = make_float4(silu_ref(g.x) * u.x, silu_ref(g.y) * u.y, silu_ref(g.z) * u.z,
+                                         silu_ref(g.w) * u.w);
+            reinterpret_cast<float4*>(out)[i] = o;
+            if (out16 != nullptr) {
+                const __nv_bfloat162 lo = __floats2bfloat162_rn(o.x, o.y), hi = __floats2bfloat162_rn(o.z, o.w);
+                uint2 packed;
+                packed.x = *reinterpret_cast<const uint32_t*>(&lo);
+                packed.y = *reinterpret_cast<const uint32_t*>(&hi);
+                reinterpret_cast<uint2*>(out16)[i] = packed;
+            }
+        }
+        return;
+    }
+    for (uint64_t i = first; i < n; i += stride) {
         const float o = silu_ref(gate[i]) * up[i];
         out[i] = o;
         if (out16 != nullptr) out16[i] = __float2bfloat16_rn(o);
@@ -330,8 +349,11 @@ int32_t launch_rope_append(float* q, const float* k, const float* v, const uint3
 
 int32_t launch_silu_mul(const DeviceContext& ctx, const float* gate, const float* up, float* out, void* out_bf16,
                         uint64_t n, cudaStream_t stream) {
-    silu_mul_kernel<<<grid_for(n, ctx.sm_count), 256, 0, stream>>>(gate, up, out,
-                                                                   static_cast<__nv_bfloat16*>(out_bf16), n);
+    const bool vec4 = n % 4 == 0 && ((reinterpret_cast<uintptr_t>(gate) | reinterpret_cast<uintptr_t>(up) |
+                                      reinterpret_cast<uintptr_t>(out)) & 15u) == 0 &&
+                      (reinterpret_cast<uintptr_t>(out_bf16) & 7u) == 0;
+    silu_mul_kernel<<<grid_for(vec4 ? n / 4 : n, ctx.sm_count), 256, 0, stream>>>(
+        gate, up, out, static_cast<__nv_bfloat16*>(out_bf16), n, vec4 ? 1u : 0u);
     B2_CUDA_TRY(cudaGetLastError());
     return B2_STATUS_OK;
 }
