@@ -147,7 +147,12 @@ B2_API int32_t b2_nf4_validate_payload(const b2_nf4_weight* weight, uint64_t cod
  * dispatch_quantized_linear_forward (quantized_linear/dispatch.cpp:317-341):
  * zero/overflowing dimensions and aliasing x/y or weight/y are rejected.
  * workspace may be NULL: the library then uses its own per-device arena, and
- * calls that share the arena must be ordered on one stream. */
+ * calls that share the arena must be ordered on one stream. The arena only
+ * grows and never frees or moves memory it has handed out, so an address a
+ * CUDA graph captured stays valid for the life of the process; a call that
+ * would have to grow the arena while its stream is being captured fails with
+ * B2_STATUS_INVALID_ARGUMENT (make the first call of a shape outside capture,
+ * or pass a workspace). */
 B2_API int32_t b2_nf4_linear_forward(const b2_nf4_weight* weight, const float* x, float* y,
                               uint64_t rows, void* workspace, size_t workspace_bytes,
                               void* stream);
