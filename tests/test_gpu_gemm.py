@@ -287,3 +287,45 @@ def test_lora_against_oracle(b2, port, rows, out_f, in_f, rank, dq):
     with pytest.raises(ValueError):
         _lora_forward(b2, w, torch.from_numpy(x).cuda(), torch.from_numpy(np.zeros((65, in_f), np.float32)).cuda(),
                       torch.from_numpy(np.zeros((out_f, 65), np.float32)).cuda(), 1.0)
+
+
+def test_library_arena_under_graph_capture(b2, port):
+    """The library's own scratch arena (workspace == NULL): a captured graph keeps working after
+    the arena has grown for a later, larger call (memory that was handed out is never freed or
+    moved), and a call that would have to grow the arena while its stream is being captured is
+    refused instead of allocating inside the capture."""
+    rng = np.random.default_rng(7)
+    W = (rng.standard_normal((512, 1024)) * 0.02).astype(np.float32)
+    host = port.quantize_nf4_double_quantized(W, 64, 256)
+    w = b2.PackedNf4Weight.from_host(host)
+    # a second call so large (1.2 GB of bf16 scratch) that no earlier test can have grown the arena past it
+    big_rows = 600000
+    x_small = torch.from_numpy(rng.standard_normal((64, 1024)).astype(np.float32)).cuda()
+    x_big = torch.randn((big_rows, 1024), device="cuda")
+    y_small = torch.empty((64, 512), device="cuda")
+    y_big = torch.empty((big_rows, 512), device="cuda")
+    shape_small, shape_big = (64, 1024, 512, 64), (big_rows, 1024, 512, 64)
+    b2.dispatch_quantized_linear_forward(x_small, w, y_small, shape_small)   # arena sized outside capture
+    torch.cuda.synchronize()
+    first = y_small.clone()
+    side = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    refused = None
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            b2.dispatch_quantized_linear_forward(x_small, w, y_small, shape_small)
+            try:
+                b2.dispatch_quantized_linear_forward(x_big, w, y_big, shape_big)
+            except ValueError as e:   # nothing of the refused call was enqueued: the capture stays valid
+                refused = str(e)
+    torch.cuda.synchronize()
+    assert refused is not None and "stream capture" in refused, refused
+    b2.dispatch_quantized_linear_forward(x_big, w, y_big, shape_big)         # grows the arena
+    torch.cuda.synchronize()
+    y_small.zero_()
+    graph.replay()                                                            # still points at the old arena
+    torch.cuda.synchronize()
+    b2.check_device_errors()
+    assert torch.equal(y_small.view(torch.int32), first.view(torch.int32))
+    sample = slice(0, 64)
+    assert rel_l2(y_big[sample].cpu().numpy(), port.linear_forward(host, x_big[sample].cpu().numpy())) <= GEMM_TOL
