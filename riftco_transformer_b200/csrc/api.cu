@@ -262,14 +262,15 @@ bool aliases_weight(const b2_nf4_weight* weight, const void* p) {
 
 
 // Which decode kernel serves a forward call of up to 32 rows: 17..32 rows go to the persistent
-// tcgen05 decode kernel, fewer to the mma.sync decode kernel. B2_DECODE_IMPL=tmem sends every
-// batch of up to 32 rows to the persistent kernel (its fp16 form for up to 16 rows is tested
-// that way).
-bool decode_tmem_wanted(uint64_t rows) {
+// tcgen05 decode kernel, fewer to the mma.sync decode kernel - except 9..16 rows on a contraction
+// of 8192 or more, where the persistent kernel (fp16 form, conversion pass included) measured
+// faster (16 rows, 14336 -> 4096: 20.7 against 24.9 us; on 4096-wide layers the mma.sync kernel
+// wins). B2_DECODE_IMPL=tmem sends every batch of up to 32 rows to the persistent kernel.
+bool decode_tmem_wanted(uint64_t rows, uint64_t in_features) {
     static const char* impl = getenv("B2_DECODE_IMPL");
     if (rows > 32) return false;
     if (impl != nullptr && strcmp(impl, "tmem") == 0) return true;
-    return rows > 16;
+    return rows > 16 || (rows > 8 && in_features >= 8192);
 }
 
 // The kernel family the calling thread's last linear or attention call was served by
@@ -324,7 +325,7 @@ int32_t decode_tmem_forward(DeviceContext* ctx, const WeightView* views, float* 
 }
 
 bool decode_tmem_takes(const WeightView* views, uint32_t count, const void* x, uint64_t rows) {
-    if (!decode_tmem_wanted(rows)) return false;
+    if (!decode_tmem_wanted(rows, views[0].in_features)) return false;
     for (uint32_t i = 0; i < count; ++i) {
         if (!nf4_decode_tmem_supported(views[i], x, rows)) return false;
         if (views[i].encoding != views[0].encoding || views[i].block_size != views[0].block_size ||
@@ -661,7 +662,7 @@ int32_t b2_nf4_linear_forward_multi(const b2_nf4_weight* weights, uint32_t count
     if (ctx == nullptr) return status;
     // One launch when every weight can take the tensor-memory kernel on the same activations;
     // otherwise the calls are simply made one after the other.
-    bool fused = (rows > 16 || decode_tmem_wanted(rows)) && count <= 4 && count > 1 && x != nullptr;
+    bool fused = (rows > 16 || decode_tmem_wanted(rows, weights[0].in_features)) && count <= 4 && count > 1 && x != nullptr;
     WeightView views[4];
     for (uint32_t i = 0; fused && i < count; ++i) {
         if (ys[i] == nullptr || x == ys[i] || aliases_weight(&weights[i], ys[i]) ||

@@ -29,6 +29,8 @@ def _weight(port, out_f, in_f, block, dq, seed):
 FORWARD = [
     ("decode_tmem", 32, 512, 1024, 64, True, 1e-2),    # bf16 operands on tcgen05
     ("decode_tmem", 17, 384, 512, 64, False, 1e-2),    # FP32 scales, ragged last 128-row tile
+    ("decode_tmem", 12, 256, 8192, 64, True, 2e-3),    # 9..16 rows on a long contraction: the fp16 form
+    ("gemv_tma", 8, 256, 8192, 64, True, 2e-3),        # ... up to 8 rows stay on mma.sync
     ("gemv_tma", 4, 4096, 4096, 64, True, 2e-3),       # fp16 operands on mma.sync
     ("gemv_tma", 16, 1024, 2048, 128, False, 2e-3),
     ("gemv_tile", 3, 1000, 192, 64, True, 2e-3),       # out_features no multiple of the TMA row tile
