@@ -332,9 +332,11 @@ def kernel_measurements(torch, b2, synth, peaks, device_index: int) -> dict:
                 us = time_graph(torch, launch, 20, n_copies)
                 gbps = algorithmic / us / 1e3
                 sweep[f"M{m}_{i}to{o}_{'dq' if dq else 'f32'}"] = {
-                    "us": round(us, 3), "gbps": round(gbps, 1), "frac": round(gbps / peaks["hbm_gbs"], 4)}
+                    "us": round(us, 3), "gbps": round(gbps, 1), "frac": round(gbps / peaks["hbm_gbs"], 4),
+                    "route": b2.last_route()}
             del ws
-    out["nf4_gemv_sweep"] = {"kernel": "nf4_gemv_tma_kernel", "bound": "hbm", "unit": "GB/s",
+    out["nf4_gemv_sweep"] = {"kernel": "nf4_gemv_tma_kernel (route gemv_tma) / nf4_decode_tmem_kernel<half> with its "
+                                       "fp32 -> fp16 pre-pass (route decode_tmem), per case", "bound": "hbm", "unit": "GB/s",
                              "bytes": "packed codes + scale payload per launch (dq: u8 scale codes + f32 per 256 "
                                       "blocks; f32: one f32 scale per block)", "cases": sweep}
 
